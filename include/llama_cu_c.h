@@ -1,0 +1,144 @@
+/* C ABI of the B200-native llama.cu inference core (libllama_cu_b200.so).
+ *
+ * Plain pointers and sizes only.  Every entry point names the reference interface it stands in
+ * for (file:line in eiz/llama.cu).  The reference has no C ABI of its own: its boundary is the
+ * C++ header llama_cu.h; the C++ classes of that header are provided by include/llama_cu.h on top
+ * of the same library, and this C layer is what a foreign-function binding (ctypes, cgo, JNI ...)
+ * loads.
+ *
+ * Conventions: functions return 0 on success or a non-zero lcu status (1 CUDA error, 2 invalid
+ * argument, 3 I/O error, 4 a kernel gave up on a bounded wait); lcu_last_error() returns the
+ * message of the calling thread's last failure.  `stream` is a cudaStream_t passed as void*
+ * (NULL = the legacy default stream).  "dev" pointers are device memory of the current device,
+ * "host" pointers are host memory.  All fp16 data is IEEE binary16.  There is no CPU fallback:
+ * every compute entry point launches sm_100a kernels and fails if no such device is present.
+ */
+#ifndef LLAMA_CU_C_H
+#define LLAMA_CU_C_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- library ------------------------------------------------------------------------------ */
+const char* lcu_last_error(void);
+/* llama_cu::initialize (llama_cu.cu:1525-1542): prints the device properties; returns the device count. */
+int lcu_initialize(int verbose);
+int lcu_device_count(void);
+/* llama_cu::matmul_type (llama_cu.h:65-68): 4 and 0 select the native kernels, 1 is accepted as an
+ * alias (the reference's "pedantic" kernels have no separate implementation here). */
+int lcu_set_matmul_type(int type);
+/* launch-shape experiments: "gemv_stages", "gemv_ctas_per_sm", "use_graph", "use_pdl", "attn_cluster" */
+int lcu_set_tuning(const char* key, int value);
+
+/* device memory helpers for callers that have no CUDA binding of their own */
+int lcu_malloc(void** dev_out, uint64_t bytes);
+int lcu_free(void* dev);
+int lcu_memcpy_h2d(void* dev, const void* host, uint64_t bytes);
+int lcu_memcpy_d2h(void* host, const void* dev, uint64_t bytes);
+int lcu_memcpy_d2d(void* dst_dev, const void* src_dev, uint64_t bytes); /* any two devices */
+int lcu_memset(void* dev, int value, uint64_t bytes);
+int lcu_set_device(int device);
+int lcu_synchronize(void);
+
+/* ---- quantizer (transform.cu) --------------------------------------------------------------- */
+/* quantize_absmax_uint8 kernel, transform.cu:28-72, launched by quantize_one at transform.cu:171.
+ * in: fp16 [h][w]; q: u8 [h][w]; scales: fp16 [h][w/bs].  Bit-identical to the reference. */
+int lcu_quantize_absmax_uint8(void* q_dev, void* scales_dev, const void* in_dev, uint64_t h, uint64_t w, int bs, void* stream);
+/* dequantize_absmax_uint8 kernel, transform.cu:74-87 */
+int lcu_dequantize_absmax_uint8(void* out_dev, const void* scales_dev, const void* q_dev, uint64_t h, uint64_t w, int bs, void* stream);
+/* error_stats kernel, transform.cu:100-150: stats_host[0..2] = mean squared / max / mean absolute error */
+int lcu_error_stats(float* stats_host, const void* a_dev, const void* b_dev, uint64_t n, void* stream);
+/* quantize_one, transform.cu:152-196, on host buffers (copies in, quantizes, copies out; stats_host may be NULL) */
+int lcu_quantize_host(uint8_t* q_host, uint16_t* scales_host, const uint16_t* in_host, uint64_t h, uint64_t w, int bs, float* stats_host);
+/* do_quantize, transform.cu:220-263 (`transform quantize <in> <out> <bs>`): weight directory -> weight directory */
+int lcu_quantize_model_dir(const char* in_dir, const char* out_dir, int bs);
+
+/* ---- operators (the reference's internal seam) ---------------------------------------------- */
+/* matmul_nt(out, lhs, rhs, beta, stream), llama_cu.cu:738-742 / 1463-1496:
+ * out(m,n) = lhs(m,k) . rhs(n,k)^T + beta * out, fp16 in/out, fp32 accumulation.  No gutter rows needed. */
+int lcu_matmul_nt_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, float beta, void* stream);
+/* matmul_nt(out, lhs, generic_tensor& rhs, beta, stream) with a quantized rhs, llama_cu.cu:743-747 / 1498-1523 */
+int lcu_matmul_nt_fp16u8(void* out_dev, const void* lhs_dev, const void* q_dev, const void* scales_dev, int m, int k, int n, int bs,
+                         float beta, void* stream);
+/* kernel::rms_norm, llama_cu.cu:66-107 (launch at 1129) */
+int lcu_rms_norm(void* out_dev, const void* in_dev, const void* weight_dev, int rows, int dim, float eps, void* stream);
+/* kernel::silu, llama_cu.cu:533-539 (launch at 1183) */
+int lcu_silu(void* out_dev, const void* a_dev, const void* b_dev, uint64_t n, void* stream);
+/* kernel::rotary, llama_cu.cu:368-389 (launches at 1146 and 1152), together with the cache write:
+ * rotates q rows in place at positions pos0+r, rotates k_new into k_cache and copies v_new into
+ * v_cache, both head-major [n_heads][ctx_len][dim/n_heads]. */
+int lcu_rope_scatter(void* q_dev, const void* k_new_dev, const void* v_new_dev, void* k_cache_dev, void* v_cache_dev, int pos0, int m,
+                     int dim, int n_heads, int ctx_len, void* stream);
+/* matmul_qk + softmax_rows + matmul_qkv, llama_cu.cu:400-531 (launches at 1163-1171), fused:
+ * q [m][dim] rotated, caches head-major as above holding positions 0 .. pos0+m-1; out [m][dim]. */
+int lcu_attention(void* out_dev, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev, int pos0, int m, int dim,
+                  int n_heads, int ctx_len, int cluster, void* stream);
+/* softmax_rows with temperature on the logits + the host-side first-maximum search,
+ * llama_cu.cu:1196-1209: probs_dev (fp16 [n_vocab], may alias logits_dev), *token_host = argmax */
+int lcu_logits_head(void* probs_dev, const void* logits_dev, int n_vocab, float temperature, int* token_host, void* stream);
+
+/* ---- synthetic data ------------------------------------------------------------------------- */
+/* out[i] = fp16(scale * z(seed, name, first + i)), z approximately N(0,1), reproducible on any host */
+int lcu_synth_fill_f16(void* out_dev, uint64_t n, uint64_t seed, const char* name, float scale, uint64_t first, void* stream);
+
+/* ---- model (llama_model, llama_cu.h:362-372) -------------------------------------------------- */
+/* params40: the 40-byte params record (llama_cu.h:280-291).  layer_gpus: n_layers device indices
+ * (llama_partition::layer_gpus, llama_cu.h:301-314; embedding on the first, output on the last),
+ * NULL = every layer on device 0 (llama_partition::use_default, llama_cu.cu:810-818). */
+int lcu_model_create(const void* params40, const int* layer_gpus, void** model_out);
+/* llama_model::load, llama_cu.cu:987-997: reads <dir>/params and the tensor files (llama_cu.cu:929-984) */
+int lcu_model_load(const char* dir, const int* layer_gpus, void** model_out);
+/* seeded synthetic weights in place of a checkpoint (matrices scale*z, norm weights 1.0) */
+int lcu_model_fill_synthetic(void* model, uint64_t seed, float scale);
+/* writes the model as a weight directory in the reference's layout (extract.py:16-41, transform.cu:179-261) */
+int lcu_model_save(void* model, const char* dir);
+/* device pointer of a tensor by file stem, e.g. "layers.0.attention.wq"; which: 0 values, 1 scales */
+int lcu_model_tensor(void* model, const char* name, int which, void** dev_out, uint64_t* bytes_out, int* device_out);
+int lcu_model_params(void* model, void* params40_out);
+uint64_t lcu_model_weight_bytes(void* model);
+void lcu_model_free(void* model);
+/* llama_params::ffn_dim, llama_cu.cu:765-767 */
+uint32_t lcu_ffn_dim(uint32_t dim, uint32_t multiple_of);
+/* llama_partition::autopipe, llama_cu.cu:819-837: fills layer_gpus_out[n_layers] greedily by free memory; returns 0 if it fits */
+int lcu_partition_autopipe(const void* params40, int context_len, int* layer_gpus_out);
+/* contiguous equal split over n_gpus devices (the hand-built partitions of the pipelined configurations) */
+int lcu_partition_even(int n_layers, int n_gpus, int* layer_gpus_out);
+
+/* ---- context (llama_context, llama_cu.h:374-390) ---------------------------------------------- */
+/* llama_context::create(model, context_len, temperature), llama_cu.cu:1306-1310 */
+int lcu_context_create(void* model, int context_len, float temperature, void** ctx_out);
+void lcu_context_free(void* ctx);
+/* llama_context::clear_tokens, llama_cu.cu:1004-1049 (resets the position; nothing is re-allocated) */
+void lcu_context_clear_tokens(void* ctx);
+/* llama_context::context_memory_usage, llama_cu.cu:1051-1072 */
+uint64_t lcu_context_memory_usage(void* ctx);
+/* llama_context::tokens_left, llama_cu.h:381 */
+int lcu_context_tokens_left(void* ctx);
+/* llama_context::next_token(new_tokens), llama_cu.cu:1073-1210: host token ids in, greedy token out */
+int lcu_context_next_token(void* ctx, const int16_t* tokens_host, int n_tokens, int* token_out);
+/* n_steps greedy single-token steps chained on the device (the loop of main.cpp:80-100 without the
+ * per-token host round trip); tokens_host_out[n_steps]; *ms_out = device time of the loop */
+int lcu_context_decode_chained(void* ctx, int16_t first_token, int n_steps, int16_t* tokens_host_out, float* ms_out);
+/* probabilities of the last step (what the reference leaves in its logits buffer, llama_cu.cu:1196-1200) */
+int lcu_context_read_probs(void* ctx, uint16_t* probs_host);
+/* residual stream row of the last token before the final norm (diagnostics) */
+int lcu_context_read_hidden(void* ctx, uint16_t* hidden_host);
+int lcu_context_kernels_per_step(void* ctx);
+
+/* ---- measurement ---------------------------------------------------------------------------- */
+/* Times one decode kernel class over all layers of `model` in rotation (distinct weights every
+ * launch, more than L2 holds), CUDA events on the launching stream.
+ * which: 0 fused norm+wq|wk|wv+RoPE, 1 wo+residual, 2 fused norm+w1|w3+SiLU, 3 w2+residual, 4 output matrix.
+ * Returns mean milliseconds per launch and the algorithmic bytes of one launch. */
+int lcu_bench_decode_kernel(void* ctx, int which, int reps, float* ms_per_launch_out, uint64_t* bytes_per_launch_out);
+/* pure-read ceiling: a kernel that only streams `bytes` from HBM with the same bulk-copy ring; ms per pass */
+int lcu_bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLAMA_CU_C_H */

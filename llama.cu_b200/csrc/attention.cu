@@ -1,0 +1,198 @@
+// Fused attention over the fp16 KV cache for sm_100a.
+//
+// Replaces the reference's matmul_qk -> softmax_rows -> matmul_qkv chain (llama_cu.cu:400-531,
+// called at 1161-1171) and its per-layer score tensor with one kernel that keeps scores and
+// probabilities on chip.  The reference's rounding points are kept ("parity" arithmetic):
+//   score  s_t = half( (sum_i q_i k_ti) / sqrtf(head_dim) )                    llama_cu.cu:420-425
+//   prob   p_t = half( expf(s_t - max) / sum_t' expf(s_t' - max) )             llama_cu.cu:443-498
+//   out    o_j = half( sum_t float(p_t) float(v_tj) )                          llama_cu.cu:524-529
+// which needs the row's max and sum before any probability is formed, so the kernel is two-pass
+// over the scores (held in shared memory as halves), not an online-softmax.
+//
+// One thread-block cluster of CS CTAs serves one (query row, head): each CTA takes a contiguous
+// slice of the cached positions, and the max / sum / partial outputs are exchanged through
+// distributed shared memory.  K and V are stored head-major ([head][position][head_dim], keys
+// already rotated), so a slice is one contiguous run of 2*head_dim-byte rows.
+#include "attention.cuh"
+
+namespace lcu {
+namespace {
+
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_WARPS = ATT_THREADS / 32;
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) {
+  constexpr int LPR = HD / 8;        // lanes that share one cached row (8 halves = 16 bytes each)
+  constexpr int RPW = 32 / LPR;      // rows a warp handles per step
+  extern __shared__ __align__(16) uint8_t smem[];
+  // layout: exchange slots (floats) | partial outputs [HD] floats | per-warp partials | scores (halves)
+  float* xchg = reinterpret_cast<float*>(smem);           // [0]=max [1]=sum (this CTA's), read by peers
+  float* cpart = xchg + 4;                                // [HD] this CTA's partial output
+  float* wpart = cpart + HD;                              // [ATT_WARPS][HD]
+  float* wred = wpart + ATT_WARPS * HD;                   // [ATT_WARPS] scratch
+  __half* sc = reinterpret_cast<__half*>(wred + ATT_WARPS);  // [chunk] scores of this CTA's slice
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = lane / LPR, gl = lane % LPR;
+  const uint32_t rank = cluster_ctarank(), cs = cluster_nctarank();
+  const int head = blockIdx.y, qrow = blockIdx.z;
+
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int start_pos = p.pos ? *p.pos : p.pos_value;
+  const int T = start_pos + qrow + 1;  // causal: row r sees positions 0 .. start_pos + r
+  const int chunk = (T + (int)cs - 1) / (int)cs;
+  const int t0 = min(T, (int)rank * chunk), t1 = min(T, t0 + chunk);
+  const int n = t1 - t0;
+
+  const __half* kbase = p.k_cache + ((size_t)head * p.ctx_len + t0) * HD;
+  const __half* vbase = p.v_cache + ((size_t)head * p.ctx_len + t0) * HD;
+
+  // this lane's 8 query values
+  float q[8];
+  {
+    const uint4 qv = *reinterpret_cast<const uint4*>(p.q + (size_t)qrow * p.ldq + head * HD + gl * 8);
+    const __half2* h = reinterpret_cast<const __half2*>(&qv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __half22float2(h[i]);
+      q[2 * i] = f.x;
+      q[2 * i + 1] = f.y;
+    }
+  }
+  const float scale_div = sqrtf((float)HD);
+
+  // ---- pass 1: scores of the slice, rounded to half, and the slice maximum
+  float lmax = -CUDART_INF_F;
+  for (int base = warp * RPW; base < n; base += ATT_WARPS * RPW) {
+    const int t = base + grp;
+    float s = 0.f;
+    if (t < n) {
+      const uint4 kv = *reinterpret_cast<const uint4*>(kbase + (size_t)t * HD + gl * 8);
+      const __half2* h = reinterpret_cast<const __half2*>(&kv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]);
+        s += q[2 * i] * f.x;
+        s += q[2 * i + 1] * f.y;
+      }
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (t < n) {
+      const __half sh = __float2half(s / scale_div);
+      if (gl == 0) sc[t] = sh;
+      lmax = fmaxf(lmax, __half2float(sh));
+    }
+  }
+  lmax = warp_max(lmax);
+  if (lane == 0) wred[warp] = lmax;
+  __syncthreads();
+  if (tid == 0) {
+    float m = wred[0];
+    for (int w = 1; w < ATT_WARPS; ++w) m = fmaxf(m, wred[w]);
+    xchg[0] = m;
+  }
+  cluster_sync();
+  float gmax = -CUDART_INF_F;
+  for (uint32_t r = 0; r < cs; ++r) gmax = fmaxf(gmax, ld_dsmem_f32(mapa(smem_u32(&xchg[0]), r)));
+
+  // ---- pass 2: sum of exponentials (fixed order: lanes, warps, then cluster ranks)
+  float lsum = 0.f;
+  for (int t = tid; t < n; t += ATT_THREADS) lsum += expf(__half2float(sc[t]) - gmax);
+  lsum = warp_sum(lsum);
+  __syncthreads();  // wred reuse
+  if (lane == 0) wred[warp] = lsum;
+  __syncthreads();
+  if (tid == 0) {
+    float s = 0.f;
+    for (int w = 0; w < ATT_WARPS; ++w) s += wred[w];
+    xchg[1] = s;
+  }
+  cluster_sync();
+  float gsum = 0.f;
+  for (uint32_t r = 0; r < cs; ++r) gsum += ld_dsmem_f32(mapa(smem_u32(&xchg[1]), r));
+
+  // ---- pass 3: probabilities rounded to half, times V
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int base = warp * RPW; base < n; base += ATT_WARPS * RPW) {
+    const int t = base + grp;
+    if (t < n) {
+      const float pr = __half2float(__float2half(expf(__half2float(sc[t]) - gmax) / gsum));
+      const uint4 vv = *reinterpret_cast<const uint4*>(vbase + (size_t)t * HD + gl * 8);
+      const __half2* h = reinterpret_cast<const __half2*>(&vv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]);
+        acc[2 * i] += pr * f.x;
+        acc[2 * i + 1] += pr * f.y;
+      }
+    }
+  }
+  // combine the row groups of a warp, then the warps, then the cluster ranks
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    for (int o = LPR; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+  if (grp == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wpart[warp * HD + gl * 8 + i] = acc[i];
+  }
+  __syncthreads();
+  if (tid < HD) {
+    float s = 0.f;
+    for (int w = 0; w < ATT_WARPS; ++w) s += wpart[w * HD + tid];
+    cpart[tid] = s;
+  }
+  cluster_sync();
+  if (rank == 0 && tid < HD) {
+    float s = 0.f;
+    for (uint32_t r = 0; r < cs; ++r) s += ld_dsmem_f32(mapa(smem_u32(&cpart[tid]), r));
+    p.out[(size_t)qrow * p.ldo + head * HD + tid] = __float2half(s);
+  }
+  cluster_sync();  // peers' shared memory stays alive until rank 0 has read it
+}
+
+template <int HD>
+int launch_hd(const attn_params& p, int m, int cs, int max_T, cudaStream_t stream, int pdl) {
+  const int chunk = (max_T + cs - 1) / cs;
+  const size_t smem = (4 + HD + ATT_WARPS * HD + ATT_WARPS) * sizeof(float) + (size_t)chunk * 2 + 16;
+  LCU_REQUIRE(smem <= 200 * 1024, "attention: %d positions per CTA do not fit in shared memory", chunk);
+  static bool attr_done[16] = {};
+  int dev = 0;
+  LCU_CUDA(cudaGetDevice(&dev));
+  if (dev < 16 && !attr_done[dev]) {
+    LCU_CUDA(cudaFuncSetAttribute(attn_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_done[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cs, p.n_heads, m);
+  cfg.blockDim = dim3(ATT_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, attn_kernel<HD>, p));
+  return LCU_OK;
+}
+
+}  // namespace
+
+int launch_attention(const attn_params& p, int m, int cluster, int max_T, cudaStream_t stream, int pdl) {
+  LCU_REQUIRE(m >= 1 && p.n_heads >= 1, "attention: empty problem");
+  LCU_REQUIRE(cluster >= 1 && cluster <= 8 && (cluster & (cluster - 1)) == 0, "attention: cluster size %d not in {1,2,4,8}", cluster);
+  LCU_REQUIRE(max_T >= 1 && max_T <= p.ctx_len, "attention: %d positions exceed the context length %d", max_T, p.ctx_len);
+  if (p.head_dim == 128) return launch_hd<128>(p, m, cluster, max_T, stream, pdl);
+  if (p.head_dim == 64) return launch_hd<64>(p, m, cluster, max_T, stream, pdl);
+  LCU_REQUIRE(false, "attention: head_dim %d not supported (64 or 128)", p.head_dim);
+}
+
+}  // namespace lcu

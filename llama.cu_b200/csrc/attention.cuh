@@ -1,0 +1,26 @@
+// Fused attention over the head-major fp16 KV cache (decode and prefill rows).
+#pragma once
+#include <math_constants.h>
+#include "common.cuh"
+
+namespace lcu {
+
+struct attn_params {
+  const __half* q;        // [m][ldq] rotated queries
+  int ldq;
+  const __half* k_cache;  // [n_heads][ctx_len][head_dim] rotated keys
+  const __half* v_cache;  // [n_heads][ctx_len][head_dim]
+  __half* out;            // [m][ldo]
+  int ldo;
+  const int* pos;         // device scalar: position of query row 0 (row r attends to 0 .. pos + r);
+  int pos_value;          // used instead when pos == nullptr
+  int ctx_len;
+  int n_heads;
+  int head_dim;
+};
+
+// m query rows; `cluster` CTAs (1, 2, 4 or 8) share one (row, head); max_T bounds pos + m so that
+// shared memory can be sized without reading the device position.
+int launch_attention(const attn_params& p, int m, int cluster, int max_T, cudaStream_t stream, int pdl);
+
+}  // namespace lcu

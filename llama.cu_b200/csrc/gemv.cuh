@@ -1,0 +1,60 @@
+// Weight-streaming matrix-vector kernels for batch-1 decode (and up to 8 activation rows).
+#pragma once
+#include "common.cuh"
+
+namespace lcu {
+
+enum gemv_epilogue : int {
+  EPI_PLAIN = 0,    // out[col][row] = half(acc + beta * float(out[col][row]))
+  EPI_ROPE_KV = 1,  // three matrices wq|wk|wv: rotate q and k pairs, write k and v into the KV cache
+  EPI_SILU = 2      // two matrices w1|w3 interleaved row by row: out[i] = half(silu(half(a_i)) * half(b_i))
+};
+
+struct gemv_params {
+  // weights: up to three [rows_per_mat][K] matrices that share K; fp16, or u8 with fp16 scales [rows][K/bs]
+  const void* w[3];
+  const __half* sc[3];
+  int n_mats;
+  int rows_per_mat;
+  int K;
+  int bs;  // 0 = fp16 weights
+  // activations: m (1..8) rows of K halves, row stride ldx.  With norm_w != nullptr (m == 1) the
+  // row is RMS-normalised first: x_i <- norm_w_i *h half(x_i * rsqrt(mean(x^2) + eps)).
+  const __half* x;
+  int m;
+  int ldx;
+  const __half* norm_w;
+  float eps;
+  // EPI_PLAIN / EPI_SILU output
+  __half* out;
+  int ldo;
+  float beta;
+  // EPI_ROPE_KV
+  const int* pos;       // device scalar: position of the token being decoded
+  __half* q_out;        // [dim]
+  __half* k_cache;      // [n_heads][ctx_len][head_dim], rotated keys
+  __half* v_cache;      // [n_heads][ctx_len][head_dim]
+  const float2* rope;   // [ctx_len][head_dim/2] (cos, sin)
+  int ctx_len;
+  int head_dim;
+  int* err;  // device error word
+};
+
+// Launch-shape knobs (defaults chosen by measurement; exposed for experiments)
+struct gemv_tuning {
+  int nstages = 4;      // shared-memory ring depth (16 rows x 1 KiB per stage)
+  int ctas_per_sm = 2;  // grid = SM count x this
+};
+gemv_tuning& gemv_tuning_ref();
+
+// Launches the kernel on `stream`; pdl != 0 marks it as a programmatic dependent of the
+// preceding launch (its weight stream starts while the previous kernel drains).
+int launch_gemv(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl);
+
+// pure-read probe with the same bulk-copy ring: mean milliseconds for one pass over `bytes` of HBM
+int bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass);
+
+// bytes one launch must move at minimum (weights + scales + activations in + out)
+size_t gemv_algorithmic_bytes(const gemv_params& p, int epilogue);
+
+}  // namespace lcu

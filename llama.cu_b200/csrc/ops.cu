@@ -1,0 +1,463 @@
+// Row-wise and element-wise kernels of the forward pass, the quantizer and the data generator.
+// Each kernel keeps the arithmetic (operation order inside an element, rounding points, libdevice
+// functions) of the reference kernel it replaces, cited beside it.
+#include "ops.cuh"
+
+#include <math_constants.h>
+
+namespace lcu {
+namespace {
+
+template <typename F>
+int launch_simple(F kernel_launch) {
+  kernel_launch();
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+// ------------------------------------------------------------------ embedding (llama_cu.cu:32-62)
+__global__ void embed_kernel(__half* x, int ldx, const void* table, const __half* scales, int bs, const short* ids, int dim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const size_t id = (size_t)ids[r];
+  if (bs == 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(table) + id * dim);
+    uint4* dst = reinterpret_cast<uint4*>(x + (size_t)r * ldx);
+    for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = src[i];
+  } else {
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(table) + id * dim;
+    const __half* sc = scales + id * (dim / bs);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+      x[(size_t)r * ldx + i] = __float2half((float(src[i]) - 127.5f) * __half2float(sc[i / bs]));
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm (llama_cu.cu:66-107)
+// Same launch shape (one 256-thread block per row) and the same reduction order as the reference.
+__global__ void __launch_bounds__(256) rms_norm_kernel(__half* out, const __half* in, const __half* weight, int w, float eps) {
+  const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const __half* x = in + (size_t)row * w;
+  __shared__ float s_warp[8];
+  __shared__ float s_rinv;
+  float s = 0.f;
+  for (int i = tid; i < w; i += 256) {
+    float v = __half2float(x[i]);
+    s += v * v;
+  }
+  s = warp_sum(s);
+  if (lane == 0) s_warp[warp] = s;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < 8 ? s_warp[lane] : 0.f;
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) s_rinv = rsqrtf(t / w + eps);
+  }
+  __syncthreads();
+  const float rinv = s_rinv;
+  for (int i = tid; i < w; i += 256) {
+    float v = __half2float(x[i]);
+    out[(size_t)row * w + i] = __hmul(weight[i], __float2half(v * rinv));
+  }
+}
+
+// ------------------------------------------------------------------ RoPE (llama_cu.cu:368-389)
+__global__ void rope_table_kernel(float2* table, int ctx_len, int head_dim, float theta) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int half_dim = head_dim >> 1;
+  if (idx >= ctx_len * half_dim) return;
+  const int pos = idx / half_dim, i = idx - pos * half_dim;
+  const int head_c = 2 * i;
+  const float angle = pos / powf(theta, float(head_c) / head_dim);
+  table[idx] = make_float2(cosf(angle), sinf(angle));
+}
+
+__global__ void rope_scatter_kernel(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
+                                    const float2* rope, const int* pos_ptr, int pos_value, int m, int dim, int n_heads, int ctx_len) {
+  const int r = blockIdx.y;
+  const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+  if (c >= dim) return;
+  const int hd = dim / n_heads;
+  const int head = c / hd, j = c - head * hd;
+  const int pos = (pos_ptr ? *pos_ptr : pos_value) + r;
+  const float2 cs = rope[(size_t)pos * (hd >> 1) + (j >> 1)];
+  const float a_cos = cs.x, a_sin = cs.y;
+  const size_t src = (size_t)r * dim + c;
+  const size_t dst = ((size_t)head * ctx_len + pos) * hd + j;
+  {
+    const float real = __half2float(q[src]), imag = __half2float(q[src + 1]);
+    q[src] = __float2half(real * a_cos - imag * a_sin);
+    q[src + 1] = __float2half(real * a_sin + imag * a_cos);
+  }
+  {
+    const float real = __half2float(k_new[src]), imag = __half2float(k_new[src + 1]);
+    k_cache[dst] = __float2half(real * a_cos - imag * a_sin);
+    k_cache[dst + 1] = __float2half(real * a_sin + imag * a_cos);
+  }
+  *reinterpret_cast<__half2*>(v_cache + dst) = *reinterpret_cast<const __half2*>(v_new + src);
+}
+
+// ------------------------------------------------------------------ SiLU gate (llama_cu.cu:533-539)
+__global__ void silu_kernel(__half* out, const __half* a, const __half* b, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const float val = __half2float(a[i]);
+    out[i] = __float2half(val / (1.0f + expf(-val)) * __half2float(b[i]));
+  }
+}
+
+// ------------------------------------------------------------------ logits head
+// softmax_rows with temperature (llama_cu.cu:433-499) followed by the host's first-maximum search
+// over the half probabilities (llama_cu.cu:1205-1209), in one block.  The exp-sum keeps the
+// reference's order: 256 strided partial sums, xor trees in 8 warps, xor tree over the warp sums.
+constexpr int HEAD_THREADS = 1024;
+__global__ void __launch_bounds__(HEAD_THREADS) logits_head_kernel(const head_params p, int cache_exp) {
+  extern __shared__ float e_cache[];
+  __shared__ float s_red[32];
+  __shared__ int s_idx[32];
+  __shared__ float s_bcast[2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int V = p.n_vocab;
+  const float temp = p.temperature;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  float mx = -CUDART_INF_F;
+  for (int i = tid; i < V; i += HEAD_THREADS) mx = fmaxf(mx, __half2float(p.logits[i]) / temp);
+  mx = warp_max(mx);
+  if (lane == 0) s_red[warp] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float m = s_red[0];
+    for (int w = 1; w < HEAD_THREADS / 32; ++w) m = fmaxf(m, s_red[w]);
+    s_bcast[0] = m;
+  }
+  __syncthreads();
+  mx = s_bcast[0];
+
+  if (cache_exp)
+    for (int i = tid; i < V; i += HEAD_THREADS) e_cache[i] = expf(__half2float(p.logits[i]) / temp - mx);
+  __syncthreads();
+  float sum = 0.f;
+  if (tid < 256) {
+    if (cache_exp)
+      for (int i = tid; i < V; i += 256) sum += e_cache[i];
+    else
+      for (int i = tid; i < V; i += 256) sum += expf(__half2float(p.logits[i]) / temp - mx);
+    sum = warp_sum(sum);
+    if (lane == 0) s_red[warp] = sum;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < 8 ? s_red[lane] : 0.f;
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) s_bcast[1] = t;
+  }
+  __syncthreads();
+  sum = s_bcast[1];
+
+  // probabilities (half), their maximum, and the first index that attains it
+  float best = -1.f;
+  int best_i = 0x7fffffff;
+  for (int i = tid; i < V; i += HEAD_THREADS) {
+    const float e = cache_exp ? e_cache[i] : expf(__half2float(p.logits[i]) / temp - mx);
+    const __half ph = __float2half(e / sum);
+    p.probs[i] = ph;
+    const float pf = __half2float(ph);
+    if (pf > best) {  // strided ascending i: keeps the first index of this thread's maximum
+      best = pf;
+      best_i = i;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ob > best || (ob == best && oi < best_i)) {
+      best = ob;
+      best_i = oi;
+    }
+  }
+  if (lane == 0) {
+    s_red[warp] = best;
+    s_idx[warp] = best_i;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < HEAD_THREADS / 32; ++w)
+      if (s_red[w] > best || (s_red[w] == best && s_idx[w] < best_i)) {
+        best = s_red[w];
+        best_i = s_idx[w];
+      }
+    if (p.token_out) *p.token_out = best_i;
+    if (p.next_ids) p.next_ids[0] = (short)best_i;
+    if (p.pos) *p.pos += p.advance;
+    if (p.log && p.step) {
+      if (*p.step < p.log_capacity) p.log[*p.step] = (short)best_i;
+      *p.step += 1;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ quantizer (transform.cu:28-87)
+// One warp per (row, K-block).  scale = half(absmax / 127.5f); q = u8(roundf(127.5f + x / float(scale))).
+__global__ void __launch_bounds__(256) quantize_kernel(uint8_t* q, __half* scales, const __half* in, size_t n_blocks, int bs) {
+  const int lane = threadIdx.x & 31;
+  const size_t warp0 = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const size_t nwarps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t blk = warp0; blk < n_blocks; blk += nwarps) {
+    const __half* x = in + blk * bs;
+    float absmax_val = 0;
+    for (int i = lane * 4; i < bs; i += 128) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(x + i);
+      const __half2* h = reinterpret_cast<const __half2*>(&raw);
+      absmax_val = fmaxf(absmax_val, fabsf(__low2float(h[0])));
+      absmax_val = fmaxf(absmax_val, fabsf(__high2float(h[0])));
+      absmax_val = fmaxf(absmax_val, fabsf(__low2float(h[1])));
+      absmax_val = fmaxf(absmax_val, fabsf(__high2float(h[1])));
+    }
+    absmax_val = warp_max(absmax_val);
+    const __half s_absmax = __float2half(absmax_val / 127.5f);
+    if (lane == 0) scales[blk] = s_absmax;
+    const float sf = __half2float(s_absmax);
+    for (int i = lane * 4; i < bs; i += 128) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(x + i);
+      const __half* h = reinterpret_cast<const __half*>(&raw);
+      uchar4 o;
+      o.x = static_cast<uint8_t>(roundf(127.5f + __half2float(h[0]) / sf));
+      o.y = static_cast<uint8_t>(roundf(127.5f + __half2float(h[1]) / sf));
+      o.z = static_cast<uint8_t>(roundf(127.5f + __half2float(h[2]) / sf));
+      o.w = static_cast<uint8_t>(roundf(127.5f + __half2float(h[3]) / sf));
+      *reinterpret_cast<uchar4*>(q + blk * bs + i) = o;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) dequantize_kernel(__half* out, const __half* scales, const uint8_t* q, size_t n, int bs) {
+  const size_t i4 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= n) return;
+  const uchar4 v = *reinterpret_cast<const uchar4*>(q + i4);
+  const float s = __half2float(scales[i4 / bs]);  // bs % 4 == 0: the four share a block
+  __half2 lo = __halves2half2(__float2half((float(v.x) - 127.5f) * s), __float2half((float(v.y) - 127.5f) * s));
+  __half2 hi = __halves2half2(__float2half((float(v.z) - 127.5f) * s), __float2half((float(v.w) - 127.5f) * s));
+  *reinterpret_cast<__half2*>(out + i4) = lo;
+  *reinterpret_cast<__half2*>(out + i4 + 2) = hi;
+}
+
+// error statistics (transform.cu:100-150) with a fixed-order two-stage reduction instead of float atomics
+__global__ void __launch_bounds__(256) error_partial_kernel(float* partial, const __half* a, const __half* b, size_t n) {
+  __shared__ float s_sq[8], s_mx[8], s_ab[8];
+  float sq = 0, mx = 0, ab = 0;
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
+    const float d = __half2float(a[i]) - __half2float(b[i]);
+    sq += d * d;
+    mx = fmaxf(mx, fabsf(d));
+    ab += fabsf(d);
+  }
+  sq = warp_sum(sq);
+  ab = warp_sum(ab);
+  mx = warp_max(mx);
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) {
+    s_sq[warp] = sq;
+    s_mx[warp] = mx;
+    s_ab[warp] = ab;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) {
+      sq += s_sq[w];
+      ab += s_ab[w];
+      mx = fmaxf(mx, s_mx[w]);
+    }
+    partial[blockIdx.x * 3 + 0] = sq;
+    partial[blockIdx.x * 3 + 1] = mx;
+    partial[blockIdx.x * 3 + 2] = ab;
+  }
+}
+__global__ void error_final_kernel(float* stats, const float* partial, int nparts, size_t n) {
+  double sq = 0, ab = 0;
+  float mx = 0;
+  for (int i = 0; i < nparts; ++i) {
+    sq += partial[i * 3];
+    mx = fmaxf(mx, partial[i * 3 + 1]);
+    ab += partial[i * 3 + 2];
+  }
+  stats[0] = (float)(sq / (double)n);
+  stats[1] = mx;
+  stats[2] = (float)(ab / (double)n);
+}
+
+// ------------------------------------------------------------------ synthetic data
+// Philox4x32-10 block per element, keyed by the seed, counter = (index, stream id); the eight
+// 16-bit lanes are summed (Irwin-Hall) and scaled to unit variance.  Integer arithmetic plus two
+// binary32 multiplications: a host implementation of the same recipe yields identical bits.
+__device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+    const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+    c[0] = n0;
+    c[1] = lo1;
+    c[2] = n2;
+    c[3] = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+__global__ void synth_kernel(__half* out, size_t n, uint64_t seed, uint64_t stream_id, float scale, uint64_t first) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint64_t idx = first + i;
+    uint32_t c[4] = {(uint32_t)idx, (uint32_t)(idx >> 32), (uint32_t)stream_id, (uint32_t)(stream_id >> 32)};
+    philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+    int s = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s += (int)(c[k] & 0xffffu) + (int)(c[k] >> 16);
+    const float z = __fmul_rn((float)(s - 262140), 0x1.3988e2p-16f);  // 1 / sqrt(8 * (65536^2 - 1) / 12)
+    out[i] = __float2half(__fmul_rn(z, scale));
+  }
+}
+__global__ void bump_pos_kernel(int* pos, int inc) { *pos += inc; }
+__global__ void token_to_ids_kernel(short* ids, const int* token) { ids[0] = (short)*token; }
+__global__ void fill_half_kernel(__half* out, size_t n, __half v) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = v;
+}
+
+}  // namespace
+
+uint64_t fnv1a64(const char* s) {
+  uint64_t h = 0xcbf29ce484222325ull;
+  for (; *s; ++s) {
+    h ^= (uint8_t)*s;
+    h *= 0x100000001b3ull;
+  }
+  return h;
+}
+
+int launch_embed(__half* x, int ldx, const void* table, const __half* scales, int bs, const short* ids, int n_ids, int dim,
+                 cudaStream_t stream, int pdl) {
+  LCU_REQUIRE(dim % 8 == 0 && ldx % 8 == 0, "embed: dim must be a multiple of 8");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_ids);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, embed_kernel, x, ldx, table, scales, bs, ids, dim));
+  return LCU_OK;
+}
+
+int launch_rms_norm(__half* out, const __half* in, const __half* weight, int rows, int dim, float eps, cudaStream_t stream) {
+  rms_norm_kernel<<<rows, 256, 0, stream>>>(out, in, weight, dim, eps);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cudaStream_t stream) {
+  const int n = ctx_len * (head_dim / 2);
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(table, ctx_len, head_dim, theta);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_rope_scatter(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
+                        const float2* rope, const int* pos, int pos_value, int m, int dim, int n_heads, int ctx_len,
+                        cudaStream_t stream) {
+  dim3 grid((dim / 2 + 127) / 128, m);
+  rope_scatter_kernel<<<grid, 128, 0, stream>>>(q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_silu(__half* out, const __half* a, const __half* b, size_t n, cudaStream_t stream) {
+  silu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(out, a, b, n);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_logits_head(const head_params& p, cudaStream_t stream, int pdl) {
+  static bool attr_done[16] = {};
+  int dev = 0;
+  LCU_CUDA(cudaGetDevice(&dev));
+  if (dev < 16 && !attr_done[dev]) {
+    LCU_CUDA(cudaFuncSetAttribute(logits_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_done[dev] = true;
+  }
+  const size_t need = (size_t)p.n_vocab * sizeof(float);
+  const int cache_exp = need <= 200 * 1024;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(HEAD_THREADS);
+  cfg.dynamicSmemBytes = cache_exp ? need : 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, logits_head_kernel, p, cache_exp));
+  return LCU_OK;
+}
+
+int launch_quantize_absmax_uint8(uint8_t* q, __half* scales, const __half* in, size_t h, size_t w, int bs, cudaStream_t stream) {
+  LCU_REQUIRE(bs > 0 && bs % 4 == 0 && w % bs == 0, "quantize: block size %d must be a multiple of 4 that divides the row length %zu", bs, w);
+  LCU_REQUIRE(((uintptr_t)in & 7) == 0 && ((uintptr_t)q & 3) == 0, "quantize: buffers must be 8-byte (input) and 4-byte (output) aligned");
+  const size_t n_blocks = h * (w / bs);
+  if (n_blocks == 0) return LCU_OK;
+  size_t grid = (n_blocks + 7) / 8;
+  if (grid > 148 * 16) grid = 148 * 16;
+  quantize_kernel<<<(unsigned)grid, 256, 0, stream>>>(q, scales, in, n_blocks, bs);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_dequantize_absmax_uint8(__half* out, const __half* scales, const uint8_t* q, size_t h, size_t w, int bs,
+                                   cudaStream_t stream) {
+  LCU_REQUIRE(bs > 0 && bs % 4 == 0 && w % bs == 0, "dequantize: block size %d must be a multiple of 4 that divides the row length %zu", bs, w);
+  const size_t n = h * w;
+  if (n == 0) return LCU_OK;
+  dequantize_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(out, scales, q, n, bs);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_error_stats(float* stats, float* partial, const __half* a, const __half* b, size_t n, cudaStream_t stream) {
+  error_partial_kernel<<<256, 256, 0, stream>>>(partial, a, b, n);
+  error_final_kernel<<<1, 1, 0, stream>>>(stats, partial, 256, n);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_synth_fill(__half* out, size_t n, uint64_t seed, uint64_t stream_id, float scale, uint64_t first, cudaStream_t stream) {
+  if (n == 0) return LCU_OK;
+  size_t grid = (n + 255) / 256;
+  if (grid > 148 * 32) grid = 148 * 32;
+  synth_kernel<<<(unsigned)grid, 256, 0, stream>>>(out, n, seed, stream_id, scale, first);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_bump_pos(int* pos, int inc, cudaStream_t stream) {
+  bump_pos_kernel<<<1, 1, 0, stream>>>(pos, inc);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+int launch_token_to_ids(short* ids, const int* token, cudaStream_t stream) {
+  token_to_ids_kernel<<<1, 1, 0, stream>>>(ids, token);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int launch_fill_half(__half* out, size_t n, float value, cudaStream_t stream) {
+  if (n == 0) return LCU_OK;
+  size_t grid = (n + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  fill_half_kernel<<<(unsigned)grid, 256, 0, stream>>>(out, n, __float2half(value));
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+}  // namespace lcu

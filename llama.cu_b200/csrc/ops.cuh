@@ -1,0 +1,63 @@
+// Element-wise and row-wise kernels around the matrix products: embedding gather, RMSNorm,
+// RoPE + KV-cache scatter, SiLU gate, logits softmax + argmax, the block-absmax quantizer and the
+// synthetic-weight generator.
+#pragma once
+#include "common.cuh"
+
+namespace lcu {
+
+// x[r][:] = table[ids[r]][:]; u8 tables are de-quantised with half((q - 127.5f) * scale) (bs > 0)
+int launch_embed(__half* x, int ldx, const void* table, const __half* scales, int bs, const short* ids, int n_ids, int dim,
+                 cudaStream_t stream, int pdl);
+
+// out[r][i] = weight[i] *h half(float(in[r][i]) * rsqrt(mean(in[r]^2) + eps))
+int launch_rms_norm(__half* out, const __half* in, const __half* weight, int rows, int dim, float eps, cudaStream_t stream);
+
+// (cos, sin) of pos / theta^(2i/head_dim) for pos < ctx_len, i < head_dim/2
+int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cudaStream_t stream);
+
+// Rotates q rows in place (row r at position *pos + r), rotates the new k rows into the head-major
+// key cache and copies the new v rows into the head-major value cache.  The position of row 0 is
+// *pos, or pos_value when pos == nullptr.
+int launch_rope_scatter(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
+                        const float2* rope, const int* pos, int pos_value, int m, int dim, int n_heads, int ctx_len,
+                        cudaStream_t stream);
+
+// out = half(silu(float(a)) * float(b)) element-wise
+int launch_silu(__half* out, const __half* a, const __half* b, size_t n, cudaStream_t stream);
+
+// probs = softmax(logits / temp) rounded to half (written over `probs`), token = first index of the
+// maximum probability.  Also advances the decode state for device-chained generation:
+// *pos += advance; next_ids[0] = token; if log != nullptr, log[*step] = token and ++*step.
+struct head_params {
+  const __half* logits;
+  __half* probs;  // may alias logits
+  int n_vocab;
+  float temperature;
+  int* token_out;
+  short* next_ids;
+  int* pos;
+  int advance;
+  short* log;
+  int* step;
+  int log_capacity;
+};
+int launch_logits_head(const head_params& p, cudaStream_t stream, int pdl);
+
+// block-absmax quantizer, bit-identical to the reference's (transform.cu:28-72)
+int launch_quantize_absmax_uint8(uint8_t* q, __half* scales, const __half* in, size_t h, size_t w, int bs, cudaStream_t stream);
+int launch_dequantize_absmax_uint8(__half* out, const __half* scales, const uint8_t* q, size_t h, size_t w, int bs,
+                                   cudaStream_t stream);
+// stats[0] = mean squared error, [1] = max abs error, [2] = mean abs error; partial is scratch of 3*256 floats
+int launch_error_stats(float* stats, float* partial, const __half* a, const __half* b, size_t n, cudaStream_t stream);
+
+// seeded synthetic data: out[i] = half(scale * z(seed, fnv1a(name), first + i)), z ~ approx N(0,1)
+int launch_synth_fill(__half* out, size_t n, uint64_t seed, uint64_t stream_id, float scale, uint64_t first, cudaStream_t stream);
+int launch_fill_half(__half* out, size_t n, float value, cudaStream_t stream);
+uint64_t fnv1a64(const char* s);
+
+// pipeline helpers: *pos += inc; ids[0] = (short)*token (ids may live on a peer GPU)
+int launch_bump_pos(int* pos, int inc, cudaStream_t stream);
+int launch_token_to_ids(short* ids, const int* token, cudaStream_t stream);
+
+}  // namespace lcu

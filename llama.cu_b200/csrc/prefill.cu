@@ -1,0 +1,31 @@
+// Prompt-processing matrix product (reference: matmul_nt dispatch, llama_cu.cu:1463-1523).
+#include "prefill.cuh"
+
+#include "gemv.cuh"
+
+namespace lcu {
+
+int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, float beta, int* err, cudaStream_t stream) {
+  const int K = (int)w.cols, N = (int)w.rows;
+  for (int t = 0; t < m; t += 8) {
+    gemv_params p{};
+    p.w[0] = w.w;
+    p.sc[0] = w.sc;
+    p.n_mats = 1;
+    p.rows_per_mat = N;
+    p.K = K;
+    p.bs = w.bs;
+    p.x = lhs + (size_t)t * K;
+    p.m = m - t < 8 ? m - t : 8;
+    p.ldx = K;
+    p.out = out + (size_t)t * N;
+    p.ldo = N;
+    p.beta = beta;
+    p.err = err;
+    int rc = launch_gemv(p, EPI_PLAIN, stream, 0);
+    if (rc) return rc;
+  }
+  return LCU_OK;
+}
+
+}  // namespace lcu

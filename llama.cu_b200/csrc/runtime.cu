@@ -1,0 +1,841 @@
+// Model storage and the forward pass.
+//
+// Drop-in scope: what the reference does in llama_model_impl (llama_cu.cu:888-997) and
+// llama_context_impl (llama_cu.cu:999-1304), re-planned for B200:
+//   * all weights of a GPU live in one arena (one cudaMalloc), tensors 256-byte aligned, in the
+//     reference's own [rows][K] row-major layout, so the files of a weight directory load as is;
+//   * the KV cache is head-major [head][position][head_dim] with keys stored already rotated
+//     (the reference re-rotates the whole prefix every step, llama_cu.cu:1150-1153);
+//   * a decode step is 5 kernels per layer (fused norm+QKV+RoPE+cache write, attention,
+//     wo+residual, norm+w1|w3+SiLU, w2+residual) instead of 15, no allocation, no host
+//     synchronisation, replayed as one CUDA graph with programmatic dependent launches;
+//   * the position is read from device memory, so the same graph serves every step and greedy
+//     decoding can run chained on the device.
+#include "runtime.cuh"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstring>
+
+#include "attention.cuh"
+#include "gemv.cuh"
+#include "ops.cuh"
+#include "prefill.cuh"
+
+namespace lcu {
+
+// ------------------------------------------------------------------ error text
+static thread_local char g_err[512] = "";
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+}
+const char* last_error() { return g_err; }
+
+struct device_guard {
+  int prev = 0;
+  explicit device_guard(int dev) {
+    cudaGetDevice(&prev);
+    cudaSetDevice(dev);
+  }
+  ~device_guard() { cudaSetDevice(prev); }
+};
+
+uint32_t ffn_dim_of(const model_params& p) {
+  uint32_t a = p.dim * 8 / 3;
+  return (a + p.multiple_of - 1) / p.multiple_of * p.multiple_of;
+}
+
+std::vector<int> partition::used_gpus() const {
+  std::vector<int> out;
+  for (int g : layer_gpus)
+    if (std::find(out.begin(), out.end(), g) == out.end()) out.push_back(g);
+  return out;
+}
+
+// ------------------------------------------------------------------ model
+namespace {
+constexpr size_t ALIGN = 256;
+struct carve {
+  size_t off = 0;
+  size_t take(size_t bytes) {
+    size_t o = off;
+    off += round_up(bytes, ALIGN);
+    return o;
+  }
+};
+
+struct tensor_slot {  // one named tensor of the weight directory
+  std::string name;
+  dev_matrix* mat;    // matrix, or
+  __half** vec;       // norm vector
+  size_t len;         // vector length
+  int device;
+};
+
+std::vector<tensor_slot> enumerate(model& m) {
+  const model_params& p = m.params;
+  std::vector<tensor_slot> out;
+  auto mat = [&](const std::string& name, dev_matrix& d, size_t rows, size_t cols, int dev) {
+    d.rows = rows;
+    d.cols = cols;
+    d.bs = p.q_type ? p.quantization_block_size : 0;
+    out.push_back({name, &d, nullptr, 0, dev});
+  };
+  auto vec = [&](const std::string& name, __half*& v, size_t len, int dev) { out.push_back({name, nullptr, &v, len, dev}); };
+  mat("tok_embeddings", m.tok_embeddings, p.n_vocab, p.dim, m.part.embedding_gpu());
+  for (uint32_t i = 0; i < p.n_layers; ++i) {
+    layer_weights& L = m.layers[i];
+    const int dev = m.part.layer_gpus[i];
+    const std::string b = "layers." + std::to_string(i) + ".";
+    vec(b + "attention_norm", L.attn_norm, p.dim, dev);
+    vec(b + "ffn_norm", L.ffn_norm, p.dim, dev);
+    mat(b + "attention.wq", L.wq, p.dim, p.dim, dev);
+    mat(b + "attention.wk", L.wk, p.dim, p.dim, dev);
+    mat(b + "attention.wv", L.wv, p.dim, p.dim, dev);
+    mat(b + "attention.wo", L.wo, p.dim, p.dim, dev);
+    mat(b + "feed_forward.w1", L.w1, m.ffn, p.dim, dev);
+    mat(b + "feed_forward.w3", L.w3, m.ffn, p.dim, dev);
+    mat(b + "feed_forward.w2", L.w2, p.dim, m.ffn, dev);
+  }
+  vec("norm", m.norm, p.dim, m.part.output_gpu());
+  mat("output", m.output, p.n_vocab, p.dim, m.part.output_gpu());
+  return out;
+}
+}  // namespace
+
+model::~model() {
+  for (auto& a : arenas) {
+    device_guard g(a.first);
+    cudaFree(a.second);
+  }
+}
+
+int model::create(std::unique_ptr<model>& out, const model_params& p, const partition& part) {
+  LCU_REQUIRE(p.magic == PARAMS_MAGIC && p.fourcc == PARAMS_FOURCC, "model: bad magic in params");
+  LCU_REQUIRE(p.dim > 0 && p.n_heads > 0 && p.n_layers > 0 && p.n_vocab > 0 && p.multiple_of > 0, "model: empty dimension in params");
+  LCU_REQUIRE(p.dim % p.n_heads == 0, "model: dim %u not divisible by n_heads %u", p.dim, p.n_heads);
+  LCU_REQUIRE(p.dim % 256 == 0, "model: dim %u must be a multiple of 256", p.dim);
+  LCU_REQUIRE(p.n_vocab <= 32768 && p.n_vocab % 2 == 0, "model: n_vocab %u must be even and fit a 16-bit token id", p.n_vocab);
+  LCU_REQUIRE(p.q_type <= 1, "model: unsupported quantization type %u", p.q_type);
+  const uint32_t ffn = ffn_dim_of(p);
+  LCU_REQUIRE(ffn % 256 == 0, "model: ffn dim %u must be a multiple of 256", ffn);
+  if (p.q_type) {
+    const int bs = p.quantization_block_size;
+    LCU_REQUIRE(bs == 32 || bs == 64 || bs == 128, "model: quantization block size %d not in {32,64,128}", bs);
+  }
+  LCU_REQUIRE(part.layer_gpus.size() == p.n_layers, "model: partition has %zu layers, params %u", part.layer_gpus.size(), p.n_layers);
+  int ndev = 0;
+  LCU_CUDA(cudaGetDeviceCount(&ndev));
+  for (int g : part.layer_gpus) LCU_REQUIRE(g >= 0 && g < ndev, "model: partition names GPU %d but %d are visible", g, ndev);
+
+  auto m = std::make_unique<model>();
+  m->params = p;
+  m->ffn = ffn;
+  m->part = part;
+  m->layers.resize(p.n_layers);
+  auto slots = enumerate(*m);
+  // size and carve one arena per GPU
+  for (int dev : part.used_gpus()) {
+    carve c;
+    for (auto& s : slots)
+      if (s.device == dev) {
+        if (s.mat) {
+          c.take(s.mat->weight_bytes());
+          c.take(s.mat->scale_bytes());
+        } else {
+          c.take(s.len * 2);
+        }
+      }
+    device_guard g(dev);
+    void* base = nullptr;
+    LCU_CUDA(cudaMalloc(&base, c.off));
+    m->arenas.push_back({dev, base});
+    m->weight_bytes_total += c.off;
+    carve c2;
+    for (auto& s : slots)
+      if (s.device == dev) {
+        if (s.mat) {
+          s.mat->w = (char*)base + c2.take(s.mat->weight_bytes());
+          size_t so = c2.take(s.mat->scale_bytes());
+          s.mat->sc = s.mat->bs ? (__half*)((char*)base + so) : nullptr;
+        } else {
+          *s.vec = (__half*)((char*)base + c2.take(s.len * 2));
+        }
+      }
+  }
+  out = std::move(m);
+  return LCU_OK;
+}
+
+int model::find_tensor(const std::string& name, int which, void** ptr, size_t* bytes, int* device) {
+  for (auto& s : enumerate(*this)) {
+    if (s.name != name) continue;
+    if (device) *device = s.device;
+    if (s.mat) {
+      LCU_REQUIRE(which == 0 || s.mat->bs, "tensor %s has no scales", name.c_str());
+      *ptr = which == 0 ? s.mat->w : (void*)s.mat->sc;
+      *bytes = which == 0 ? s.mat->weight_bytes() : s.mat->scale_bytes();
+    } else {
+      LCU_REQUIRE(which == 0, "tensor %s has no scales", name.c_str());
+      *ptr = *s.vec;
+      *bytes = s.len * 2;
+    }
+    return LCU_OK;
+  }
+  LCU_REQUIRE(false, "no tensor named %s", name.c_str());
+}
+
+namespace {
+// copies a whole file of exactly `bytes` bytes into device memory
+int load_file(const std::string& path, void* dst, size_t bytes) {
+  int fd = open(path.c_str(), O_RDONLY);
+  if (fd < 0) {
+    set_last_error("cannot open %s", path.c_str());
+    return LCU_ERR_IO;
+  }
+  struct stat st;
+  if (fstat(fd, &st) != 0 || (size_t)st.st_size != bytes) {
+    close(fd);
+    set_last_error("%s: expected %zu bytes, file has %lld", path.c_str(), bytes, (long long)st.st_size);
+    return LCU_ERR_IO;
+  }
+  void* map = bytes ? mmap(nullptr, bytes, PROT_READ, MAP_PRIVATE, fd, 0) : nullptr;
+  close(fd);
+  if (bytes && map == MAP_FAILED) {
+    set_last_error("cannot map %s", path.c_str());
+    return LCU_ERR_IO;
+  }
+  cudaError_t e = bytes ? cudaMemcpy(dst, map, bytes, cudaMemcpyHostToDevice) : cudaSuccess;
+  if (bytes) munmap(map, bytes);
+  if (e != cudaSuccess) {
+    set_last_error("copy of %s to the device failed: %s", path.c_str(), cudaGetErrorString(e));
+    return LCU_ERR_CUDA;
+  }
+  return LCU_OK;
+}
+}  // namespace
+
+int model::load_dir(const std::string& dir) {
+  for (auto& s : enumerate(*this)) {
+    device_guard g(s.device);
+    const std::string base = dir + "/" + s.name;
+    int rc;
+    if (s.mat) {
+      const std::string dims = std::to_string(s.mat->rows) + "_" + std::to_string(s.mat->cols);
+      rc = load_file(base + ".weight__" + dims, s.mat->w, s.mat->weight_bytes());
+      if (rc == LCU_OK && s.mat->bs)
+        rc = load_file(base + ".scale__" + std::to_string(s.mat->rows) + "_" + std::to_string(s.mat->cols / s.mat->bs), s.mat->sc,
+                       s.mat->scale_bytes());
+    } else {
+      rc = load_file(base + ".weight__" + std::to_string(s.len), *s.vec, s.len * 2);
+    }
+    if (rc != LCU_OK) return rc;
+  }
+  return LCU_OK;
+}
+
+int model::fill_synthetic(uint64_t seed, float scale) {
+  for (auto& s : enumerate(*this)) {
+    device_guard g(s.device);
+    if (!s.mat) {
+      int rc = launch_fill_half(*s.vec, s.len, 1.0f, 0);
+      if (rc) return rc;
+      continue;
+    }
+    const size_t n = s.mat->rows * s.mat->cols;
+    const uint64_t sid = fnv1a64(s.name.c_str());
+    if (s.mat->bs == 0) {
+      int rc = launch_synth_fill((__half*)s.mat->w, n, seed, sid, scale, 0, 0);
+      if (rc) return rc;
+    } else {
+      __half* tmp = nullptr;
+      LCU_CUDA(cudaMalloc(&tmp, n * 2));
+      int rc = launch_synth_fill(tmp, n, seed, sid, scale, 0, 0);
+      if (!rc) rc = launch_quantize_absmax_uint8((uint8_t*)s.mat->w, s.mat->sc, tmp, s.mat->rows, s.mat->cols, s.mat->bs, 0);
+      cudaError_t e = cudaDeviceSynchronize();
+      cudaFree(tmp);
+      if (rc) return rc;
+      LCU_CUDA(e);
+    }
+  }
+  for (auto& a : arenas) {
+    device_guard g(a.first);
+    LCU_CUDA(cudaDeviceSynchronize());
+  }
+  return LCU_OK;
+}
+
+// ------------------------------------------------------------------ context
+struct gpu_state {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev = nullptr;
+  void* arena = nullptr;
+  size_t arena_bytes = 0;
+  __half *x = nullptr, *norm = nullptr, *q = nullptr, *kn = nullptr, *vn = nullptr, *att = nullptr;
+  __half *h1 = nullptr, *h3 = nullptr, *hs = nullptr;
+  float2* rope = nullptr;
+  int* state = nullptr;  // [0] position, [1] step counter, [2] last token, [3] error word
+};
+
+struct context_impl {
+  model* m = nullptr;
+  context_options opt;
+  int start_pos = 0;
+  std::vector<gpu_state> gpus;           // in order of first use
+  std::vector<int> layer_slot;           // layer -> index into gpus
+  std::vector<__half*> k_cache, v_cache; // per layer, on the layer's GPU
+  std::vector<void*> kv_arenas;          // one per GPU
+  size_t kv_bytes = 0;
+  short* ids = nullptr;                  // token ids on the embedding GPU [context_len]
+  __half* logits = nullptr;              // on the output GPU
+  __half* probs = nullptr;
+  short* log = nullptr;                  // generated tokens of a chained run [context_len]
+  int* h_stage = nullptr;                // pinned: [0] position, [1] zero, [2] token read-back
+  short* h_ids = nullptr;                // pinned token staging [context_len]
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  cudaGraphExec_t graph = nullptr;
+  bool graph_failed = false;
+  bool warmed = false;                   // the first decode step runs un-captured (one-time kernel attribute set-up)
+  int last_row = 0;                      // row of x that holds the last token's residual stream
+
+  gpu_state& first() { return gpus.front(); }
+  gpu_state& last() { return gpus.back(); }
+
+  gemv_params params_base(gpu_state& g, int K);
+  gemv_params params_qkv(int l);
+  gemv_params params_wo(int l);
+  gemv_params params_w13(int l);
+  gemv_params params_w2(int l);
+  gemv_params params_out(int row);
+  int enqueue_hop(int from, int to, int m_rows);
+  int enqueue_decode_step();
+  int enqueue_prefill(int m_rows);
+  int build_graph();
+  int run_decode_step();
+  int stage_inputs(const short* tokens, int n);
+};
+
+context::~context() {
+  if (!impl) return;
+  context_impl& c = *impl;
+  if (c.graph) cudaGraphExecDestroy(c.graph);
+  for (size_t i = 0; i < c.gpus.size(); ++i) {
+    device_guard g(c.gpus[i].device);
+    cudaDeviceSynchronize();
+    if (c.gpus[i].arena) cudaFree(c.gpus[i].arena);
+    if (i < c.kv_arenas.size() && c.kv_arenas[i]) cudaFree(c.kv_arenas[i]);
+    if (c.gpus[i].stream) cudaStreamDestroy(c.gpus[i].stream);
+    if (c.gpus[i].ev) cudaEventDestroy(c.gpus[i].ev);
+  }
+  if (c.t0) cudaEventDestroy(c.t0);
+  if (c.t1) cudaEventDestroy(c.t1);
+  if (c.h_stage) cudaFreeHost(c.h_stage);
+  if (c.h_ids) cudaFreeHost(c.h_ids);
+}
+
+int context::create(std::unique_ptr<context>& out, model* m, const context_options& opt) {
+  LCU_REQUIRE(m != nullptr, "context: null model");
+  LCU_REQUIRE(opt.context_len >= 1 && opt.context_len <= 32768, "context: context length %d outside 1..32768", opt.context_len);
+  LCU_REQUIRE(opt.temperature > 0.f, "context: temperature must be positive");
+  const model_params& p = m->params;
+  const int hd = p.dim / p.n_heads;
+  LCU_REQUIRE(hd == 64 || hd == 128, "context: head_dim %d not supported (64 or 128)", hd);
+  auto ctx = std::make_unique<context>();
+  ctx->impl = std::make_unique<context_impl>();
+  context_impl& c = *ctx->impl;
+  c.m = m;
+  c.opt = opt;
+  const size_t ctxl = opt.context_len, d = p.dim, f = m->ffn;
+  const std::vector<int> used = m->part.used_gpus();
+  c.gpus.resize(used.size());
+  c.kv_arenas.assign(used.size(), nullptr);
+  c.layer_slot.resize(p.n_layers);
+  for (uint32_t l = 0; l < p.n_layers; ++l)
+    c.layer_slot[l] = (int)(std::find(used.begin(), used.end(), m->part.layer_gpus[l]) - used.begin());
+  c.k_cache.resize(p.n_layers);
+  c.v_cache.resize(p.n_layers);
+
+  for (size_t gi = 0; gi < used.size(); ++gi) {
+    gpu_state& g = c.gpus[gi];
+    g.device = used[gi];
+    device_guard dg(g.device);
+    for (int other : used)
+      if (other != g.device) {
+        cudaError_t e = cudaDeviceEnablePeerAccess(other, 0);
+        if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+          set_last_error("context: GPU %d cannot access GPU %d: %s", g.device, other, cudaGetErrorString(e));
+          return LCU_ERR_CUDA;
+        }
+        cudaGetLastError();
+      }
+    LCU_CUDA(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
+    LCU_CUDA(cudaEventCreateWithFlags(&g.ev, cudaEventDisableTiming));
+    // scratch arena: activations for up to context_len rows, rope table, state words,
+    // and (first / last GPU) token ids, logits, probabilities, token log
+    carve cv;
+    const size_t o_x = cv.take(ctxl * d * 2), o_norm = cv.take(ctxl * d * 2), o_q = cv.take(ctxl * d * 2);
+    const size_t o_kn = cv.take(ctxl * d * 2), o_vn = cv.take(ctxl * d * 2), o_att = cv.take(ctxl * d * 2);
+    const size_t o_h1 = cv.take(ctxl * f * 2), o_h3 = cv.take(ctxl * f * 2), o_hs = cv.take(ctxl * f * 2);
+    const size_t o_rope = cv.take(ctxl * (hd / 2) * sizeof(float2));
+    const size_t o_state = cv.take(64);
+    const size_t o_ids = cv.take(ctxl * 2), o_log = cv.take(ctxl * 2);
+    const size_t o_logits = cv.take((size_t)p.n_vocab * 2), o_probs = cv.take((size_t)p.n_vocab * 2);
+    LCU_CUDA(cudaMalloc(&g.arena, cv.off));
+    g.arena_bytes = cv.off;
+    LCU_CUDA(cudaMemset(g.arena, 0, cv.off));
+    char* b = (char*)g.arena;
+    g.x = (__half*)(b + o_x);
+    g.norm = (__half*)(b + o_norm);
+    g.q = (__half*)(b + o_q);
+    g.kn = (__half*)(b + o_kn);
+    g.vn = (__half*)(b + o_vn);
+    g.att = (__half*)(b + o_att);
+    g.h1 = (__half*)(b + o_h1);
+    g.h3 = (__half*)(b + o_h3);
+    g.hs = (__half*)(b + o_hs);
+    g.rope = (float2*)(b + o_rope);
+    g.state = (int*)(b + o_state);
+    if (gi == 0) c.ids = (short*)(b + o_ids);
+    if (gi + 1 == used.size()) {
+      c.logits = (__half*)(b + o_logits);
+      c.probs = (__half*)(b + o_probs);
+      c.log = (short*)(b + o_log);
+    }
+    int rc = launch_rope_table(g.rope, opt.context_len, hd, 10000.0f, g.stream);
+    if (rc) return rc;
+    // KV cache of this GPU's layers
+    size_t n_local = 0;
+    for (uint32_t l = 0; l < p.n_layers; ++l) n_local += c.layer_slot[l] == (int)gi;
+    const size_t per = round_up(ctxl * d * 2, ALIGN);
+    LCU_CUDA(cudaMalloc(&c.kv_arenas[gi], std::max<size_t>(per * 2 * n_local, ALIGN)));
+    LCU_CUDA(cudaMemset(c.kv_arenas[gi], 0, std::max<size_t>(per * 2 * n_local, ALIGN)));
+    c.kv_bytes += per * 2 * n_local;
+    size_t k = 0;
+    for (uint32_t l = 0; l < p.n_layers; ++l)
+      if (c.layer_slot[l] == (int)gi) {
+        c.k_cache[l] = (__half*)((char*)c.kv_arenas[gi] + per * (2 * k));
+        c.v_cache[l] = (__half*)((char*)c.kv_arenas[gi] + per * (2 * k + 1));
+        ++k;
+      }
+    LCU_CUDA(cudaStreamSynchronize(g.stream));
+  }
+  {
+    device_guard dg(c.first().device);
+    LCU_CUDA(cudaMallocHost(&c.h_stage, 64));
+    LCU_CUDA(cudaMallocHost(&c.h_ids, ctxl * 2));
+    memset(c.h_stage, 0, 64);
+    LCU_CUDA(cudaEventCreate(&c.t0));
+    LCU_CUDA(cudaEventCreate(&c.t1));
+  }
+  out = std::move(ctx);
+  return LCU_OK;
+}
+
+void context::clear_tokens() { impl->start_pos = 0; }  // the reference re-allocates everything here (llama_cu.cu:1004-1049)
+
+size_t context::memory_usage() const {
+  size_t n = impl->kv_bytes;
+  for (auto& g : impl->gpus) n += g.arena_bytes;
+  return n;
+}
+int context::tokens_left() const { return impl->opt.context_len - impl->start_pos; }
+int context::position() const { return impl->start_pos; }
+int context::kernels_per_step() const { return 1 + 5 * (int)impl->m->params.n_layers + 2; }
+
+int context::device_error() {
+  int worst = 0;
+  for (auto& g : impl->gpus) {
+    int e = 0;
+    device_guard dg(g.device);
+    if (cudaMemcpy(&e, g.state + 3, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (e) worst = e;
+  }
+  return worst;
+}
+
+// residual stream hand-off between pipeline stages: m_rows x dim halves over NVLink
+// (the reference copies the whole context-length buffer, llama_cu.cu:1110-1114)
+int context_impl::enqueue_hop(int from, int to, int m_rows) {
+  gpu_state& a = gpus[from];
+  gpu_state& b = gpus[to];
+  LCU_CUDA(cudaMemcpyPeerAsync(b.x, b.device, a.x, a.device, (size_t)m_rows * m->params.dim * 2, a.stream));
+  LCU_CUDA(cudaEventRecord(a.ev, a.stream));
+  LCU_CUDA(cudaStreamWaitEvent(b.stream, a.ev, 0));
+  return LCU_OK;
+}
+
+#define LCU_TRY(expr)      \
+  do {                     \
+    int _rc = (expr);      \
+    if (_rc) return _rc;   \
+  } while (0)
+
+// ---- kernel arguments of the decode step
+gemv_params context_impl::params_base(gpu_state& g, int K) {
+  gemv_params a{};
+  a.K = K;
+  a.bs = m->params.q_type ? m->params.quantization_block_size : 0;
+  a.m = 1;
+  a.ldx = K;
+  a.eps = m->params.norm_eps;
+  a.err = g.state + 3;
+  a.pos = g.state;
+  return a;
+}
+gemv_params context_impl::params_qkv(int l) {
+  gpu_state& g = gpus[layer_slot[l]];
+  const layer_weights& L = m->layers[l];
+  const int d = m->params.dim;
+  gemv_params a = params_base(g, d);
+  a.w[0] = L.wq.w; a.w[1] = L.wk.w; a.w[2] = L.wv.w;
+  a.sc[0] = L.wq.sc; a.sc[1] = L.wk.sc; a.sc[2] = L.wv.sc;
+  a.n_mats = 3;
+  a.rows_per_mat = d;
+  a.x = g.x;
+  a.norm_w = L.attn_norm;
+  a.q_out = g.q;
+  a.k_cache = k_cache[l];
+  a.v_cache = v_cache[l];
+  a.rope = g.rope;
+  a.ctx_len = opt.context_len;
+  a.head_dim = d / m->params.n_heads;
+  return a;
+}
+gemv_params context_impl::params_wo(int l) {
+  gpu_state& g = gpus[layer_slot[l]];
+  const layer_weights& L = m->layers[l];
+  const int d = m->params.dim;
+  gemv_params a = params_base(g, d);
+  a.w[0] = L.wo.w; a.sc[0] = L.wo.sc; a.n_mats = 1; a.rows_per_mat = d;
+  a.x = g.att; a.out = g.x; a.ldo = d; a.beta = 1.0f;
+  return a;
+}
+gemv_params context_impl::params_w13(int l) {
+  gpu_state& g = gpus[layer_slot[l]];
+  const layer_weights& L = m->layers[l];
+  const int d = m->params.dim, f = m->ffn;
+  gemv_params a = params_base(g, d);
+  a.w[0] = L.w1.w; a.w[1] = L.w3.w; a.sc[0] = L.w1.sc; a.sc[1] = L.w3.sc;
+  a.n_mats = 2; a.rows_per_mat = f;
+  a.x = g.x; a.norm_w = L.ffn_norm; a.out = g.hs; a.ldo = f;
+  return a;
+}
+gemv_params context_impl::params_w2(int l) {
+  gpu_state& g = gpus[layer_slot[l]];
+  const layer_weights& L = m->layers[l];
+  const int d = m->params.dim, f = m->ffn;
+  gemv_params a = params_base(g, f);
+  a.w[0] = L.w2.w; a.sc[0] = L.w2.sc; a.n_mats = 1; a.rows_per_mat = d;
+  a.x = g.hs; a.out = g.x; a.ldo = d; a.beta = 1.0f;
+  return a;
+}
+gemv_params context_impl::params_out(int row) {
+  gpu_state& g = last();
+  const int d = m->params.dim;
+  gemv_params a = params_base(g, d);
+  a.w[0] = m->output.w; a.sc[0] = m->output.sc; a.n_mats = 1; a.rows_per_mat = m->params.n_vocab;
+  a.x = g.x + (size_t)row * d; a.norm_w = m->norm; a.out = logits; a.ldo = m->params.n_vocab;
+  return a;
+}
+
+int context_impl::enqueue_decode_step() {
+  const model_params& p = m->params;
+  const int d = p.dim, hd = d / p.n_heads, f = m->ffn, bs = p.q_type ? p.quantization_block_size : 0;
+  const int pdl = opt.use_pdl;
+  {
+    gpu_state& g = first();
+    device_guard dg(g.device);
+    LCU_TRY(launch_embed(g.x, d, m->tok_embeddings.w, m->tok_embeddings.sc, bs, ids, 1, d, g.stream, 0));
+  }
+  for (uint32_t l = 0; l < p.n_layers; ++l) {
+    const int gi = layer_slot[l];
+    bool hopped = false;
+    if (l > 0 && layer_slot[l - 1] != gi) {
+      // the stage being left advances its own position word, then hands the residual row over
+      gpu_state& prev = gpus[layer_slot[l - 1]];
+      {
+        device_guard dgp(prev.device);
+        LCU_TRY(launch_bump_pos(prev.state, 1, prev.stream));
+      }
+      LCU_TRY(enqueue_hop(layer_slot[l - 1], gi, 1));
+      hopped = true;
+    }
+    gpu_state& g = gpus[gi];
+    device_guard dg(g.device);
+    const layer_weights& L = m->layers[l];
+    // fused RMSNorm + wq|wk|wv + RoPE + cache write (reference llama_cu.cu:1129-1156)
+    LCU_TRY(launch_gemv(params_qkv(l), EPI_ROPE_KV, g.stream, pdl && !hopped));
+    // attention over the cache (reference llama_cu.cu:1161-1171)
+    attn_params at{};
+    at.q = g.q; at.ldq = d;
+    at.k_cache = k_cache[l]; at.v_cache = v_cache[l];
+    at.out = g.att; at.ldo = d;
+    at.pos = g.state;
+    at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd;
+    LCU_TRY(launch_attention(at, 1, opt.attn_cluster, opt.context_len, g.stream, pdl));
+    LCU_TRY(launch_gemv(params_wo(l), EPI_PLAIN, g.stream, pdl));   // wo + residual (llama_cu.cu:1174)
+    LCU_TRY(launch_gemv(params_w13(l), EPI_SILU, g.stream, pdl));   // RMSNorm + w1|w3 + SiLU gate (llama_cu.cu:1176-1183)
+    LCU_TRY(launch_gemv(params_w2(l), EPI_PLAIN, g.stream, pdl));   // w2 + residual (llama_cu.cu:1185)
+  }
+  {
+    // final RMSNorm + output matrix, softmax(T) + first-maximum token (llama_cu.cu:1191-1209)
+    gpu_state& g = last();
+    device_guard dg(g.device);
+    LCU_TRY(launch_gemv(params_out(0), EPI_PLAIN, g.stream, pdl));
+    head_params h{};
+    h.logits = logits; h.probs = probs; h.n_vocab = p.n_vocab; h.temperature = opt.temperature;
+    h.token_out = g.state + 2; h.next_ids = gpus.size() == 1 ? ids : nullptr;
+    h.pos = g.state; h.advance = 1; h.log = log; h.step = g.state + 1; h.log_capacity = opt.context_len;
+    LCU_TRY(launch_logits_head(h, g.stream, pdl));
+    if (gpus.size() > 1) {
+      // multi-GPU: the token returns to stage 0 (the other stages advanced their position word on the way)
+      LCU_TRY(launch_token_to_ids(ids, g.state + 2, g.stream));  // peer store into stage 0's id buffer
+      LCU_CUDA(cudaEventRecord(g.ev, g.stream));
+      LCU_CUDA(cudaStreamWaitEvent(first().stream, g.ev, 0));
+    }
+  }
+  return LCU_OK;
+}
+
+int context_impl::enqueue_prefill(int m_rows) {
+  const model_params& p = m->params;
+  const int d = p.dim, hd = d / p.n_heads, f = m->ffn, bs = p.q_type ? p.quantization_block_size : 0;
+  {
+    gpu_state& g = first();
+    device_guard dg(g.device);
+    LCU_TRY(launch_embed(g.x, d, m->tok_embeddings.w, m->tok_embeddings.sc, bs, ids, m_rows, d, g.stream, 0));
+  }
+  for (uint32_t l = 0; l < p.n_layers; ++l) {
+    const int gi = layer_slot[l];
+    if (l > 0 && layer_slot[l - 1] != gi) LCU_TRY(enqueue_hop(layer_slot[l - 1], gi, m_rows));
+    gpu_state& g = gpus[gi];
+    device_guard dg(g.device);
+    const layer_weights& L = m->layers[l];
+    int* err = g.state + 3;
+    LCU_TRY(launch_rms_norm(g.norm, g.x, L.attn_norm, m_rows, d, p.norm_eps, g.stream));
+    LCU_TRY(matmul_rows(g.q, g.norm, L.wq, m_rows, 0.f, err, g.stream));
+    LCU_TRY(matmul_rows(g.kn, g.norm, L.wk, m_rows, 0.f, err, g.stream));
+    LCU_TRY(matmul_rows(g.vn, g.norm, L.wv, m_rows, 0.f, err, g.stream));
+    LCU_TRY(launch_rope_scatter(g.q, g.kn, g.vn, k_cache[l], v_cache[l], g.rope, g.state, 0, m_rows, d, p.n_heads, opt.context_len, g.stream));
+    attn_params at{};
+    at.q = g.q; at.ldq = d;
+    at.k_cache = k_cache[l]; at.v_cache = v_cache[l];
+    at.out = g.att; at.ldo = d;
+    at.pos = g.state;
+    at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd;
+    LCU_TRY(launch_attention(at, m_rows, 1, start_pos + m_rows, g.stream, 0));
+    LCU_TRY(matmul_rows(g.x, g.att, L.wo, m_rows, 1.0f, err, g.stream));
+    LCU_TRY(launch_rms_norm(g.norm, g.x, L.ffn_norm, m_rows, d, p.norm_eps, g.stream));
+    LCU_TRY(matmul_rows(g.h1, g.norm, L.w1, m_rows, 0.f, err, g.stream));
+    LCU_TRY(matmul_rows(g.h3, g.norm, L.w3, m_rows, 0.f, err, g.stream));
+    LCU_TRY(launch_silu(g.hs, g.h1, g.h3, (size_t)m_rows * f, g.stream));
+    LCU_TRY(matmul_rows(g.x, g.hs, L.w2, m_rows, 1.0f, err, g.stream));
+  }
+  {
+    gpu_state& g = last();
+    device_guard dg(g.device);
+    // only the last row's logits are used (llama_cu.cu:1194-1195)
+    LCU_TRY(launch_gemv(params_out(m_rows - 1), EPI_PLAIN, g.stream, 0));
+    head_params h{};
+    h.logits = logits; h.probs = probs; h.n_vocab = p.n_vocab; h.temperature = opt.temperature;
+    h.token_out = g.state + 2; h.next_ids = nullptr;
+    h.pos = g.state; h.advance = m_rows; h.log = nullptr; h.step = nullptr; h.log_capacity = 0;
+    LCU_TRY(launch_logits_head(h, g.stream, 0));
+    if (gpus.size() > 1) {
+      LCU_CUDA(cudaEventRecord(g.ev, g.stream));
+      LCU_CUDA(cudaStreamWaitEvent(first().stream, g.ev, 0));
+    }
+  }
+  return LCU_OK;
+}
+
+int context_impl::build_graph() {
+  gpu_state& g0 = first();
+  device_guard dg(g0.device);
+  cudaGraph_t graph = nullptr;
+  if (cudaStreamBeginCapture(g0.stream, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+    cudaGetLastError();
+    return LCU_ERR_CUDA;
+  }
+  int rc = enqueue_decode_step();
+  cudaError_t e = cudaStreamEndCapture(g0.stream, &graph);
+  if (rc != LCU_OK || e != cudaSuccess || graph == nullptr) {
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    return rc ? rc : LCU_ERR_CUDA;
+  }
+  e = cudaGraphInstantiate(&this->graph, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    this->graph = nullptr;
+    set_last_error("cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    return LCU_ERR_CUDA;
+  }
+  return LCU_OK;
+}
+
+int context_impl::run_decode_step() {
+  if (!warmed) {
+    warmed = true;
+    return enqueue_decode_step();
+  }
+  if (opt.use_graph && !graph && !graph_failed) {
+    if (build_graph() != LCU_OK) {
+      graph_failed = true;
+      fprintf(stderr, "llama_cu_b200: CUDA graph capture of the decode step failed (%s); launching kernels directly\n",
+              last_error());
+    }
+  }
+  if (graph) {
+    device_guard dg(first().device);
+    LCU_CUDA(cudaGraphLaunch(graph, first().stream));
+    return LCU_OK;
+  }
+  return enqueue_decode_step();
+}
+
+// position word (and a zeroed step counter) to every stage, token ids to stage 0
+int context_impl::stage_inputs(const short* tokens, int n) {
+  h_stage[0] = start_pos;
+  h_stage[1] = 0;
+  for (size_t gi = 0; gi < gpus.size(); ++gi) {
+    gpu_state& g = gpus[gi];
+    device_guard dg(g.device);
+    if (gi > 0) {  // order the other stages' copies after stage 0's stream position
+      LCU_CUDA(cudaEventRecord(first().ev, first().stream));
+      LCU_CUDA(cudaStreamWaitEvent(g.stream, first().ev, 0));
+    }
+    LCU_CUDA(cudaMemcpyAsync(g.state, h_stage, 8, cudaMemcpyHostToDevice, g.stream));
+  }
+  memcpy(h_ids, tokens, (size_t)n * 2);
+  device_guard dg(first().device);
+  LCU_CUDA(cudaMemcpyAsync(ids, h_ids, (size_t)n * 2, cudaMemcpyHostToDevice, first().stream));
+  if (gpus.size() > 1) {
+    // stage 0 must not start before every stage has its position word
+    for (size_t gi = 1; gi < gpus.size(); ++gi) {
+      device_guard dg2(gpus[gi].device);
+      LCU_CUDA(cudaEventRecord(gpus[gi].ev, gpus[gi].stream));
+      LCU_CUDA(cudaStreamWaitEvent(first().stream, gpus[gi].ev, 0));
+    }
+  }
+  return LCU_OK;
+}
+
+int context::next_token(const short* tokens, int n, int* token_out) {
+  context_impl& c = *impl;
+  LCU_REQUIRE(n >= 1, "next_token: no tokens given");
+  LCU_REQUIRE(n + c.start_pos <= c.opt.context_len, "next_token: %d new tokens at position %d exceed the context length %d", n,
+              c.start_pos, c.opt.context_len);
+  for (int i = 0; i < n; ++i)
+    LCU_REQUIRE(tokens[i] >= 0 && (uint32_t)tokens[i] < c.m->params.n_vocab, "next_token: token id %d outside the vocabulary", tokens[i]);
+  LCU_TRY(c.stage_inputs(tokens, n));
+  if (n == 1)
+    LCU_TRY(c.run_decode_step());
+  else
+    LCU_TRY(c.enqueue_prefill(n));
+  c.last_row = n == 1 ? 0 : n - 1;
+  device_guard dg(c.first().device);
+  LCU_CUDA(cudaMemcpyAsync(c.h_stage + 2, c.last().state + 2, 8, cudaMemcpyDeviceToHost, c.first().stream));
+  LCU_CUDA(cudaStreamSynchronize(c.first().stream));
+  if (c.h_stage[3] != 0) {
+    set_last_error("next_token: a kernel gave up on a bounded wait (device error 0x%x)", c.h_stage[3]);
+    return LCU_ERR_DEVICE_WAIT;
+  }
+  c.start_pos += n;
+  *token_out = c.h_stage[2];
+  return LCU_OK;
+}
+
+int context::decode_chained(short first_token, int n_steps, short* tokens_out, float* ms_out) {
+  context_impl& c = *impl;
+  LCU_REQUIRE(n_steps >= 1 && n_steps + c.start_pos <= c.opt.context_len, "decode_chained: %d steps at position %d exceed the context length %d",
+              n_steps, c.start_pos, c.opt.context_len);
+  LCU_REQUIRE(first_token >= 0 && (uint32_t)first_token < c.m->params.n_vocab, "decode_chained: token id %d outside the vocabulary", first_token);
+  LCU_TRY(c.stage_inputs(&first_token, 1));
+  device_guard dg(c.first().device);
+  LCU_CUDA(cudaEventRecord(c.t0, c.first().stream));
+  for (int i = 0; i < n_steps; ++i) LCU_TRY(c.run_decode_step());
+  LCU_CUDA(cudaEventRecord(c.t1, c.first().stream));
+  LCU_CUDA(cudaMemcpyAsync(c.h_ids, c.log, (size_t)n_steps * 2, cudaMemcpyDeviceToHost, c.first().stream));
+  LCU_CUDA(cudaMemcpyAsync(c.h_stage + 2, c.last().state + 2, 8, cudaMemcpyDeviceToHost, c.first().stream));
+  LCU_CUDA(cudaStreamSynchronize(c.first().stream));
+  if (c.h_stage[3] != 0) {
+    set_last_error("decode_chained: a kernel gave up on a bounded wait (device error 0x%x)", c.h_stage[3]);
+    return LCU_ERR_DEVICE_WAIT;
+  }
+  c.start_pos += n_steps;
+  c.last_row = 0;
+  memcpy(tokens_out, c.h_ids, (size_t)n_steps * 2);
+  if (ms_out) LCU_CUDA(cudaEventElapsedTime(ms_out, c.t0, c.t1));
+  return LCU_OK;
+}
+
+int context::read_probs(__half* out_host) {
+  context_impl& c = *impl;
+  device_guard dg(c.last().device);
+  LCU_CUDA(cudaMemcpy(out_host, c.probs, (size_t)c.m->params.n_vocab * 2, cudaMemcpyDeviceToHost));
+  return LCU_OK;
+}
+
+int context::read_hidden(__half* out_host) {
+  context_impl& c = *impl;
+  device_guard dg(c.last().device);
+  // decode leaves the token's row at x[0]; a prefill of n rows leaves it at x[n-1] - the caller
+  // reads right after next_token, so the row index is kept
+  LCU_CUDA(cudaMemcpy(out_host, c.last().x + (size_t)c.last_row * c.m->params.dim, (size_t)c.m->params.dim * 2, cudaMemcpyDeviceToHost));
+  return LCU_OK;
+}
+
+int context::bench_kernel(int which, int reps, float* ms_per_launch, uint64_t* bytes_per_launch) {
+  context_impl& c = *impl;
+  LCU_REQUIRE(which >= 0 && which <= 4 && reps >= 1, "bench_kernel: bad arguments");
+  const int L = (int)c.m->params.n_layers;
+  auto params_of = [&](int i, int& epi) {
+    const int l = i % L;
+    switch (which) {
+      case 0: epi = EPI_ROPE_KV; return c.params_qkv(l);
+      case 1: epi = EPI_PLAIN; return c.params_wo(l);
+      case 2: epi = EPI_SILU; return c.params_w13(l);
+      case 3: epi = EPI_PLAIN; return c.params_w2(l);
+      default: epi = EPI_PLAIN; return c.params_out(0);
+    }
+  };
+  LCU_REQUIRE(c.gpus.size() == 1, "bench_kernel: single-GPU contexts only");
+  gpu_state& g = c.first();
+  device_guard dg(g.device);
+  const int saved_pos = c.start_pos;
+  c.h_stage[0] = 0;
+  c.h_stage[1] = 0;
+  LCU_CUDA(cudaMemcpyAsync(g.state, c.h_stage, 8, cudaMemcpyHostToDevice, g.stream));
+  int epi = 0;
+  for (int i = 0; i < std::min(reps, 8); ++i) {  // warm-up
+    gemv_params a = params_of(i, epi);
+    LCU_TRY(launch_gemv(a, epi, g.stream, 0));
+  }
+  LCU_CUDA(cudaEventRecord(c.t0, g.stream));
+  for (int i = 0; i < reps; ++i) {
+    gemv_params a = params_of(i, epi);
+    LCU_TRY(launch_gemv(a, epi, g.stream, c.opt.use_pdl));
+  }
+  LCU_CUDA(cudaEventRecord(c.t1, g.stream));
+  LCU_CUDA(cudaStreamSynchronize(g.stream));
+  float ms = 0.f;
+  LCU_CUDA(cudaEventElapsedTime(&ms, c.t0, c.t1));
+  *ms_per_launch = ms / reps;
+  gemv_params a0 = params_of(0, epi);
+  *bytes_per_launch = gemv_algorithmic_bytes(a0, epi);
+  c.start_pos = saved_pos;
+  return LCU_OK;
+}
+
+}  // namespace lcu

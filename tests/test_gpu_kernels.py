@@ -1,0 +1,218 @@
+"""Parity of the sm_100a kernels (through the C ABI) with the CPU oracle and, where the reference
+library is present, with the reference's own kernels on the same inputs."""
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import ref_lib as R
+
+pytestmark = pytest.mark.gpu
+L = O.lib()
+
+
+def f16(a):
+    return np.asarray(a, np.float32).astype(np.float16).view(np.uint16)
+
+
+def f32(u):
+    return np.asarray(u, np.uint16).view(np.float16).astype(np.float32)
+
+
+def rel_to_max(x, gold):
+    return float(np.abs(x - gold).max() / np.abs(gold).max())
+
+
+# ------------------------------------------------------------------ generator
+def test_synth_generator_bits_equal_oracle(lcu):
+    for name, n, first in [("layers.0.attention.wq", 1 << 18, 0), ("output", 12345, 1 << 33)]:
+        assert (lcu.synth_f16(n, 1234, name, 0.02, first) == O.synth_f16(n, 1234, name, 0.02, first)).all()
+
+
+# ------------------------------------------------------------------ quantizer: bit exact
+@pytest.mark.parametrize("h,w,bs", [(16, 256, 128), (7, 512, 64), (5, 128, 32), (33, 11008, 128), (4096, 4096, 128)])
+def test_quantizer_bit_exact(lcu, h, w, bs):
+    x = O.synth_f16(h * w, 1234, f"quant{h}x{w}", 0.02).reshape(h, w)
+    if h >= 5:
+        x[1, :bs] = 0          # all-zero block: 0/0
+        x[2, :] = f16(np.linspace(-3, 3, w))
+        x[3, :bs] = 0x0001     # smallest subnormal
+    q, s, st = lcu.quantize(x, bs, stats=True)
+    qo, so = O.quantize(x, h, w, bs)
+    assert (s == so).all()
+    assert (q == qo).all()
+    if R.available():
+        qr, sr, str_ = R.quantize(x, bs)
+        assert (s == sr).all() and (q == qr).all()
+        assert np.allclose(st, str_, rtol=1e-3, atol=1e-9)
+    dq = lcu.dequantize(q, s, bs)
+    do = np.empty_like(dq)
+    L.orc_dequantize_absmax_uint8(do, s, q, h, w, bs)
+    assert (dq == do).all()
+
+
+def test_quantizer_empty_and_bad_block(lcu):
+    q, s = lcu.quantize(np.zeros((0, 128), np.uint16), 128)
+    assert q.shape == (0, 128) and s.shape == (0, 1)
+    with pytest.raises(lcu.LcuError):
+        lcu.quantize(np.zeros((2, 128), np.uint16), 96)
+
+
+# ------------------------------------------------------------------ matmul: the single-layer configuration
+def test_single_layer_fp16_4096(lcu):
+    n = k = 4096
+    w = O.synth_f16(n * k, 1234, "W", 0.02).reshape(n, k)
+    x = O.synth_f16(k, 1234, "x", 1.0).reshape(1, k)
+    y = lcu.matmul_nt(x, w)
+    gold = np.zeros((1, n), np.float64)
+    L.orc_matmul_nt_gold(gold.reshape(-1), x.reshape(-1), w.ctypes.data, None, None, 1, k, n, 0, 0)
+    mine = rel_to_max(f32(y).astype(np.float64), gold)
+    assert mine <= 1e-2, mine              # tolerance of the task: 1e-2 max relative error
+    assert mine <= 1e-3, mine              # what fp32 accumulation + one fp16 rounding gives
+    yo = np.zeros((1, n), np.uint16)
+    L.orc_matmul_nt_f16(yo.reshape(-1), x.reshape(-1), w.reshape(-1), 1, k, n, 0.0, 0)
+    assert np.abs(f32(y) - f32(yo)).max() <= 2 * 2.0 ** -8  # within 2 ulp of the oracle's fp32 evaluation at |y| < 8
+    if R.available():
+        for mtype in (4, 1):
+            yr = R.matmul_f16(x, w, mtype=mtype)
+            theirs = rel_to_max(f32(yr).astype(np.float64), gold)
+            assert mine <= theirs * 1.5 + 1e-6, (mine, theirs, mtype)  # no worse than the reference's own kernels
+
+
+def test_single_layer_int8_4096(lcu):
+    n = k = 4096
+    bs = 128
+    w = O.synth_f16(n * k, 1234, "W", 0.02).reshape(n, k)
+    x = O.synth_f16(k, 1234, "x", 1.0).reshape(1, k)
+    q, s = lcu.quantize(w, bs)
+    y = lcu.matmul_nt(x, q, s, bs)
+    gold = np.zeros((1, n), np.float64)  # double accumulation over the half-rounded de-quantized weights
+    L.orc_matmul_nt_gold(gold.reshape(-1), x.reshape(-1), None, q.ctypes.data, s.ctypes.data, 1, k, n, bs, 1)
+    mine = rel_to_max(f32(y).astype(np.float64), gold)
+    assert mine <= 1e-3, mine
+    if R.available():
+        yr = R.matmul_u8(x, q, s, bs, mtype=4)
+        theirs = rel_to_max(f32(yr).astype(np.float64), gold)
+        assert mine <= theirs * 1.5 + 1e-6, (mine, theirs)
+
+
+@pytest.mark.parametrize("m,k,n,bs,beta", [(1, 256, 64, 0, 0.0), (1, 768, 256, 0, 1.0), (2, 512, 130, 0, 0.0), (5, 256, 64, 128, 1.0),
+                                           (8, 1280, 96, 64, 0.0), (9, 512, 64, 32, 0.0), (16, 256, 32, 0, 1.0), (3, 11008, 64, 128, 0.0),
+                                           (1, 22016, 34, 0, 0.0)])
+def test_matmul_small_shapes(lcu, m, k, n, bs, beta):
+    rng = np.random.default_rng(m * 1000 + n)
+    x = f16(rng.standard_normal((m, k)))
+    w = O.synth_f16(n * k, 99, f"w{n}x{k}", 0.05).reshape(n, k)
+    prev = f16(rng.standard_normal((m, n)))
+    yo = prev.copy()
+    if bs == 0:
+        y = lcu.matmul_nt(x, w, beta=beta, out_u16=prev)
+        L.orc_matmul_nt_f16(yo.reshape(-1), x.reshape(-1), w.reshape(-1), m, k, n, beta, 1)
+    else:
+        q, s = O.quantize(w, n, k, bs)
+        y = lcu.matmul_nt(x, q, s, bs, beta=beta, out_u16=prev)
+        L.orc_matmul_nt_fp16u8(yo.reshape(-1), x.reshape(-1), q.reshape(-1), s.reshape(-1), m, k, n, bs, beta, 2)
+    scale = max(1.0, float(np.abs(f32(yo)).max()))
+    assert np.abs(f32(y) - f32(yo)).max() <= 2e-3 * scale, (m, k, n, bs)
+
+
+def test_matmul_rejects_bad_shapes(lcu):
+    with pytest.raises(lcu.LcuError, match="multiple of 256"):
+        lcu.matmul_nt(np.zeros((1, 100), np.uint16), np.zeros((4, 100), np.uint16))
+
+
+# ------------------------------------------------------------------ row-wise operators
+def test_rms_norm_silu(lcu):
+    rng = np.random.default_rng(5)
+    x, w = f16(rng.standard_normal((6, 4096)) * 2), f16(1 + 0.1 * rng.standard_normal(4096))
+    y = lcu.rms_norm(x, w, 1e-6)
+    yo = np.zeros_like(x)
+    L.orc_rms_norm(yo.reshape(-1), x.reshape(-1), w, 6, 4096, 1e-6)
+    ulp_diff = np.abs(y.astype(np.int32) - yo.astype(np.int32))
+    assert ulp_diff.max() <= 1 and (ulp_diff > 0).mean() < 0.02  # rsqrt: device intrinsic vs libm
+    if R.available():
+        yr = np.zeros_like(x)
+        assert R.lib().ref_rms_norm(yr, x, w, 6, 4096, 1e-6) == 0
+        assert (y == yr).all()  # same summation order, same intrinsics: bit exact
+    a, b = f16(rng.standard_normal(11008) * 3), f16(rng.standard_normal(11008))
+    o = lcu.silu(a, b)
+    oo = np.zeros_like(a)
+    L.orc_silu(oo, a, b, a.size)
+    d = np.abs(o.astype(np.int32) - oo.astype(np.int32))
+    assert d.max() <= 1 and (d > 0).mean() < 0.02  # expf: device vs libm
+    if R.available():
+        orf = np.zeros_like(a)
+        assert R.lib().ref_silu(orf, a, b, a.size) == 0
+        assert (o == orf).all()
+
+
+def test_rope_scatter(lcu):
+    rng = np.random.default_rng(6)
+    m, dim, H, pos0, ctx = 5, 256, 2, 9, 32
+    q, k, v = (f16(rng.standard_normal((m, dim))) for _ in range(3))
+    qr, kc, vc = lcu.rope_scatter(q, k, v, H, pos0, ctx)
+    qo, ko = np.zeros_like(q), np.zeros_like(k)
+    L.orc_rotary(qo.reshape(-1), q.reshape(-1), m, dim, H, pos0, 10000.0)
+    L.orc_rotary(ko.reshape(-1), k.reshape(-1), m, dim, H, pos0, 10000.0)
+    hd = dim // H
+    k_rows = kc[:, pos0:pos0 + m, :].transpose(1, 0, 2).reshape(m, dim)
+    v_rows = vc[:, pos0:pos0 + m, :].transpose(1, 0, 2).reshape(m, dim)
+    assert (v_rows == v).all()
+    assert (kc[:, :pos0] == 0).all() and (kc[:, pos0 + m:] == 0).all()
+    for mine, want in ((qr, qo), (k_rows, ko)):
+        assert np.abs(f32(mine) - f32(want)).max() <= 4e-3  # powf/sinf/cosf: device vs libm
+    if R.available():
+        rr = np.zeros_like(q)
+        assert R.lib().ref_rotary(rr, q, m, dim, H, pos0) == 0
+        assert (qr == rr).all()  # same libdevice calls as the reference kernel: bit exact
+
+
+@pytest.mark.parametrize("m,T0,H,cluster", [(1, 0, 2, 1), (1, 1, 2, 8), (1, 37, 2, 4), (1, 383, 4, 8), (1, 2047, 2, 8), (7, 5, 2, 1),
+                                            (16, 0, 3, 1), (1, 100, 2, 2)])
+def test_attention_against_oracle(lcu, m, T0, H, cluster):
+    rng = np.random.default_rng(T0 + m)
+    dim = H * 128
+    T = T0 + m
+    q, k, v = f16(rng.standard_normal((m, dim))), f16(rng.standard_normal((T, dim))), f16(rng.standard_normal((T, dim)))
+    out = lcu.attention(q, k, v, H, T0, cluster)
+    oo = np.zeros_like(q)
+    L.orc_attention(oo.reshape(-1), q.reshape(-1), k.reshape(-1), v.reshape(-1), m, T, dim, H, T0, 0)
+    # identical rounding points; only the order of fp32 sums and expf ulps differ
+    assert np.abs(f32(out) - f32(oo)).max() <= 4e-3, (m, T0, H, cluster)
+    # The reference's score kernel writes rows with stride m while its softmax / PV kernels read them
+    # with stride T (llama_cu.cu:418 vs 437, 526); the two agree only for m == 1 or start_pos == 0,
+    # which are the only cases its own client produces - the comparison is limited to those.
+    if R.available() and (m == 1 or T0 == 0):
+        orf = np.zeros_like(q)
+        assert R.lib().ref_attention(orf, q, k, v, m, T, dim, H, T0) == 0
+        assert np.abs(f32(out) - f32(orf)).max() <= 4e-3
+
+
+def test_attention_head_dim_64(lcu):
+    rng = np.random.default_rng(8)
+    m, T0, H, dim = 1, 50, 4, 256
+    T = T0 + m
+    q, k, v = f16(rng.standard_normal((m, dim))), f16(rng.standard_normal((T, dim))), f16(rng.standard_normal((T, dim)))
+    out = lcu.attention(q, k, v, H, T0, 4)
+    oo = np.zeros_like(q)
+    L.orc_attention(oo.reshape(-1), q.reshape(-1), k.reshape(-1), v.reshape(-1), m, T, dim, H, T0, 0)
+    assert np.abs(f32(out) - f32(oo)).max() <= 4e-3
+
+
+def test_logits_head_first_maximum_and_ties(lcu):
+    rng = np.random.default_rng(9)
+    V = 32000
+    lg = f16(rng.standard_normal(V) * 1.3)
+    tok, probs = lcu.logits_head(lg, 0.8)
+    po = np.zeros(V, np.uint16)
+    L.orc_softmax_rows(po, lg, 1, V, 0.8)
+    assert np.abs(probs.astype(np.int32) - po.astype(np.int32)).max() <= 1
+    assert tok == int(np.argmax(f32(probs)))  # numpy argmax = first maximum, like std::max_element
+    # exact ties in the logits and ties created by the fp16 rounding of the probabilities
+    lg2 = lg.copy()
+    top = int(np.argmax(f32(lg2)))
+    lg2[[17, 4000, 31999]] = lg2[top]
+    tok2, probs2 = lcu.logits_head(lg2, 0.8)
+    assert tok2 == min(17, top) and tok2 == int(np.argmax(f32(probs2)))
+    flat = np.full(1000, f16(0.25), np.uint16)
+    tok3, _ = lcu.logits_head(flat, 1.0)
+    assert tok3 == 0

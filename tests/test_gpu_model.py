@@ -1,0 +1,177 @@
+"""End-to-end parity of the forward pass: new library vs the CPU oracle (small shapes) and vs the
+reference's own llama_context::next_token (when the reference library is present)."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import ref_lib as R
+
+pytestmark = pytest.mark.gpu
+
+SMALL = dict(dim=256, n_heads=2, n_layers=3, n_vocab=1000)
+
+
+def f32(u):
+    return np.asarray(u, np.uint16).view(np.float16).astype(np.float32)
+
+
+def run_tokens(ctx, prompt, steps):
+    toks = [ctx.next_token(prompt)]
+    for _ in range(steps):
+        toks.append(ctx.next_token([toks[-1]]))
+    return toks
+
+
+@pytest.mark.parametrize("bs", [0, 128])
+def test_small_model_matches_oracle(lcu, bs):
+    scale = 0.08
+    model = lcu.Model.synthetic(block_size=bs, seed=1234, scale=scale, **SMALL)
+    ctx = lcu.Context(model, context_len=64, temperature=0.8)
+    om = O.OracleModel(dim=256, multiple_of=256, n_heads=2, n_layers=3, n_vocab=1000, block_size=bs, seed=1234, scale=scale,
+                       context_len=64, temperature=0.8)
+    # identical weights on both sides (generator and quantizer are bit exact)
+    wq = model.tensor_host("layers.1.attention.wq", 0, np.uint8 if bs else np.uint16)
+    want = O.synth_f16(256 * 256, 1234, "layers.1.attention.wq", scale)
+    if bs:
+        q, s = O.quantize(want.reshape(256, 256), 256, 256, bs)
+        assert (wq == q.reshape(-1)).all() and (model.tensor_host("layers.1.attention.wq", 1) == s.reshape(-1)).all()
+    else:
+        assert (wq == want).all()
+    prompt = O.synth_tokens(12, 1234, lo=3, hi=1000)
+    mine, theirs = [], []
+    t, to = ctx.next_token(prompt), om.next_token(prompt)
+    for step in range(20):
+        p, po = f32(ctx.probs()), f32(om.probs())
+        assert np.abs(p - po).max() <= 0.02 * po.max() + 1e-4, step  # same distribution up to summation order / libm ulps
+        h, ho = f32(ctx.hidden()), f32(om.last_hidden())
+        assert np.abs(h - ho).max() <= 0.02 * np.abs(ho).max(), step
+        mine.append(t)
+        theirs.append(to)
+        # teacher forcing on the oracle's token keeps the two runs on the same trajectory
+        t, to = ctx.next_token([to]), om.next_token([to])
+    agree = np.mean(np.array(mine) == np.array(theirs))
+    assert agree >= 0.9, (mine, theirs)
+    assert ctx.tokens_left() == 64 - 12 - 20
+    om.close()
+    ctx.close()
+    model.close()
+
+
+def test_chained_decode_equals_host_loop_and_graph_equals_direct(lcu):
+    model = lcu.Model.synthetic(block_size=0, seed=7, scale=0.08, **SMALL)
+    prompt = O.synth_tokens(9, 7, lo=3, hi=1000)
+    runs = {}
+    for name, graph, pdl in (("graph+pdl", 1, 1), ("direct", 0, 0), ("graph", 1, 0), ("pdl", 0, 1)):
+        lcu.check(lcu.lib.lcu_set_tuning(b"use_graph", graph))
+        lcu.check(lcu.lib.lcu_set_tuning(b"use_pdl", pdl))
+        ctx = lcu.Context(model, context_len=64, temperature=0.8)
+        first = ctx.next_token(prompt)
+        host = [first]
+        for _ in range(16):
+            host.append(ctx.next_token([host[-1]]))
+        ctx.clear_tokens()
+        assert ctx.next_token(prompt) == first
+        chained, ms = ctx.decode_chained(first, 16)
+        assert chained.tolist() == host[1:], name
+        assert ms > 0 and ctx.tokens_left() == 64 - 9 - 16
+        runs[name] = host
+        ctx.close()
+    lcu.check(lcu.lib.lcu_set_tuning(b"use_graph", 1))
+    lcu.check(lcu.lib.lcu_set_tuning(b"use_pdl", 1))
+    assert all(r == runs["direct"] for r in runs.values())  # every launch mode is bit-deterministic and identical
+    model.close()
+
+
+def test_context_limits_and_errors(lcu):
+    model = lcu.Model.synthetic(block_size=0, seed=7, scale=0.08, **SMALL)
+    ctx = lcu.Context(model, context_len=16, temperature=0.8)
+    with pytest.raises(lcu.LcuError, match="exceed the context length"):
+        ctx.next_token(list(range(3, 20)))
+    with pytest.raises(lcu.LcuError, match="outside the vocabulary"):
+        ctx.next_token([5000])
+    ctx.next_token(list(range(3, 19)))  # exactly fills the context
+    assert ctx.tokens_left() == 0
+    with pytest.raises(lcu.LcuError):
+        ctx.next_token([3])
+    ctx.clear_tokens()
+    assert ctx.tokens_left() == 16 and ctx.memory_usage() > 0
+    ctx.close()
+    model.close()
+    with pytest.raises(lcu.LcuError, match="multiple of 256"):
+        lcu.Model.synthetic(dim=200, n_heads=2, n_layers=1, n_vocab=1000)
+
+
+@pytest.mark.parametrize("bs", [0, 128])
+def test_weight_directory_round_trip(lcu, tmp_path, bs):
+    """The on-disk layout is the reference's: a saved model loads back bit-identically, the CPU oracle
+    reads the same files, and (when present) the reference's own loader runs them."""
+    model = lcu.Model.synthetic(block_size=bs, seed=11, scale=0.08, **SMALL)
+    d = str(tmp_path / "m")
+    model.save(d)
+    names = sorted(os.listdir(d))
+    assert "params" in names and "tok_embeddings.weight__1000_256" in names and "layers.2.feed_forward.w2.weight__256_768" in names
+    assert ("layers.0.attention.wq.scale__256_2" in names) == bool(bs)
+    assert os.path.getsize(os.path.join(d, "params")) == 40
+    again = lcu.Model.load(d)
+    for name in ("tok_embeddings", "layers.2.feed_forward.w3", "norm"):
+        assert (again.tensor_host(name, 0, np.uint8) == model.tensor_host(name, 0, np.uint8)).all()
+    prompt = O.synth_tokens(10, 11, lo=3, hi=1000)
+    c1, c2 = lcu.Context(model, 32, 0.8), lcu.Context(again, 32, 0.8)
+    assert run_tokens(c1, prompt, 6) == run_tokens(c2, prompt, 6)
+    om = O.OracleModel(n_vocab=1000, dim=256, context_len=32, temperature=0.8, path=d)
+    assert om.next_token(prompt) >= 0
+    om.close()
+    if R.available():
+        h = R.lib().ref_model_load(d.encode(), None)
+        assert h
+        R.lib().ref_model_free(h)
+    # truncated / missing files are I/O errors, not crashes
+    os.truncate(os.path.join(d, "norm.weight__256"), 100)
+    with pytest.raises(lcu.LcuError, match="expected 512 bytes"):
+        lcu.Model.load(d)
+    os.remove(os.path.join(d, "params"))
+    with pytest.raises(lcu.LcuError, match="params"):
+        lcu.Model.load(d)
+    for c in (c1, c2):
+        c.close()
+    model.close()
+    again.close()
+
+
+def test_quantize_model_dir_matches_in_memory_quantizer(lcu, tmp_path):
+    fp = lcu.Model.synthetic(block_size=0, seed=5, scale=0.08, **SMALL)
+    src, dst = str(tmp_path / "fp16"), str(tmp_path / "q8")
+    fp.save(src)
+    lcu.check(lcu.lib.lcu_quantize_model_dir(src.encode(), dst.encode(), 128))
+    q8 = lcu.Model.load(dst)
+    mem = lcu.Model.synthetic(block_size=128, seed=5, scale=0.08, **SMALL)
+    for name in ("output", "layers.0.feed_forward.w1"):
+        for which in (0, 1):
+            assert (q8.tensor_host(name, which, np.uint8) == mem.tensor_host(name, which, np.uint8)).all()
+    assert q8.params()["q_type"] == 1 and q8.params()["block_size"] == 128
+    for m in (fp, q8, mem):
+        m.close()
+
+
+@pytest.mark.skipif(not R.available(), reason="reference library not built")
+@pytest.mark.parametrize("bs", [0, 128])
+def test_small_model_against_reference_forward(lcu, bs):
+    cfg = dict(dim=512, n_heads=4, n_layers=4, n_vocab=2000)
+    model = lcu.Model.synthetic(block_size=bs, seed=1234, scale=0.06, **cfg)
+    ctx = lcu.Context(model, context_len=128, temperature=0.8)
+    ref = R.RefModel(lcu, model, 512, 256, 4, 4, 2000, 1e-6, bs, 128, 0.8, mtype=4)
+    prompt = O.synth_tokens(32, 1234, lo=3, hi=2000)
+    t, tr = ctx.next_token(prompt), ref.next_token(prompt)
+    mine, theirs = [], []
+    for step in range(48):
+        p, pr = f32(ctx.probs()), f32(ref.probs())
+        assert np.abs(p - pr).max() <= 0.03 * pr.max() + 1e-4, step
+        mine.append(t)
+        theirs.append(tr)
+        t, tr = ctx.next_token([tr]), ref.next_token([tr])  # teacher-forced on the reference's token
+    assert np.mean(np.array(mine) == np.array(theirs)) >= 0.95, (mine, theirs)
+    ref.close()
+    ctx.close()
+    model.close()
