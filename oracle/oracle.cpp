@@ -179,6 +179,7 @@ struct context_t {
   std::vector<uint16_t> probs;                          // last softmax output (n_vocab)
   std::vector<uint16_t> logits;                         // last logits before softmax (n_vocab)
   std::vector<uint16_t> last_hidden;                    // residual stream of the last new token
+  double t_layers = 0, t_head = 0;                      // wall seconds of the last call: layer loop / final norm + logits + softmax
 };
 
 uint32_t ffn_dim(const params_t& p) {  // llama_cu.cu:765-767 (integer division first)
@@ -542,6 +543,7 @@ int next_token(context_t* c, const int16_t* tokens, int m) {
   std::vector<uint16_t> x((size_t)m * d), nrm((size_t)m * d), xq((size_t)m * d), xk((size_t)T * d), att((size_t)m * d);
   std::vector<uint16_t> qk((size_t)H * m * T), h1((size_t)m * f), h3((size_t)m * f), hs((size_t)m * f);
   embed(x.data(), M.tok_embeddings, tokens, m);  // :1086-1097
+  auto clk0 = std::chrono::steady_clock::now();
   for (size_t l = 0; l < M.layers.size(); ++l) {
     layer_t& L = M.layers[l];
     uint16_t* kc = c->k_cache[l].data();
@@ -566,6 +568,7 @@ int next_token(context_t* c, const int16_t* tokens, int m) {
     silu(hs.data(), h1.data(), h3.data(), (size_t)m * f);                          // :1183
     matmul_w(x.data(), hs.data(), L.w2, m, 1.0f, c->wmma_rounding);                // :1185 residual
   }
+  auto clk1 = std::chrono::steady_clock::now();
   c->last_hidden.assign(x.begin() + (size_t)(m - 1) * d, x.end());
   rms_norm(nrm.data(), x.data() + (size_t)(m - 1) * d, M.norm.data(), 1, d, p.norm_eps);  // :1191 (only the last row is used)
   c->logits.resize(V);
@@ -573,6 +576,9 @@ int next_token(context_t* c, const int16_t* tokens, int m) {
   matmul_w(c->logits.data(), nrm.data(), M.output, 1, 0.f, c->wmma_rounding);      // :1195
   softmax_rows(c->probs.data(), c->logits.data(), 1, V, c->temperature);          // :1196
   c->start_pos += m;                                                               // :1201
+  auto clk2 = std::chrono::steady_clock::now();
+  c->t_layers = std::chrono::duration<double>(clk1 - clk0).count();
+  c->t_head = std::chrono::duration<double>(clk2 - clk1).count();
   int best = 0;                                                                    // :1205-1209 first maximum
   for (int i = 1; i < V; ++i)
     if (h2f(c->probs[best]) < h2f(c->probs[i])) best = i;
@@ -801,6 +807,8 @@ void orc_get_last_hidden(void* c, uint16_t* out) {
   context_t* x = (context_t*)c;
   memcpy(out, x->last_hidden.data(), x->last_hidden.size() * 2);
 }
+// wall seconds of the last orc_next_token call: which 0 = all layers, 1 = final norm + logits + softmax
+double orc_last_timing(void* c, int which) { return which == 0 ? ((context_t*)c)->t_layers : ((context_t*)c)->t_head; }
 int orc_num_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();
