@@ -73,6 +73,15 @@ int lcu_silu(void* out_dev, const void* a_dev, const void* b_dev, uint64_t n, vo
  * v_cache, both head-major [n_heads][ctx_len][dim/n_heads]. */
 int lcu_rope_scatter(void* q_dev, const void* k_new_dev, const void* v_new_dev, void* k_cache_dev, void* v_cache_dev, int pos0, int m,
                      int dim, int n_heads, int ctx_len, void* stream);
+/* Same operator for callers that cannot allocate device memory (a server whose memory pool owns
+ * all of HBM, a loop that must not hit cudaMalloc's device-wide synchronisation, a host that forbids
+ * allocation after start-up).  No counterpart in the reference.  The cos/sin table lives in a fixed
+ * 2 MiB device array inside the library instead of a per-call allocation; (pos0 + m) * (dim / n_heads / 2)
+ * must not exceed 262144 entries (4096 positions at head_dim 128) or the call is rejected.  All calls
+ * share that array: calls whose kernels overlap on the GPU race.  The first call on each device resolves
+ * the array's address and should be made outside stream capture.  Returns without synchronising. */
+int lcu_rope_scatter_static(void* q_dev, const void* k_new_dev, const void* v_new_dev, void* k_cache_dev, void* v_cache_dev, int pos0,
+                            int m, int dim, int n_heads, int ctx_len, void* stream);
 /* matmul_qk + softmax_rows + matmul_qkv, llama_cu.cu:400-531 (launches at 1163-1171), fused:
  * q [m][dim] rotated, caches head-major as above holding positions 0 .. pos0+m-1; out [m][dim]. */
 int lcu_attention(void* out_dev, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev, int pos0, int m, int dim,

@@ -45,6 +45,7 @@ _SIG = {
     "lcu_rms_norm": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_float, vp]),
     "lcu_silu": (C.c_int, [vp, vp, vp, C.c_uint64, vp]),
     "lcu_rope_scatter": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
+    "lcu_rope_scatter_static": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "lcu_attention": (C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "lcu_logits_head": (C.c_int, [vp, vp, C.c_int, C.c_float, C.POINTER(C.c_int), vp]),
     "lcu_synth_fill_f16": (C.c_int, [vp, C.c_uint64, C.c_uint64, C.c_char_p, C.c_float, C.c_uint64, vp]),
