@@ -1,0 +1,73 @@
+"""The 7B-shaped configurations at full size: greedy tokens of the new library against the tokens the
+reference itself produced on a B200 (tests/golden/reference_7b_tokens.json), fp16 and int8.
+
+Batch-1 greedy decoding of a random-init model is chaotic: the reference's own two kernel sets
+(matmul_type 4 vs 1) part ways after 13 steps on this input, because a different fp32 summation order
+moves logits by an fp16 ulp and top-2 probability margins are often that small.  So the test pins what
+is stable: a free-running prefix, teacher-forced top-1 agreement, and that every disagreement sits at a
+margin of a few fp16 ulps of the reference's own probabilities."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+
+pytestmark = pytest.mark.gpu
+GOLD = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_7b_tokens.json")))
+CFG = dict(dim=4096, n_heads=32, n_layers=32, n_vocab=32000)
+
+
+@pytest.mark.parametrize("bs", [0, 128])
+def test_7b_tokens_against_reference(lcu, bs):
+    ref = np.array(GOLD[f"tokens_bs{bs}_t4"])
+    margin = np.array(GOLD[f"top1_bs{bs}_t4"]) - np.array(GOLD[f"top2_bs{bs}_t4"])
+    prompt = O.synth_tokens(128, 1234)
+    model = lcu.Model.synthetic(block_size=bs, seed=1234, scale=0.02, **CFG)
+    ctx = lcu.Context(model, 512, 0.8)
+    first = ctx.next_token(prompt)
+    chained, _ = ctx.decode_chained(first, 256)
+    free = np.concatenate([[first], chained])
+    diverge = int(np.argmax(free != ref)) if (free != ref).any() else len(ref)
+    # the reference's own matmul_type 1 leaves its matmul_type 4 after 13 steps on the fp16 model
+    assert diverge >= 13, diverge
+    ctx.clear_tokens()
+    forced = [ctx.next_token(prompt)]
+    for i in range(256):
+        forced.append(ctx.next_token([int(ref[i])]))
+    agree = np.array(forced) == ref
+    assert agree.mean() >= 0.95, agree.mean()
+    assert (margin[~agree] <= 5e-4).all(), margin[~agree]  # median margin is 1.2e-3; mismatches only where the reference itself is undecided
+    # determinism: the chained run repeats bit for bit
+    ctx.clear_tokens()
+    assert ctx.next_token(prompt) == first
+    again, _ = ctx.decode_chained(first, 256)
+    assert (again == chained).all()
+    ctx.close()
+    model.close()
+
+
+def test_7b_int8_top1_agreement_with_fp16(lcu):
+    """Top-1 agreement of the quantized model with the fp16 model, teacher-forced on the fp16 run."""
+    prompt = O.synth_tokens(128, 1234)
+    runs = {}
+    for bs in (0, 128):
+        model = lcu.Model.synthetic(block_size=bs, seed=1234, scale=0.02, **CFG)
+        ctx = lcu.Context(model, 512, 0.8)
+        if bs == 0:
+            t = ctx.next_token(prompt)
+            toks = [t]
+            for _ in range(64):
+                t = ctx.next_token([t])
+                toks.append(t)
+            runs[0] = toks
+        else:
+            toks = [ctx.next_token(prompt)]
+            for i in range(64):
+                toks.append(ctx.next_token([runs[0][i]]))
+            runs[128] = toks
+        ctx.close()
+        model.close()
+    agree = np.mean(np.array(runs[0]) == np.array(runs[128]))
+    assert agree >= 0.6, agree  # random-init logits are nearly flat; the quantization error moves many argmaxes
