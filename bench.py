@@ -39,12 +39,14 @@ WORKLOADS = {
     "7b-fp16": dict(dim=4096, n_heads=32, n_layers=32, n_vocab=32000, block_size=0),
     "7b-int8": dict(dim=4096, n_heads=32, n_layers=32, n_vocab=32000, block_size=128),
     "13b-fp16": dict(dim=5120, n_heads=40, n_layers=40, n_vocab=32000, block_size=0),
+    "7b-l4-fp16": dict(dim=4096, n_heads=32, n_layers=4, n_vocab=32000, block_size=0),   # 7B kernel shapes, 4 layers: profiler captures
+    "7b-l4-int8": dict(dim=4096, n_heads=32, n_layers=4, n_vocab=32000, block_size=128),
     "tiny-fp16": dict(dim=512, n_heads=4, n_layers=4, n_vocab=2000, block_size=0),  # plumbing checks only
 }
 SEED, SCALE, PROMPT_LEN, CONTEXT_LEN, TEMPERATURE = 1234, 0.02, 128, 2048, 0.8
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
 # profiles/gemv_w13_7b_fp16.md (dram__bytes_read.sum + dram__bytes_write.sum); None until captured
-NCU_TRAFFIC_BYTES = {"7b-fp16": None, "7b-int8": None}
+NCU_TRAFFIC_BYTES = {"7b-fp16": 180413440 + 3508736, "7b-int8": None}
 
 
 def load_package():
@@ -205,7 +207,11 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     barrier_sync(dist, lcu)
+    if args.profile:
+        lcu.check(lcu.lib.lcu_profiler_start())
     tokens, ms = ctx.decode_chained(int(warm_tokens[-1]), K)
+    if args.profile:
+        lcu.check(lcu.lib.lcu_profiler_stop())
     barrier_sync(dist, lcu)
     ms_all = reduce_max_time(ms, dist)
     value = world * K / (ms_all / 1e3)
@@ -333,6 +339,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="7b-fp16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true", help="cudaProfilerStart/Stop around the device-chained timed region")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

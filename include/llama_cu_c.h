@@ -144,6 +144,9 @@ int lcu_context_kernels_per_step(void* ctx);
  * which: 0 fused norm+wq|wk|wv+RoPE, 1 wo+residual, 2 fused norm+w1|w3+SiLU, 3 w2+residual, 4 output matrix.
  * Returns mean milliseconds per launch and the algorithmic bytes of one launch. */
 int lcu_bench_decode_kernel(void* ctx, int which, int reps, float* ms_per_launch_out, uint64_t* bytes_per_launch_out);
+/* cudaProfilerStart / cudaProfilerStop, so that a profiler attached with --profile-from-start off sees only the timed region */
+int lcu_profiler_start(void);
+int lcu_profiler_stop(void);
 /* pure-read ceiling: a kernel that only streams `bytes` from HBM with the same bulk-copy ring; ms per pass */
 int lcu_bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass_out);
 

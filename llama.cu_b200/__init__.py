@@ -71,6 +71,8 @@ _SIG = {
     "lcu_context_read_hidden": (C.c_int, [vp, vp]),
     "lcu_context_kernels_per_step": (C.c_int, [vp]),
     "lcu_bench_decode_kernel": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
+    "lcu_profiler_start": (C.c_int, []),
+    "lcu_profiler_stop": (C.c_int, []),
     "lcu_bench_read_ceiling": (C.c_int, [C.c_uint64, C.c_int, C.POINTER(C.c_float)]),
 }
 EXPORTS = sorted(_SIG)

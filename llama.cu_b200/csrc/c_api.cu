@@ -1,6 +1,8 @@
 // extern "C" surface of libllama_cu_b200.so (declared in include/llama_cu_c.h).
 #include "../../include/llama_cu_c.h"
 
+#include <cuda_profiler_api.h>
+
 #include <cstring>
 #include <memory>
 #include <string>
@@ -369,6 +371,14 @@ int lcu_context_kernels_per_step(void* ctx) { return ((context*)ctx)->kernels_pe
 // ---- measurement
 int lcu_bench_decode_kernel(void* ctx, int which, int reps, float* ms_per_launch_out, uint64_t* bytes_per_launch_out) {
   return ((context*)ctx)->bench_kernel(which, reps, ms_per_launch_out, bytes_per_launch_out);
+}
+int lcu_profiler_start(void) {
+  LCU_CUDA(cudaProfilerStart());
+  return LCU_OK;
+}
+int lcu_profiler_stop(void) {
+  LCU_CUDA(cudaProfilerStop());
+  return LCU_OK;
 }
 int lcu_bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass_out) {
   NEED_DEVICE();
