@@ -147,8 +147,9 @@ int lcu_bench_decode_kernel(void* ctx, int which, int reps, float* ms_per_launch
 /* cudaProfilerStart / cudaProfilerStop, so that a profiler attached with --profile-from-start off sees only the timed region */
 int lcu_profiler_start(void);
 int lcu_profiler_stop(void);
-/* pure-read ceiling: a kernel that only streams `bytes` from HBM with the same bulk-copy ring; ms per pass */
-int lcu_bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass_out);
+/* pure-read ceiling: a kernel that only streams `bytes` from HBM with the same bulk-copy ring (16 KiB stages, each
+ * fetched as copies_per_stage bulk copies, 1..32); ms per pass */
+int lcu_bench_read_ceiling(uint64_t bytes, int reps, int copies_per_stage, float* ms_per_pass_out);
 
 #ifdef __cplusplus
 }

@@ -73,7 +73,7 @@ _SIG = {
     "lcu_bench_decode_kernel": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
     "lcu_profiler_start": (C.c_int, []),
     "lcu_profiler_stop": (C.c_int, []),
-    "lcu_bench_read_ceiling": (C.c_int, [C.c_uint64, C.c_int, C.POINTER(C.c_float)]),
+    "lcu_bench_read_ceiling": (C.c_int, [C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_float)]),
 }
 EXPORTS = sorted(_SIG)
 for _name, (_res, _args) in _SIG.items():
@@ -345,7 +345,7 @@ class Context:
             self.handle = None
 
 
-def read_ceiling_ms(nbytes, reps=10):
+def read_ceiling_ms(nbytes, reps=10, copies_per_stage=1):
     ms = C.c_float(0)
-    check(lib.lcu_bench_read_ceiling(nbytes, reps, C.byref(ms)))
+    check(lib.lcu_bench_read_ceiling(nbytes, reps, copies_per_stage, C.byref(ms)))
     return ms.value

@@ -96,6 +96,9 @@ int lcu_set_tuning(const char* key, int value) {
   const std::string k(key ? key : "");
   if (k == "gemv_stages") gemv_tuning_ref().nstages = value;
   else if (k == "gemv_ctas_per_sm") gemv_tuning_ref().ctas_per_sm = value;
+  else if (k == "gemv_warp_stages") gemv_tuning_ref().warp_stages = value;
+  else if (k == "gemv_variant") gemv_tuning_ref().variant = value;
+  else if (k == "gemv_prefetch_kb") gemv_tuning_ref().prefetch_kb_per_cta = value;
   else if (k == "use_graph") g_default_opts.use_graph = value;
   else if (k == "use_pdl") g_default_opts.use_pdl = value;
   else if (k == "attn_cluster") g_default_opts.attn_cluster = value;
@@ -380,9 +383,9 @@ int lcu_profiler_stop(void) {
   LCU_CUDA(cudaProfilerStop());
   return LCU_OK;
 }
-int lcu_bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass_out) {
+int lcu_bench_read_ceiling(uint64_t bytes, int reps, int copies_per_stage, float* ms_per_pass_out) {
   NEED_DEVICE();
-  return bench_read_ceiling(bytes, reps, ms_per_pass_out);
+  return bench_read_ceiling(bytes, reps, copies_per_stage, ms_per_pass_out);
 }
 
 }  // extern "C"

@@ -29,6 +29,7 @@ constexpr int SCROW = KCB / 16;         // scale bytes reserved per row per stag
 constexpr int STAGE_W = RB * ROWSTRIDE;
 constexpr int STAGE_BYTES = STAGE_W + RB * SCROW;
 constexpr int MAX_STAGES = 8;
+constexpr int NACC = 4;                  // independent accumulator sets per warp
 constexpr int RED_FLOATS = NCW * 16 * 8;  // per-warp partial sums of a row block, double buffered
 constexpr int SMEM_FIXED = 256 /*barriers: 2 x MAX_STAGES x 8 bytes, padded*/ + 2 * RED_FLOATS * 4 + 64 /*reduction scratch*/;
 
@@ -59,7 +60,7 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t word, uint32_t selecto
 }
 
 template <int WT /*0 fp16, 1 u8*/, int EPI>
-__global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, const int nstages) {
+__global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, const int nstages, const int pf_bytes, const int mode) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full[MAX_STAGES], empty[MAX_STAGES]
   float* red = reinterpret_cast<float*>(smem + 256);
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
   if (tid == 0) {
     for (int i = 0; i < nstages; ++i) {
       mbar_init(smem_u32(&bars[i]), WT == 0 ? 1 : 33);
-      mbar_init(smem_u32(&bars[MAX_STAGES + i]), NCW);
+      mbar_init(smem_u32(&bars[MAX_STAGES + i]), mode == 0 ? NCW : 1);
     }
     fence_mbar_init();
   }
@@ -95,6 +96,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
   if (warp == NCW) {
     // ------------------------------------------------------------ producer
     const uint64_t pol = policy_evict_first();
+    // Look-ahead into L2: the first pf_bytes of this CTA's rows are requested before the ring starts.
+    // Under programmatic dependent launch this runs while the previous kernels are still busy (or,
+    // like attention, latency-bound), so HBM keeps streaming across kernel boundaries.
+    if (pf_bytes > 0) {
+      int rows_pf = pf_bytes / rowbytes;
+      rows_pf = max(1, min(rows_pf, r1 - r0));
+      for (int r = lane; r < rows_pf; r += 32) {
+        int mat, row;
+        map_row<EPI>(p, r0 + r, mat, row);
+        l2_prefetch(reinterpret_cast<const uint8_t*>(p.w[mat]) + (size_t)row * rowbytes, (uint32_t)rowbytes);
+      }
+    }
     int stage = 0;
     uint32_t phase = 0;
     for (int b = 0; b < nblocks; ++b) {
@@ -182,17 +195,31 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
   int pos = 0;
   if (EPI == EPI_ROPE_KV) pos = *p.pos;
 
-  int stage = 0;
+  // Two ways to share a stage among the consumer warps: mode 0 - every warp takes 1/8 of the 64-byte
+  // steps of every stage; mode 1 - whole stages go to the warps in turn, so the hand-over latency of one
+  // stage (mbarrier wake-up, first shared loads) overlaps with the work of the other warps on other stages.
+  int stage = 0, turn = 0;
   uint32_t phase = 0;
   for (int b = 0; b < nblocks; ++b) {
     const int rb = r0 + b * RB;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    // Independent accumulators: consecutive tensor-core instructions of a warp must not wait for
+    // each other's result (a chain on one accumulator serialises on the instruction's latency).
+    float accs[NACC][4];
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) accs[a][0] = accs[a][1] = accs[a][2] = accs[a][3] = 0.f;
     for (int ci = 0; ci < nchunks; ++ci) {
+     if (mode == 0 || turn == warp) {
       mbar_wait(smem_u32(&bars[stage]), phase, p.err, DEV_ERR_FULL_WAIT);
       const int cbytes = min(KCB, rowbytes - ci * KCB);
       const int nsteps = cbytes >> 6;
       const uint8_t* st = stages + (size_t)stage * STAGE_BYTES;
-      for (int s = warp; s < nsteps; s += NCW) {
+      const int s_first = mode == 0 ? warp : 0, s_stride = mode == 0 ? NCW : 1;
+#pragma unroll
+      for (int it = 0; it < KCB / 64; ++it) {
+        const int s = s_first + it * s_stride;
+        if (s >= nsteps) break;
+        float* acc = accs[(it * 2) % NACC];
+        float* acc_b = accs[(it * 2 + 1) % NACC];
         const uint8_t* pa = st + g * ROWSTRIDE + s * 64 + c * 16;
         const uint4 lo = *reinterpret_cast<const uint4*>(pa);
         const uint4 hi = *reinterpret_cast<const uint4*>(pa + 8 * ROWSTRIDE);
@@ -201,7 +228,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
           uint4 xb = make_uint4(0, 0, 0, 0);
           if (g < p.m) xb = *reinterpret_cast<const uint4*>(xs + (size_t)g * xstride + kx * 2);
           mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
-          mma_16816(acc, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
+          mma_16816(acc_b, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
         } else {
           const int kl = s * 64 + c * 16;  // k offset inside the chunk
           const int kx = ci * KCB + kl;
@@ -217,23 +244,33 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
           const __half2 s_hi = __half2half2(scs[(g + 8) * (SCROW / 2) + si]);
           mma_16816(acc, dequant_pair(lo.x, 0x4140, s_lo), dequant_pair(hi.x, 0x4140, s_hi), dequant_pair(lo.x, 0x4342, s_lo),
                     dequant_pair(hi.x, 0x4342, s_hi), x0.x, x0.y);
-          mma_16816(acc, dequant_pair(lo.y, 0x4140, s_lo), dequant_pair(hi.y, 0x4140, s_hi), dequant_pair(lo.y, 0x4342, s_lo),
+          mma_16816(acc_b, dequant_pair(lo.y, 0x4140, s_lo), dequant_pair(hi.y, 0x4140, s_hi), dequant_pair(lo.y, 0x4342, s_lo),
                     dequant_pair(hi.y, 0x4342, s_hi), x0.z, x0.w);
           mma_16816(acc, dequant_pair(lo.z, 0x4140, s_lo), dequant_pair(hi.z, 0x4140, s_hi), dequant_pair(lo.z, 0x4342, s_lo),
                     dequant_pair(hi.z, 0x4342, s_hi), x1.x, x1.y);
-          mma_16816(acc, dequant_pair(lo.w, 0x4140, s_lo), dequant_pair(hi.w, 0x4140, s_hi), dequant_pair(lo.w, 0x4342, s_lo),
+          mma_16816(acc_b, dequant_pair(lo.w, 0x4140, s_lo), dequant_pair(hi.w, 0x4140, s_hi), dequant_pair(lo.w, 0x4342, s_lo),
                     dequant_pair(hi.w, 0x4342, s_hi), x1.z, x1.w);
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[MAX_STAGES + stage]));
+     }
+      if (++turn == NCW) turn = 0;
       if (++stage == nstages) {
         stage = 0;
         phase ^= 1;
       }
     }
 
-    // combine the warps' k-slices (fixed order) and run the epilogue
+    // combine the accumulators, then the warps' k-slices (fixed order), and run the epilogue
+    float acc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float t = accs[0][i];
+#pragma unroll
+      for (int a = 1; a < NACC; ++a) t += accs[a][i];
+      acc[i] = t;
+    }
     float* rbuf = red + (b & 1) * RED_FLOATS;
     {
       float* mine = rbuf + warp * 128;
@@ -301,7 +338,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
 }
 
 template <int WT, int EPI>
-int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, int grid, int nstages) {
+int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, int grid, int nstages, int pf_bytes, int mode) {
   static bool attr_done[16] = {};
   int dev = 0;
   LCU_CUDA(cudaGetDevice(&dev));
@@ -319,13 +356,13 @@ int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemv_kernel<WT, EPI>, p, nstages));
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemv_kernel<WT, EPI>, p, nstages, pf_bytes, mode));
   return LCU_OK;
 }
 
 // Read-only ceiling probe: the same bulk-copy ring as the GEMV with consumers that only release
 // the stages, so its time is what the memory system allows for a pure stream of `bytes`.
-__global__ void __launch_bounds__(64, 2) read_ring_kernel(const uint8_t* src, size_t bytes, int nstages, int* err) {
+__global__ void __launch_bounds__(64, 2) read_ring_kernel(const uint8_t* src, size_t bytes, int nstages, int ncopy, int* err) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   uint8_t* stages = smem + 256;
@@ -342,12 +379,17 @@ __global__ void __launch_bounds__(64, 2) read_ring_kernel(const uint8_t* src, si
   __syncthreads();
   int stage = 0;
   uint32_t phase = 0;
-  if (threadIdx.x == 0) {
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    // producer warp: each 16 KiB stage arrives as `ncopy` bulk copies issued by the first ncopy lanes
     const uint64_t pol = policy_evict_first();
+    const int sub = PIECE / ncopy;
     for (size_t i = p0; i < p1; ++i) {
       mbar_wait(smem_u32(&bars[MAX_STAGES + stage]), phase ^ 1, err, DEV_ERR_EMPTY_WAIT);
-      mbar_arrive_expect_tx(smem_u32(&bars[stage]), PIECE);
-      bulk_g2s_hint(smem_u32(stages + (size_t)stage * PIECE), src + i * PIECE, PIECE, smem_u32(&bars[stage]), pol);
+      if (lane == 0) mbar_arrive_expect_tx(smem_u32(&bars[stage]), PIECE);
+      __syncwarp();
+      if (lane < ncopy)
+        bulk_g2s_hint(smem_u32(stages + (size_t)stage * PIECE + lane * sub), src + i * PIECE + (size_t)lane * sub, sub, smem_u32(&bars[stage]), pol);
       if (++stage == nstages) {
         stage = 0;
         phase ^= 1;
@@ -383,7 +425,8 @@ gemv_tuning& gemv_tuning_ref() {
   return t;
 }
 
-int bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass) {
+int bench_read_ceiling(uint64_t bytes, int reps, int ncopy, float* ms_per_pass) {
+  LCU_REQUIRE(ncopy == 1 || ncopy == 2 || ncopy == 4 || ncopy == 8 || ncopy == 16 || ncopy == 32, "read ceiling: copies per stage must be a power of two <= 32");
   LCU_REQUIRE(bytes >= (1u << 20) && reps >= 1, "read ceiling: need at least 1 MiB and one repetition");
   const gemv_tuning& t = gemv_tuning_ref();
   const int nstages = t.nstages < 2 ? 2 : (t.nstages > MAX_STAGES ? MAX_STAGES : t.nstages);
@@ -399,9 +442,9 @@ int bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass) {
   cudaEvent_t e0, e1;
   LCU_CUDA(cudaEventCreate(&e0));
   LCU_CUDA(cudaEventCreate(&e1));
-  for (int i = 0; i < 3; ++i) read_ring_kernel<<<grid, 64, smem>>>(buf, bytes, nstages, err);
+  for (int i = 0; i < 3; ++i) read_ring_kernel<<<grid, 64, smem>>>(buf, bytes, nstages, ncopy, err);
   LCU_CUDA(cudaEventRecord(e0, 0));
-  for (int i = 0; i < reps; ++i) read_ring_kernel<<<grid, 64, smem>>>(buf, bytes, nstages, err);
+  for (int i = 0; i < reps; ++i) read_ring_kernel<<<grid, 64, smem>>>(buf, bytes, nstages, ncopy, err);
   LCU_CUDA(cudaEventRecord(e1, 0));
   cudaError_t e = cudaEventSynchronize(e1);
   float ms = 0.f;
@@ -443,6 +486,12 @@ int launch_gemv(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl
     LCU_REQUIRE(p.bs == 0 || ((uintptr_t)p.sc[i] & 3) == 0, "gemv: scale matrix %d is not 4-byte aligned", i);
   }
   const gemv_tuning& t = gemv_tuning_ref();
+  if (p.m == 1 && t.variant == 1) {
+    LCU_REQUIRE((epilogue == EPI_PLAIN && p.n_mats == 1) || (epilogue == EPI_ROPE_KV && p.n_mats == 3 && p.head_dim % 2 == 0 && p.rows_per_mat % p.head_dim == 0) ||
+                    (epilogue == EPI_SILU && p.n_mats == 2),
+                "gemv: matrix count %d does not fit epilogue %d", p.n_mats, epilogue);
+    return launch_gemv_single_row(p, epilogue, stream, pdl, sm_count());
+  }
   int nstages = t.nstages < 2 ? 2 : (t.nstages > MAX_STAGES ? MAX_STAGES : t.nstages);
   size_t smem = SMEM_FIXED + (size_t)p.m * x_stride_bytes(p.K) + (size_t)nstages * STAGE_BYTES;
   while (smem > 227 * 1024 && nstages > 2) {
@@ -451,19 +500,21 @@ int launch_gemv(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl
   }
   LCU_REQUIRE(smem <= 227 * 1024, "gemv: m=%d rows of K=%d do not fit in shared memory", p.m, p.K);
   const int units = p.n_mats * p.rows_per_mat / 2;
+  const int pf_bytes = t.prefetch_kb_per_cta * 1024;
+  const int mode = (t.variant == 2 && p.m == 1) ? 1 : 0;
   int grid = sm_count() * (t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);
   if (grid > units) grid = units;
   const bool q = p.bs != 0;
   switch (epilogue) {
     case EPI_PLAIN:
       LCU_REQUIRE(p.n_mats == 1, "gemv: plain epilogue takes one matrix");
-      return q ? launch_one<1, EPI_PLAIN>(p, stream, pdl, smem, grid, nstages) : launch_one<0, EPI_PLAIN>(p, stream, pdl, smem, grid, nstages);
+      return q ? launch_one<1, EPI_PLAIN>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode) : launch_one<0, EPI_PLAIN>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode);
     case EPI_ROPE_KV:
       LCU_REQUIRE(p.n_mats == 3 && p.head_dim % 2 == 0 && p.rows_per_mat % p.head_dim == 0, "gemv: bad q/k/v shapes");
-      return q ? launch_one<1, EPI_ROPE_KV>(p, stream, pdl, smem, grid, nstages) : launch_one<0, EPI_ROPE_KV>(p, stream, pdl, smem, grid, nstages);
+      return q ? launch_one<1, EPI_ROPE_KV>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode) : launch_one<0, EPI_ROPE_KV>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode);
     case EPI_SILU:
       LCU_REQUIRE(p.n_mats == 2, "gemv: SiLU-gate epilogue takes w1 and w3");
-      return q ? launch_one<1, EPI_SILU>(p, stream, pdl, smem, grid, nstages) : launch_one<0, EPI_SILU>(p, stream, pdl, smem, grid, nstages);
+      return q ? launch_one<1, EPI_SILU>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode) : launch_one<0, EPI_SILU>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode);
   }
   LCU_REQUIRE(false, "gemv: unknown epilogue %d", epilogue);
 }

@@ -44,6 +44,9 @@ struct gemv_params {
 struct gemv_tuning {
   int nstages = 4;      // shared-memory ring depth (16 rows x 1 KiB per stage)
   int ctas_per_sm = 2;  // grid = SM count x this
+  int variant = 1;      // m == 1: 1 = per-warp row-pair kernel (gemv1.cu), 0 / 2 = 16-row-block kernel (gemv.cu)
+  int warp_stages = 3;  // gemv1.cu: ring depth of every consumer warp (8 KiB per stage)
+  int prefetch_kb_per_cta = 32;  // L2 look-ahead issued by each CTA's producer at kernel start
 };
 gemv_tuning& gemv_tuning_ref();
 
@@ -51,8 +54,11 @@ gemv_tuning& gemv_tuning_ref();
 // preceding launch (its weight stream starts while the previous kernel drains).
 int launch_gemv(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl);
 
+// single-row kernel (gemv1.cu); called by launch_gemv after argument checks
+int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl, int sms);
+
 // pure-read probe with the same bulk-copy ring: mean milliseconds for one pass over `bytes` of HBM
-int bench_read_ceiling(uint64_t bytes, int reps, float* ms_per_pass);
+int bench_read_ceiling(uint64_t bytes, int reps, int ncopy, float* ms_per_pass);  // ncopy bulk copies per 16 KiB stage
 
 // bytes one launch must move at minimum (weights + scales + activations in + out)
 size_t gemv_algorithmic_bytes(const gemv_params& p, int epilogue);

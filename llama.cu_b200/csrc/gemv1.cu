@@ -1,0 +1,370 @@
+// Single-row (batch-1) weight-streaming GEMV: every consumer warp is an independent streaming
+// dot-product engine with a private shared-memory ring; no block-wide synchronisation in the loop.
+//
+// Measured on B200 with this library's read probe (bench_read_ceiling): a 16 KiB ring stage
+// fetched as sixteen 1 KiB bulk copies tops out near 4.4 TB/s with one CTA per SM, while copies
+// of 4 KiB or more reach the read ceiling of ~7.2 TB/s.  So a stage here is TWO bulk copies: one
+// contiguous 4 KiB chunk (2048 fp16 / 4096 u8 weights) from each row of a row pair, and the chunk
+// is mapped onto the tensor-core tile like this:
+//
+//   m16n8k16 tile row  m = 8*rr + seg : segment `seg` (1/8 of the chunk, 512 B) of row `rr` of the pair
+//   tile column        n = seg        : the activation values of that same segment
+//
+// D[m][n] is wanted only on the "diagonal" n == seg(m): lane (g, c = g/2) ends up with the partial
+// dot products of segment g for both rows.  All 16 tile rows still consume distinct weight bytes.
+// Odd segments walk their 64-byte steps in swapped order (step ^ 1) on both operands, so the eight
+// lanes of a quarter warp hit eight distinct 16-byte bank groups without padding the staged rows.
+//
+// A row pair (the unit RoPE and the SiLU gate need) belongs to ONE warp from its first chunk to its
+// epilogue: the warp waits on its own mbarriers, accumulates in registers, reduces with shuffles and
+// writes the result.  The producer warp deals chunks to the warps' rings round-robin.  As in the
+// multi-row kernel (gemv.cu) the producer does not depend on the activations, so under programmatic
+// dependent launch the rings of kernel n+1 fill while kernel n drains; every wait is bounded; int8
+// weights are de-quantised in registers bit-identically to half((q - 127.5f) * scale)
+// (reference llama_cu.cu:287-289); the RMSNorm prologue keeps the reference's summation order.
+#include "gemv.cuh"
+
+namespace lcu {
+namespace {
+
+constexpr int NW = 4;                       // consumer warps per CTA
+constexpr int NTHREADS = (NW + 1) * 32;
+constexpr int NCONS = NW * 32;
+constexpr int ROWB = 4096;                  // bytes of one row per stage (one bulk copy)
+constexpr int SEG = ROWB / 8;               // 512-byte segments
+constexpr int NSTEPS = SEG / 64;            // 64-byte steps per segment
+constexpr int MAX_SW = 4;                   // ring depth per warp
+constexpr int NACC = 4;                     // independent accumulator sets (no chain on one result)
+constexpr int SC_BYTES_ROW = 256;           // scale bytes reserved per row per stage: 4096 / 32 * 2
+constexpr int SMEM_FIXED = 256 + 64;        // barriers: full[NW][MAX_SW], empty[NW][MAX_SW]; scratch
+
+template <int EPI>
+__device__ __forceinline__ void map_row(const gemv_params& p, int vrow, int& mat, int& row) {
+  if (EPI == EPI_SILU) {
+    mat = vrow & 1;
+    row = vrow >> 1;
+  } else if (EPI == EPI_ROPE_KV) {
+    mat = vrow / p.rows_per_mat;
+    row = vrow - mat * p.rows_per_mat;
+  } else {
+    mat = 0;
+    row = vrow;
+  }
+}
+
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t word, uint32_t selector, __half2 scale2) {
+  uint32_t v = __byte_perm(word, 0x64646464u, selector);  // bytes -> halves 1024 + q
+  __half2 h = *reinterpret_cast<__half2*>(&v);
+  h = __hsub2(h, __half2half2(__ushort_as_half(0x6400)));  // - 1024   (exact)
+  h = __hsub2(h, __half2half2(__ushort_as_half(0x57f8)));  // - 127.5  (exact)
+  h = __hmul2(h, scale2);                                  // one rounding, as the reference
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int WT /*0 fp16, 1 u8*/, int EPI>
+__global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p, const int sw, const int pf_bytes) {
+  constexpr int ESZ = WT == 0 ? 2 : 1;
+  constexpr int CHUNK_K = ROWB / ESZ;        // weights of one row per stage: 2048 fp16, 4096 u8
+  constexpr int STAGE_BYTES = 2 * ROWB + (WT ? 2 * SC_BYTES_ROW : 0);
+
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [16 + w * MAX_SW + s]
+  float* scratch = reinterpret_cast<float*>(smem + 256);
+  uint8_t* xs = smem + SMEM_FIXED;                     // activation row, K halves
+  uint8_t* stages = xs + ((p.K * 2 + 127) & ~127);     // [NW][sw][STAGE_BYTES]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
+
+  const int pairs = (p.n_mats * p.rows_per_mat) >> 1;
+  const int pr0 = (int)(((long long)pairs * blockIdx.x) / gridDim.x);
+  const int npairs = (int)(((long long)pairs * (blockIdx.x + 1)) / gridDim.x) - pr0;
+  const int rowbytes = p.K * ESZ;
+  const int nchunks = (rowbytes + ROWB - 1) / ROWB;
+
+  if (tid == 0) {
+    for (int i = 0; i < NW * MAX_SW; ++i) {
+      mbar_init(smem_u32(&bars[i]), WT == 0 ? 1 : 33);
+      mbar_init(smem_u32(&bars[16 + i]), 1);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == NW) {
+    // ------------------------------------------------------------ producer
+    const uint64_t pol = policy_evict_first();
+    if (pf_bytes > 0) {  // L2 look-ahead over the first rows of this CTA
+      const int rows_pf = max(1, min(pf_bytes / rowbytes, 2 * npairs));
+      for (int r = lane; r < rows_pf; r += 32) {
+        int mat, row;
+        map_row<EPI>(p, 2 * pr0 + r, mat, row);
+        l2_prefetch(reinterpret_cast<const uint8_t*>(p.w[mat]) + (size_t)row * rowbytes, (uint32_t)rowbytes);
+      }
+    }
+    int slot[NW];
+    uint32_t par[NW];
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      slot[w] = 0;
+      par[w] = 0;
+    }
+    // chunks are dealt round-robin: chunk ci of the pairs base .. base+NW-1 goes to warps 0 .. NW-1
+    for (int base = 0; base < npairs; base += NW) {
+      const uint8_t* src_row[NW];
+      const __half* src_sc[NW];
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        src_row[w] = nullptr;
+        src_sc[w] = nullptr;
+        if (base + w < npairs) {
+          // lanes 0 and 1 copy the weight rows 0 and 1 of the pair
+          int mat, row;
+          map_row<EPI>(p, 2 * (pr0 + base + w) + (lane & 1), mat, row);
+          src_row[w] = reinterpret_cast<const uint8_t*>(p.w[mat]) + (size_t)row * rowbytes;
+          if (WT) {  // scales: lanes 0-15 serve row 0, lanes 16-31 row 1
+            int m2, r2;
+            map_row<EPI>(p, 2 * (pr0 + base + w) + (lane >> 4), m2, r2);
+            src_sc[w] = p.sc[m2] + (size_t)r2 * (p.K / p.bs);
+          }
+        }
+      }
+      for (int ci = 0; ci < nchunks; ++ci) {
+        const int cbytes = min(ROWB, rowbytes - ci * ROWB);
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          if (base + w >= npairs) continue;
+          const uint32_t full = smem_u32(&bars[w * MAX_SW + slot[w]]);
+          mbar_wait(smem_u32(&bars[16 + w * MAX_SW + slot[w]]), par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
+          uint8_t* st = stages + (size_t)(w * sw + slot[w]) * STAGE_BYTES;
+          if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes));
+          __syncwarp();
+          if (lane < 2) bulk_g2s_hint(smem_u32(st + lane * ROWB), src_row[w] + (size_t)ci * ROWB, (uint32_t)cbytes, full, pol);
+          if (WT == 1) {
+            const int ppr = (cbytes / p.bs) >> 1;  // 4-byte pieces per row
+            const __half* src = src_sc[w] + (ci * CHUNK_K) / p.bs;
+            for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * SC_BYTES_ROW + j * 4), src + 2 * j);
+            cp_async_mbar_arrive_noinc(full);
+          }
+          if (++slot[w] == sw) {
+            slot[w] = 0;
+            par[w] ^= 1;
+          }
+        }
+      }
+    }
+    if (WT == 1) cp_async_wait<0>();
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  pdl_wait();
+  if (npairs > 0) {
+    const int vec = p.K >> 3;
+    for (int i = tid; i < vec; i += NCONS) *reinterpret_cast<uint4*>(xs + i * 16) = *reinterpret_cast<const uint4*>(p.x + i * 8);
+    bar_sync(1, NCONS);
+    if (p.norm_w != nullptr) {
+      // RMSNorm with the reference's summation order (llama_cu.cu:72-106): 256 strided partial sums,
+      // xor trees inside 8 warps, xor tree over the 8 warp sums.  Each of the 128 threads here plays
+      // two of the reference's threads (t and t + 128), each warp two of its warps (w and w + 4).
+      __half* xh = reinterpret_cast<__half*>(xs);
+      float s0 = 0.f, s1 = 0.f;
+      for (int i = tid; i < p.K; i += 256) {
+        float v = __half2float(xh[i]);
+        s0 += v * v;
+      }
+      for (int i = tid + 128; i < p.K; i += 256) {
+        float v = __half2float(xh[i]);
+        s1 += v * v;
+      }
+      s0 = warp_sum(s0);
+      s1 = warp_sum(s1);
+      if (lane == 0) {
+        scratch[warp] = s0;
+        scratch[warp + 4] = s1;
+      }
+      bar_sync(1, NCONS);
+      if (warp == 0) {
+        float t = lane < 8 ? scratch[lane] : 0.f;
+        for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) scratch[8] = rsqrtf(t / p.K + p.eps);
+      }
+      bar_sync(1, NCONS);
+      const float rinv = scratch[8];
+      for (int i = tid; i < p.K; i += NCONS) {
+        float v = __half2float(xh[i]);
+        xh[i] = __hmul(p.norm_w[i], __float2half(v * rinv));
+      }
+      bar_sync(1, NCONS);
+    }
+  }
+
+  const int g = lane >> 2, c = lane & 3;
+  const int flip = g & 1;
+  const bool diag = c == (g >> 1);
+  int pos = 0;
+  if (EPI == EPI_ROPE_KV) pos = *p.pos;
+
+  int slot = 0;
+  uint32_t par = 0;
+  for (int i = warp; i < npairs; i += NW) {
+    float accs[NACC][4];
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) accs[a][0] = accs[a][1] = accs[a][2] = accs[a][3] = 0.f;
+    for (int ci = 0; ci < nchunks; ++ci) {
+      mbar_wait(smem_u32(&bars[warp * MAX_SW + slot]), par, p.err, DEV_ERR_FULL_WAIT);
+      const int cbytes = min(ROWB, rowbytes - ci * ROWB);
+      const int vb = min(max(cbytes - g * SEG, 0), SEG);  // valid bytes of this lane's segment
+      const uint8_t* st = stages + (size_t)(warp * sw + slot) * STAGE_BYTES;
+      const uint8_t* seg0 = st + g * SEG;
+      const uint8_t* xseg = xs + ((size_t)ci * CHUNK_K + (size_t)g * (SEG / ESZ)) * 2;
+#pragma unroll
+      for (int s = 0; s < NSTEPS; ++s) {
+        float* acc = accs[(2 * s) % NACC];
+        float* acc_b = accs[(2 * s + 1) % NACC];
+        const int off = ((s ^ flip) << 6) + c * 16;  // byte offset inside the segment
+        const bool ok = off < vb;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (ok) {
+          lo = *reinterpret_cast<const uint4*>(seg0 + off);
+          hi = *reinterpret_cast<const uint4*>(seg0 + ROWB + off);
+        }
+        if (WT == 0) {
+          uint4 xb = make_uint4(0, 0, 0, 0);
+          if (ok) xb = *reinterpret_cast<const uint4*>(xseg + off);
+          mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
+          mma_16816(acc_b, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
+        } else {
+          uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+          __half2 s_lo = __half2half2(__ushort_as_half(0)), s_hi = s_lo;
+          if (ok) {
+            x0 = *reinterpret_cast<const uint4*>(xseg + 2 * off);
+            x1 = *reinterpret_cast<const uint4*>(xseg + 2 * off + 16);
+            const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
+            const int si = (g * SEG + off) / p.bs;  // k offset inside the chunk / block size
+            s_lo = __half2half2(scs[si]);
+            s_hi = __half2half2(scs[SC_BYTES_ROW / 2 + si]);
+          }
+          mma_16816(acc, dequant_pair(lo.x, 0x4140, s_lo), dequant_pair(hi.x, 0x4140, s_hi), dequant_pair(lo.x, 0x4342, s_lo),
+                    dequant_pair(hi.x, 0x4342, s_hi), x0.x, x0.y);
+          mma_16816(acc_b, dequant_pair(lo.y, 0x4140, s_lo), dequant_pair(hi.y, 0x4140, s_hi), dequant_pair(lo.y, 0x4342, s_lo),
+                    dequant_pair(hi.y, 0x4342, s_hi), x0.z, x0.w);
+          mma_16816(acc, dequant_pair(lo.z, 0x4140, s_lo), dequant_pair(hi.z, 0x4140, s_hi), dequant_pair(lo.z, 0x4342, s_lo),
+                    dequant_pair(hi.z, 0x4342, s_hi), x1.x, x1.y);
+          mma_16816(acc_b, dequant_pair(lo.w, 0x4140, s_lo), dequant_pair(hi.w, 0x4140, s_hi), dequant_pair(lo.w, 0x4342, s_lo),
+                    dequant_pair(hi.w, 0x4342, s_hi), x1.z, x1.w);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[16 + warp * MAX_SW + slot]));
+      if (++slot == sw) {
+        slot = 0;
+        par ^= 1;
+      }
+    }
+
+    // the diagonal lanes hold segment g of row 0 (d0/d1) and of row 1 (d2/d3): fixed-order shuffle tree
+    float v0 = 0.f, v1 = 0.f;
+    if (diag) {
+      const float a0 = (accs[0][0] + accs[1][0]) + (accs[2][0] + accs[3][0]), a1 = (accs[0][1] + accs[1][1]) + (accs[2][1] + accs[3][1]);
+      const float a2 = (accs[0][2] + accs[1][2]) + (accs[2][2] + accs[3][2]), a3 = (accs[0][3] + accs[1][3]) + (accs[2][3] + accs[3][3]);
+      v0 = (g & 1) ? a1 : a0;
+      v1 = (g & 1) ? a3 : a2;
+    }
+    v0 = warp_sum(v0);
+    v1 = warp_sum(v1);
+    if (lane == 0) {
+      const int pr = pr0 + i;
+      const int vrow = 2 * pr;
+      if (EPI == EPI_PLAIN) {
+        float a0 = v0, a1 = v1;
+        __half* o = p.out + vrow;
+        if (p.beta != 0.f) {
+          a0 = a0 + p.beta * __half2float(o[0]);
+          a1 = a1 + p.beta * __half2float(o[1]);
+        }
+        *reinterpret_cast<__half2*>(o) = __halves2half2(__float2half(a0), __float2half(a1));
+      } else {
+        const __half a = __float2half(v0), bq = __float2half(v1);  // the matmul's own output rounding
+        if (EPI == EPI_SILU) {
+          const float val = __half2float(a);  // llama_cu.cu:536-537 on the half-rounded w1 / w3 outputs
+          p.out[pr] = __float2half(val / (1.0f + expf(-val)) * __half2float(bq));
+        } else {
+          int mat, row;
+          map_row<EPI_ROPE_KV>(p, vrow, mat, row);
+          const int head = row / p.head_dim, j = row - head * p.head_dim;
+          __half o0 = a, o1 = bq;
+          if (mat < 2) {  // llama_cu.cu:381-387, cos/sin from the context's table
+            const float2 cs = p.rope[(size_t)pos * (p.head_dim >> 1) + (j >> 1)];
+            const float real = __half2float(a), imag = __half2float(bq);
+            const float a_cos = cs.x, a_sin = cs.y;
+            o0 = __float2half(real * a_cos - imag * a_sin);
+            o1 = __float2half(real * a_sin + imag * a_cos);
+          }
+          const __half2 pr2 = __halves2half2(o0, o1);
+          if (mat == 0) {
+            *reinterpret_cast<__half2*>(p.q_out + row) = pr2;
+          } else {
+            __half* cache = mat == 1 ? p.k_cache : p.v_cache;
+            *reinterpret_cast<__half2*>(cache + ((size_t)head * p.ctx_len + pos) * p.head_dim + j) = pr2;
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int WT, int EPI>
+int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, int grid, int sw, int pf_bytes) {
+  static bool attr_done[16] = {};
+  int dev = 0;
+  LCU_CUDA(cudaGetDevice(&dev));
+  if (dev < 16 && !attr_done[dev]) {
+    LCU_CUDA(cudaFuncSetAttribute(gemv1_kernel<WT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_done[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemv1_kernel<WT, EPI>, p, sw, pf_bytes));
+  return LCU_OK;
+}
+
+}  // namespace
+
+// m == 1 entry used by launch_gemv (argument checks are done there)
+int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl, int sms) {
+  const gemv_tuning& t = gemv_tuning_ref();
+  const bool q = p.bs != 0;
+  const size_t stage_bytes = 2 * ROWB + (q ? 2 * SC_BYTES_ROW : 0);
+  int sw = t.warp_stages < 2 ? 2 : (t.warp_stages > MAX_SW ? MAX_SW : t.warp_stages);
+  size_t smem = SMEM_FIXED + (((size_t)p.K * 2 + 127) & ~(size_t)127) + (size_t)NW * sw * stage_bytes;
+  // keep two CTAs per SM resident (a deeper ring that halves the occupancy loses more than it gains)
+  const size_t per_cta = t.ctas_per_sm >= 2 ? (size_t)(227 * 1024) / 2 - 1024 : (size_t)227 * 1024;
+  while (smem > per_cta && sw > 2) {
+    --sw;
+    smem -= NW * stage_bytes;
+  }
+  LCU_REQUIRE(smem <= 227 * 1024, "gemv: a row of K=%d does not fit in shared memory", p.K);
+  const int pairs = p.n_mats * p.rows_per_mat / 2;
+  int grid = sms * (t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);
+  if (grid > pairs) grid = pairs;
+  const int pf = t.prefetch_kb_per_cta * 1024;
+  switch (epilogue) {
+    case EPI_PLAIN:
+      return q ? launch_one<1, EPI_PLAIN>(p, stream, pdl, smem, grid, sw, pf) : launch_one<0, EPI_PLAIN>(p, stream, pdl, smem, grid, sw, pf);
+    case EPI_ROPE_KV:
+      return q ? launch_one<1, EPI_ROPE_KV>(p, stream, pdl, smem, grid, sw, pf) : launch_one<0, EPI_ROPE_KV>(p, stream, pdl, smem, grid, sw, pf);
+    default:
+      return q ? launch_one<1, EPI_SILU>(p, stream, pdl, smem, grid, sw, pf) : launch_one<0, EPI_SILU>(p, stream, pdl, smem, grid, sw, pf);
+  }
+}
+
+}  // namespace lcu
