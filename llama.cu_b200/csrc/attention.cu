@@ -10,9 +10,12 @@
 // over the scores (held in shared memory as halves), not an online-softmax.
 //
 // One thread-block cluster of CS CTAs serves one (query row, head): each CTA takes a contiguous
-// slice of the cached positions, and the max / sum / partial outputs are exchanged through
-// distributed shared memory.  K and V are stored head-major ([head][position][head_dim], keys
-// already rotated), so a slice is one contiguous run of 2*head_dim-byte rows.
+// slice of the cached positions.  K and V are stored head-major ([head][position][head_dim], keys
+// already rotated), so a slice is one contiguous run of 2*head_dim-byte rows.  Latency plan for
+// decode (short slices): the K rows AND the V rows of the first rounds are requested up front, so
+// there is one trip to memory instead of two; every CTA pushes its (max, sum) pair into all peers'
+// shared memory (st.shared::cluster) and its partial output into CTA 0's, which leaves two cluster
+// barriers in the kernel.  Slice sums are combined as sum_r lsum_r * expf(lmax_r - max) in rank order.
 #include "attention.cuh"
 
 namespace lcu {
@@ -20,18 +23,24 @@ namespace {
 
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_WARPS = ATT_THREADS / 32;
+constexpr int PRE_ROUNDS = 4;  // rounds of V rows kept in registers from the first request
+
+__device__ __forceinline__ void st_dsmem_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) {
-  constexpr int LPR = HD / 8;        // lanes that share one cached row (8 halves = 16 bytes each)
-  constexpr int RPW = 32 / LPR;      // rows a warp handles per step
+  constexpr int LPR = HD / 8;    // lanes that share one cached row (8 halves = 16 bytes each)
+  constexpr int RPW = 32 / LPR;  // rows a warp handles per round
+  constexpr int RPR = ATT_WARPS * RPW;  // rows per round of the whole CTA
   extern __shared__ __align__(16) uint8_t smem[];
-  // layout: exchange slots (floats) | partial outputs [HD] floats | per-warp partials | scores (halves)
-  float* xchg = reinterpret_cast<float*>(smem);           // [0]=max [1]=sum (this CTA's), read by peers
-  float* cpart = xchg + 4;                                // [HD] this CTA's partial output
-  float* wpart = cpart + HD;                              // [ATT_WARPS][HD]
-  float* wred = wpart + ATT_WARPS * HD;                   // [ATT_WARPS] scratch
-  __half* sc = reinterpret_cast<__half*>(wred + ATT_WARPS);  // [chunk] scores of this CTA's slice
+  float* xmax = reinterpret_cast<float*>(smem);  // [8] slice maxima of all ranks (pushed by the peers)
+  float* xsum = xmax + 8;                        // [8] slice exp-sums relative to the slice maximum
+  float* rpart = xsum + 8;                       // [8][HD] partial outputs of all ranks (used on rank 0)
+  float* wpart = rpart + 8 * HD;                 // [ATT_WARPS][HD]
+  float* wred = wpart + ATT_WARPS * HD;          // [2 * ATT_WARPS] scratch
+  __half* sc = reinterpret_cast<__half*>(wred + 2 * ATT_WARPS);  // [chunk] scores of this CTA's slice
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = lane / LPR, gl = lane % LPR;
@@ -39,6 +48,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
   const int head = blockIdx.y, qrow = blockIdx.z;
 
   pdl_launch_dependents();
+  // Remote shared-memory stores need the target CTA to have started: arrive now, wait right before
+  // the first push (split-phase, so the wait is free by then).
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   pdl_wait();
 
   const int start_pos = p.pos ? *p.pos : p.pos_value;
@@ -47,10 +59,21 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
   const int t0 = min(T, (int)rank * chunk), t1 = min(T, t0 + chunk);
   const int n = t1 - t0;
 
-  const __half* kbase = p.k_cache + ((size_t)head * p.ctx_len + t0) * HD;
-  const __half* vbase = p.v_cache + ((size_t)head * p.ctx_len + t0) * HD;
+  const __half* kbase = p.k_cache + ((size_t)head * p.ctx_len + t0) * HD + gl * 8;
+  const __half* vbase = p.v_cache + ((size_t)head * p.ctx_len + t0) * HD + gl * 8;
 
-  // this lane's 8 query values
+  // requests for the first rounds of K and V go out together
+  uint4 kreg[PRE_ROUNDS], vreg[PRE_ROUNDS];
+#pragma unroll
+  for (int r = 0; r < PRE_ROUNDS; ++r) {
+    const int t = r * RPR + warp * RPW + grp;
+    kreg[r] = make_uint4(0, 0, 0, 0);
+    vreg[r] = make_uint4(0, 0, 0, 0);
+    if (t < n) {
+      kreg[r] = *reinterpret_cast<const uint4*>(kbase + (size_t)t * HD);
+      vreg[r] = *reinterpret_cast<const uint4*>(vbase + (size_t)t * HD);
+    }
+  }
   float q[8];
   {
     const uint4 qv = *reinterpret_cast<const uint4*>(p.q + (size_t)qrow * p.ldq + head * HD + gl * 8);
@@ -66,11 +89,20 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
 
   // ---- pass 1: scores of the slice, rounded to half, and the slice maximum
   float lmax = -CUDART_INF_F;
-  for (int base = warp * RPW; base < n; base += ATT_WARPS * RPW) {
-    const int t = base + grp;
+  for (int base = 0; base < n; base += RPR) {
+    const int r = base / RPR;
+    const int t = base + warp * RPW + grp;
     float s = 0.f;
     if (t < n) {
-      const uint4 kv = *reinterpret_cast<const uint4*>(kbase + (size_t)t * HD + gl * 8);
+      uint4 kv;
+      if (r < PRE_ROUNDS) {
+        kv = kreg[0];
+#pragma unroll
+        for (int j = 1; j < PRE_ROUNDS; ++j)
+          if (r == j) kv = kreg[j];
+      } else {
+        kv = *reinterpret_cast<const uint4*>(kbase + (size_t)t * HD);
+      }
       const __half2* h = reinterpret_cast<const __half2*>(&kv);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -90,38 +122,48 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
   lmax = warp_max(lmax);
   if (lane == 0) wred[warp] = lmax;
   __syncthreads();
-  if (tid == 0) {
-    float m = wred[0];
-    for (int w = 1; w < ATT_WARPS; ++w) m = fmaxf(m, wred[w]);
-    xchg[0] = m;
+  lmax = wred[0];
+#pragma unroll
+  for (int w = 1; w < ATT_WARPS; ++w) lmax = fmaxf(lmax, wred[w]);
+
+  // slice exp-sum relative to the slice maximum (fixed order: lanes, then warps)
+  float lsum = 0.f;
+  for (int t = tid; t < n; t += ATT_THREADS) lsum += expf(__half2float(sc[t]) - lmax);
+  lsum = warp_sum(lsum);
+  if (lane == 0) wred[ATT_WARPS + warp] = lsum;
+  __syncthreads();
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+  if (tid < (int)cs) {  // thread r pushes this slice's pair into rank r's table
+    float s = 0.f;
+    for (int w = 0; w < ATT_WARPS; ++w) s += wred[ATT_WARPS + w];
+    st_dsmem_f32(mapa(smem_u32(&xmax[rank]), tid), lmax);
+    st_dsmem_f32(mapa(smem_u32(&xsum[rank]), tid), s);
   }
   cluster_sync();
   float gmax = -CUDART_INF_F;
-  for (uint32_t r = 0; r < cs; ++r) gmax = fmaxf(gmax, ld_dsmem_f32(mapa(smem_u32(&xchg[0]), r)));
-
-  // ---- pass 2: sum of exponentials (fixed order: lanes, warps, then cluster ranks)
-  float lsum = 0.f;
-  for (int t = tid; t < n; t += ATT_THREADS) lsum += expf(__half2float(sc[t]) - gmax);
-  lsum = warp_sum(lsum);
-  __syncthreads();  // wred reuse
-  if (lane == 0) wred[warp] = lsum;
-  __syncthreads();
-  if (tid == 0) {
-    float s = 0.f;
-    for (int w = 0; w < ATT_WARPS; ++w) s += wred[w];
-    xchg[1] = s;
-  }
-  cluster_sync();
+  for (uint32_t r = 0; r < cs; ++r) gmax = fmaxf(gmax, xmax[r]);
   float gsum = 0.f;
-  for (uint32_t r = 0; r < cs; ++r) gsum += ld_dsmem_f32(mapa(smem_u32(&xchg[1]), r));
+  for (uint32_t r = 0; r < cs; ++r) {
+    const float m = xmax[r];
+    if (m > -CUDART_INF_F) gsum += xsum[r] * expf(m - gmax);  // an empty slice contributes nothing
+  }
 
-  // ---- pass 3: probabilities rounded to half, times V
+  // ---- pass 2: probabilities rounded to half, times V
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int base = warp * RPW; base < n; base += ATT_WARPS * RPW) {
-    const int t = base + grp;
+  for (int base = 0; base < n; base += RPR) {
+    const int r = base / RPR;
+    const int t = base + warp * RPW + grp;
     if (t < n) {
       const float pr = __half2float(__float2half(expf(__half2float(sc[t]) - gmax) / gsum));
-      const uint4 vv = *reinterpret_cast<const uint4*>(vbase + (size_t)t * HD + gl * 8);
+      uint4 vv;
+      if (r < PRE_ROUNDS) {
+        vv = vreg[0];
+#pragma unroll
+        for (int j = 1; j < PRE_ROUNDS; ++j)
+          if (r == j) vv = vreg[j];
+      } else {
+        vv = *reinterpret_cast<const uint4*>(vbase + (size_t)t * HD);
+      }
       const __half2* h = reinterpret_cast<const __half2*>(&vv);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -131,7 +173,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
       }
     }
   }
-  // combine the row groups of a warp, then the warps, then the cluster ranks
+  // combine the row groups of a warp, then the warps, then the cluster ranks (all in fixed order)
 #pragma unroll
   for (int i = 0; i < 8; ++i)
     for (int o = LPR; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
@@ -143,21 +185,20 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
   if (tid < HD) {
     float s = 0.f;
     for (int w = 0; w < ATT_WARPS; ++w) s += wpart[w * HD + tid];
-    cpart[tid] = s;
+    st_dsmem_f32(mapa(smem_u32(&rpart[rank * HD + tid]), 0), s);  // into rank 0's table
   }
   cluster_sync();
   if (rank == 0 && tid < HD) {
     float s = 0.f;
-    for (uint32_t r = 0; r < cs; ++r) s += ld_dsmem_f32(mapa(smem_u32(&cpart[tid]), r));
+    for (uint32_t r = 0; r < cs; ++r) s += rpart[r * HD + tid];
     p.out[(size_t)qrow * p.ldo + head * HD + tid] = __float2half(s);
   }
-  cluster_sync();  // peers' shared memory stays alive until rank 0 has read it
 }
 
 template <int HD>
 int launch_hd(const attn_params& p, int m, int cs, int max_T, cudaStream_t stream, int pdl) {
   const int chunk = (max_T + cs - 1) / cs;
-  const size_t smem = (4 + HD + ATT_WARPS * HD + ATT_WARPS) * sizeof(float) + (size_t)chunk * 2 + 16;
+  const size_t smem = (16 + 8 * HD + ATT_WARPS * HD + 2 * ATT_WARPS) * sizeof(float) + (size_t)chunk * 2 + 16;
   LCU_REQUIRE(smem <= 200 * 1024, "attention: %d positions per CTA do not fit in shared memory", chunk);
   static bool attr_done[16] = {};
   int dev = 0;

@@ -378,7 +378,7 @@ int launch_silu(__half* out, const __half* a, const __half* b, size_t n, cudaStr
   return LCU_OK;
 }
 
-int launch_logits_head(const head_params& p, cudaStream_t stream, int pdl) {
+int launch_logits_head_single(const head_params& p, cudaStream_t stream, int pdl) {
   static bool attr_done[16] = {};
   int dev = 0;
   LCU_CUDA(cudaGetDevice(&dev));

@@ -43,6 +43,8 @@ struct head_params {
   int log_capacity;
 };
 int launch_logits_head(const head_params& p, cudaStream_t stream, int pdl);
+// one-block version of the same computation (any vocabulary size; used when the clustered kernel does not fit)
+int launch_logits_head_single(const head_params& p, cudaStream_t stream, int pdl);
 
 // block-absmax quantizer, bit-identical to the reference's (transform.cu:28-72)
 int launch_quantize_absmax_uint8(uint8_t* q, __half* scales, const __half* in, size_t h, size_t w, int bs, cudaStream_t stream);
