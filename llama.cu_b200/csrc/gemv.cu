@@ -420,6 +420,8 @@ int sm_count() {
 
 }  // namespace
 
+int gemv_sm_count() { return sm_count(); }
+
 gemv_tuning& gemv_tuning_ref() {
   static gemv_tuning t;
   return t;

@@ -61,7 +61,75 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t word, uint32_t selecto
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int WT /*0 fp16, 1 u8*/, int EPI>
+// One 64-byte step of every segment: 16 tile rows x 32 (fp16) or 64 (u8) weights per lane group.
+template <int WT, bool FULL>
+__device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const int flip, const int c, const int g, const int vb,
+                                     const uint8_t* seg0, const uint8_t* xseg, const uint8_t* st, const float* xs64, const int ci,
+                                     const int bs) {
+  constexpr int ESZ = WT == 0 ? 2 : 1;
+  constexpr int CHUNK_K = ROWB / ESZ;
+  float* acc = accs[(2 * s) % NACC];
+  float* acc_b = accs[(2 * s + 1) % NACC];
+  const int off = ((s ^ flip) << 6) + c * 16;  // byte offset inside the segment
+  const bool ok = FULL || off < vb;
+  uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+  if (ok) {
+    lo = *reinterpret_cast<const uint4*>(seg0 + off);
+    hi = *reinterpret_cast<const uint4*>(seg0 + ROWB + off);
+  }
+  if (WT == 0) {
+    uint4 xb = make_uint4(0, 0, 0, 0);
+    if (ok) xb = *reinterpret_cast<const uint4*>(xseg + off);
+    mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
+    mma_16816(acc_b, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
+  } else {
+    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+    __half sc_lo = __ushort_as_half(0), sc_hi = sc_lo;
+    float corr = 0.f;
+    if (ok) {
+      x0 = *reinterpret_cast<const uint4*>(xseg + 2 * off);
+      x1 = *reinterpret_cast<const uint4*>(xseg + 2 * off + 16);
+      const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
+      const int si = (g * SEG + off) / bs;  // k offset inside the chunk / block size
+      sc_lo = scs[si];
+      sc_hi = scs[SC_BYTES_ROW / 2 + si];
+      // WT 2: sum of x over this lane's segment and step (the diagonal column of the tile)
+      if (WT == 2) corr = 1151.5f * xs64[ci * (CHUNK_K / 64) + g * NSTEPS + (s ^ flip)];
+    }
+    if (WT == 2) {
+      float ta[4] = {0.f, 0.f, 0.f, 0.f}, tb[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t M = 0x64646464u;  // bytes -> halves 1024 + q
+      mma_16816(ta, __byte_perm(lo.x, M, 0x4140), __byte_perm(hi.x, M, 0x4140), __byte_perm(lo.x, M, 0x4342), __byte_perm(hi.x, M, 0x4342), x0.x, x0.y);
+      mma_16816(tb, __byte_perm(lo.y, M, 0x4140), __byte_perm(hi.y, M, 0x4140), __byte_perm(lo.y, M, 0x4342), __byte_perm(hi.y, M, 0x4342), x0.z, x0.w);
+      mma_16816(ta, __byte_perm(lo.z, M, 0x4140), __byte_perm(hi.z, M, 0x4140), __byte_perm(lo.z, M, 0x4342), __byte_perm(hi.z, M, 0x4342), x1.x, x1.y);
+      mma_16816(tb, __byte_perm(lo.w, M, 0x4140), __byte_perm(hi.w, M, 0x4140), __byte_perm(lo.w, M, 0x4342), __byte_perm(hi.w, M, 0x4342), x1.z, x1.w);
+      // only the diagonal entries (column == this lane's segment) are meaningful, and they share `corr`
+      const float sl = __half2float(sc_lo), sh = __half2float(sc_hi);
+      acc[0] += sl * ((ta[0] + tb[0]) - corr);
+      acc[1] += sl * ((ta[1] + tb[1]) - corr);
+      acc[2] += sh * ((ta[2] + tb[2]) - corr);
+      acc[3] += sh * ((ta[3] + tb[3]) - corr);
+    } else {
+      const __half2 s_lo = __half2half2(sc_lo), s_hi = __half2half2(sc_hi);
+      mma_16816(acc, dequant_pair(lo.x, 0x4140, s_lo), dequant_pair(hi.x, 0x4140, s_hi), dequant_pair(lo.x, 0x4342, s_lo),
+                dequant_pair(hi.x, 0x4342, s_hi), x0.x, x0.y);
+      mma_16816(acc_b, dequant_pair(lo.y, 0x4140, s_lo), dequant_pair(hi.y, 0x4140, s_hi), dequant_pair(lo.y, 0x4342, s_lo),
+                dequant_pair(hi.y, 0x4342, s_hi), x0.z, x0.w);
+      mma_16816(acc, dequant_pair(lo.z, 0x4140, s_lo), dequant_pair(hi.z, 0x4140, s_hi), dequant_pair(lo.z, 0x4342, s_lo),
+                dequant_pair(hi.z, 0x4342, s_hi), x1.x, x1.y);
+      mma_16816(acc_b, dequant_pair(lo.w, 0x4140, s_lo), dequant_pair(hi.w, 0x4140, s_hi), dequant_pair(lo.w, 0x4342, s_lo),
+                dequant_pair(hi.w, 0x4342, s_hi), x1.z, x1.w);
+    }
+  }
+}
+
+// Weight types (WT): 0 = fp16; 1 = u8, every weight rounded to half((q - 127.5) * scale) before the
+// product exactly as the reference's tensor-core kernel does (llama_cu.cu:287-289, 332-341); 2 = u8
+// with the scale factored out of each 64-weight group: sum_k x_k (q_k - 127.5) s = s * (sum_k x_k
+// (1024 + q_k) - 1151.5 * sum_k x_k), the bytes going to the tensor core as the exact halves
+// 1024 + q (one PRMT per two weights) and the group sums of x coming from the prologue.  Mode 2 has
+// no per-weight rounding: it is closer to the exact product but is not the reference's rounding.
+template <int WT, int EPI>
 __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p, const int sw, const int pf_bytes) {
   constexpr int ESZ = WT == 0 ? 2 : 1;
   constexpr int CHUNK_K = ROWB / ESZ;        // weights of one row per stage: 2048 fp16, 4096 u8
@@ -71,7 +139,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [16 + w * MAX_SW + s]
   float* scratch = reinterpret_cast<float*>(smem + 256);
   uint8_t* xs = smem + SMEM_FIXED;                     // activation row, K halves
-  uint8_t* stages = xs + ((p.K * 2 + 127) & ~127);     // [NW][sw][STAGE_BYTES]
+  float* xs64 = reinterpret_cast<float*>(xs + ((p.K * 2 + 127) & ~127));  // sums of x over aligned groups of 64
+  uint8_t* stages = reinterpret_cast<uint8_t*>(xs64) + ((p.K / 64 * 4 + 127) & ~127);  // [NW][sw][STAGE_BYTES]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   pdl_launch_dependents();
@@ -140,7 +209,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
           if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes));
           __syncwarp();
           if (lane < 2) bulk_g2s_hint(smem_u32(st + lane * ROWB), src_row[w] + (size_t)ci * ROWB, (uint32_t)cbytes, full, pol);
-          if (WT == 1) {
+          if (WT != 0) {
             const int ppr = (cbytes / p.bs) >> 1;  // 4-byte pieces per row
             const __half* src = src_sc[w] + (ci * CHUNK_K) / p.bs;
             for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * SC_BYTES_ROW + j * 4), src + 2 * j);
@@ -153,7 +222,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
         }
       }
     }
-    if (WT == 1) cp_async_wait<0>();
+    if (WT != 0) cp_async_wait<0>();
     return;
   }
 
@@ -197,6 +266,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
       }
       bar_sync(1, NCONS);
     }
+    if (WT == 2) {  // group sums of the (normalised) activations: one warp per group of 64, two halves per lane
+      for (int grp64 = warp; grp64 < p.K / 64; grp64 += NW) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(xs + grp64 * 128 + lane * 4));
+        const float s = warp_sum(f.x + f.y);
+        if (lane == 0) xs64[grp64] = s;
+      }
+      bar_sync(1, NCONS);
+    }
   }
 
   const int g = lane >> 2, c = lane & 3;
@@ -218,42 +295,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
       const uint8_t* st = stages + (size_t)(warp * sw + slot) * STAGE_BYTES;
       const uint8_t* seg0 = st + g * SEG;
       const uint8_t* xseg = xs + ((size_t)ci * CHUNK_K + (size_t)g * (SEG / ESZ)) * 2;
+      // A full chunk (every chunk but possibly the last of a row) takes the branch-free path, so that the
+      // shared loads of all eight steps can be issued ahead of the tensor-core instructions.
+      if (cbytes == ROWB) {
 #pragma unroll
-      for (int s = 0; s < NSTEPS; ++s) {
-        float* acc = accs[(2 * s) % NACC];
-        float* acc_b = accs[(2 * s + 1) % NACC];
-        const int off = ((s ^ flip) << 6) + c * 16;  // byte offset inside the segment
-        const bool ok = off < vb;
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-        if (ok) {
-          lo = *reinterpret_cast<const uint4*>(seg0 + off);
-          hi = *reinterpret_cast<const uint4*>(seg0 + ROWB + off);
-        }
-        if (WT == 0) {
-          uint4 xb = make_uint4(0, 0, 0, 0);
-          if (ok) xb = *reinterpret_cast<const uint4*>(xseg + off);
-          mma_16816(acc, lo.x, hi.x, lo.y, hi.y, xb.x, xb.y);
-          mma_16816(acc_b, lo.z, hi.z, lo.w, hi.w, xb.z, xb.w);
-        } else {
-          uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-          __half2 s_lo = __half2half2(__ushort_as_half(0)), s_hi = s_lo;
-          if (ok) {
-            x0 = *reinterpret_cast<const uint4*>(xseg + 2 * off);
-            x1 = *reinterpret_cast<const uint4*>(xseg + 2 * off + 16);
-            const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
-            const int si = (g * SEG + off) / p.bs;  // k offset inside the chunk / block size
-            s_lo = __half2half2(scs[si]);
-            s_hi = __half2half2(scs[SC_BYTES_ROW / 2 + si]);
-          }
-          mma_16816(acc, dequant_pair(lo.x, 0x4140, s_lo), dequant_pair(hi.x, 0x4140, s_hi), dequant_pair(lo.x, 0x4342, s_lo),
-                    dequant_pair(hi.x, 0x4342, s_hi), x0.x, x0.y);
-          mma_16816(acc_b, dequant_pair(lo.y, 0x4140, s_lo), dequant_pair(hi.y, 0x4140, s_hi), dequant_pair(lo.y, 0x4342, s_lo),
-                    dequant_pair(hi.y, 0x4342, s_hi), x0.z, x0.w);
-          mma_16816(acc, dequant_pair(lo.z, 0x4140, s_lo), dequant_pair(hi.z, 0x4140, s_hi), dequant_pair(lo.z, 0x4342, s_lo),
-                    dequant_pair(hi.z, 0x4342, s_hi), x1.x, x1.y);
-          mma_16816(acc_b, dequant_pair(lo.w, 0x4140, s_lo), dequant_pair(hi.w, 0x4140, s_hi), dequant_pair(lo.w, 0x4342, s_lo),
-                    dequant_pair(hi.w, 0x4342, s_hi), x1.z, x1.w);
-        }
+        for (int s = 0; s < NSTEPS; ++s) step<WT, true>(accs, s, flip, c, g, SEG, seg0, xseg, st, xs64, ci, p.bs);
+      } else {
+#pragma unroll
+        for (int s = 0; s < NSTEPS; ++s) step<WT, false>(accs, s, flip, c, g, vb, seg0, xseg, st, xs64, ci, p.bs);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[16 + warp * MAX_SW + slot]));
@@ -314,6 +363,23 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
   }
 }
 
+// L2 look-ahead for a GEMV that has not been launched yet: requests, for every CTA of that future
+// launch (same grid, same row ranges), the rows after the first skip_bytes of its range up to
+// skip_bytes + pf_bytes.  Meant for a side stream while a latency-bound kernel leaves HBM idle.
+template <int EPI>
+__global__ void __launch_bounds__(32) gemv1_prefetch_kernel(const gemv_params p, const int rowbytes, const int skip_bytes, const int pf_bytes) {
+  const int pairs = (p.n_mats * p.rows_per_mat) >> 1;
+  const int pr0 = (int)(((long long)pairs * blockIdx.x) / gridDim.x);
+  const int nrows = 2 * ((int)(((long long)pairs * (blockIdx.x + 1)) / gridDim.x) - pr0);
+  const int first = skip_bytes / rowbytes;
+  const int last = min(nrows, (skip_bytes + pf_bytes) / rowbytes);
+  for (int r = first + threadIdx.x; r < last; r += 32) {
+    int mat, row;
+    map_row<EPI>(p, 2 * pr0 + r, mat, row);
+    l2_prefetch(reinterpret_cast<const uint8_t*>(p.w[mat]) + (size_t)row * rowbytes, (uint32_t)rowbytes);
+  }
+}
+
 template <int WT, int EPI>
 int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, int grid, int sw, int pf_bytes) {
   static bool attr_done[16] = {};
@@ -337,7 +403,30 @@ int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, 
   return LCU_OK;
 }
 
+int grid_of(const gemv_params& p, int sms) {
+  const gemv_tuning& t = gemv_tuning_ref();
+  const int pairs = p.n_mats * p.rows_per_mat / 2;
+  const int grid = sms * (t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);
+  return grid > pairs ? pairs : grid;
+}
+
 }  // namespace
+
+int launch_gemv_prefetch(const gemv_params& p, int epilogue, int sms, int kb_per_cta, cudaStream_t stream) {
+  const gemv_tuning& t = gemv_tuning_ref();
+  if (kb_per_cta <= 0 || t.variant != 1) return LCU_OK;
+  const int grid = grid_of(p, sms);
+  const int rowbytes = p.bs ? p.K : p.K * 2;
+  const int skip = t.prefetch_kb_per_cta * 1024, pf = kb_per_cta * 1024;
+  if (epilogue == EPI_SILU)
+    gemv1_prefetch_kernel<EPI_SILU><<<grid, 32, 0, stream>>>(p, rowbytes, skip, pf);
+  else if (epilogue == EPI_ROPE_KV)
+    gemv1_prefetch_kernel<EPI_ROPE_KV><<<grid, 32, 0, stream>>>(p, rowbytes, skip, pf);
+  else
+    gemv1_prefetch_kernel<EPI_PLAIN><<<grid, 32, 0, stream>>>(p, rowbytes, skip, pf);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
 
 // m == 1 entry used by launch_gemv (argument checks are done there)
 int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl, int sms) {
@@ -345,26 +434,32 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   const bool q = p.bs != 0;
   const size_t stage_bytes = 2 * ROWB + (q ? 2 * SC_BYTES_ROW : 0);
   int sw = t.warp_stages < 2 ? 2 : (t.warp_stages > MAX_SW ? MAX_SW : t.warp_stages);
-  size_t smem = SMEM_FIXED + (((size_t)p.K * 2 + 127) & ~(size_t)127) + (size_t)NW * sw * stage_bytes;
-  // keep two CTAs per SM resident (a deeper ring that halves the occupancy loses more than it gains)
-  const size_t per_cta = t.ctas_per_sm >= 2 ? (size_t)(227 * 1024) / 2 - 1024 : (size_t)227 * 1024;
+  size_t smem = SMEM_FIXED + (((size_t)p.K * 2 + 127) & ~(size_t)127) + (((size_t)p.K / 64 * 4 + 127) & ~(size_t)127) +
+                (size_t)NW * sw * stage_bytes;
+  // keep `ctas_per_sm` CTAs resident (a deeper ring that lowers the occupancy loses more than it gains)
+  const int cps = t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm;
+  const size_t per_cta = (size_t)(227 * 1024) / cps - 1024;
   while (smem > per_cta && sw > 2) {
     --sw;
     smem -= NW * stage_bytes;
   }
   LCU_REQUIRE(smem <= 227 * 1024, "gemv: a row of K=%d does not fit in shared memory", p.K);
-  const int pairs = p.n_mats * p.rows_per_mat / 2;
-  int grid = sms * (t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);
-  if (grid > pairs) grid = pairs;
+  const int grid = grid_of(p, sms);
   const int pf = t.prefetch_kb_per_cta * 1024;
+  // weight type of the kernel: fp16; u8 with the reference's per-weight rounding; u8 with factored scales
+  const int wt = !q ? 0 : ((t.int8_factored && p.bs >= 64) ? 2 : 1);
+#define LCU_GEMV1_CASE(E)                                                     \
+  case E:                                                                     \
+    if (wt == 0) return launch_one<0, E>(p, stream, pdl, smem, grid, sw, pf); \
+    if (wt == 1) return launch_one<1, E>(p, stream, pdl, smem, grid, sw, pf); \
+    return launch_one<2, E>(p, stream, pdl, smem, grid, sw, pf);
   switch (epilogue) {
-    case EPI_PLAIN:
-      return q ? launch_one<1, EPI_PLAIN>(p, stream, pdl, smem, grid, sw, pf) : launch_one<0, EPI_PLAIN>(p, stream, pdl, smem, grid, sw, pf);
-    case EPI_ROPE_KV:
-      return q ? launch_one<1, EPI_ROPE_KV>(p, stream, pdl, smem, grid, sw, pf) : launch_one<0, EPI_ROPE_KV>(p, stream, pdl, smem, grid, sw, pf);
-    default:
-      return q ? launch_one<1, EPI_SILU>(p, stream, pdl, smem, grid, sw, pf) : launch_one<0, EPI_SILU>(p, stream, pdl, smem, grid, sw, pf);
+    LCU_GEMV1_CASE(EPI_PLAIN)
+    LCU_GEMV1_CASE(EPI_ROPE_KV)
+    LCU_GEMV1_CASE(EPI_SILU)
   }
+#undef LCU_GEMV1_CASE
+  LCU_REQUIRE(false, "gemv: unknown epilogue %d", epilogue);
 }
 
 }  // namespace lcu
