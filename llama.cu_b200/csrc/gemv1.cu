@@ -90,7 +90,7 @@ __device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const 
       x0 = *reinterpret_cast<const uint4*>(xseg + 2 * off);
       x1 = *reinterpret_cast<const uint4*>(xseg + 2 * off + 16);
       const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
-      const int si = (g * SEG + off) / bs;  // k offset inside the chunk / block size
+      const int si = (g * SEG + off) >> bs;  // k offset inside the chunk / block size (bs is log2 of it here)
       sc_lo = scs[si];
       sc_hi = scs[SC_BYTES_ROW / 2 + si];
       // WT 2: sum of x over this lane's segment and step (the diagonal column of the tile)
@@ -278,6 +278,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
 
   const int g = lane >> 2, c = lane & 3;
   const int flip = g & 1;
+  const int bs_shift = p.bs > 0 ? 31 - __clz(p.bs) : 0;  // block size is a power of two (32, 64, 128)
   const bool diag = c == (g >> 1);
   int pos = 0;
   if (EPI == EPI_ROPE_KV) pos = *p.pos;
@@ -299,10 +300,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
       // shared loads of all eight steps can be issued ahead of the tensor-core instructions.
       if (cbytes == ROWB) {
 #pragma unroll
-        for (int s = 0; s < NSTEPS; ++s) step<WT, true>(accs, s, flip, c, g, SEG, seg0, xseg, st, xs64, ci, p.bs);
+        for (int s = 0; s < NSTEPS; ++s) step<WT, true>(accs, s, flip, c, g, SEG, seg0, xseg, st, xs64, ci, bs_shift);
       } else {
 #pragma unroll
-        for (int s = 0; s < NSTEPS; ++s) step<WT, false>(accs, s, flip, c, g, vb, seg0, xseg, st, xs64, ci, p.bs);
+        for (int s = 0; s < NSTEPS; ++s) step<WT, false>(accs, s, flip, c, g, vb, seg0, xseg, st, xs64, ci, bs_shift);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[16 + warp * MAX_SW + slot]));
