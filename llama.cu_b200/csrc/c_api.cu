@@ -101,6 +101,8 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "gemv_warp_stages") gemv_tuning_ref().warp_stages = value;
   else if (k == "gemv_variant") gemv_tuning_ref().variant = value;
   else if (k == "gemv_prefetch_kb") gemv_tuning_ref().prefetch_kb_per_cta = value;
+  else if (k == "prefill_tc_min_rows") prefill_tuning_ref().tc_min_rows = value;
+  else if (k == "prefill_tc_tile_n") prefill_tuning_ref().tc_tile_n = value;
   else if (k == "use_graph") g_default_opts.use_graph = value;
   else if (k == "use_pdl") g_default_opts.use_pdl = value;
   else if (k == "attn_cluster") g_default_opts.attn_cluster = value;

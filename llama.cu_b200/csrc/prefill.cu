@@ -1,12 +1,21 @@
 // Prompt-processing matrix product (reference: matmul_nt dispatch, llama_cu.cu:1463-1523).
 #include "prefill.cuh"
 
+#include "gemm_tc.cuh"
 #include "gemv.cuh"
 
 namespace lcu {
 
+prefill_tuning& prefill_tuning_ref() {
+  static prefill_tuning t;
+  return t;
+}
+
 int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, float beta, int* err, cudaStream_t stream) {
   const int K = (int)w.cols, N = (int)w.rows;
+  const prefill_tuning& pt = prefill_tuning_ref();
+  if (w.bs == 0 && pt.tc_min_rows > 0 && m >= pt.tc_min_rows && gemm_tc_supported(m, N, K, K, lhs, w.w, out))
+    return launch_gemm_tc(out, lhs, K, (const __half*)w.w, m, N, K, beta, err, stream, pt.tc_tile_n);
   for (int t = 0; t < m; t += 8) {
     gemv_params p{};
     p.w[0] = w.w;

@@ -115,6 +115,33 @@ def test_matmul_small_shapes(lcu, m, k, n, bs, beta):
     assert np.abs(f32(y) - f32(yo)).max() <= 2e-3 * scale, (m, k, n, bs)
 
 
+@pytest.mark.parametrize("m,k,n,beta,tile", [(9, 64, 32, 0.0, 0), (16, 256, 32, 1.0, 0), (128, 64, 128, 0.0, 128), (129, 512, 192, 1.0, 0),
+                                             (200, 1024, 256, 1.0, 64), (77, 4096, 1024, 0.0, 32), (300, 11008, 128, 0.0, 0),
+                                             (257, 4096, 4096, 1.0, 0)])
+def test_prefill_tensor_core_gemm(lcu, m, k, n, beta, tile):
+    """fp16 weights with more than 8 rows run on tcgen05 with the accumulator in tensor memory: compared with
+    the oracle's binary64-accumulated product (tolerance 2e-3 of the largest output: fp32 accumulation in a
+    different order plus one rounding to half) and with the 8-row GEMV passes it replaces."""
+    rng = np.random.default_rng(m * 7 + n)
+    x = f16(rng.standard_normal((m, k)))
+    w = O.synth_f16(n * k, 5, f"tc{n}x{k}", 0.05).reshape(n, k)
+    prev = f16(rng.standard_normal((m, n)))
+    yo = prev.copy()
+    L.orc_matmul_nt_f16(yo.reshape(-1), x.reshape(-1), w.reshape(-1), m, k, n, beta, 1)
+    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_tile_n", tile))
+    try:
+        y = lcu.matmul_nt(x, w, beta=beta, out_u16=prev)
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_min_rows", 0))
+        y_gemv = lcu.matmul_nt(x, w, beta=beta, out_u16=prev) if k % 256 == 0 else None
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_tile_n", 0))
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_min_rows", 9))
+    scale = max(1.0, float(np.abs(f32(yo)).max()))
+    assert np.abs(f32(y) - f32(yo)).max() <= 2e-3 * scale
+    if y_gemv is not None:
+        assert np.abs(f32(y) - f32(y_gemv)).max() <= 2e-3 * scale
+
+
 def test_matmul_rejects_bad_shapes(lcu):
     with pytest.raises(lcu.LcuError, match="multiple of 256"):
         lcu.matmul_nt(np.zeros((1, 100), np.uint16), np.zeros((4, 100), np.uint16))
