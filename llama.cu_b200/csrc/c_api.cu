@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "attention.cuh"
+#include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "ops.cuh"
 #include "prefill.cuh"
@@ -103,6 +104,9 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "gemv_prefetch_kb") gemv_tuning_ref().prefetch_kb_per_cta = value;
   else if (k == "prefill_tc_min_rows") prefill_tuning_ref().tc_min_rows = value;
   else if (k == "prefill_tc_tile_n") prefill_tuning_ref().tc_tile_n = value;
+  else if (k == "prefill_u8_deq_min_rows") prefill_tuning_ref().u8_deq_min_rows = value;
+  else if (k == "prefill_tc_split") prefill_tuning_ref().tc_split = value;
+  else if (k == "prefill_tc_pair") prefill_tuning_ref().tc_pair = value;
   else if (k == "use_graph") g_default_opts.use_graph = value;
   else if (k == "use_pdl") g_default_opts.use_pdl = value;
   else if (k == "attn_cluster") g_default_opts.attn_cluster = value;

@@ -17,6 +17,9 @@
 // the error word, skips ahead and still frees its tensor memory.
 #include <cuda.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "gemm_tc.cuh"
 
 namespace lcu {
@@ -70,21 +73,59 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-template <int BN>
+// half(acc + beta * previous) for 32 consecutive outputs of one row (64 bytes, 16-byte aligned)
+__device__ __forceinline__ void store_row_piece(__half* o, const float (&acc)[32], float beta) {
+  uint4 v[4];
+  if (beta != 0.f) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = reinterpret_cast<const uint4*>(o)[i];
+  }
+  __half2* h = reinterpret_cast<__half2*>(v);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float a0 = acc[2 * i], a1 = acc[2 * i + 1];
+    if (beta != 0.f) {
+      const float2 prev = __half22float2(h[i]);
+      a0 = fmaf(beta, prev.x, a0);
+      a1 = fmaf(beta, prev.y, a1);
+    }
+    h[i] = __floats2half2_rn(a0, a1);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(o)[i] = v[i];
+}
+__device__ __forceinline__ void st_dsmem_f4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// One-SM kernel.  S > 1 splits K over a cluster of S CTAs that share one output tile (few rows and a
+// narrow matrix would otherwise leave most SMs without a tile while the weights stream from HBM):
+// CTA r accumulates k-blocks [r nk / S, (r+1) nk / S), then owns the BN / S output columns starting at
+// r BN / S: every CTA pushes its fp32 partials of the columns it does not own into the owner's shared
+// memory (distributed shared memory), one cluster barrier, and the owner adds them in rank order.
+template <int BN, int S>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                                                __half* out, int m, int N, int K, float beta, int nstages, int* err) {
+                                                                __half* out, int m, int N, int K, float beta, int nstages, int a_box_rows,
+                                                                int* err) {
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
   // instruction descriptor: fp32 accumulate, fp16 x fp16, both K-major, N = BN, M = 128
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  constexpr int CW = BN / S;        // columns owned by each CTA of the cluster
+  constexpr int CPR = CW / 32;      // 32-column pieces per owner
+  constexpr uint32_t RED_BYTES = S > 1 ? (S - 1) * BM * CW * 4 : 0;
+  static_assert(CW % 32 == 0, "each CTA of a split-K cluster owns whole 32-column pieces");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms are 1024-byte aligned
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)nstages * STAGE);  // full[8], empty[8], tmem_full
+  const uint32_t red = base + (uint32_t)nstages * STAGE;  // [S-1 senders][CW/4][128 rows] float4
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)nstages * STAGE + RED_BYTES);  // full[8], empty[8], tmem_full
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-  const int nk = K / BK;
+  const int rank = S > 1 ? (int)cluster_ctarank() : 0;
+  const int n0 = (blockIdx.x / S) * BN, m0 = blockIdx.y * BM;
+  const int nk_all = K / BK;
+  const int kb0 = rank * nk_all / S, nk = (rank + 1) * nk_all / S - kb0;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < nstages; ++i) {
@@ -100,8 +141,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   }
   tc_fence_before();
   __syncthreads();
+  if (S > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");  // waited for before the first remote store
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  float own[S == 1 ? 1 : CPR][32];  // epilogue warps: this CTA's partial of the columns it owns
+  bool go = false;
 
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer
@@ -110,9 +155,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         if (use > 0 && !mbar_wait(smem_u32(&bars[8 + s]), (use - 1) & 1, err, DEV_ERR_EMPTY_WAIT)) break;
         const uint32_t full = smem_u32(&bars[s]);
         const uint32_t dst = base + (uint32_t)s * STAGE;
-        mbar_arrive_expect_tx(full, STAGE);
-        tma_load_2d(dst, &map_a, kb * BK, m0, full);
-        tma_load_2d(dst + A_BYTES, &map_b, kb * BK, n0, full);
+        // few rows: the activation box covers a_box_rows rows only; the rest of the 128-row operand keeps whatever
+        // shared memory held, which reaches output rows >= m only, and those are never stored
+        mbar_arrive_expect_tx(full, (uint32_t)a_box_rows * (BK * 2) + B_BYTES);
+        tma_load_2d(dst, &map_a, (kb0 + kb) * BK, m0, full);
+        tma_load_2d(dst + A_BYTES, &map_b, (kb0 + kb) * BK, n0, full);
       }
     }
   } else if (warp == 1) {
@@ -135,36 +182,57 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   } else {
     // ---- epilogue: warp w may touch TMEM lanes 32 * (w % 4) ... + 31 only
     const int quad = warp & 3;
-    const int row = m0 + quad * 32 + lane;
+    const int trow = quad * 32 + lane;  // row of the tile = TMEM lane
     const bool ok = mbar_wait(smem_u32(&bars[16]), 0, err, DEV_ERR_TMEM_WAIT);
     tc_fence_after();
-    if (__all_sync(0xffffffffu, ok && *(volatile int*)err == 0)) {  // warp-uniform: tcgen05.ld is .aligned
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+    go = __all_sync(0xffffffffu, ok && *(volatile int*)err == 0);  // warp-uniform: tcgen05.ld is .aligned
+    if (S > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // every CTA of the cluster is running
+    if (go) {
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        tc_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
+        tc_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < m) {
-          __half* o = out + (size_t)row * N + n0 + c;
-          uint4 v[4];
-          if (beta != 0.f) {
+        const int owner = c / CPR;
+        if (S == 1 || owner == rank) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) v[i] = reinterpret_cast<const uint4*>(o)[i];
+          for (int i = 0; i < 32; ++i) own[S == 1 ? 0 : c % CPR][i] = __uint_as_float(r[i]);
+          if (S == 1) {
+            if (m0 + trow < m) store_row_piece(out + (size_t)(m0 + trow) * N + n0 + c * 32, own[0], beta);
           }
-          __half2* h = reinterpret_cast<__half2*>(v);
+        } else {
+          // float4 number j4 of this row goes to ((j4 * 128 + row) * 16) so that a warp's stores are contiguous
+          const uint32_t slot = (uint32_t)(rank < owner ? rank : rank - 1);
+          const uint32_t dst = mapa(red + slot * (uint32_t)(BM * CW * 4), (uint32_t)owner);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float a0 = __uint_as_float(r[2 * i]), a1 = __uint_as_float(r[2 * i + 1]);
-            if (beta != 0.f) {
-              const float2 prev = __half22float2(h[i]);
-              a0 = fmaf(beta, prev.x, a0);
-              a1 = fmaf(beta, prev.y, a1);
-            }
-            h[i] = __floats2half2_rn(a0, a1);
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(o)[i] = v[i];
+          for (int j4 = 0; j4 < 8; ++j4)
+            st_dsmem_f4(dst + (uint32_t)((((c % CPR) * 8 + j4) * BM + trow) * 16), __uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]),
+                        __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
         }
+      }
+    }
+  }
+  if (S > 1) {
+    __syncwarp();
+    if (warp < 2) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // complete the start barrier (epilogue warps did already)
+    cluster_sync();  // all partials have landed in their owners' shared memory
+    if (warp >= 2 && go && *(volatile int*)err == 0) {
+      const int trow = (warp & 3) * 32 + lane;
+      const float4* part = reinterpret_cast<const float4*>(smem + (size_t)nstages * STAGE);
+#pragma unroll
+      for (int cc = 0; cc < CPR; ++cc) {
+#pragma unroll
+        for (int s = 0; s < S - 1; ++s) {  // senders in rank order
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 v = part[(size_t)s * (BM * CW / 4) + (cc * 8 + j4) * BM + trow];
+            own[cc][4 * j4] += v.x;
+            own[cc][4 * j4 + 1] += v.y;
+            own[cc][4 * j4 + 2] += v.z;
+            own[cc][4 * j4 + 3] += v.w;
+          }
+        }
+        if (m0 + trow < m) store_row_piece(out + (size_t)(m0 + trow) * N + n0 + rank * CW + cc * 32, own[cc], beta);
       }
     }
   }
@@ -174,6 +242,169 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Two-SM variant for more than 128 rows: a cluster of two CTAs owns a 256 x BN output tile
+// (tcgen05.mma.cta_group::2, M = 256).  Each CTA loads its own 128 activation rows and its own half of
+// the BN weight rows, so a stage costs each SM (128 + BN/2) x 128 bytes of L2 traffic for
+// 128 x BN x 64 multiply-adds - half of what the one-SM kernel needs, which is what bounds that kernel.
+// The pair is persistent: it walks the tile list with a stride of the number of clusters and keeps two
+// accumulators in tensor memory, so the epilogue of one tile runs under the main loop of the next.
+//
+// Barriers (all waits bounded):
+//   full[s]       leader CTA only; the leader's producer arrives with the byte count of both CTAs' boxes,
+//                 both producers' TMA loads complete on it (the peer addresses it through the cluster window)
+//   empty[s]      one per CTA; the leader's MMA thread commits to both (commit with a CTA mask)
+//   acc_full[b]   one per CTA; committed to both when a tile's last MMA has been issued
+//   acc_empty[b]  leader only, 8 arrivals: the four epilogue warps of both CTAs
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(cta_mask)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int BN>  // weight rows per pair tile: 128 or 256
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+    gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, __half* out, int m, int N, int K,
+                        float beta, int nstages, int tiles_m, int n_tiles, int* err) {
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE = A_BYTES + B_BYTES;
+  constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)nstages * STAGE);  // full[8] empty[8] acc_full[2] acc_empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int n_clusters = gridDim.x / 2, cluster_id = blockIdx.x / 2;
+  const int nk = K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < nstages; ++i) {
+      mbar_init(smem_u32(&bars[i]), 1);
+      mbar_init(smem_u32(&bars[8 + i]), 1);
+    }
+    mbar_init(smem_u32(&bars[16]), 1);
+    mbar_init(smem_u32(&bars[17]), 1);
+    mbar_init(smem_u32(&bars[18]), 8);
+    mbar_init(smem_u32(&bars[19]), 8);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer (both CTAs)
+      int it = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+        const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;
+        const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % nstages;
+          const uint32_t ph = (uint32_t)(it / nstages) & 1u;
+          ok = mbar_wait(smem_u32(&bars[8 + s]), ph ^ 1u, err, DEV_ERR_EMPTY_WAIT);
+          if (!ok) break;
+          const uint32_t full_leader = mapa(smem_u32(&bars[s]), 0);
+          const uint32_t dst = base + (uint32_t)s * STAGE;
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bars[s]), 2 * STAGE);
+          tma_load_2d_pair(dst, &map_a, kb * BK, m0, full_leader);
+          tma_load_2d_pair(dst + A_BYTES, &map_b, kb * BK, n0, full_leader);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {  // ---- MMA issuer (leader CTA only)
+      int it = 0, ti = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters, ++ti) {
+        const int b = ti & 1;
+        const uint32_t acc_ph = (uint32_t)(ti >> 1) & 1u;
+        ok = mbar_wait(smem_u32(&bars[18 + b]), acc_ph ^ 1u, err, DEV_ERR_TMEM_WAIT);  // both epilogues have drained buffer b
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % nstages;
+          const uint32_t ph = (uint32_t)(it / nstages) & 1u;
+          ok = mbar_wait(smem_u32(&bars[s]), ph, err, DEV_ERR_FULL_WAIT);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = base + (uint32_t)s * STAGE;
+          const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0);
+          tc_commit_pair(smem_u32(&bars[8 + s]), 3);  // frees the stage in both CTAs
+        }
+        tc_commit_pair(smem_u32(&bars[16 + b]), 3);  // accumulator b complete (also after a failed wait: lets the epilogues leave)
+      }
+    }
+  } else {
+    // ---- epilogue (both CTAs): warp w reads TMEM lanes 32 * (w % 4) ... + 31 of its own CTA
+    const int quad = warp & 3;
+    const uint32_t acc_empty_leader = mapa(smem_u32(&bars[18]), 0);
+    int ti = 0;
+    bool go = true;
+    for (int t = cluster_id; t < n_tiles && go; t += n_clusters, ++ti) {
+      const int b = ti & 1;
+      const uint32_t acc_ph = (uint32_t)(ti >> 1) & 1u;
+      const int row = (t % tiles_m) * (2 * BM) + (int)rank * BM + quad * 32 + lane;
+      const int n0 = (t / tiles_m) * BN;
+      const bool ok = mbar_wait(smem_u32(&bars[16 + b]), acc_ph, err, DEV_ERR_TMEM_WAIT);
+      tc_fence_after();
+      go = __all_sync(0xffffffffu, ok && *(volatile int*)err == 0);
+      if (!go) break;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tc_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN + c), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < m) {
+          float acc[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(r[i]);
+          store_row_piece(out + (size_t)row * N + n0 + c, acc, beta);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader + (uint32_t)(b * 8));  // buffer b may be overwritten
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync();  // nobody leaves while the other CTA's MMAs, loads or arrivals may still touch this CTA
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -194,8 +425,34 @@ int get_encoder(encode_fn* out) {
   return LCU_OK;
 }
 
-// [rows][K] halves, row-major; box = box_rows x 64 halves with 128-byte swizzle; rows past the end read as zero
+// [rows][K] halves, row-major; box = box_rows x 64 halves with 128-byte swizzle; rows past the end read as zero.
+// Encoded maps are kept (a map depends on address and shape only), so that a prompt's 7 products per layer
+// do not pay for two driver calls each.
+struct map_key {
+  const void* ptr;
+  uint64_t rows, K, ld;
+  uint32_t box_rows;
+  bool operator==(const map_key& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows; }
+};
+struct map_key_hash {
+  size_t operator()(const map_key& k) const {
+    uint64_t h = (uint64_t)(uintptr_t)k.ptr * 0x9e3779b97f4a7c15ull;
+    h ^= (k.rows + 0x632be59bd9b4e019ull) * 0xff51afd7ed558ccdull;
+    h ^= (k.K * 31 + k.ld * 17 + k.box_rows) * 0xc4ceb9fe1a85ec53ull;
+    return (size_t)(h ^ (h >> 29));
+  }
+};
+
 int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t K, uint64_t ld, uint32_t box_rows, bool streamed) {
+  static std::mutex mu;
+  static std::unordered_map<map_key, CUtensorMap, map_key_hash> cache;
+  const map_key key{ptr, rows, K, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *map = it->second;
+    return LCU_OK;
+  }
   encode_fn enc;
   int rc = get_encoder(&enc);
   if (rc) return rc;
@@ -208,30 +465,70 @@ int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t K, uint6
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   LCU_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (ptr %p rows %llu K %llu ld %llu)", (int)r, ptr,
               (unsigned long long)rows, (unsigned long long)K, (unsigned long long)ld);
+  if (cache.size() >= 8192) cache.clear();
+  cache.emplace(key, *map);
   return LCU_OK;
 }
 
-template <int BN>
+template <int BN, int S>
 int launch_bn(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream) {
   CUtensorMap map_a, map_b;
-  int rc = make_map(&map_a, lhs, (uint64_t)m, (uint64_t)K, (uint64_t)ldx, BM, false);
+  const int a_box_rows = m > 64 ? BM : m > 32 ? 64 : m > 16 ? 32 : 16;
+  int rc = make_map(&map_a, lhs, (uint64_t)m, (uint64_t)K, (uint64_t)ldx, a_box_rows, false);
   if (rc) return rc;
   rc = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN, true);
   if (rc) return rc;
   constexpr size_t STAGE = (size_t)(BM + BN) * BK * 2;
-  int nstages = (int)((200 * 1024) / STAGE);
+  constexpr size_t RED = S > 1 ? (size_t)(S - 1) * BM * (BN / S) * 4 : 0;
+  int nstages = (int)((200 * 1024 - RED) / STAGE);
   if (nstages > 8) nstages = 8;
   if (nstages > K / BK) nstages = K / BK;
+  const size_t smem = nstages * STAGE + RED + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
+  static bool attr_done[16] = {};
+  int dev = 0;
+  LCU_CUDA(cudaGetDevice(&dev));
+  if (dev < 16 && !attr_done[dev]) {
+    LCU_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_done[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N / BN) * S, (m + BM - 1) / BM);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = S > 1 ? 1 : 0;
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, S>, map_a, map_b, out, m, N, K, beta, nstages, a_box_rows, err));
+  return LCU_OK;
+}
+
+template <int BN>
+int launch_pair(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  int rc = make_map(&map_a, lhs, (uint64_t)m, (uint64_t)K, (uint64_t)ldx, BM, false);
+  if (rc) return rc;
+  rc = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN / 2, true);
+  if (rc) return rc;
+  constexpr size_t STAGE = (size_t)(BM + BN / 2) * BK * 2;
+  int nstages = (int)((200 * 1024) / STAGE);
+  if (nstages > 8) nstages = 8;
   const size_t smem = nstages * STAGE + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
   static bool attr_done[16] = {};
   int dev = 0;
   LCU_CUDA(cudaGetDevice(&dev));
   if (dev < 16 && !attr_done[dev]) {
-    LCU_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    LCU_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_done[dev] = true;
   }
-  const dim3 grid(N / BN, (m + BM - 1) / BM);
-  gemm_tc_kernel<BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, out, m, N, K, beta, nstages, err);
+  const int tiles_m = (m + 2 * BM - 1) / (2 * BM), n_tiles = tiles_m * (N / BN);
+  int clusters = gemv_sm_count() / 2;
+  if (clusters > n_tiles) clusters = n_tiles;
+  gemm_tc_pair_kernel<BN><<<2 * clusters, TC_THREADS, smem, stream>>>(map_a, map_b, out, m, N, K, beta, nstages, tiles_m, n_tiles, err);
   LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }
@@ -244,14 +541,40 @@ bool gemm_tc_supported(int m, int N, int K, int ldx, const void* lhs, const void
 }
 
 int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream,
-                   int force_bn) {
+                   int force_bn, int force_pair, int force_split) {
   LCU_REQUIRE(gemm_tc_supported(m, N, K, ldx, lhs, w, out), "gemm_tc: unsupported shape m=%d N=%d K=%d ldx=%d or unaligned pointers", m, N, K, ldx);
+  const int sms = gemv_sm_count();
+  // Large products: the two-SM kernel, with its 256-wide tile when that still gives (nearly) every SM pair a tile.
+  // Up to 256 rows of a matrix with few tiles stay on the one-SM kernel, which can split K to fill the SMs.
+  int pair = force_pair;
+  if (pair < 0) {
+    pair = 0;
+    if (m > BM && N % 128 == 0 && !force_bn && (m > 2 * BM || N > 8192)) {
+      const long tiles_m = (m + 2 * BM - 1) / (2 * BM), clusters = sms / 2;
+      pair = (N % 256 == 0 && tiles_m * (N / 256) * 4 >= clusters * 3) ? 256 : 128;
+    }
+  }
+  if (pair) {
+    LCU_REQUIRE((pair == 128 || pair == 256) && N % pair == 0, "gemm_tc: pair tile width %d does not divide N=%d", pair, N);
+    return pair == 256 ? launch_pair<256>(out, lhs, ldx, w, m, N, K, beta, err, stream) : launch_pair<128>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+  }
   int bn = force_bn;
   if (!bn) bn = N % 128 == 0 ? 128 : N % 64 == 0 ? 64 : 32;  // measured: the widest tile wins even when it leaves SMs idle
   LCU_REQUIRE((bn == 32 || bn == 64 || bn == 128) && N % bn == 0, "gemm_tc: tile width %d does not divide N=%d", bn, N);
-  if (bn == 128) return launch_bn<128>(out, lhs, ldx, w, m, N, K, beta, err, stream);
-  if (bn == 64) return launch_bn<64>(out, lhs, ldx, w, m, N, K, beta, err, stream);
-  return launch_bn<32>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+  if (bn == 128) {
+    int split = force_split;
+    if (split < 0) {
+      const long tiles = (long)(N / 128) * ((m + BM - 1) / BM);
+      split = tiles * 4 <= sms ? 4 : tiles * 2 <= sms ? 2 : 1;
+    }
+    if (K / BK < 8 * split) split = 1;  // every CTA of the cluster needs k-blocks of its own
+    LCU_REQUIRE(split == 1 || split == 2 || split == 4, "gemm_tc: split-K factor %d is not 1, 2 or 4", split);
+    if (split == 4) return launch_bn<128, 4>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+    if (split == 2) return launch_bn<128, 2>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+    return launch_bn<128, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+  }
+  if (bn == 64) return launch_bn<64, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+  return launch_bn<32, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
 }
 
 }  // namespace lcu

@@ -243,6 +243,24 @@ __global__ void __launch_bounds__(256) dequantize_kernel(__half* out, const __ha
   *reinterpret_cast<__half2*>(out + i4 + 2) = hi;
 }
 
+// same, 16 weights per thread (one 16-byte load, two 16-byte stores); needs bs % 16 == 0
+__global__ void __launch_bounds__(256) dequantize16_kernel(__half* out, const __half* scales, const uint8_t* q, size_t n, int bs) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 16;
+  if (i >= n) return;
+  const uint4 v = *reinterpret_cast<const uint4*>(q + i);
+  const float s = __half2float(scales[i / bs]);
+  const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+  __align__(16) __half2 o[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t u = wds[j];
+    o[2 * j] = __halves2half2(__float2half((float(u & 0xff) - 127.5f) * s), __float2half((float((u >> 8) & 0xff) - 127.5f) * s));
+    o[2 * j + 1] = __halves2half2(__float2half((float((u >> 16) & 0xff) - 127.5f) * s), __float2half((float(u >> 24) - 127.5f) * s));
+  }
+  reinterpret_cast<uint4*>(out + i)[0] = reinterpret_cast<const uint4*>(o)[0];
+  reinterpret_cast<uint4*>(out + i)[1] = reinterpret_cast<const uint4*>(o)[1];
+}
+
 // error statistics (transform.cu:100-150) with a fixed-order two-stage reduction instead of float atomics
 __global__ void __launch_bounds__(256) error_partial_kernel(float* partial, const __half* a, const __half* b, size_t n) {
   __shared__ float s_sq[8], s_mx[8], s_ab[8];
@@ -419,7 +437,10 @@ int launch_dequantize_absmax_uint8(__half* out, const __half* scales, const uint
   LCU_REQUIRE(bs > 0 && bs % 4 == 0 && w % bs == 0, "dequantize: block size %d must be a multiple of 4 that divides the row length %zu", bs, w);
   const size_t n = h * w;
   if (n == 0) return LCU_OK;
-  dequantize_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(out, scales, q, n, bs);
+  if (bs % 16 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0)
+    dequantize16_kernel<<<(unsigned)((n / 16 + 255) / 256), 256, 0, stream>>>(out, scales, q, n, bs);
+  else
+    dequantize_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(out, scales, q, n, bs);
   LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }

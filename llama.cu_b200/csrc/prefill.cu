@@ -3,6 +3,7 @@
 
 #include "gemm_tc.cuh"
 #include "gemv.cuh"
+#include "ops.cuh"
 
 namespace lcu {
 
@@ -11,11 +12,18 @@ prefill_tuning& prefill_tuning_ref() {
   return t;
 }
 
-int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, float beta, int* err, cudaStream_t stream) {
+int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, float beta, int* err, cudaStream_t stream, __half* deq,
+                size_t deq_halves) {
   const int K = (int)w.cols, N = (int)w.rows;
   const prefill_tuning& pt = prefill_tuning_ref();
   if (w.bs == 0 && pt.tc_min_rows > 0 && m >= pt.tc_min_rows && gemm_tc_supported(m, N, K, K, lhs, w.w, out))
-    return launch_gemm_tc(out, lhs, K, (const __half*)w.w, m, N, K, beta, err, stream, pt.tc_tile_n);
+    return launch_gemm_tc(out, lhs, K, (const __half*)w.w, m, N, K, beta, err, stream, pt.tc_tile_n, pt.tc_pair, pt.tc_split);
+  if (w.bs > 0 && deq && pt.u8_deq_min_rows > 0 && m >= pt.u8_deq_min_rows && (size_t)N * K <= deq_halves &&
+      gemm_tc_supported(m, N, K, K, lhs, deq, out)) {
+    int rc = launch_dequantize_absmax_uint8(deq, w.sc, (const uint8_t*)w.w, (size_t)N, (size_t)K, w.bs, stream);
+    if (rc) return rc;
+    return launch_gemm_tc(out, lhs, K, deq, m, N, K, beta, err, stream, pt.tc_tile_n, pt.tc_pair, pt.tc_split);
+  }
   for (int t = 0; t < m; t += 8) {
     gemv_params p{};
     p.w[0] = w.w;

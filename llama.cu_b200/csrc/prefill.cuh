@@ -7,13 +7,20 @@ namespace lcu {
 
 struct prefill_tuning {
   int tc_min_rows = 9;  // fp16 weights: this many rows or more go to the tcgen05 GEMM (0 = never)
-  int tc_tile_n = 0;    // 0 = pick the tile width per shape; 32 / 64 / 128 forces it
+  int tc_tile_n = 0;    // one-SM kernel: 0 = pick the tile width per shape; 32 / 64 / 128 forces it
+  int u8_deq_min_rows = 48;  // u8 weights: this many rows or more are worth a dequantization pass (0 = never)
+  int tc_split = -1;    // one-SM kernel: -1 = split K over 2 / 4 CTAs when tiles are few, 1 / 2 / 4 = always that factor
+  int tc_pair = -1;     // two-SM kernel: -1 = when m > 128, 0 = never, 128 / 256 = always with that tile width
 };
 prefill_tuning& prefill_tuning_ref();
 
 // Dispatch: fp16 weights with more than 8 rows go to the tcgen05 GEMM (gemm_tc.cu); up to 8 rows, and
 // u8 weights in passes of 8 rows, go through the weight-streaming GEMV.
 // lhs and out are dense row-major ([m][K], [m][N]); err is the device error word.
-int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, float beta, int* err, cudaStream_t stream);
+// deq / deq_halves: scratch for one dequantized matrix; with it, u8 weights and at least u8_deq_min_rows rows are
+// expanded to fp16 (the values the reference's tile kernel builds in shared memory, llama_cu.cu:222-300) and
+// go through the tcgen05 GEMM as well.
+int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, float beta, int* err, cudaStream_t stream, __half* deq = nullptr,
+                size_t deq_halves = 0);
 
 }  // namespace lcu

@@ -284,6 +284,8 @@ struct gpu_state {
   size_t arena_bytes = 0;
   __half *x = nullptr, *norm = nullptr, *q = nullptr, *kn = nullptr, *vn = nullptr, *att = nullptr;
   __half *h1 = nullptr, *h3 = nullptr, *hs = nullptr;
+  __half* deq = nullptr;  // u8 models: one dequantized [ffn][dim] matrix for the prompt GEMM
+  size_t deq_halves = 0;
   float2* rope = nullptr;
   int* state = nullptr;  // [0] position, [1] step counter, [2] last token, [3] error word
 };
@@ -393,6 +395,8 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     const size_t o_x = cv.take(ctxl * d * 2), o_norm = cv.take(ctxl * d * 2), o_q = cv.take(ctxl * d * 2);
     const size_t o_kn = cv.take(ctxl * d * 2), o_vn = cv.take(ctxl * d * 2), o_att = cv.take(ctxl * d * 2);
     const size_t o_h1 = cv.take(ctxl * f * 2), o_h3 = cv.take(ctxl * f * 2), o_hs = cv.take(ctxl * f * 2);
+    const size_t deq_halves = p.q_type ? (size_t)f * d : 0;
+    const size_t o_deq = cv.take(deq_halves * 2);
     const size_t o_rope = cv.take(ctxl * (hd / 2) * sizeof(float2));
     const size_t o_state = cv.take(64);
     const size_t o_ids = cv.take(ctxl * 2), o_log = cv.take(ctxl * 2);
@@ -410,6 +414,8 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     g.h1 = (__half*)(b + o_h1);
     g.h3 = (__half*)(b + o_h3);
     g.hs = (__half*)(b + o_hs);
+    g.deq = deq_halves ? (__half*)(b + o_deq) : nullptr;
+    g.deq_halves = deq_halves;
     g.rope = (float2*)(b + o_rope);
     g.state = (int*)(b + o_state);
     if (gi == 0) c.ids = (short*)(b + o_ids);
@@ -640,9 +646,9 @@ int context_impl::enqueue_prefill(int m_rows) {
     const layer_weights& L = m->layers[l];
     int* err = g.state + 3;
     LCU_TRY(launch_rms_norm(g.norm, g.x, L.attn_norm, m_rows, d, p.norm_eps, g.stream));
-    LCU_TRY(matmul_rows(g.q, g.norm, L.wq, m_rows, 0.f, err, g.stream));
-    LCU_TRY(matmul_rows(g.kn, g.norm, L.wk, m_rows, 0.f, err, g.stream));
-    LCU_TRY(matmul_rows(g.vn, g.norm, L.wv, m_rows, 0.f, err, g.stream));
+    LCU_TRY(matmul_rows(g.q, g.norm, L.wq, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
+    LCU_TRY(matmul_rows(g.kn, g.norm, L.wk, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
+    LCU_TRY(matmul_rows(g.vn, g.norm, L.wv, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
     LCU_TRY(launch_rope_scatter(g.q, g.kn, g.vn, k_cache[l], v_cache[l], g.rope, g.state, 0, m_rows, d, p.n_heads, opt.context_len, g.stream));
     attn_params at{};
     at.q = g.q; at.ldq = d;
@@ -651,12 +657,12 @@ int context_impl::enqueue_prefill(int m_rows) {
     at.pos = g.state;
     at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd;
     LCU_TRY(launch_attention(at, m_rows, 1, start_pos + m_rows, g.stream, 0));
-    LCU_TRY(matmul_rows(g.x, g.att, L.wo, m_rows, 1.0f, err, g.stream));
+    LCU_TRY(matmul_rows(g.x, g.att, L.wo, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
     LCU_TRY(launch_rms_norm(g.norm, g.x, L.ffn_norm, m_rows, d, p.norm_eps, g.stream));
-    LCU_TRY(matmul_rows(g.h1, g.norm, L.w1, m_rows, 0.f, err, g.stream));
-    LCU_TRY(matmul_rows(g.h3, g.norm, L.w3, m_rows, 0.f, err, g.stream));
+    LCU_TRY(matmul_rows(g.h1, g.norm, L.w1, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
+    LCU_TRY(matmul_rows(g.h3, g.norm, L.w3, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
     LCU_TRY(launch_silu(g.hs, g.h1, g.h3, (size_t)m_rows * f, g.stream));
-    LCU_TRY(matmul_rows(g.x, g.hs, L.w2, m_rows, 1.0f, err, g.stream));
+    LCU_TRY(matmul_rows(g.x, g.hs, L.w2, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
   }
   {
     gpu_state& g = last();
