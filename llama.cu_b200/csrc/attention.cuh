@@ -23,4 +23,7 @@ struct attn_params {
 // shared memory can be sized without reading the device position.
 int launch_attention(const attn_params& p, int m, int cluster, int max_T, cudaStream_t stream, int pdl);
 
+// Prompt rows: 64-row query tiles on tensor cores (attention_prefill.cu); same arithmetic, no clusters.
+int launch_attention_prefill(const attn_params& p, int m, int max_T, cudaStream_t stream);
+
 }  // namespace lcu

@@ -656,7 +656,10 @@ int context_impl::enqueue_prefill(int m_rows) {
     at.out = g.att; at.ldo = d;
     at.pos = g.state;
     at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd;
-    LCU_TRY(launch_attention(at, m_rows, 1, start_pos + m_rows, g.stream, 0));
+    if (prefill_tuning_ref().attn_tiles)
+      LCU_TRY(launch_attention_prefill(at, m_rows, start_pos + m_rows, g.stream));
+    else
+      LCU_TRY(launch_attention(at, m_rows, 1, start_pos + m_rows, g.stream, 0));
     LCU_TRY(matmul_rows(g.x, g.att, L.wo, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
     LCU_TRY(launch_rms_norm(g.norm, g.x, L.ffn_norm, m_rows, d, p.norm_eps, g.stream));
     LCU_TRY(matmul_rows(g.h1, g.norm, L.w1, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));

@@ -194,7 +194,9 @@ def test_rope_scatter(lcu):
 
 
 @pytest.mark.parametrize("m,T0,H,cluster", [(1, 0, 2, 1), (1, 1, 2, 8), (1, 37, 2, 4), (1, 383, 4, 8), (1, 2047, 2, 8), (7, 5, 2, 1),
-                                            (16, 0, 3, 1), (1, 100, 2, 2)])
+                                            (16, 0, 3, 1), (1, 100, 2, 2),
+                                            # cluster 0 = the prompt kernel (64-row query tiles on tensor cores)
+                                            (7, 5, 2, 0), (64, 0, 2, 0), (65, 37, 1, 0), (200, 0, 2, 0), (130, 300, 2, 0), (1, 77, 2, 0)])
 def test_attention_against_oracle(lcu, m, T0, H, cluster):
     rng = np.random.default_rng(T0 + m)
     dim = H * 128
@@ -214,12 +216,13 @@ def test_attention_against_oracle(lcu, m, T0, H, cluster):
         assert np.abs(f32(out) - f32(orf)).max() <= 4e-3
 
 
-def test_attention_head_dim_64(lcu):
+@pytest.mark.parametrize("m,T0,cluster", [(1, 50, 4), (70, 9, 0)])
+def test_attention_head_dim_64(lcu, m, T0, cluster):
     rng = np.random.default_rng(8)
-    m, T0, H, dim = 1, 50, 4, 256
+    H, dim = 4, 256
     T = T0 + m
     q, k, v = f16(rng.standard_normal((m, dim))), f16(rng.standard_normal((T, dim))), f16(rng.standard_normal((T, dim)))
-    out = lcu.attention(q, k, v, H, T0, 4)
+    out = lcu.attention(q, k, v, H, T0, cluster)
     oo = np.zeros_like(q)
     L.orc_attention(oo.reshape(-1), q.reshape(-1), k.reshape(-1), v.reshape(-1), m, T, dim, H, T0, 0)
     assert np.abs(f32(out) - f32(oo)).max() <= 4e-3
