@@ -30,6 +30,16 @@ __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// x / d from r = RN(1 / d): one multiplication and one residual correction.  This is the core of the correctly
+// rounded division sequence without its special-case handling (operands here are finite, d >= 1): it returns
+// RN(x / d) in all but vanishingly rare double-rounding cases, at a third of the instructions.
+__device__ __forceinline__ float div_by(float x, float d, float r) {
+  const float q = x * r;
+  return fmaf(fmaf(-q, d, x), r, q);
+}
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   const __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -50,7 +60,7 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_kernel(const attn_par
   const int ntiles = (nkeys + PA_KT - 1) / PA_KT;
   const __half* kb = p.k_cache + (size_t)head * p.ctx_len * HD;
   const __half* vb = p.v_cache + (size_t)head * p.ctx_len * HD;
-  const float scale_div = sqrtf((float)HD);
+  const float scale_div = sqrtf((float)HD), scale_rcp = __frcp_rn(scale_div);
 
   // Q fragments (A operand, 16 rows x HD per warp): rows g and g + 8 of the warp's block
   const int r_lo = q0 + warp * 16 + g, r_hi = r_lo + 8;
@@ -66,6 +76,7 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_kernel(const attn_par
     qa[ks][3] = r_hi < m ? *reinterpret_cast<const uint32_t*>(qh + 8) : 0u;
   }
   const int last_lo = start_pos + r_lo, last_hi = start_pos + r_hi;  // last key each row may see
+  const int warp_last = start_pos + q0 + warp * 16 + 15;
 
   auto stage_tile = [&](int tile, int stage, bool with_v) {
     __half* ks = pa_smem + (size_t)stage * 2 * TILE;
@@ -86,21 +97,23 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_kernel(const attn_par
 #pragma unroll
     for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
+    for (int kk = 0; kk < HD / 16; kk += 2) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const __half* kr = ks + (j * 8 + g) * LDS + kk * 16 + 2 * c;
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr), b1 = *reinterpret_cast<const uint32_t*>(kr + 8);
+        // four 8x8 blocks of keys 8j .. 8j+7: d = 16kk, 16kk + 8, 16kk + 16, 16kk + 24
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(smem_u32(ks + (j * 8 + (lane & 7)) * LDS + kk * 16 + (lane >> 3) * 8), b0, b1, b2, b3);
         mma_16816(s[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
+        mma_16816(s[j], qa[kk + 1][0], qa[kk + 1][1], qa[kk + 1][2], qa[kk + 1][3], b2, b3);
       }
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int t = t0 + j * 8 + 2 * c;
-      s[j][0] = t <= last_lo ? __half2float(__float2half(s[j][0] / scale_div)) : -CUDART_INF_F;
-      s[j][1] = t + 1 <= last_lo ? __half2float(__float2half(s[j][1] / scale_div)) : -CUDART_INF_F;
-      s[j][2] = t <= last_hi ? __half2float(__float2half(s[j][2] / scale_div)) : -CUDART_INF_F;
-      s[j][3] = t + 1 <= last_hi ? __half2float(__float2half(s[j][3] / scale_div)) : -CUDART_INF_F;
+      s[j][0] = t <= last_lo ? __half2float(__float2half(div_by(s[j][0], scale_div, scale_rcp))) : -CUDART_INF_F;
+      s[j][1] = t + 1 <= last_lo ? __half2float(__float2half(div_by(s[j][1], scale_div, scale_rcp))) : -CUDART_INF_F;
+      s[j][2] = t <= last_hi ? __half2float(__float2half(div_by(s[j][2], scale_div, scale_rcp))) : -CUDART_INF_F;
+      s[j][3] = t + 1 <= last_hi ? __half2float(__float2half(div_by(s[j][3], scale_div, scale_rcp))) : -CUDART_INF_F;
     }
   };
 
@@ -115,6 +128,10 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_kernel(const attn_par
       cp_async_wait<0>();
     }
     __syncthreads();
+    if (tile * PA_KT > warp_last) {  // every key of the tile lies in the future of all 16 rows of this warp
+      __syncthreads();
+      continue;
+    }
     float s[8][4];
     score_tile(pa_smem + (size_t)(tile & 1) * 2 * TILE, tile * PA_KT, s);
     float tm_lo = -CUDART_INF_F, tm_hi = -CUDART_INF_F;
@@ -146,6 +163,7 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_kernel(const attn_par
   }
 
   // ---- pass 2: probabilities (half) times V
+  const float rs_lo = __frcp_rn(sum_lo), rs_hi = __frcp_rn(sum_hi);
   float o[HD / 8][4];
 #pragma unroll
   for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -158,6 +176,10 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_kernel(const attn_par
       cp_async_wait<0>();
     }
     __syncthreads();
+    if (tile * PA_KT > warp_last) {
+      __syncthreads();
+      continue;
+    }
     const __half* ks = pa_smem + (size_t)(tile & 1) * 2 * TILE;
     const __half* vs = ks + TILE;
     float s[8][4];
@@ -166,10 +188,10 @@ __global__ void __launch_bounds__(PA_THREADS) attn_prefill_kernel(const attn_par
     uint32_t pa[4][4];  // A fragments of the 16 x 64 probability block, 16 keys each
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-      pa[kk][0] = pack_half2(expf(s[2 * kk][0] - mx_lo) / sum_lo, expf(s[2 * kk][1] - mx_lo) / sum_lo);
-      pa[kk][1] = pack_half2(expf(s[2 * kk][2] - mx_hi) / sum_hi, expf(s[2 * kk][3] - mx_hi) / sum_hi);
-      pa[kk][2] = pack_half2(expf(s[2 * kk + 1][0] - mx_lo) / sum_lo, expf(s[2 * kk + 1][1] - mx_lo) / sum_lo);
-      pa[kk][3] = pack_half2(expf(s[2 * kk + 1][2] - mx_hi) / sum_hi, expf(s[2 * kk + 1][3] - mx_hi) / sum_hi);
+      pa[kk][0] = pack_half2(div_by(expf(s[2 * kk][0] - mx_lo), sum_lo, rs_lo), div_by(expf(s[2 * kk][1] - mx_lo), sum_lo, rs_lo));
+      pa[kk][1] = pack_half2(div_by(expf(s[2 * kk][2] - mx_hi), sum_hi, rs_hi), div_by(expf(s[2 * kk][3] - mx_hi), sum_hi, rs_hi));
+      pa[kk][2] = pack_half2(div_by(expf(s[2 * kk + 1][0] - mx_lo), sum_lo, rs_lo), div_by(expf(s[2 * kk + 1][1] - mx_lo), sum_lo, rs_lo));
+      pa[kk][3] = pack_half2(div_by(expf(s[2 * kk + 1][2] - mx_hi), sum_hi, rs_hi), div_by(expf(s[2 * kk + 1][3] - mx_hi), sum_hi, rs_hi));
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
