@@ -99,7 +99,8 @@ int lcu_synth_fill_f16(void* out_dev, uint64_t n, uint64_t seed, const char* nam
 /* ---- model (llama_model, llama_cu.h:362-372) -------------------------------------------------- */
 /* params40: the 40-byte params record (llama_cu.h:280-291).  layer_gpus: n_layers device indices
  * (llama_partition::layer_gpus, llama_cu.h:301-314; embedding on the first, output on the last),
- * NULL = every layer on device 0 (llama_partition::use_default, llama_cu.cu:810-818). */
+ * NULL = every layer on the calling thread's current device (lcu_set_device; device 0 unless changed, which is
+ * llama_partition::use_default, llama_cu.cu:810-818). */
 int lcu_model_create(const void* params40, const int* layer_gpus, void** model_out);
 /* llama_model::load, llama_cu.cu:987-997: reads <dir>/params and the tensor files (llama_cu.cu:929-984) */
 int lcu_model_load(const char* dir, const int* layer_gpus, void** model_out);

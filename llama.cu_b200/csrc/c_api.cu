@@ -38,7 +38,9 @@ int require_device() {
 
 partition make_partition(const model_params& p, const int* layer_gpus) {
   partition part;
-  for (uint32_t i = 0; i < p.n_layers; ++i) part.layer_gpus.push_back(layer_gpus ? layer_gpus[i] : 0);
+  int cur = 0;
+  cudaGetDevice(&cur);  // no partition given: everything on the calling thread's current device
+  for (uint32_t i = 0; i < p.n_layers; ++i) part.layer_gpus.push_back(layer_gpus ? layer_gpus[i] : cur);
   return part;
 }
 

@@ -295,6 +295,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
           __half* o = p.out + (size_t)col * p.ldo + vrow;
           if (p.beta != 0.f) sum = sum + p.beta * __half2float(*o);
           *o = __float2half(sum);
+          if (p.out_peer) p.out_peer[(size_t)col * p.ldo + vrow] = __float2half(sum);
         }
       }
     } else if (ct < RB / 2) {

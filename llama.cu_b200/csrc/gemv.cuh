@@ -29,6 +29,7 @@ struct gemv_params {
   __half* out;
   int ldo;
   float beta;
+  __half* out_peer;     // EPI_PLAIN, optional: the same values are also stored here (another GPU's buffer: the pipeline hop)
   // EPI_ROPE_KV
   const int* pos;       // device scalar: position of the token being decoded
   __half* q_out;        // [dim]

@@ -333,7 +333,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
           a0 = a0 + p.beta * __half2float(o[0]);
           a1 = a1 + p.beta * __half2float(o[1]);
         }
-        *reinterpret_cast<__half2*>(o) = __halves2half2(__float2half(a0), __float2half(a1));
+        const __half2 r2 = __halves2half2(__float2half(a0), __float2half(a1));
+        *reinterpret_cast<__half2*>(o) = r2;
+        if (p.out_peer) *reinterpret_cast<__half2*>(p.out_peer + vrow) = r2;  // peer store over NVLink
       } else {
         const __half a = __float2half(v0), bq = __float2half(v1);  // the matmul's own output rounding
         if (EPI == EPI_SILU) {

@@ -550,6 +550,8 @@ gemv_params context_impl::params_w2(int l) {
   gemv_params a = params_base(g, f);
   a.w[0] = L.w2.w; a.sc[0] = L.w2.sc; a.n_mats = 1; a.rows_per_mat = d;
   a.x = g.hs; a.out = g.x; a.ldo = d; a.beta = 1.0f;
+  // last layer of a pipeline stage: the residual row is also written straight into the next stage's buffer
+  if (l + 1 < (int)m->params.n_layers && layer_slot[l + 1] != layer_slot[l]) a.out_peer = gpus[layer_slot[l + 1]].x;
   return a;
 }
 gemv_params context_impl::params_out(int row) {
@@ -580,7 +582,9 @@ int context_impl::enqueue_decode_step() {
         device_guard dgp(prev.device);
         LCU_TRY(launch_bump_pos(prev.state, 1, prev.stream));
       }
-      LCU_TRY(enqueue_hop(layer_slot[l - 1], gi, 1));
+      // the row itself arrived with the previous layer's w2 kernel (peer stores); only the ordering is left
+      LCU_CUDA(cudaEventRecord(prev.ev, prev.stream));
+      LCU_CUDA(cudaStreamWaitEvent(gpus[gi].stream, prev.ev, 0));
       hopped = true;
     }
     gpu_state& g = gpus[gi];
