@@ -35,7 +35,10 @@ constexpr int SEG = ROWB / 8;               // 512-byte segments
 constexpr int NSTEPS = SEG / 64;            // 64-byte steps per segment
 constexpr int MAX_SW = 4;                   // ring depth per warp
 constexpr int NACC = 4;                     // independent accumulator sets (no chain on one result)
-constexpr int SC_BYTES_ROW = 256;           // scale bytes reserved per row per stage: 4096 / 32 * 2
+// scale bytes reserved per row per stage: 4096 / 32 * 2 for the smallest block size; the factored mode needs
+// block sizes of 64 or more, and its smaller stage lets three CTAs share an SM
+template <int WT>
+__host__ __device__ constexpr int sc_bytes_row() { return WT == 2 ? 128 : 256; }
 constexpr int SMEM_FIXED = 256 + 64;        // barriers: full[NW][MAX_SW], empty[NW][MAX_SW]; scratch
 
 template <int EPI>
@@ -92,7 +95,7 @@ __device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const 
       const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
       const int si = (g * SEG + off) >> bs;  // k offset inside the chunk / block size (bs is log2 of it here)
       sc_lo = scs[si];
-      sc_hi = scs[SC_BYTES_ROW / 2 + si];
+      sc_hi = scs[sc_bytes_row<WT>() / 2 + si];
       // WT 2: sum of x over this lane's segment and step (the diagonal column of the tile)
       if (WT == 2) corr = 1151.5f * xs64[ci * (CHUNK_K / 64) + g * NSTEPS + (s ^ flip)];
     }
@@ -130,10 +133,10 @@ __device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const 
 // 1024 + q (one PRMT per two weights) and the group sums of x coming from the prologue.  Mode 2 has
 // no per-weight rounding: it is closer to the exact product but is not the reference's rounding.
 template <int WT, int EPI>
-__global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p, const int sw, const int pf_bytes) {
+__global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p, const int sw, const int pf_bytes) {
   constexpr int ESZ = WT == 0 ? 2 : 1;
   constexpr int CHUNK_K = ROWB / ESZ;        // weights of one row per stage: 2048 fp16, 4096 u8
-  constexpr int STAGE_BYTES = 2 * ROWB + (WT ? 2 * SC_BYTES_ROW : 0);
+  constexpr int STAGE_BYTES = 2 * ROWB + (WT ? 2 * sc_bytes_row<WT>() : 0);
 
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [16 + w * MAX_SW + s]
@@ -212,7 +215,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
           if (WT != 0) {
             const int ppr = (cbytes / p.bs) >> 1;  // 4-byte pieces per row
             const __half* src = src_sc[w] + (ci * CHUNK_K) / p.bs;
-            for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * SC_BYTES_ROW + j * 4), src + 2 * j);
+            for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * sc_bytes_row<WT>() + j * 4), src + 2 * j);
             cp_async_mbar_arrive_noinc(full);
           }
           if (++slot[w] == sw) {
@@ -227,10 +230,29 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
   }
 
   // -------------------------------------------------------------- consumers
+  // The norm weights do not depend on the previous kernel: their loads are in flight while this one waits for it.
+  constexpr int NVEC = 4;  // 16-byte vectors per thread kept in registers (covers K <= 4096)
+  const int vec = p.K >> 3;
+  uint4 nw[NVEC];
+  if (p.norm_w != nullptr && npairs > 0) {
+#pragma unroll
+    for (int j = 0; j < NVEC; ++j) {
+      const int i = tid + j * NCONS;
+      nw[j] = i < vec ? *reinterpret_cast<const uint4*>(p.norm_w + i * 8) : make_uint4(0, 0, 0, 0);
+    }
+  }
   pdl_wait();
   if (npairs > 0) {
-    const int vec = p.K >> 3;
-    for (int i = tid; i < vec; i += NCONS) *reinterpret_cast<uint4*>(xs + i * 16) = *reinterpret_cast<const uint4*>(p.x + i * 8);
+    uint4 xv[NVEC];
+#pragma unroll
+    for (int j = 0; j < NVEC; ++j) {
+      const int i = tid + j * NCONS;
+      if (i < vec) {
+        xv[j] = *reinterpret_cast<const uint4*>(p.x + i * 8);
+        *reinterpret_cast<uint4*>(xs + i * 16) = xv[j];
+      }
+    }
+    for (int i = tid + NVEC * NCONS; i < vec; i += NCONS) *reinterpret_cast<uint4*>(xs + i * 16) = *reinterpret_cast<const uint4*>(p.x + i * 8);
     bar_sync(1, NCONS);
     if (p.norm_w != nullptr) {
       // RMSNorm with the reference's summation order (llama_cu.cu:72-106): 256 strided partial sums,
@@ -253,24 +275,43 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv1_kernel(const gemv_params p,
         scratch[warp + 4] = s1;
       }
       bar_sync(1, NCONS);
-      if (warp == 0) {
-        float t = lane < 8 ? scratch[lane] : 0.f;
-        for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        if (lane == 0) scratch[8] = rsqrtf(t / p.K + p.eps);
+      float t = lane < 8 ? scratch[lane] : 0.f;  // every warp repeats the last tree: no second hand-over
+      for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      const float rinv = rsqrtf(__shfl_sync(0xffffffffu, t, 0) / p.K + p.eps);
+      // x_i <- norm_w_i *h half(x_i * rinv), eight elements at a time from the registers filled above
+      auto norm8 = [&](uint4 xq, uint4 wq) {
+        __half2* xq2 = reinterpret_cast<__half2*>(&xq);
+        const __half2* wq2 = reinterpret_cast<const __half2*>(&wq);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(xq2[e]);
+          xq2[e] = __hmul2(wq2[e], __floats2half2_rn(f.x * rinv, f.y * rinv));
+        }
+        return xq;
+      };
+#pragma unroll
+      for (int j = 0; j < NVEC; ++j) {
+        const int i = tid + j * NCONS;
+        if (i < vec) *reinterpret_cast<uint4*>(xs + i * 16) = norm8(xv[j], nw[j]);
       }
-      bar_sync(1, NCONS);
-      const float rinv = scratch[8];
-      for (int i = tid; i < p.K; i += NCONS) {
-        float v = __half2float(xh[i]);
-        xh[i] = __hmul(p.norm_w[i], __float2half(v * rinv));
-      }
+      for (int i = tid + NVEC * NCONS; i < vec; i += NCONS)
+        *reinterpret_cast<uint4*>(xs + i * 16) = norm8(*reinterpret_cast<const uint4*>(xs + i * 16), *reinterpret_cast<const uint4*>(p.norm_w + i * 8));
       bar_sync(1, NCONS);
     }
-    if (WT == 2) {  // group sums of the (normalised) activations: one warp per group of 64, two halves per lane
-      for (int grp64 = warp; grp64 < p.K / 64; grp64 += NW) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(xs + grp64 * 128 + lane * 4));
-        const float s = warp_sum(f.x + f.y);
-        if (lane == 0) xs64[grp64] = s;
+    if (WT == 2) {  // sums of the (normalised) activations over aligned groups of 64: eight lanes per group, 16 bytes per lane
+      for (int grp64 = warp * 4 + (lane >> 3); grp64 < p.K / 64; grp64 += NW * 4) {
+        const uint4 q = *reinterpret_cast<const uint4*>(xs + grp64 * 128 + (lane & 7) * 16);
+        const __half2* h = reinterpret_cast<const __half2*>(&q);
+        float s = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(h[e]);
+          s += f.x + f.y;
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if ((lane & 7) == 0) xs64[grp64] = s;
       }
       bar_sync(1, NCONS);
     }
@@ -435,22 +476,23 @@ int launch_gemv_prefetch(const gemv_params& p, int epilogue, int sms, int kb_per
 int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl, int sms) {
   const gemv_tuning& t = gemv_tuning_ref();
   const bool q = p.bs != 0;
-  const size_t stage_bytes = 2 * ROWB + (q ? 2 * SC_BYTES_ROW : 0);
-  int sw = t.warp_stages < 2 ? 2 : (t.warp_stages > MAX_SW ? MAX_SW : t.warp_stages);
-  size_t smem = SMEM_FIXED + (((size_t)p.K * 2 + 127) & ~(size_t)127) + (((size_t)p.K / 64 * 4 + 127) & ~(size_t)127) +
-                (size_t)NW * sw * stage_bytes;
-  // keep `ctas_per_sm` CTAs resident (a deeper ring that lowers the occupancy loses more than it gains)
-  const int cps = t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm;
-  const size_t per_cta = (size_t)(227 * 1024) / cps - 1024;
-  while (smem > per_cta && sw > 2) {
-    --sw;
-    smem -= NW * stage_bytes;
-  }
-  LCU_REQUIRE(smem <= 227 * 1024, "gemv: a row of K=%d does not fit in shared memory", p.K);
-  const int grid = grid_of(p, sms);
-  const int pf = t.prefetch_kb_per_cta * 1024;
   // weight type of the kernel: fp16; u8 with the reference's per-weight rounding; u8 with factored scales
   const int wt = !q ? 0 : ((t.int8_factored && p.bs >= 64) ? 2 : 1);
+  const size_t stage_bytes = 2 * ROWB + (wt == 2 ? 2 * sc_bytes_row<2>() : wt == 1 ? 2 * sc_bytes_row<1>() : 0);
+  const size_t fixed = SMEM_FIXED + (((size_t)p.K * 2 + 127) & ~(size_t)127) + (((size_t)p.K / 64 * 4 + 127) & ~(size_t)127);
+  // CTAs per SM: as many as asked for that still fit with a two-deep ring per warp (the factored u8 kernel is
+  // latency-bound and compiled for three); then the deepest ring that keeps them resident
+  int cps = wt == 2 ? t.ctas_per_sm_int8 : t.ctas_per_sm;
+  if (cps < 1) cps = 1;
+  if (cps > 3) cps = 3;
+  while (cps > 1 && fixed + (size_t)NW * 2 * stage_bytes > (size_t)(227 * 1024) / cps - 1024) --cps;
+  int sw = t.warp_stages < 2 ? 2 : (t.warp_stages > MAX_SW ? MAX_SW : t.warp_stages);
+  while (sw > 2 && fixed + (size_t)NW * sw * stage_bytes > (size_t)(227 * 1024) / cps - 1024) --sw;
+  const size_t smem = fixed + (size_t)NW * sw * stage_bytes;
+  LCU_REQUIRE(smem <= 227 * 1024, "gemv: a row of K=%d does not fit in shared memory", p.K);
+  const int pairs = p.n_mats * p.rows_per_mat / 2;
+  const int grid = sms * cps > pairs ? pairs : sms * cps;
+  const int pf = t.prefetch_kb_per_cta * 1024;
 #define LCU_GEMV1_CASE(E)                                                     \
   case E:                                                                     \
     if (wt == 0) return launch_one<0, E>(p, stream, pdl, smem, grid, sw, pf); \
