@@ -126,6 +126,41 @@ __device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const 
   }
 }
 
+// Factored u8, block size >= 128: the two 64-byte steps of a 128-weight block share their scale, so the eight
+// tensor-core products of both steps are summed before the one multiplication by the scale.
+__device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const int sp, const int flip, const int c, const int g, const uint8_t* seg0,
+                                                   const uint8_t* xseg, const uint8_t* st, const float* xs64, const int ci, const int bs) {
+  constexpr int CHUNK_K = ROWB;
+  float* acc = accs[sp % NACC];
+  const uint32_t M = 0x64646464u;  // bytes -> halves 1024 + q
+  float t[4][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int off = (((2 * sp + h) ^ flip) << 6) + c * 16;  // odd segments take the two steps in swapped order (bank spread)
+    const uint4 lo = *reinterpret_cast<const uint4*>(seg0 + off);
+    const uint4 hi = *reinterpret_cast<const uint4*>(seg0 + ROWB + off);
+    const uint4 x0 = *reinterpret_cast<const uint4*>(xseg + 2 * off);
+    const uint4 x1 = *reinterpret_cast<const uint4*>(xseg + 2 * off + 16);
+    float* ta = t[2 * h];
+    float* tb = t[2 * h + 1];
+    ta[0] = ta[1] = ta[2] = ta[3] = 0.f;
+    tb[0] = tb[1] = tb[2] = tb[3] = 0.f;
+    mma_16816(ta, __byte_perm(lo.x, M, 0x4140), __byte_perm(hi.x, M, 0x4140), __byte_perm(lo.x, M, 0x4342), __byte_perm(hi.x, M, 0x4342), x0.x, x0.y);
+    mma_16816(tb, __byte_perm(lo.y, M, 0x4140), __byte_perm(hi.y, M, 0x4140), __byte_perm(lo.y, M, 0x4342), __byte_perm(hi.y, M, 0x4342), x0.z, x0.w);
+    mma_16816(ta, __byte_perm(lo.z, M, 0x4140), __byte_perm(hi.z, M, 0x4140), __byte_perm(lo.z, M, 0x4342), __byte_perm(hi.z, M, 0x4342), x1.x, x1.y);
+    mma_16816(tb, __byte_perm(lo.w, M, 0x4140), __byte_perm(hi.w, M, 0x4140), __byte_perm(lo.w, M, 0x4342), __byte_perm(hi.w, M, 0x4342), x1.z, x1.w);
+  }
+  const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
+  const int si = (g * SEG + (sp << 7)) >> bs;
+  const float sl = __half2float(scs[si]), sh = __half2float(scs[sc_bytes_row<2>() / 2 + si]);
+  const float2 xs2 = *reinterpret_cast<const float2*>(xs64 + ci * (CHUNK_K / 64) + g * NSTEPS + 2 * sp);
+  const float corr = 1151.5f * (xs2.x + xs2.y);
+  acc[0] += sl * (((t[0][0] + t[1][0]) + (t[2][0] + t[3][0])) - corr);
+  acc[1] += sl * (((t[0][1] + t[1][1]) + (t[2][1] + t[3][1])) - corr);
+  acc[2] += sh * (((t[0][2] + t[1][2]) + (t[2][2] + t[3][2])) - corr);
+  acc[3] += sh * (((t[0][3] + t[1][3]) + (t[2][3] + t[3][3])) - corr);
+}
+
 // Weight types (WT): 0 = fp16; 1 = u8, every weight rounded to half((q - 127.5) * scale) before the
 // product exactly as the reference's tensor-core kernel does (llama_cu.cu:287-289, 332-341); 2 = u8
 // with the scale factored out of each 64-weight group: sum_k x_k (q_k - 127.5) s = s * (sum_k x_k
@@ -141,8 +176,13 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [16 + w * MAX_SW + s]
   float* scratch = reinterpret_cast<float*>(smem + 256);
-  uint8_t* xs = smem + SMEM_FIXED;                     // activation row, K halves
-  float* xs64 = reinterpret_cast<float*>(xs + ((p.K * 2 + 127) & ~127));  // sums of x over aligned groups of 64
+  uint8_t* xs = smem + SMEM_FIXED;                     // activation row, K halves (u8 kernels: skewed, see xoff)
+  // u8 kernels read 32 activation bytes per 16 weight bytes; with the row stored flat, the two segments of a
+  // quarter warp would meet on the same banks.  Every 512-element segment is therefore shifted by 16 more bytes
+  // than the one before (vector i of eight halves lives at byte 16 * (i + i / 64)).
+  auto xoff = [](int vec_index) { return WT == 0 ? vec_index * 16 : (vec_index + (vec_index >> 6)) * 16; };
+  const int xbytes = WT == 0 ? p.K * 2 : p.K * 2 + (p.K >> 9) * 16 + 16;
+  float* xs64 = reinterpret_cast<float*>(xs + ((xbytes + 127) & ~127));  // sums of x over aligned groups of 64
   uint8_t* stages = reinterpret_cast<uint8_t*>(xs64) + ((p.K / 64 * 4 + 127) & ~127);  // [NW][sw][STAGE_BYTES]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -249,23 +289,23 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
       const int i = tid + j * NCONS;
       if (i < vec) {
         xv[j] = *reinterpret_cast<const uint4*>(p.x + i * 8);
-        *reinterpret_cast<uint4*>(xs + i * 16) = xv[j];
+        *reinterpret_cast<uint4*>(xs + xoff(i)) = xv[j];
       }
     }
-    for (int i = tid + NVEC * NCONS; i < vec; i += NCONS) *reinterpret_cast<uint4*>(xs + i * 16) = *reinterpret_cast<const uint4*>(p.x + i * 8);
+    for (int i = tid + NVEC * NCONS; i < vec; i += NCONS) *reinterpret_cast<uint4*>(xs + xoff(i)) = *reinterpret_cast<const uint4*>(p.x + i * 8);
     bar_sync(1, NCONS);
     if (p.norm_w != nullptr) {
       // RMSNorm with the reference's summation order (llama_cu.cu:72-106): 256 strided partial sums,
       // xor trees inside 8 warps, xor tree over the 8 warp sums.  Each of the 128 threads here plays
       // two of the reference's threads (t and t + 128), each warp two of its warps (w and w + 4).
-      __half* xh = reinterpret_cast<__half*>(xs);
+      auto xat = [&](int i) { return __half2float(*reinterpret_cast<const __half*>(xs + xoff(i >> 3) + (i & 7) * 2)); };
       float s0 = 0.f, s1 = 0.f;
       for (int i = tid; i < p.K; i += 256) {
-        float v = __half2float(xh[i]);
+        float v = xat(i);
         s0 += v * v;
       }
       for (int i = tid + 128; i < p.K; i += 256) {
-        float v = __half2float(xh[i]);
+        float v = xat(i);
         s1 += v * v;
       }
       s0 = warp_sum(s0);
@@ -292,15 +332,15 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
 #pragma unroll
       for (int j = 0; j < NVEC; ++j) {
         const int i = tid + j * NCONS;
-        if (i < vec) *reinterpret_cast<uint4*>(xs + i * 16) = norm8(xv[j], nw[j]);
+        if (i < vec) *reinterpret_cast<uint4*>(xs + xoff(i)) = norm8(xv[j], nw[j]);
       }
       for (int i = tid + NVEC * NCONS; i < vec; i += NCONS)
-        *reinterpret_cast<uint4*>(xs + i * 16) = norm8(*reinterpret_cast<const uint4*>(xs + i * 16), *reinterpret_cast<const uint4*>(p.norm_w + i * 8));
+        *reinterpret_cast<uint4*>(xs + xoff(i)) = norm8(*reinterpret_cast<const uint4*>(xs + xoff(i)), *reinterpret_cast<const uint4*>(p.norm_w + i * 8));
       bar_sync(1, NCONS);
     }
     if (WT == 2) {  // sums of the (normalised) activations over aligned groups of 64: eight lanes per group, 16 bytes per lane
       for (int grp64 = warp * 4 + (lane >> 3); grp64 < p.K / 64; grp64 += NW * 4) {
-        const uint4 q = *reinterpret_cast<const uint4*>(xs + grp64 * 128 + (lane & 7) * 16);
+        const uint4 q = *reinterpret_cast<const uint4*>(xs + xoff(grp64 * 8 + (lane & 7)));
         const __half2* h = reinterpret_cast<const __half2*>(&q);
         float s = 0.f;
 #pragma unroll
@@ -336,10 +376,13 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
       const int vb = min(max(cbytes - g * SEG, 0), SEG);  // valid bytes of this lane's segment
       const uint8_t* st = stages + (size_t)(warp * sw + slot) * STAGE_BYTES;
       const uint8_t* seg0 = st + g * SEG;
-      const uint8_t* xseg = xs + ((size_t)ci * CHUNK_K + (size_t)g * (SEG / ESZ)) * 2;
+      const uint8_t* xseg = xs + xoff((ci * CHUNK_K + g * (SEG / ESZ)) >> 3);
       // A full chunk (every chunk but possibly the last of a row) takes the branch-free path, so that the
       // shared loads of all eight steps can be issued ahead of the tensor-core instructions.
-      if (cbytes == ROWB) {
+      if (WT == 2 && cbytes == ROWB && bs_shift >= 7) {
+#pragma unroll
+        for (int sp = 0; sp < NSTEPS / 2; ++sp) step_pair_factored(accs, sp, flip, c, g, seg0, xseg, st, xs64, ci, bs_shift);
+      } else if (cbytes == ROWB) {
 #pragma unroll
         for (int s = 0; s < NSTEPS; ++s) step<WT, true>(accs, s, flip, c, g, SEG, seg0, xseg, st, xs64, ci, bs_shift);
       } else {
@@ -479,15 +522,16 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   // weight type of the kernel: fp16; u8 with the reference's per-weight rounding; u8 with factored scales
   const int wt = !q ? 0 : ((t.int8_factored && p.bs >= 64) ? 2 : 1);
   const size_t stage_bytes = 2 * ROWB + (wt == 2 ? 2 * sc_bytes_row<2>() : wt == 1 ? 2 * sc_bytes_row<1>() : 0);
-  const size_t fixed = SMEM_FIXED + (((size_t)p.K * 2 + 127) & ~(size_t)127) + (((size_t)p.K / 64 * 4 + 127) & ~(size_t)127);
+  const size_t xbytes = wt == 0 ? (size_t)p.K * 2 : (size_t)p.K * 2 + ((size_t)p.K >> 9) * 16 + 16;  // u8: skewed activation row
+  const size_t fixed = SMEM_FIXED + ((xbytes + 127) & ~(size_t)127) + (((size_t)p.K / 64 * 4 + 127) & ~(size_t)127);
   // CTAs per SM: as many as asked for that still fit with a two-deep ring per warp (the factored u8 kernel is
   // latency-bound and compiled for three); then the deepest ring that keeps them resident
   int cps = wt == 2 ? t.ctas_per_sm_int8 : t.ctas_per_sm;
   if (cps < 1) cps = 1;
   if (cps > 3) cps = 3;
-  while (cps > 1 && fixed + (size_t)NW * 2 * stage_bytes > (size_t)(227 * 1024) / cps - 1024) --cps;
+  while (cps > 1 && fixed + (size_t)NW * 2 * stage_bytes > (size_t)(228 * 1024) / cps - 1024) --cps;
   int sw = t.warp_stages < 2 ? 2 : (t.warp_stages > MAX_SW ? MAX_SW : t.warp_stages);
-  while (sw > 2 && fixed + (size_t)NW * sw * stage_bytes > (size_t)(227 * 1024) / cps - 1024) --sw;
+  while (sw > 2 && fixed + (size_t)NW * sw * stage_bytes > (size_t)(228 * 1024) / cps - 1024) --sw;
   const size_t smem = fixed + (size_t)NW * sw * stage_bytes;
   LCU_REQUIRE(smem <= 227 * 1024, "gemv: a row of K=%d does not fit in shared memory", p.K);
   const int pairs = p.n_mats * p.rows_per_mat / 2;
