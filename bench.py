@@ -15,6 +15,9 @@ Printed JSON line (rank 0):
   roofline  the dominant kernel (fused RMSNorm + w1|w3 + SiLU GEMV) timed alone over all layers in
             rotation with CUDA events: algorithmic bytes per launch / mean launch time vs the measured
             HBM copy bandwidth
+  prefill   (N = 1) the prompt path: tok/s of a 512-token prompt through lcu_context_next_token, and the largest
+            prompt GEMM (512 x 4096 x 11008, tcgen05 kernel) timed alone with CUDA events against the measured
+            dense bf16 tensor peak
   cpu_baseline  the CPU oracle on a bounded sample (one of the 32 layers + the output head), host threads
 With N > 1 (torchrun) every rank runs an independent replica on its own GPU (the path does not
 shard at batch 1: layers are sequentially dependent), value = N*K / max-rank time, scaling "weak".
@@ -44,9 +47,10 @@ WORKLOADS = {
     "tiny-fp16": dict(dim=512, n_heads=4, n_layers=4, n_vocab=2000, block_size=0),  # plumbing checks only
 }
 SEED, SCALE, PROMPT_LEN, CONTEXT_LEN, TEMPERATURE = 1234, 0.02, 128, 2048, 0.8
-# DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
-# profiles/gemv_w13_7b_fp16.md (dram__bytes_read.sum + dram__bytes_write.sum); None until captured
-NCU_TRAFFIC_BYTES = {"7b-fp16": 180413440 + 3508736, "7b-int8": None}
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
+# captures summarised in profiles/gemv_w13_7b_fp16.md and profiles/gemv_w13_7b_int8.md
+NCU_TRAFFIC_BYTES = {"7b-fp16": 180413440 + 3508736, "7b-int8": 91670016 + 3379200}
+PREFILL_LEN = 512
 
 
 def load_package():
@@ -124,6 +128,53 @@ def measured_peak():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def measured_tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, cuBLAS burst)"
+        except Exception:
+            pass
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+def prefill_sample(lcu, ctx, cfg, ffn, profile=False):
+    """Prompt path: a PREFILL_LEN-token prompt through the public call (wall clock, host tokens in, token out),
+    and the largest prompt GEMM alone (CUDA events) against the dense tensor peak."""
+    import oracle_lib as O
+    prompt = O.synth_tokens(PREFILL_LEN, SEED + 1, lo=3, hi=min(32000, cfg["n_vocab"]))
+    best = None
+    for _ in range(3):
+        ctx.clear_tokens()
+        lcu.check(lcu.lib.lcu_synchronize())
+        t0 = time.perf_counter()
+        ctx.next_token(prompt)
+        dt = time.perf_counter() - t0
+        best = dt if best is None or dt < best else best
+    out = {"prompt_tokens": PREFILL_LEN, "ms": round(best * 1e3, 3), "tok_s": round(PREFILL_LEN / best, 1)}
+    if profile:  # one more prompt pass and a few GEMM launches inside the profiler's window
+        ctx.clear_tokens()
+        lcu.check(lcu.lib.lcu_profiler_start())
+        ctx.next_token(prompt)
+        if cfg["block_size"] == 0:
+            lcu.bench_matmul_f16_ms(2048, cfg["dim"], ffn, reps=2)
+        lcu.check(lcu.lib.lcu_profiler_stop())
+    if cfg["block_size"] == 0:
+        peak, src = measured_tensor_peak()
+        m, k, n = PREFILL_LEN, cfg["dim"], ffn
+        ms = lcu.bench_matmul_f16_ms(m, k, n, reps=50)
+        tf = 2.0 * m * k * n / (ms * 1e-3) / 1e12
+        m2 = 2048
+        ms2 = lcu.bench_matmul_f16_ms(m2, k, n, reps=20)
+        tf2 = 2.0 * m2 * k * n / (ms2 * 1e-3) / 1e12
+        out["gemm_roofline"] = {"bound": "tensor", "kernel": "gemm_tc_pair_kernel (tcgen05.mma cta_group::2, TMA-fed, accumulator in TMEM)",
+                                "shape": [m, k, n], "us_per_launch": round(ms * 1e3, 2), "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s",
+                                "frac": round(tf / peak, 4), "peak_source": src,
+                                "at_2048_rows": {"shape": [m2, k, n], "us_per_launch": round(ms2 * 1e3, 2), "achieved": round(tf2, 1),
+                                                 "frac": round(tf2 / peak, 4)}}
+    return out
+
+
 def cpu_baseline_sample(cfg, ffn, steps=6):
     """CPU oracle on one layer + the head of the same shapes; extrapolated to all layers."""
     import numpy as np
@@ -158,7 +209,8 @@ def dist_setup(n_gpus):
     if world > 1:
         import torch
         import torch.distributed as dist_mod
-        torch.cuda.set_device(local)
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local)
         dist_mod.init_process_group(backend="nccl" if torch.cuda.is_available() else "gloo")
         dist = dist_mod
     return world, rank, local, dist
@@ -207,10 +259,10 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     barrier_sync(dist, lcu)
-    if args.profile:
+    if args.profile == "decode":
         lcu.check(lcu.lib.lcu_profiler_start())
     tokens, ms = ctx.decode_chained(int(warm_tokens[-1]), K)
-    if args.profile:
+    if args.profile == "decode":
         lcu.check(lcu.lib.lcu_profiler_stop())
     barrier_sync(dist, lcu)
     ms_all = reduce_max_time(ms, dist)
@@ -244,7 +296,7 @@ def run_ours(args):
         kms, kbytes = ctx.bench_kernel(which, reps if which < 4 else 20)
         kernels[name] = {"us": round(kms * 1e3, 3), "bytes": kbytes, "gbs": round(kbytes / (kms * 1e-3) / 1e9, 1)}
     dom = kernels["norm+w1|w3+silu"]
-    roofline = {"bound": "hbm", "kernel": "gemv_kernel<EPI_SILU> (fused RMSNorm + w1|w3 + SiLU gate)", "achieved": dom["gbs"], "peak": peak,
+    roofline = {"bound": "hbm", "kernel": "gemv1_kernel<WT, EPI_SILU> (fused RMSNorm + w1|w3 + SiLU gate)", "achieved": dom["gbs"], "peak": peak,
                 "unit": "GB/s", "frac": round(dom["gbs"] / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                 "algorithmic_bytes_per_launch": dom["bytes"], "us_per_launch": dom["us"], "peak_source": peak_src,
                 "frac_of_nominal_8tbs": round(dom["gbs"] / 8000.0, 4)}
@@ -254,6 +306,7 @@ def run_ours(args):
                   "frac_of_measured_peak": round(step_bytes * (K / (ms_all / 1e3)) / 1e9 / peak, 4),
                   "frac_of_nominal_8tbs": round(step_bytes * (K / (ms_all / 1e3)) / 1e9 / 8000.0, 4)}
     kps = ctx.kernels_per_step()
+    prefill = prefill_sample(lcu, ctx, cfg, ffn, args.profile == "prefill") if world == 1 and ctx_len >= PREFILL_LEN + 2 else None
     ctx.close()
     model.close()
 
@@ -270,6 +323,8 @@ def run_ours(args):
         "gpu_launches": K * kps, "kernels_per_step": kps,
         "roofline": roofline, "kernels": kernels, "whole_step": whole_step, "clocks": clocks,
     }
+    if prefill is not None:
+        line["prefill"] = prefill
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample(cfg, ffn)
@@ -339,7 +394,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="7b-fp16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile", action="store_true", help="cudaProfilerStart/Stop around the device-chained timed region")
+    ap.add_argument("--profile", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
+                    help="cudaProfilerStart/Stop around the device-chained timed region (decode) or around the prompt pass and GEMM (prefill)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -150,6 +150,9 @@ int lcu_bench_decode_kernel(void* ctx, int which, int reps, float* ms_per_launch
 /* cudaProfilerStart / cudaProfilerStop, so that a profiler attached with --profile-from-start off sees only the timed region */
 int lcu_profiler_start(void);
 int lcu_profiler_stop(void);
+/* lcu_matmul_nt_f16 (beta = 0, default stream) launched `reps` times back to back between two CUDA events on that
+ * stream: mean milliseconds per launch.  Used to put the prompt GEMM against the tensor-core roofline. */
+int lcu_bench_matmul_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, int reps, float* ms_per_launch_out);
 /* pure-read ceiling: a kernel that only streams `bytes` from HBM with the same bulk-copy ring (16 KiB stages, each
  * fetched as copies_per_stage bulk copies, 1..32); ms per pass */
 int lcu_bench_read_ceiling(uint64_t bytes, int reps, int copies_per_stage, float* ms_per_pass_out);

@@ -48,6 +48,7 @@ _SIG = {
     "lcu_rope_scatter_static": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "lcu_attention": (C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "lcu_logits_head": (C.c_int, [vp, vp, C.c_int, C.c_float, C.POINTER(C.c_int), vp]),
+    "lcu_bench_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "lcu_synth_fill_f16": (C.c_int, [vp, C.c_uint64, C.c_uint64, C.c_char_p, C.c_float, C.c_uint64, vp]),
     "lcu_model_create": (C.c_int, [vp, vp, C.POINTER(vp)]),
     "lcu_model_load": (C.c_int, [C.c_char_p, vp, C.POINTER(vp)]),
@@ -343,6 +344,16 @@ class Context:
         if self.handle:
             lib.lcu_context_free(self.handle)
             self.handle = None
+
+
+def bench_matmul_f16_ms(m, k, n, reps=20, seed=7):
+    """Mean milliseconds of one out(m,n) = lhs(m,k) . w(n,k)^T on seeded device-resident operands (CUDA events)."""
+    x, w, o = DeviceBuffer(m * k * 2), DeviceBuffer(n * k * 2), DeviceBuffer(m * n * 2)
+    check(lib.lcu_synth_fill_f16(x.ptr, m * k, seed, b"bench.x", 1.0, 0, None))
+    check(lib.lcu_synth_fill_f16(w.ptr, n * k, seed, b"bench.w", 0.02, 0, None))
+    ms = C.c_float(0)
+    check(lib.lcu_bench_matmul_f16(o.ptr, x.ptr, w.ptr, m, k, n, reps, C.byref(ms)))
+    return ms.value
 
 
 def read_ceiling_ms(nbytes, reps=10, copies_per_stage=1):

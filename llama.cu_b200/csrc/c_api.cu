@@ -396,6 +396,26 @@ int lcu_profiler_stop(void) {
   LCU_CUDA(cudaProfilerStop());
   return LCU_OK;
 }
+int lcu_bench_matmul_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, int reps, float* ms_per_launch_out) {
+  NEED_DEVICE();
+  LCU_REQUIRE(reps >= 1 && ms_per_launch_out, "bench_matmul: bad arguments");
+  cudaEvent_t e0, e1;
+  LCU_CUDA(cudaEventCreate(&e0));
+  LCU_CUDA(cudaEventCreate(&e1));
+  int rc = lcu_matmul_nt_f16(out_dev, lhs_dev, rhs_dev, m, k, n, 0.f, nullptr);  // warm: attributes, tensor maps
+  if (rc == LCU_OK) {
+    cudaEventRecord(e0, 0);
+    for (int i = 0; i < reps && rc == LCU_OK; ++i) rc = lcu_matmul_nt_f16(out_dev, lhs_dev, rhs_dev, m, k, n, 0.f, nullptr);
+    cudaEventRecord(e1, 0);
+    if (cudaEventSynchronize(e1) != cudaSuccess) rc = LCU_ERR_CUDA;
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    *ms_per_launch_out = ms / reps;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return rc;
+}
 int lcu_bench_read_ceiling(uint64_t bytes, int reps, int copies_per_stage, float* ms_per_pass_out) {
   NEED_DEVICE();
   return bench_read_ceiling(bytes, reps, copies_per_stage, ms_per_pass_out);
