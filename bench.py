@@ -42,6 +42,7 @@ WORKLOADS = {
     "7b-fp16": dict(dim=4096, n_heads=32, n_layers=32, n_vocab=32000, block_size=0),
     "7b-int8": dict(dim=4096, n_heads=32, n_layers=32, n_vocab=32000, block_size=128),
     "13b-fp16": dict(dim=5120, n_heads=40, n_layers=40, n_vocab=32000, block_size=0),
+    "65b-int8": dict(dim=8192, n_heads=64, n_layers=80, n_vocab=32000, block_size=128),
     "7b-l4-fp16": dict(dim=4096, n_heads=32, n_layers=4, n_vocab=32000, block_size=0),   # 7B kernel shapes, 4 layers: profiler captures
     "7b-l4-int8": dict(dim=4096, n_heads=32, n_layers=4, n_vocab=32000, block_size=128),
     "tiny-fp16": dict(dim=512, n_heads=4, n_layers=4, n_vocab=2000, block_size=0),  # plumbing checks only
@@ -245,8 +246,19 @@ def run_ours(args):
     cfg = WORKLOADS[args.workload]
     ffn = lcu.lib.lcu_ffn_dim(cfg["dim"], 256)
     K, W = args.steps, args.warmup
+    PROMPT_LEN = args.prompt_len
     ctx_len = max(CONTEXT_LEN, PROMPT_LEN + W + K + 2)
-    model = lcu.Model.synthetic(seed=SEED, scale=SCALE, **cfg)
+    layer_gpus = None
+    if args.pipeline > 1:  # one process, layers split evenly over the first P devices (the reference's pipelined configurations)
+        if world > 1:
+            raise SystemExit("--pipeline is a single-process mode; launch it without torchrun")
+        if lcu.lib.lcu_device_count() < args.pipeline:
+            raise SystemExit(f"--pipeline {args.pipeline} needs {args.pipeline} GPUs")
+        per = (cfg["n_layers"] + args.pipeline - 1) // args.pipeline
+        layer_gpus = [min(i // per, args.pipeline - 1) for i in range(cfg["n_layers"])]
+    t_gen0 = time.perf_counter()
+    model = lcu.Model.synthetic(seed=SEED, scale=SCALE, layer_gpus=layer_gpus, **cfg)
+    gen_s = time.perf_counter() - t_gen0
     ctx = lcu.Context(model, context_len=ctx_len, temperature=TEMPERATURE)
     prompt = O.synth_tokens(PROMPT_LEN, SEED, lo=3, hi=min(32000, cfg["n_vocab"]))
 
@@ -311,11 +323,14 @@ def run_ours(args):
     model.close()
 
     line = {
-        "metric": "7B batch-1 decode tok/s", "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "metric": "7B batch-1 decode tok/s" if args.workload.startswith("7b") else f"{args.workload} batch-1 decode tok/s",
+        "value": round(value, 2), "unit": "tok/s", "n_gpus": world if args.pipeline <= 1 else args.pipeline, "steps": K, "warmup": W,
         "ms_per_step": round(ms_all / K, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16" if cfg["block_size"] == 0 else "u8 weights x f16 activations, f32 accumulate", "data": "synthetic",
         "config": {"workload": f"llama-{args.workload} greedy decode, batch 1, {PROMPT_LEN}-token seeded prompt, context {ctx_len}",
-                   "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (replicas only: batch-1 decode does not shard)",
+                   "parallelism": (f"layer pipeline over {args.pipeline} GPUs in one process (one stage active at a time at batch 1)" if args.pipeline > 1
+                                   else "1 GPU" if world == 1 else f"{world} independent replicas (replicas only: batch-1 decode does not shard)"),
+                   "weights_generated_s": round(gen_s, 1),
                    "l2": "inputs larger than L2: each step streams its weights once, far more than the 126 MB L2",
                    "weights": f"random-init ~N(0,{SCALE}) (Irwin-Hall, seed {SEED}), RMSNorm weights 1.0", "prefill_s": round(prefill_s, 4)},
         "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": 10, "d2h_bytes_per_step": 8,
@@ -394,6 +409,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="7b-fp16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="seeded prompt length (128 for the headline configuration)")
+    ap.add_argument("--pipeline", type=int, default=1, help="single process: split the layers evenly over this many GPUs")
     ap.add_argument("--profile", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                     help="cudaProfilerStart/Stop around the device-chained timed region (decode) or around the prompt pass and GEMM (prefill)")
     args = ap.parse_args()

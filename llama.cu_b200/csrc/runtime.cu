@@ -830,9 +830,15 @@ int context::read_hidden(__half* out_host) {
 int context::bench_kernel(int which, int reps, float* ms_per_launch, uint64_t* bytes_per_launch) {
   context_impl& c = *impl;
   LCU_REQUIRE(which >= 0 && which <= 4 && reps >= 1, "bench_kernel: bad arguments");
-  const int L = (int)c.m->params.n_layers;
+  // layers of one pipeline stage in rotation: the first stage, or the last one for the output matrix
+  const int stage = which == 4 ? (int)c.gpus.size() - 1 : 0;
+  std::vector<int> stage_layers;
+  for (int l = 0; l < (int)c.m->params.n_layers; ++l)
+    if (c.layer_slot[l] == stage && !(which == 3 && l + 1 < (int)c.m->params.n_layers && c.layer_slot[l + 1] != stage))
+      stage_layers.push_back(l);  // (a w2 that also stores into the next stage is left out of the rotation)
+  LCU_REQUIRE(!stage_layers.empty(), "bench_kernel: no layer to rotate over");
   auto params_of = [&](int i, int& epi) {
-    const int l = i % L;
+    const int l = stage_layers[i % stage_layers.size()];
     switch (which) {
       case 0: epi = EPI_ROPE_KV; return c.params_qkv(l);
       case 1: epi = EPI_PLAIN; return c.params_wo(l);
@@ -841,8 +847,7 @@ int context::bench_kernel(int which, int reps, float* ms_per_launch, uint64_t* b
       default: epi = EPI_PLAIN; return c.params_out(0);
     }
   };
-  LCU_REQUIRE(c.gpus.size() == 1, "bench_kernel: single-GPU contexts only");
-  gpu_state& g = c.first();
+  gpu_state& g = c.gpus[stage];
   device_guard dg(g.device);
   const int saved_pos = c.start_pos;
   c.h_stage[0] = 0;
@@ -853,15 +858,20 @@ int context::bench_kernel(int which, int reps, float* ms_per_launch, uint64_t* b
     gemv_params a = params_of(i, epi);
     LCU_TRY(launch_gemv(a, epi, g.stream, 0));
   }
-  LCU_CUDA(cudaEventRecord(c.t0, g.stream));
+  cudaEvent_t e0 = nullptr, e1 = nullptr;  // on this stage's device
+  LCU_CUDA(cudaEventCreate(&e0));
+  LCU_CUDA(cudaEventCreate(&e1));
+  LCU_CUDA(cudaEventRecord(e0, g.stream));
   for (int i = 0; i < reps; ++i) {
     gemv_params a = params_of(i, epi);
     LCU_TRY(launch_gemv(a, epi, g.stream, c.opt.use_pdl));
   }
-  LCU_CUDA(cudaEventRecord(c.t1, g.stream));
+  LCU_CUDA(cudaEventRecord(e1, g.stream));
   LCU_CUDA(cudaStreamSynchronize(g.stream));
   float ms = 0.f;
-  LCU_CUDA(cudaEventElapsedTime(&ms, c.t0, c.t1));
+  LCU_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
   *ms_per_launch = ms / reps;
   gemv_params a0 = params_of(0, epi);
   *bytes_per_launch = gemv_algorithmic_bytes(a0, epi);
