@@ -30,15 +30,18 @@ namespace {
 constexpr int NW = 4;                       // consumer warps per CTA
 constexpr int NTHREADS = (NW + 1) * 32;
 constexpr int NCONS = NW * 32;
-constexpr int ROWB = 4096;                  // bytes of one row per stage (one bulk copy)
-constexpr int SEG = ROWB / 8;               // 512-byte segments
-constexpr int NSTEPS = SEG / 64;            // 64-byte steps per segment
+// Stage geometry per weight type: 4 KiB of each row per stage (measured: 2 KiB stages in a ring twice as deep lose a
+// third of the u8 throughput - the per-stage cost of the producer counts).
+template <int WT>
+struct geom {
+  static constexpr int ROWB = 4096;                    // bytes of one row per stage (one bulk copy)
+  static constexpr int SEG = ROWB / 8;                 // the chunk is cut into 8 segments, one per tile column
+  static constexpr int NSTEPS = SEG / 64;              // 64-byte steps per segment
+  static constexpr int SC_ROW = WT == 2 ? ROWB / 64 * 2 : 256;  // scale bytes reserved per row per stage (block size >= 64 / >= 32)
+  static constexpr int SEG_SHIFT = 9;                  // log2(SEG)
+};
 constexpr int MAX_SW = 4;                   // ring depth per warp
 constexpr int NACC = 4;                     // independent accumulator sets (no chain on one result)
-// scale bytes reserved per row per stage: 4096 / 32 * 2 for the smallest block size; the factored mode needs
-// block sizes of 64 or more, and its smaller stage lets three CTAs share an SM
-template <int WT>
-__host__ __device__ constexpr int sc_bytes_row() { return WT == 2 ? 128 : 256; }
 constexpr int SMEM_FIXED = 256 + 64;        // barriers: full[NW][MAX_SW], empty[NW][MAX_SW]; scratch
 
 template <int EPI>
@@ -70,6 +73,7 @@ __device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const 
                                      const uint8_t* seg0, const uint8_t* xseg, const uint8_t* st, const float* xs64, const int ci,
                                      const int bs) {
   constexpr int ESZ = WT == 0 ? 2 : 1;
+  constexpr int ROWB = geom<WT>::ROWB, SEG = geom<WT>::SEG, NSTEPS = geom<WT>::NSTEPS;
   constexpr int CHUNK_K = ROWB / ESZ;
   float* acc = accs[(2 * s) % NACC];
   float* acc_b = accs[(2 * s + 1) % NACC];
@@ -95,7 +99,7 @@ __device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const 
       const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
       const int si = (g * SEG + off) >> bs;  // k offset inside the chunk / block size (bs is log2 of it here)
       sc_lo = scs[si];
-      sc_hi = scs[sc_bytes_row<WT>() / 2 + si];
+      sc_hi = scs[geom<WT>::SC_ROW / 2 + si];
       // WT 2: sum of x over this lane's segment and step (the diagonal column of the tile)
       if (WT == 2) corr = 1151.5f * xs64[ci * (CHUNK_K / 64) + g * NSTEPS + (s ^ flip)];
     }
@@ -130,6 +134,7 @@ __device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const 
 // tensor-core products of both steps are summed before the one multiplication by the scale.
 __device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const int sp, const int flip, const int c, const int g, const uint8_t* seg0,
                                                    const uint8_t* xseg, const uint8_t* st, const float* xs64, const int ci, const int bs) {
+  constexpr int ROWB = geom<2>::ROWB, SEG = geom<2>::SEG, NSTEPS = geom<2>::NSTEPS;
   constexpr int CHUNK_K = ROWB;
   float* acc = accs[sp % NACC];
   const uint32_t M = 0x64646464u;  // bytes -> halves 1024 + q
@@ -152,7 +157,7 @@ __device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const
   }
   const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
   const int si = (g * SEG + (sp << 7)) >> bs;
-  const float sl = __half2float(scs[si]), sh = __half2float(scs[sc_bytes_row<2>() / 2 + si]);
+  const float sl = __half2float(scs[si]), sh = __half2float(scs[geom<2>::SC_ROW / 2 + si]);
   const float2 xs2 = *reinterpret_cast<const float2*>(xs64 + ci * (CHUNK_K / 64) + g * NSTEPS + 2 * sp);
   const float corr = 1151.5f * (xs2.x + xs2.y);
   acc[0] += sl * (((t[0][0] + t[1][0]) + (t[2][0] + t[3][0])) - corr);
@@ -170,18 +175,19 @@ __device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const
 template <int WT, int EPI>
 __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p, const int sw, const int pf_bytes) {
   constexpr int ESZ = WT == 0 ? 2 : 1;
-  constexpr int CHUNK_K = ROWB / ESZ;        // weights of one row per stage: 2048 fp16, 4096 u8
-  constexpr int STAGE_BYTES = 2 * ROWB + (WT ? 2 * sc_bytes_row<WT>() : 0);
+  constexpr int ROWB = geom<WT>::ROWB, SEG = geom<WT>::SEG, NSTEPS = geom<WT>::NSTEPS;
+  constexpr int CHUNK_K = ROWB / ESZ;        // weights of one row per stage
+  constexpr int STAGE_BYTES = 2 * ROWB + (WT ? 2 * geom<WT>::SC_ROW : 0);
 
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [16 + w * MAX_SW + s]
   float* scratch = reinterpret_cast<float*>(smem + 256);
   uint8_t* xs = smem + SMEM_FIXED;                     // activation row, K halves (u8 kernels: skewed, see xoff)
   // u8 kernels read 32 activation bytes per 16 weight bytes; with the row stored flat, the two segments of a
-  // quarter warp would meet on the same banks.  Every 512-element segment is therefore shifted by 16 more bytes
-  // than the one before (vector i of eight halves lives at byte 16 * (i + i / 64)).
-  auto xoff = [](int vec_index) { return WT == 0 ? vec_index * 16 : (vec_index + (vec_index >> 6)) * 16; };
-  const int xbytes = WT == 0 ? p.K * 2 : p.K * 2 + (p.K >> 9) * 16 + 16;
+  // quarter warp would meet on the same banks.  The activations of every segment are therefore shifted by 16 more
+  // bytes than those of the one before (vector i of eight halves lives at byte 16 * (i + i / (SEG / 8))).
+  auto xoff = [](int vec_index) { return WT == 0 ? vec_index * 16 : (vec_index + (vec_index >> (geom<WT>::SEG_SHIFT - 3))) * 16; };
+  const int xbytes = WT == 0 ? p.K * 2 : p.K * 2 + (p.K >> geom<WT>::SEG_SHIFT) * 16 + 16;
   float* xs64 = reinterpret_cast<float*>(xs + ((xbytes + 127) & ~127));  // sums of x over aligned groups of 64
   uint8_t* stages = reinterpret_cast<uint8_t*>(xs64) + ((p.K / 64 * 4 + 127) & ~127);  // [NW][sw][STAGE_BYTES]
 
@@ -194,9 +200,12 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
   const int rowbytes = p.K * ESZ;
   const int nchunks = (rowbytes + ROWB - 1) / ROWB;
 
+  // Scales of a row chunk are one contiguous run; when rows start 16-byte aligned they travel as one more bulk copy
+  // per row on the same barrier, otherwise as 4-byte cp.async pieces issued by all lanes (32 more barrier arrivals).
+  const bool sc_bulk = WT != 0 && ((p.K / p.bs) & 7) == 0 && ((ROWB / p.bs) & 7) == 0;
   if (tid == 0) {
     for (int i = 0; i < NW * MAX_SW; ++i) {
-      mbar_init(smem_u32(&bars[i]), WT == 0 ? 1 : 33);
+      mbar_init(smem_u32(&bars[i]), (WT == 0 || sc_bulk) ? 1 : 33);
       mbar_init(smem_u32(&bars[16 + i]), 1);
     }
     fence_mbar_init();
@@ -249,14 +258,19 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
           const uint32_t full = smem_u32(&bars[w * MAX_SW + slot[w]]);
           mbar_wait(smem_u32(&bars[16 + w * MAX_SW + slot[w]]), par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
           uint8_t* st = stages + (size_t)(w * sw + slot[w]) * STAGE_BYTES;
-          if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes));
+          const uint32_t scbytes = WT != 0 ? (uint32_t)(cbytes / p.bs) * 2 : 0;  // scale bytes per row of this chunk
+          if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes) + (sc_bulk ? 2 * scbytes : 0));
           __syncwarp();
           if (lane < 2) bulk_g2s_hint(smem_u32(st + lane * ROWB), src_row[w] + (size_t)ci * ROWB, (uint32_t)cbytes, full, pol);
           if (WT != 0) {
-            const int ppr = (cbytes / p.bs) >> 1;  // 4-byte pieces per row
             const __half* src = src_sc[w] + (ci * CHUNK_K) / p.bs;
-            for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * sc_bytes_row<WT>() + j * 4), src + 2 * j);
-            cp_async_mbar_arrive_noinc(full);
+            if (sc_bulk) {  // lanes 0 and 16 copy the scale runs of rows 0 and 1 (src_sc is set per half warp)
+              if ((lane & 15) == 0) bulk_g2s(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW), src, scbytes, full);
+            } else {
+              const int ppr = (cbytes / p.bs) >> 1;  // 4-byte pieces per row
+              for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW + j * 4), src + 2 * j);
+              cp_async_mbar_arrive_noinc(full);
+            }
           }
           if (++slot[w] == sw) {
             slot[w] = 0;
@@ -521,8 +535,9 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   const bool q = p.bs != 0;
   // weight type of the kernel: fp16; u8 with the reference's per-weight rounding; u8 with factored scales
   const int wt = !q ? 0 : ((t.int8_factored && p.bs >= 64) ? 2 : 1);
-  const size_t stage_bytes = 2 * ROWB + (wt == 2 ? 2 * sc_bytes_row<2>() : wt == 1 ? 2 * sc_bytes_row<1>() : 0);
-  const size_t xbytes = wt == 0 ? (size_t)p.K * 2 : (size_t)p.K * 2 + ((size_t)p.K >> 9) * 16 + 16;  // u8: skewed activation row
+  const size_t stage_bytes = wt == 2 ? 2 * geom<2>::ROWB + 2 * geom<2>::SC_ROW : wt == 1 ? 2 * geom<1>::ROWB + 2 * geom<1>::SC_ROW : 2 * geom<0>::ROWB;
+  const int seg_shift = wt == 2 ? geom<2>::SEG_SHIFT : geom<1>::SEG_SHIFT;
+  const size_t xbytes = wt == 0 ? (size_t)p.K * 2 : (size_t)p.K * 2 + ((size_t)p.K >> seg_shift) * 16 + 16;  // u8: skewed activation row
   const size_t fixed = SMEM_FIXED + ((xbytes + 127) & ~(size_t)127) + (((size_t)p.K / 64 * 4 + 127) & ~(size_t)127);
   // CTAs per SM: as many as asked for that still fit with a two-deep ring per warp (the factored u8 kernel is
   // latency-bound and compiled for three); then the deepest ring that keeps them resident
@@ -530,7 +545,8 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   if (cps < 1) cps = 1;
   if (cps > 3) cps = 3;
   while (cps > 1 && fixed + (size_t)NW * 2 * stage_bytes > (size_t)(228 * 1024) / cps - 1024) --cps;
-  int sw = t.warp_stages < 2 ? 2 : (t.warp_stages > MAX_SW ? MAX_SW : t.warp_stages);
+  const int want_sw = wt == 2 ? t.warp_stages_int8 : t.warp_stages;
+  int sw = want_sw < 2 ? 2 : (want_sw > MAX_SW ? MAX_SW : want_sw);
   while (sw > 2 && fixed + (size_t)NW * sw * stage_bytes > (size_t)(228 * 1024) / cps - 1024) --sw;
   const size_t smem = fixed + (size_t)NW * sw * stage_bytes;
   LCU_REQUIRE(smem <= 227 * 1024, "gemv: a row of K=%d does not fit in shared memory", p.K);
