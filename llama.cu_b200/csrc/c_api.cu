@@ -100,7 +100,6 @@ int lcu_set_tuning(const char* key, int value) {
   if (k == "gemv_stages") gemv_tuning_ref().nstages = value;
   else if (k == "gemv_ctas_per_sm") gemv_tuning_ref().ctas_per_sm = value;
   else if (k == "gemv_ctas_per_sm_int8") gemv_tuning_ref().ctas_per_sm_int8 = value;
-  else if (k == "side_prefetch_kb") gemv_tuning_ref().side_prefetch_kb = value;
   else if (k == "int8_factored") gemv_tuning_ref().int8_factored = value;
   else if (k == "gemv_warp_stages_int8") gemv_tuning_ref().warp_stages_int8 = value;
   else if (k == "gemv_warp_stages") gemv_tuning_ref().warp_stages = value;

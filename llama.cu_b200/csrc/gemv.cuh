@@ -47,7 +47,6 @@ struct gemv_tuning {
   int ctas_per_sm = 2;  // grid = SM count x this
   int ctas_per_sm_int8 = 3;  // same for the factored u8 single-row kernel (more resident warps: it is latency-bound)
   int variant = 1;      // m == 1: 1 = per-warp row-pair kernel (gemv1.cu), 0 / 2 = 16-row-block kernel (gemv.cu)
-  int side_prefetch_kb = 0;  // per CTA: L2 look-ahead for w1|w3 on a side stream while attention runs (measured: no gain, off)
   int int8_factored = 1;  // u8 weights: 1 = scale factored out of 64-weight groups (fast), 0 = the reference's per-weight rounding
   int warp_stages = 3;  // gemv1.cu: ring depth of every consumer warp (8 KiB per stage)
   int warp_stages_int8 = 3;  // same for the factored u8 kernel
@@ -59,8 +58,6 @@ gemv_tuning& gemv_tuning_ref();
 // preceding launch (its weight stream starts while the previous kernel drains).
 int launch_gemv(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl);
 
-// L2 look-ahead for a single-row GEMV that will be launched later with the same parameters (gemv1.cu)
-int launch_gemv_prefetch(const gemv_params& p, int epilogue, int sms, int kb_per_cta, cudaStream_t stream);
 int gemv_sm_count();
 
 // single-row kernel (gemv1.cu); called by launch_gemv after argument checks

@@ -464,23 +464,6 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
   }
 }
 
-// L2 look-ahead for a GEMV that has not been launched yet: requests, for every CTA of that future
-// launch (same grid, same row ranges), the rows after the first skip_bytes of its range up to
-// skip_bytes + pf_bytes.  Meant for a side stream while a latency-bound kernel leaves HBM idle.
-template <int EPI>
-__global__ void __launch_bounds__(32) gemv1_prefetch_kernel(const gemv_params p, const int rowbytes, const int skip_bytes, const int pf_bytes) {
-  const int pairs = (p.n_mats * p.rows_per_mat) >> 1;
-  const int pr0 = (int)(((long long)pairs * blockIdx.x) / gridDim.x);
-  const int nrows = 2 * ((int)(((long long)pairs * (blockIdx.x + 1)) / gridDim.x) - pr0);
-  const int first = skip_bytes / rowbytes;
-  const int last = min(nrows, (skip_bytes + pf_bytes) / rowbytes);
-  for (int r = first + threadIdx.x; r < last; r += 32) {
-    int mat, row;
-    map_row<EPI>(p, 2 * pr0 + r, mat, row);
-    l2_prefetch(reinterpret_cast<const uint8_t*>(p.w[mat]) + (size_t)row * rowbytes, (uint32_t)rowbytes);
-  }
-}
-
 template <int WT, int EPI>
 int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, int grid, int sw, int pf_bytes) {
   static bool attr_done[16] = {};
@@ -504,30 +487,7 @@ int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, 
   return LCU_OK;
 }
 
-int grid_of(const gemv_params& p, int sms) {
-  const gemv_tuning& t = gemv_tuning_ref();
-  const int pairs = p.n_mats * p.rows_per_mat / 2;
-  const int grid = sms * (t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);
-  return grid > pairs ? pairs : grid;
-}
-
 }  // namespace
-
-int launch_gemv_prefetch(const gemv_params& p, int epilogue, int sms, int kb_per_cta, cudaStream_t stream) {
-  const gemv_tuning& t = gemv_tuning_ref();
-  if (kb_per_cta <= 0 || t.variant != 1) return LCU_OK;
-  const int grid = grid_of(p, sms);
-  const int rowbytes = p.bs ? p.K : p.K * 2;
-  const int skip = t.prefetch_kb_per_cta * 1024, pf = kb_per_cta * 1024;
-  if (epilogue == EPI_SILU)
-    gemv1_prefetch_kernel<EPI_SILU><<<grid, 32, 0, stream>>>(p, rowbytes, skip, pf);
-  else if (epilogue == EPI_ROPE_KV)
-    gemv1_prefetch_kernel<EPI_ROPE_KV><<<grid, 32, 0, stream>>>(p, rowbytes, skip, pf);
-  else
-    gemv1_prefetch_kernel<EPI_PLAIN><<<grid, 32, 0, stream>>>(p, rowbytes, skip, pf);
-  LCU_CUDA(cudaGetLastError());
-  return LCU_OK;
-}
 
 // m == 1 entry used by launch_gemv (argument checks are done there)
 int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl, int sms) {

@@ -278,8 +278,6 @@ struct gpu_state {
   int device = 0;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev = nullptr;
-  cudaStream_t side = nullptr;               // L2 look-ahead kernels run here, beside the main stream
-  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   void* arena = nullptr;
   size_t arena_bytes = 0;
   __half *x = nullptr, *norm = nullptr, *q = nullptr, *kn = nullptr, *vn = nullptr, *att = nullptr;
@@ -339,9 +337,6 @@ context::~context() {
     if (i < c.kv_arenas.size() && c.kv_arenas[i]) cudaFree(c.kv_arenas[i]);
     if (c.gpus[i].stream) cudaStreamDestroy(c.gpus[i].stream);
     if (c.gpus[i].ev) cudaEventDestroy(c.gpus[i].ev);
-    if (c.gpus[i].side) cudaStreamDestroy(c.gpus[i].side);
-    if (c.gpus[i].ev_fork) cudaEventDestroy(c.gpus[i].ev_fork);
-    if (c.gpus[i].ev_join) cudaEventDestroy(c.gpus[i].ev_join);
   }
   if (c.t0) cudaEventDestroy(c.t0);
   if (c.t1) cudaEventDestroy(c.t1);
@@ -386,9 +381,6 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
       }
     LCU_CUDA(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
     LCU_CUDA(cudaEventCreateWithFlags(&g.ev, cudaEventDisableTiming));
-    LCU_CUDA(cudaStreamCreateWithFlags(&g.side, cudaStreamNonBlocking));
-    LCU_CUDA(cudaEventCreateWithFlags(&g.ev_fork, cudaEventDisableTiming));
-    LCU_CUDA(cudaEventCreateWithFlags(&g.ev_join, cudaEventDisableTiming));
     // scratch arena: activations for up to context_len rows, rope table, state words,
     // and (first / last GPU) token ids, logits, probabilities, token log
     carve cv;
@@ -565,7 +557,7 @@ gemv_params context_impl::params_out(int row) {
 
 int context_impl::enqueue_decode_step() {
   const model_params& p = m->params;
-  const int d = p.dim, hd = d / p.n_heads, f = m->ffn, bs = p.q_type ? p.quantization_block_size : 0;
+  const int d = p.dim, hd = d / p.n_heads, bs = p.q_type ? p.quantization_block_size : 0;
   const int pdl = opt.use_pdl;
   {
     gpu_state& g = first();
@@ -592,15 +584,6 @@ int context_impl::enqueue_decode_step() {
     const layer_weights& L = m->layers[l];
     // fused RMSNorm + wq|wk|wv + RoPE + cache write (reference llama_cu.cu:1129-1156)
     LCU_TRY(launch_gemv(params_qkv(l), EPI_ROPE_KV, g.stream, pdl && !hopped));
-    // While attention (latency-bound, a few MB) runs, HBM would idle: a side-stream kernel asks L2 for
-    // the head of every CTA's share of w1|w3, the largest stream of the layer.  Hint only, no data hazard.
-    const int side_kb = gemv_tuning_ref().side_prefetch_kb;
-    if (side_kb > 0) {
-      LCU_CUDA(cudaEventRecord(g.ev_fork, g.stream));
-      LCU_CUDA(cudaStreamWaitEvent(g.side, g.ev_fork, 0));
-      LCU_TRY(launch_gemv_prefetch(params_w13(l), EPI_SILU, gemv_sm_count(), side_kb, g.side));
-      LCU_CUDA(cudaEventRecord(g.ev_join, g.side));
-    }
     // attention over the cache (reference llama_cu.cu:1161-1171)
     attn_params at{};
     at.q = g.q; at.ldq = d;
@@ -612,7 +595,6 @@ int context_impl::enqueue_decode_step() {
     LCU_TRY(launch_gemv(params_wo(l), EPI_PLAIN, g.stream, pdl));   // wo + residual (llama_cu.cu:1174)
     LCU_TRY(launch_gemv(params_w13(l), EPI_SILU, g.stream, pdl));   // RMSNorm + w1|w3 + SiLU gate (llama_cu.cu:1176-1183)
     LCU_TRY(launch_gemv(params_w2(l), EPI_PLAIN, g.stream, pdl));   // w2 + residual (llama_cu.cu:1185)
-    if (side_kb > 0) LCU_CUDA(cudaStreamWaitEvent(g.stream, g.ev_join, 0));  // rejoin the side stream (graph capture needs it)
   }
   {
     // final RMSNorm + output matrix, softmax(T) + first-maximum token (llama_cu.cu:1191-1209)
