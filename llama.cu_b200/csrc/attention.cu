@@ -23,7 +23,8 @@ namespace {
 
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_WARPS = ATT_THREADS / 32;
-constexpr int PRE_ROUNDS = 4;  // rounds of V rows kept in registers from the first request
+constexpr int PRE_ROUNDS = 4;  // rounds of K and V rows requested together at kernel start
+constexpr int BATCH = 4;       // rounds whose row loads are issued before the first of them is used
 
 __device__ __forceinline__ void st_dsmem_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
@@ -87,36 +88,36 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
   }
   const float scale_div = sqrtf((float)HD);
 
-  // ---- pass 1: scores of the slice, rounded to half, and the slice maximum
+  // ---- pass 1: scores of the slice, rounded to half, and the slice maximum.  Rounds are taken BATCH at a time with
+  // all their row loads issued before the first use (long slices would otherwise pay one memory latency per round).
   float lmax = -CUDART_INF_F;
-  for (int base = 0; base < n; base += RPR) {
-    const int r = base / RPR;
-    const int t = base + warp * RPW + grp;
-    float s = 0.f;
-    if (t < n) {
-      uint4 kv;
-      if (r < PRE_ROUNDS) {
-        kv = kreg[0];
+  for (int base = 0; base < n; base += BATCH * RPR) {
+    uint4 kv[BATCH];
 #pragma unroll
-        for (int j = 1; j < PRE_ROUNDS; ++j)
-          if (r == j) kv = kreg[j];
-      } else {
-        kv = *reinterpret_cast<const uint4*>(kbase + (size_t)t * HD);
-      }
-      const __half2* h = reinterpret_cast<const __half2*>(&kv);
+    for (int j = 0; j < BATCH; ++j) {
+      const int t = base + j * RPR + warp * RPW + grp;
+      if (base == 0 && j < PRE_ROUNDS) kv[j] = kreg[j < PRE_ROUNDS ? j : 0];
+      else if (t < n) kv[j] = *reinterpret_cast<const uint4*>(kbase + (size_t)t * HD);
+      else kv[j] = make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < BATCH; ++j) {
+      const int t = base + j * RPR + warp * RPW + grp;
+      float s = 0.f;
+      const __half2* h = reinterpret_cast<const __half2*>(&kv[j]);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float2 f = __half22float2(h[i]);
         s += q[2 * i] * f.x;
         s += q[2 * i + 1] * f.y;
       }
-    }
 #pragma unroll
-    for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (t < n) {
-      const __half sh = __float2half(s / scale_div);
-      if (gl == 0) sc[t] = sh;
-      lmax = fmaxf(lmax, __half2float(sh));
+      for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (t < n) {
+        const __half sh = __float2half(s / scale_div);
+        if (gl == 0) sc[t] = sh;
+        lmax = fmaxf(lmax, __half2float(sh));
+      }
     }
   }
   lmax = warp_max(lmax);
@@ -148,28 +149,29 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
     if (m > -CUDART_INF_F) gsum += xsum[r] * expf(m - gmax);  // an empty slice contributes nothing
   }
 
-  // ---- pass 2: probabilities rounded to half, times V
+  // ---- pass 2: probabilities rounded to half, times V (rounds in batches, as above)
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int base = 0; base < n; base += RPR) {
-    const int r = base / RPR;
-    const int t = base + warp * RPW + grp;
-    if (t < n) {
-      const float pr = __half2float(__float2half(expf(__half2float(sc[t]) - gmax) / gsum));
-      uint4 vv;
-      if (r < PRE_ROUNDS) {
-        vv = vreg[0];
+  for (int base = 0; base < n; base += BATCH * RPR) {
+    uint4 vv[BATCH];
 #pragma unroll
-        for (int j = 1; j < PRE_ROUNDS; ++j)
-          if (r == j) vv = vreg[j];
-      } else {
-        vv = *reinterpret_cast<const uint4*>(vbase + (size_t)t * HD);
-      }
-      const __half2* h = reinterpret_cast<const __half2*>(&vv);
+    for (int j = 0; j < BATCH; ++j) {
+      const int t = base + j * RPR + warp * RPW + grp;
+      if (base == 0 && j < PRE_ROUNDS) vv[j] = vreg[j < PRE_ROUNDS ? j : 0];
+      else if (t < n) vv[j] = *reinterpret_cast<const uint4*>(vbase + (size_t)t * HD);
+      else vv[j] = make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 f = __half22float2(h[i]);
-        acc[2 * i] += pr * f.x;
-        acc[2 * i + 1] += pr * f.y;
+    for (int j = 0; j < BATCH; ++j) {
+      const int t = base + j * RPR + warp * RPW + grp;
+      if (t < n) {
+        const float pr = __half2float(__float2half(expf(__half2float(sc[t]) - gmax) / gsum));
+        const __half2* h = reinterpret_cast<const __half2*>(&vv[j]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __half22float2(h[i]);
+          acc[2 * i] += pr * f.x;
+          acc[2 * i + 1] += pr * f.y;
+        }
       }
     }
   }

@@ -24,8 +24,10 @@ def run_tokens(ctx, prompt, steps):
     return toks
 
 
-@pytest.mark.parametrize("bs", [0, 128])
-def test_small_model_matches_oracle(lcu, bs):
+@pytest.mark.parametrize("bs,prompt_len", [(0, 12), (128, 12), (0, 40), (128, 40)])
+def test_small_model_matches_oracle(lcu, bs, prompt_len):
+    """12-token prompts go through the multi-row GEMV passes; 40-token prompts through the tcgen05 GEMM (u8 weights
+    with prefill_u8_deq_min_rows lowered: expanded to fp16 first) and the tiled prompt attention."""
     scale = 0.08
     model = lcu.Model.synthetic(block_size=bs, seed=1234, scale=scale, **SMALL)
     ctx = lcu.Context(model, context_len=64, temperature=0.8)
@@ -39,9 +41,14 @@ def test_small_model_matches_oracle(lcu, bs):
         assert (wq == q.reshape(-1)).all() and (model.tensor_host("layers.1.attention.wq", 1) == s.reshape(-1)).all()
     else:
         assert (wq == want).all()
-    prompt = O.synth_tokens(12, 1234, lo=3, hi=1000)
+    prompt = O.synth_tokens(prompt_len, 1234, lo=3, hi=1000)
     mine, theirs = [], []
-    t, to = ctx.next_token(prompt), om.next_token(prompt)
+    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 16))
+    try:
+        t = ctx.next_token(prompt)
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 48))
+    to = om.next_token(prompt)
     for step in range(20):
         p, po = f32(ctx.probs()), f32(om.probs())
         assert np.abs(p - po).max() <= 0.02 * po.max() + 1e-4, step  # same distribution up to summation order / libm ulps
@@ -53,7 +60,7 @@ def test_small_model_matches_oracle(lcu, bs):
         t, to = ctx.next_token([to]), om.next_token([to])
     agree = np.mean(np.array(mine) == np.array(theirs))
     assert agree >= 0.9, (mine, theirs)
-    assert ctx.tokens_left() == 64 - 12 - 20
+    assert ctx.tokens_left() == 64 - prompt_len - 20
     om.close()
     ctx.close()
     model.close()
