@@ -17,11 +17,15 @@ struct attn_params {
   int ctx_len;
   int n_heads;
   int head_dim;
+  int* err;               // device error word for the bounded waits of the streaming kernel (nullptr: that kernel is not used)
 };
 
 // m query rows; `cluster` CTAs (1, 2, 4 or 8) share one (row, head); max_T bounds pos + m so that
 // shared memory can be sized without reading the device position.
 int launch_attention(const attn_params& p, int m, int cluster, int max_T, cudaStream_t stream, int pdl);
+
+// -1 = rows through a shared-memory ring of bulk copies when a CTA's slice can exceed 64 rows (default), 0 = never, 1 = always
+void attention_set_stream_mode(int mode);
 
 // Prompt rows: 64-row query tiles on tensor cores (attention_prefill.cu); same arithmetic, no clusters.
 int launch_attention_prefill(const attn_params& p, int m, int max_T, cudaStream_t stream);

@@ -108,6 +108,7 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "prefill_tc_min_rows") prefill_tuning_ref().tc_min_rows = value;
   else if (k == "prefill_tc_tile_n") prefill_tuning_ref().tc_tile_n = value;
   else if (k == "prefill_u8_deq_min_rows") prefill_tuning_ref().u8_deq_min_rows = value;
+  else if (k == "attn_stream") attention_set_stream_mode(value);
   else if (k == "prefill_attn_tiles") prefill_tuning_ref().attn_tiles = value;
   else if (k == "prefill_tc_split") prefill_tuning_ref().tc_split = value;
   else if (k == "prefill_tc_pair") prefill_tuning_ref().tc_pair = value;
@@ -268,6 +269,7 @@ int lcu_attention(void* out_dev, const void* q_dev, const void* k_cache_dev, con
   at.ctx_len = ctx_len;
   at.n_heads = n_heads;
   at.head_dim = dim / n_heads;
+  at.err = scratch_err();
   if (cluster == 0) return launch_attention_prefill(at, m, pos0 + m, (cudaStream_t)stream);
   return launch_attention(at, m, cluster, pos0 + m, (cudaStream_t)stream, 0);
 }

@@ -590,7 +590,7 @@ int context_impl::enqueue_decode_step() {
     at.k_cache = k_cache[l]; at.v_cache = v_cache[l];
     at.out = g.att; at.ldo = d;
     at.pos = g.state;
-    at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd;
+    at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd; at.err = g.state + 3;
     LCU_TRY(launch_attention(at, 1, opt.attn_cluster, opt.context_len, g.stream, pdl));
     LCU_TRY(launch_gemv(params_wo(l), EPI_PLAIN, g.stream, pdl));   // wo + residual (llama_cu.cu:1174)
     LCU_TRY(launch_gemv(params_w13(l), EPI_SILU, g.stream, pdl));   // RMSNorm + w1|w3 + SiLU gate (llama_cu.cu:1176-1183)
@@ -641,7 +641,7 @@ int context_impl::enqueue_prefill(int m_rows) {
     at.k_cache = k_cache[l]; at.v_cache = v_cache[l];
     at.out = g.att; at.ldo = d;
     at.pos = g.state;
-    at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd;
+    at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd; at.err = g.state + 3;
     if (prefill_tuning_ref().attn_tiles)
       LCU_TRY(launch_attention_prefill(at, m_rows, start_pos + m_rows, g.stream));
     else

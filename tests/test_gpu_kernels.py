@@ -216,6 +216,27 @@ def test_attention_against_oracle(lcu, m, T0, H, cluster):
         assert np.abs(f32(out) - f32(orf)).max() <= 4e-3
 
 
+@pytest.mark.parametrize("T0,H,hd,cluster", [(0, 2, 128, 1), (37, 2, 128, 4), (383, 4, 128, 8), (2047, 2, 128, 8), (600, 1, 128, 2), (1500, 3, 64, 8),
+                                              (129, 2, 128, 1)])
+def test_attention_streaming_kernel_gives_the_same_bits(lcu, T0, H, hd, cluster):
+    """Long slices come through a shared-memory ring of bulk copies instead of per-thread loads; thread-to-row
+    assignment and summation order are the same, so the two kernels must agree bit for bit."""
+    rng = np.random.default_rng(T0 + H)
+    dim, T = H * hd, T0 + 1
+    q, k, v = f16(rng.standard_normal((1, dim))), f16(rng.standard_normal((T, dim))), f16(rng.standard_normal((T, dim)))
+    outs = []
+    try:
+        for mode in (0, 1):
+            lcu.check(lcu.lib.lcu_set_tuning(b"attn_stream", mode))
+            outs.append(lcu.attention(q, k, v, H, T0, cluster))
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"attn_stream", -1))
+    assert (outs[0] == outs[1]).all()
+    oo = np.zeros_like(q)
+    L.orc_attention(oo.reshape(-1), q.reshape(-1), k.reshape(-1), v.reshape(-1), 1, T, dim, H, T0, 0)
+    assert np.abs(f32(outs[1]) - f32(oo)).max() <= 4e-3
+
+
 @pytest.mark.parametrize("m,T0,cluster", [(1, 50, 4), (70, 9, 0)])
 def test_attention_head_dim_64(lcu, m, T0, cluster):
     rng = np.random.default_rng(8)
