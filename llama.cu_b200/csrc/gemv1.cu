@@ -132,20 +132,27 @@ __device__ __forceinline__ void step(float (&accs)[NACC][4], const int s, const 
 
 // Factored u8, block size >= 128: the two 64-byte steps of a 128-weight block share their scale, so the eight
 // tensor-core products of both steps are summed before the one multiplication by the scale.
-__device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const int sp, const int flip, const int c, const int g, const uint8_t* seg0,
-                                                   const uint8_t* xseg, const uint8_t* st, const float* xs64, const int ci, const int bs) {
+template <bool FULL>
+__device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const int sp, const int flip, const int c, const int g, const int vb,
+                                                   const uint8_t* seg0, const uint8_t* xseg, const uint8_t* st, const float* xs64, const int ci,
+                                                   const int bs) {
   constexpr int ROWB = geom<2>::ROWB, SEG = geom<2>::SEG, NSTEPS = geom<2>::NSTEPS;
   constexpr int CHUNK_K = ROWB;
   float* acc = accs[sp % NACC];
   const uint32_t M = 0x64646464u;  // bytes -> halves 1024 + q
+  // a row's last chunk may be short; its length is a multiple of the block size, so a 128-byte pair is valid or not as a whole
+  const bool ok = FULL || (sp << 7) < vb;
   float t[4][4];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int off = (((2 * sp + h) ^ flip) << 6) + c * 16;  // odd segments take the two steps in swapped order (bank spread)
-    const uint4 lo = *reinterpret_cast<const uint4*>(seg0 + off);
-    const uint4 hi = *reinterpret_cast<const uint4*>(seg0 + ROWB + off);
-    const uint4 x0 = *reinterpret_cast<const uint4*>(xseg + 2 * off);
-    const uint4 x1 = *reinterpret_cast<const uint4*>(xseg + 2 * off + 16);
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo, x0 = lo, x1 = lo;
+    if (ok) {
+      lo = *reinterpret_cast<const uint4*>(seg0 + off);
+      hi = *reinterpret_cast<const uint4*>(seg0 + ROWB + off);
+      x0 = *reinterpret_cast<const uint4*>(xseg + 2 * off);
+      x1 = *reinterpret_cast<const uint4*>(xseg + 2 * off + 16);
+    }
     float* ta = t[2 * h];
     float* tb = t[2 * h + 1];
     ta[0] = ta[1] = ta[2] = ta[3] = 0.f;
@@ -155,6 +162,7 @@ __device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const
     mma_16816(ta, __byte_perm(lo.z, M, 0x4140), __byte_perm(hi.z, M, 0x4140), __byte_perm(lo.z, M, 0x4342), __byte_perm(hi.z, M, 0x4342), x1.x, x1.y);
     mma_16816(tb, __byte_perm(lo.w, M, 0x4140), __byte_perm(hi.w, M, 0x4140), __byte_perm(lo.w, M, 0x4342), __byte_perm(hi.w, M, 0x4342), x1.z, x1.w);
   }
+  if (!ok) return;  // (after the warp-wide tensor-core instructions)
   const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
   const int si = (g * SEG + (sp << 7)) >> bs;
   const float sl = __half2float(scs[si]), sh = __half2float(scs[geom<2>::SC_ROW / 2 + si]);
@@ -395,7 +403,10 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
       // shared loads of all eight steps can be issued ahead of the tensor-core instructions.
       if (WT == 2 && cbytes == ROWB && bs_shift >= 7) {
 #pragma unroll
-        for (int sp = 0; sp < NSTEPS / 2; ++sp) step_pair_factored(accs, sp, flip, c, g, seg0, xseg, st, xs64, ci, bs_shift);
+        for (int sp = 0; sp < NSTEPS / 2; ++sp) step_pair_factored<true>(accs, sp, flip, c, g, SEG, seg0, xseg, st, xs64, ci, bs_shift);
+      } else if (WT == 2 && bs_shift >= 7) {
+#pragma unroll
+        for (int sp = 0; sp < NSTEPS / 2; ++sp) step_pair_factored<false>(accs, sp, flip, c, g, vb, seg0, xseg, st, xs64, ci, bs_shift);
       } else if (cbytes == ROWB) {
 #pragma unroll
         for (int s = 0; s < NSTEPS; ++s) step<WT, true>(accs, s, flip, c, g, SEG, seg0, xseg, st, xs64, ci, bs_shift);
