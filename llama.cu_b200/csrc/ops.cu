@@ -73,7 +73,7 @@ __global__ void rope_table_kernel(float2* table, int ctx_len, int head_dim, floa
 }
 
 __global__ void rope_scatter_kernel(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
-                                    const float2* rope, const int* pos_ptr, int pos_value, int m, int dim, int n_heads, int ctx_len) {
+                                    const float2* rope, const int* pos_ptr, int pos_value, int m, int dim, int n_heads, int ctx_len, int ld) {
   const int r = blockIdx.y;
   const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
   if (c >= dim) return;
@@ -82,7 +82,7 @@ __global__ void rope_scatter_kernel(__half* q, const __half* k_new, const __half
   const int pos = (pos_ptr ? *pos_ptr : pos_value) + r;
   const float2 cs = rope[(size_t)pos * (hd >> 1) + (j >> 1)];
   const float a_cos = cs.x, a_sin = cs.y;
-  const size_t src = (size_t)r * dim + c;
+  const size_t src = (size_t)r * ld + c;
   const size_t dst = ((size_t)head * ctx_len + pos) * hd + j;
   {
     const float real = __half2float(q[src]), imag = __half2float(q[src + 1]);
@@ -398,9 +398,36 @@ int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cud
 
 int launch_rope_scatter(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
                         const float2* rope, const int* pos, int pos_value, int m, int dim, int n_heads, int ctx_len,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, int ld) {
   dim3 grid((dim / 2 + 127) / 128, m);
-  rope_scatter_kernel<<<grid, 128, 0, stream>>>(q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len);
+  rope_scatter_kernel<<<grid, 128, 0, stream>>>(q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len,
+                                                ld > 0 ? ld : dim);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+// rows of [a | b] pairs: out[r][j] = silu(ab[r][j]) * ab[r][f + j], f % 8 == 0
+__global__ void __launch_bounds__(256) silu_rows_kernel(__half* out, const __half* ab, int m, int f) {
+  const int fv = f >> 3;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)m * fv) return;
+  const size_t r = i / fv, jv = i - r * fv;
+  const uint4 av = reinterpret_cast<const uint4*>(ab + r * 2 * f)[jv], bv = reinterpret_cast<const uint4*>(ab + r * 2 * f + f)[jv];
+  const __half* ah = reinterpret_cast<const __half*>(&av);
+  const __half* bh = reinterpret_cast<const __half*>(&bv);
+  __align__(16) __half o[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float val = __half2float(ah[e]);
+    o[e] = __float2half(val / (1.0f + expf(-val)) * __half2float(bh[e]));
+  }
+  reinterpret_cast<uint4*>(out + r * f)[jv] = *reinterpret_cast<const uint4*>(o);
+}
+
+int launch_silu_rows(__half* out, const __half* ab, int m, int f, cudaStream_t stream) {
+  LCU_REQUIRE(f % 8 == 0 && (((uintptr_t)out | (uintptr_t)ab) & 15) == 0, "silu_rows: rows of %d elements are not 16-byte vectors", f);
+  const size_t n = (size_t)m * (f / 8);
+  silu_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(out, ab, m, f);
   LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }

@@ -21,10 +21,12 @@ int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cud
 // *pos, or pos_value when pos == nullptr.
 int launch_rope_scatter(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
                         const float2* rope, const int* pos, int pos_value, int m, int dim, int n_heads, int ctx_len,
-                        cudaStream_t stream);
+                        cudaStream_t stream, int ld = 0);  // ld: row stride of q / k_new / v_new in elements (0 = dim)
 
 // out = half(silu(float(a)) * float(b)) element-wise
 int launch_silu(__half* out, const __half* a, const __half* b, size_t n, cudaStream_t stream);
+// rows of [a | b]: out[r][j] = silu(ab[r][j]) * ab[r][f + j] for the fused w1|w3 prompt product
+int launch_silu_rows(__half* out, const __half* ab, int m, int f, cudaStream_t stream);
 
 // probs = softmax(logits / temp) rounded to half (written over `probs`), token = first index of the
 // maximum probability.  Also advances the decode state for device-chained generation:

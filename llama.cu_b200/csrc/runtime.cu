@@ -632,12 +632,27 @@ int context_impl::enqueue_prefill(int m_rows) {
     const layer_weights& L = m->layers[l];
     int* err = g.state + 3;
     LCU_TRY(launch_rms_norm(g.norm, g.x, L.attn_norm, m_rows, d, p.norm_eps, g.stream));
-    LCU_TRY(matmul_rows(g.q, g.norm, L.wq, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
-    LCU_TRY(matmul_rows(g.kn, g.norm, L.wk, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
-    LCU_TRY(matmul_rows(g.vn, g.norm, L.wv, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
-    LCU_TRY(launch_rope_scatter(g.q, g.kn, g.vn, k_cache[l], v_cache[l], g.rope, g.state, 0, m_rows, d, p.n_heads, opt.context_len, g.stream));
+    // fp16 weights lie back to back in the arena (wq, wk, wv; w1, w3), and so do the q / new-k / new-v and the h1 / h3
+    // scratch buffers: the three (two) products run as one GEMM over the stacked matrix into rows of [q | k | v]
+    // ([h1 | h3]) - more tiles per launch, fewer launches
+    const bool fuse = prefill_tuning_ref().fuse && bs == 0 && m_rows > 8;
+    const bool qkv_stacked = fuse && (char*)L.wk.w == (char*)L.wq.w + (size_t)d * d * 2 && (char*)L.wv.w == (char*)L.wk.w + (size_t)d * d * 2 &&
+                             g.kn == g.q + (size_t)opt.context_len * d && g.vn == g.kn + (size_t)opt.context_len * d;
+    const int ldq = qkv_stacked ? 3 * d : d;
+    if (qkv_stacked) {
+      dev_matrix wqkv = L.wq;
+      wqkv.rows = 3 * (size_t)d;
+      LCU_TRY(matmul_rows(g.q, g.norm, wqkv, m_rows, 0.f, err, g.stream));
+      LCU_TRY(launch_rope_scatter(g.q, g.q + d, g.q + 2 * d, k_cache[l], v_cache[l], g.rope, g.state, 0, m_rows, d, p.n_heads, opt.context_len,
+                                  g.stream, ldq));
+    } else {
+      LCU_TRY(matmul_rows(g.q, g.norm, L.wq, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
+      LCU_TRY(matmul_rows(g.kn, g.norm, L.wk, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
+      LCU_TRY(matmul_rows(g.vn, g.norm, L.wv, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
+      LCU_TRY(launch_rope_scatter(g.q, g.kn, g.vn, k_cache[l], v_cache[l], g.rope, g.state, 0, m_rows, d, p.n_heads, opt.context_len, g.stream));
+    }
     attn_params at{};
-    at.q = g.q; at.ldq = d;
+    at.q = g.q; at.ldq = ldq;
     at.k_cache = k_cache[l]; at.v_cache = v_cache[l];
     at.out = g.att; at.ldo = d;
     at.pos = g.state;
@@ -648,9 +663,16 @@ int context_impl::enqueue_prefill(int m_rows) {
       LCU_TRY(launch_attention(at, m_rows, 1, start_pos + m_rows, g.stream, 0));
     LCU_TRY(matmul_rows(g.x, g.att, L.wo, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
     LCU_TRY(launch_rms_norm(g.norm, g.x, L.ffn_norm, m_rows, d, p.norm_eps, g.stream));
-    LCU_TRY(matmul_rows(g.h1, g.norm, L.w1, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
-    LCU_TRY(matmul_rows(g.h3, g.norm, L.w3, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
-    LCU_TRY(launch_silu(g.hs, g.h1, g.h3, (size_t)m_rows * f, g.stream));
+    if (fuse && (char*)L.w3.w == (char*)L.w1.w + (size_t)f * d * 2 && g.h3 == g.h1 + (size_t)opt.context_len * f) {
+      dev_matrix w13 = L.w1;
+      w13.rows = 2 * (size_t)f;
+      LCU_TRY(matmul_rows(g.h1, g.norm, w13, m_rows, 0.f, err, g.stream));
+      LCU_TRY(launch_silu_rows(g.hs, g.h1, m_rows, f, g.stream));
+    } else {
+      LCU_TRY(matmul_rows(g.h1, g.norm, L.w1, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
+      LCU_TRY(matmul_rows(g.h3, g.norm, L.w3, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
+      LCU_TRY(launch_silu(g.hs, g.h1, g.h3, (size_t)m_rows * f, g.stream));
+    }
     LCU_TRY(matmul_rows(g.x, g.hs, L.w2, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
   }
   {

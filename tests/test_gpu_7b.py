@@ -3,9 +3,11 @@ reference itself produced on a B200 (tests/golden/reference_7b_tokens.json), fp1
 
 Batch-1 greedy decoding of a random-init model is chaotic: the reference's own two kernel sets
 (matmul_type 4 vs 1) part ways after 13 steps on this input, because a different fp32 summation order
-moves logits by an fp16 ulp and top-2 probability margins are often that small.  So the test pins what
-is stable: a free-running prefix, teacher-forced top-1 agreement, and that every disagreement sits at a
-margin of a few fp16 ulps of the reference's own probabilities."""
+moves logits by an fp16 ulp and top-2 probability margins are often that small.  Where the free run leaves
+the reference's is therefore luck (31 steps with one tiling of the prompt GEMMs, 12 with another); what the
+test pins is what is stable: the free run may part only at a step where the reference itself is undecided
+(top-1 / top-2 margin of a few fp16 ulps of its own probabilities), teacher-forced top-1 agreement is high,
+and every teacher-forced disagreement sits at such a margin too."""
 import json
 import os
 
@@ -30,8 +32,10 @@ def test_7b_tokens_against_reference(lcu, bs):
     chained, _ = ctx.decode_chained(first, 256)
     free = np.concatenate([[first], chained])
     diverge = int(np.argmax(free != ref)) if (free != ref).any() else len(ref)
-    # the reference's own matmul_type 1 leaves its matmul_type 4 after 13 steps on the fp16 model
-    assert diverge >= 13, diverge
+    # (the reference's own matmul_type 1 leaves its matmul_type 4 after 13 steps on the fp16 model)
+    assert diverge >= 4, diverge
+    if diverge < len(ref):
+        assert margin[diverge] <= 5e-4, (diverge, margin[diverge])
     ctx.clear_tokens()
     forced = [ctx.next_token(prompt)]
     for i in range(256):
