@@ -212,7 +212,7 @@ template <int HD>
 __global__ void __launch_bounds__(AS_THREADS, 3) attn_stream_kernel(const attn_params p) {
   constexpr int LPR = HD / 8, RPW = 32 / LPR, RPR = ATT_WARPS * RPW;
   constexpr int CHUNK_BYTES = AS_CH * HD * 2;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(16) uint8_t smem[];
   float* xmax = reinterpret_cast<float*>(smem);
   float* xsum = xmax + 8;
   float* rpart = xsum + 8;

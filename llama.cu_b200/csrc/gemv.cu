@@ -60,7 +60,7 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t word, uint32_t selecto
 }
 
 template <int WT /*0 fp16, 1 u8*/, int EPI>
-__global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, const int nstages, const int pf_bytes, const int mode) {
+__global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, const int nstages, const int pf_bytes) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full[MAX_STAGES], empty[MAX_STAGES]
   float* red = reinterpret_cast<float*>(smem + 256);
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
   if (tid == 0) {
     for (int i = 0; i < nstages; ++i) {
       mbar_init(smem_u32(&bars[i]), WT == 0 ? 1 : 33);
-      mbar_init(smem_u32(&bars[MAX_STAGES + i]), mode == 0 ? NCW : 1);
+      mbar_init(smem_u32(&bars[MAX_STAGES + i]), NCW);
     }
     fence_mbar_init();
   }
@@ -195,10 +195,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
   int pos = 0;
   if (EPI == EPI_ROPE_KV) pos = *p.pos;
 
-  // Two ways to share a stage among the consumer warps: mode 0 - every warp takes 1/8 of the 64-byte
-  // steps of every stage; mode 1 - whole stages go to the warps in turn, so the hand-over latency of one
-  // stage (mbarrier wake-up, first shared loads) overlaps with the work of the other warps on other stages.
-  int stage = 0, turn = 0;
+  // every consumer warp takes 1/8 of the 64-byte steps of every stage
+  int stage = 0;
   uint32_t phase = 0;
   for (int b = 0; b < nblocks; ++b) {
     const int rb = r0 + b * RB;
@@ -208,12 +206,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
 #pragma unroll
     for (int a = 0; a < NACC; ++a) accs[a][0] = accs[a][1] = accs[a][2] = accs[a][3] = 0.f;
     for (int ci = 0; ci < nchunks; ++ci) {
-     if (mode == 0 || turn == warp) {
       mbar_wait(smem_u32(&bars[stage]), phase, p.err, DEV_ERR_FULL_WAIT);
       const int cbytes = min(KCB, rowbytes - ci * KCB);
       const int nsteps = cbytes >> 6;
       const uint8_t* st = stages + (size_t)stage * STAGE_BYTES;
-      const int s_first = mode == 0 ? warp : 0, s_stride = mode == 0 ? NCW : 1;
+      const int s_first = warp, s_stride = NCW;
 #pragma unroll
       for (int it = 0; it < KCB / 64; ++it) {
         const int s = s_first + it * s_stride;
@@ -254,8 +251,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[MAX_STAGES + stage]));
-     }
-      if (++turn == NCW) turn = 0;
       if (++stage == nstages) {
         stage = 0;
         phase ^= 1;
@@ -339,7 +334,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) gemv_kernel(const gemv_params p, 
 }
 
 template <int WT, int EPI>
-int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, int grid, int nstages, int pf_bytes, int mode) {
+int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, int grid, int nstages, int pf_bytes) {
   static bool attr_done[16] = {};
   int dev = 0;
   LCU_CUDA(cudaGetDevice(&dev));
@@ -357,7 +352,7 @@ int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemv_kernel<WT, EPI>, p, nstages, pf_bytes, mode));
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemv_kernel<WT, EPI>, p, nstages, pf_bytes));
   return LCU_OK;
 }
 
@@ -504,20 +499,19 @@ int launch_gemv(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl
   LCU_REQUIRE(smem <= 227 * 1024, "gemv: m=%d rows of K=%d do not fit in shared memory", p.m, p.K);
   const int units = p.n_mats * p.rows_per_mat / 2;
   const int pf_bytes = t.prefetch_kb_per_cta * 1024;
-  const int mode = (t.variant == 2 && p.m == 1) ? 1 : 0;
   int grid = sm_count() * (t.ctas_per_sm < 1 ? 1 : t.ctas_per_sm);
   if (grid > units) grid = units;
   const bool q = p.bs != 0;
   switch (epilogue) {
     case EPI_PLAIN:
       LCU_REQUIRE(p.n_mats == 1, "gemv: plain epilogue takes one matrix");
-      return q ? launch_one<1, EPI_PLAIN>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode) : launch_one<0, EPI_PLAIN>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode);
+      return q ? launch_one<1, EPI_PLAIN>(p, stream, pdl, smem, grid, nstages, pf_bytes) : launch_one<0, EPI_PLAIN>(p, stream, pdl, smem, grid, nstages, pf_bytes);
     case EPI_ROPE_KV:
       LCU_REQUIRE(p.n_mats == 3 && p.head_dim % 2 == 0 && p.rows_per_mat % p.head_dim == 0, "gemv: bad q/k/v shapes");
-      return q ? launch_one<1, EPI_ROPE_KV>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode) : launch_one<0, EPI_ROPE_KV>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode);
+      return q ? launch_one<1, EPI_ROPE_KV>(p, stream, pdl, smem, grid, nstages, pf_bytes) : launch_one<0, EPI_ROPE_KV>(p, stream, pdl, smem, grid, nstages, pf_bytes);
     case EPI_SILU:
       LCU_REQUIRE(p.n_mats == 2, "gemv: SiLU-gate epilogue takes w1 and w3");
-      return q ? launch_one<1, EPI_SILU>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode) : launch_one<0, EPI_SILU>(p, stream, pdl, smem, grid, nstages, pf_bytes, mode);
+      return q ? launch_one<1, EPI_SILU>(p, stream, pdl, smem, grid, nstages, pf_bytes) : launch_one<0, EPI_SILU>(p, stream, pdl, smem, grid, nstages, pf_bytes);
   }
   LCU_REQUIRE(false, "gemv: unknown epilogue %d", epilogue);
 }

@@ -46,7 +46,7 @@ struct gemv_tuning {
   int nstages = 4;      // shared-memory ring depth (16 rows x 1 KiB per stage)
   int ctas_per_sm = 2;  // grid = SM count x this
   int ctas_per_sm_int8 = 3;  // same for the factored u8 single-row kernel (more resident warps: it is latency-bound)
-  int variant = 1;      // m == 1: 1 = per-warp row-pair kernel (gemv1.cu), 0 / 2 = 16-row-block kernel (gemv.cu)
+  int variant = 1;      // m == 1: 1 = per-warp row-pair kernel (gemv1.cu), 0 = 16-row-block kernel (gemv.cu)
   int int8_factored = 1;  // u8 weights: 1 = scale factored out of 64-weight groups (fast), 0 = the reference's per-weight rounding
   int warp_stages = 3;  // gemv1.cu: ring depth of every consumer warp (8 KiB per stage)
   int warp_stages_int8 = 3;  // same for the factored u8 kernel
