@@ -282,7 +282,7 @@ struct gpu_state {
   size_t arena_bytes = 0;
   __half *x = nullptr, *norm = nullptr, *q = nullptr, *kn = nullptr, *vn = nullptr, *att = nullptr;
   __half *h1 = nullptr, *h3 = nullptr, *hs = nullptr;
-  __half* deq = nullptr;  // u8 models: one dequantized [ffn][dim] matrix for the prompt GEMM
+  __half* deq = nullptr;  // u8 models: the dequantized matrix (or stack of matrices) of the prompt GEMM in flight
   size_t deq_halves = 0;
   float2* rope = nullptr;
   int* state = nullptr;  // [0] position, [1] step counter, [2] last token, [3] error word
@@ -387,7 +387,7 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     const size_t o_x = cv.take(ctxl * d * 2), o_norm = cv.take(ctxl * d * 2), o_q = cv.take(ctxl * d * 2);
     const size_t o_kn = cv.take(ctxl * d * 2), o_vn = cv.take(ctxl * d * 2), o_att = cv.take(ctxl * d * 2);
     const size_t o_h1 = cv.take(ctxl * f * 2), o_h3 = cv.take(ctxl * f * 2), o_hs = cv.take(ctxl * f * 2);
-    const size_t deq_halves = p.q_type ? (size_t)f * d : 0;
+    const size_t deq_halves = p.q_type ? std::max((size_t)2 * f * d, (size_t)3 * d * d) : 0;  // room for the stacked w1|w3 or wq|wk|wv
     const size_t o_deq = cv.take(deq_halves * 2);
     const size_t o_rope = cv.take(ctxl * (hd / 2) * sizeof(float2));
     const size_t o_state = cv.take(64);
@@ -635,13 +635,25 @@ int context_impl::enqueue_prefill(int m_rows) {
     // fp16 weights lie back to back in the arena (wq, wk, wv; w1, w3), and so do the q / new-k / new-v and the h1 / h3
     // scratch buffers: the three (two) products run as one GEMM over the stacked matrix into rows of [q | k | v]
     // ([h1 | h3]) - more tiles per launch, fewer launches
-    const bool fuse = prefill_tuning_ref().fuse && bs == 0 && m_rows > 8;
-    const bool qkv_stacked = fuse && (char*)L.wk.w == (char*)L.wq.w + (size_t)d * d * 2 && (char*)L.wv.w == (char*)L.wk.w + (size_t)d * d * 2 &&
-                             g.kn == g.q + (size_t)opt.context_len * d && g.vn == g.kn + (size_t)opt.context_len * d;
+    const prefill_tuning& pt = prefill_tuning_ref();
+    const bool rows_stacked = g.kn == g.q + (size_t)opt.context_len * d && g.vn == g.kn + (size_t)opt.context_len * d &&
+                              g.h3 == g.h1 + (size_t)opt.context_len * f;
+    // u8 weights: the same, with the matrices expanded to fp16 one after the other into the scratch buffer
+    const bool fuse_u8 = pt.fuse && bs > 0 && rows_stacked && pt.u8_deq_min_rows > 0 && m_rows >= pt.u8_deq_min_rows && g.deq != nullptr;
+    const bool fuse = pt.fuse && bs == 0 && m_rows > 8 && rows_stacked;
+    const bool qkv_stacked = fuse_u8 || (fuse && (char*)L.wk.w == (char*)L.wq.w + (size_t)d * d * 2 && (char*)L.wv.w == (char*)L.wk.w + (size_t)d * d * 2);
     const int ldq = qkv_stacked ? 3 * d : d;
     if (qkv_stacked) {
       dev_matrix wqkv = L.wq;
       wqkv.rows = 3 * (size_t)d;
+      if (fuse_u8) {
+        const dev_matrix* src[3] = {&L.wq, &L.wk, &L.wv};
+        for (int i = 0; i < 3; ++i)
+          LCU_TRY(launch_dequantize_absmax_uint8(g.deq + (size_t)i * d * d, src[i]->sc, (const uint8_t*)src[i]->w, d, d, bs, g.stream));
+        wqkv.w = g.deq;
+        wqkv.sc = nullptr;
+        wqkv.bs = 0;
+      }
       LCU_TRY(matmul_rows(g.q, g.norm, wqkv, m_rows, 0.f, err, g.stream));
       LCU_TRY(launch_rope_scatter(g.q, g.q + d, g.q + 2 * d, k_cache[l], v_cache[l], g.rope, g.state, 0, m_rows, d, p.n_heads, opt.context_len,
                                   g.stream, ldq));
@@ -663,9 +675,16 @@ int context_impl::enqueue_prefill(int m_rows) {
       LCU_TRY(launch_attention(at, m_rows, 1, start_pos + m_rows, g.stream, 0));
     LCU_TRY(matmul_rows(g.x, g.att, L.wo, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
     LCU_TRY(launch_rms_norm(g.norm, g.x, L.ffn_norm, m_rows, d, p.norm_eps, g.stream));
-    if (fuse && (char*)L.w3.w == (char*)L.w1.w + (size_t)f * d * 2 && g.h3 == g.h1 + (size_t)opt.context_len * f) {
+    if (fuse_u8 || (fuse && (char*)L.w3.w == (char*)L.w1.w + (size_t)f * d * 2)) {
       dev_matrix w13 = L.w1;
       w13.rows = 2 * (size_t)f;
+      if (fuse_u8) {
+        LCU_TRY(launch_dequantize_absmax_uint8(g.deq, L.w1.sc, (const uint8_t*)L.w1.w, f, d, bs, g.stream));
+        LCU_TRY(launch_dequantize_absmax_uint8(g.deq + (size_t)f * d, L.w3.sc, (const uint8_t*)L.w3.w, f, d, bs, g.stream));
+        w13.w = g.deq;
+        w13.sc = nullptr;
+        w13.bs = 0;
+      }
       LCU_TRY(matmul_rows(g.h1, g.norm, w13, m_rows, 0.f, err, g.stream));
       LCU_TRY(launch_silu_rows(g.hs, g.h1, m_rows, f, g.stream));
     } else {

@@ -27,7 +27,7 @@ def run_tokens(ctx, prompt, steps):
 @pytest.mark.parametrize("bs,prompt_len", [(0, 12), (128, 12), (0, 40), (128, 40)])
 def test_small_model_matches_oracle(lcu, bs, prompt_len):
     """12-token prompts go through the multi-row GEMV passes; 40-token prompts through the tcgen05 GEMM (u8 weights
-    with prefill_u8_deq_min_rows lowered: expanded to fp16 first) and the tiled prompt attention."""
+    expanded to fp16 first) and the tiled prompt attention."""
     scale = 0.08
     model = lcu.Model.synthetic(block_size=bs, seed=1234, scale=scale, **SMALL)
     ctx = lcu.Context(model, context_len=64, temperature=0.8)
@@ -43,11 +43,12 @@ def test_small_model_matches_oracle(lcu, bs, prompt_len):
         assert (wq == want).all()
     prompt = O.synth_tokens(prompt_len, 1234, lo=3, hi=1000)
     mine, theirs = [], []
-    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 16))
+    # u8 weights: once through the GEMV passes (threshold raised), once through dequantization + tcgen05 GEMM (default)
+    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 9 if prompt_len >= 40 else 1000))
     try:
         t = ctx.next_token(prompt)
     finally:
-        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 48))
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 9))
     to = om.next_token(prompt)
     for step in range(20):
         p, po = f32(ctx.probs()), f32(om.probs())
