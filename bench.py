@@ -16,7 +16,7 @@ Printed JSON line (rank 0):
             rotation with CUDA events: algorithmic bytes per launch / mean launch time vs the measured
             HBM copy bandwidth
   prefill   (N = 1) the prompt path: tok/s of a 512-token prompt through lcu_context_next_token, and the largest
-            prompt GEMM (512 x 4096 x 11008, tcgen05 kernel) timed alone with CUDA events against the measured
+            prompt GEMM (the stacked w1|w3 product, 512 x 4096 x 22016, tcgen05 kernel) timed alone with CUDA events against the measured
             dense bf16 tensor peak
   cpu_baseline  the CPU oracle on a bounded sample (one of the 32 layers + the output head), host threads
 With N > 1 (torchrun) every rank runs an independent replica on its own GPU (the path does not
@@ -162,7 +162,7 @@ def prefill_sample(lcu, ctx, cfg, ffn, profile=False):
         lcu.check(lcu.lib.lcu_profiler_stop())
     if cfg["block_size"] == 0:
         peak, src = measured_tensor_peak()
-        m, k, n = PREFILL_LEN, cfg["dim"], ffn
+        m, k, n = PREFILL_LEN, cfg["dim"], 2 * ffn  # the stacked w1|w3 product, the largest GEMM of a prompt pass
         ms = lcu.bench_matmul_f16_ms(m, k, n, reps=50)
         tf = 2.0 * m * k * n / (ms * 1e-3) / 1e12
         m2 = 2048
