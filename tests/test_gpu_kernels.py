@@ -117,7 +117,9 @@ def test_matmul_small_shapes(lcu, m, k, n, bs, beta):
 
 @pytest.mark.parametrize("m,k,n,beta,tile", [(9, 64, 32, 0.0, 0), (16, 256, 32, 1.0, 0), (128, 64, 128, 0.0, 128), (129, 512, 192, 1.0, 0),
                                              (200, 1024, 256, 1.0, 64), (77, 4096, 1024, 0.0, 32), (300, 11008, 128, 0.0, 0),
-                                             (257, 4096, 4096, 1.0, 0)])
+                                             (257, 4096, 4096, 1.0, 0),
+                                             # more pair tiles than SM pairs: the persistent loop takes several tiles per pair
+                                             (300, 256, 22016, 1.0, 0), (257, 320, 12288, 0.0, 0)])
 def test_prefill_tensor_core_gemm(lcu, m, k, n, beta, tile):
     """fp16 weights with more than 8 rows run on tcgen05 with the accumulator in tensor memory: compared with
     the oracle's binary64-accumulated product (tolerance 2e-3 of the largest output: fp32 accumulation in a
