@@ -154,6 +154,11 @@ int lcu_bench_decode_kernel(void* ctx, int which, int reps, float* ms_per_launch
 /* cudaProfilerStart / cudaProfilerStop, so that a profiler attached with --profile-from-start off sees only the timed region */
 int lcu_profiler_start(void);
 int lcu_profiler_stop(void);
+/* Self-test of the failure path: launches one warp that waits on an mbarrier nothing completes.  The bounded wait
+ * expires after about one second of SM clock, the kernel ends normally, and the call returns status 4
+ * (LCU_ERR_DEVICE_WAIT) with the device code (0x101) in *device_code_out; the context stays usable.  No counterpart
+ * in the reference (its kernels have no waits). */
+int lcu_selftest_bounded_wait(int* device_code_out);
 /* lcu_matmul_nt_f16 (beta = 0, default stream) launched `reps` times back to back between two CUDA events on that
  * stream: mean milliseconds per launch.  Used to put the prompt GEMM against the tensor-core roofline. */
 int lcu_bench_matmul_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, int reps, float* ms_per_launch_out);

@@ -399,6 +399,24 @@ int lcu_profiler_stop(void) {
   LCU_CUDA(cudaProfilerStop());
   return LCU_OK;
 }
+int lcu_selftest_bounded_wait(int* device_code_out) {
+  NEED_DEVICE();
+  int* err = scratch_err();
+  LCU_REQUIRE(err != nullptr, "selftest: no scratch");
+  LCU_CUDA(cudaMemset(err, 0, 4));
+  int rc = run_bounded_wait_probe(err, 0);
+  if (rc) return rc;
+  LCU_CUDA(cudaDeviceSynchronize());
+  int code = 0;
+  LCU_CUDA(cudaMemcpy(&code, err, 4, cudaMemcpyDeviceToHost));
+  LCU_CUDA(cudaMemset(err, 0, 4));
+  if (device_code_out) *device_code_out = code;
+  if (code != 0) {
+    set_last_error("a kernel gave up on a bounded wait (device code 0x%x)", code);
+    return LCU_ERR_DEVICE_WAIT;
+  }
+  return LCU_OK;
+}
 int lcu_bench_matmul_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, int reps, float* ms_per_launch_out) {
   NEED_DEVICE();
   LCU_REQUIRE(reps >= 1 && ms_per_launch_out, "bench_matmul: bad arguments");

@@ -424,6 +424,24 @@ __global__ void __launch_bounds__(256) silu_rows_kernel(__half* out, const __hal
   reinterpret_cast<uint4*>(out + r * f)[jv] = *reinterpret_cast<const uint4*>(o);
 }
 
+// Self-test of the bounded wait every pipeline in this library relies on: one warp waits on an mbarrier that nothing
+// will ever complete.  The wait gives up after about a second of SM clock, records its code and the kernel ends.
+__global__ void bounded_wait_probe_kernel(int* err) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  mbar_wait(smem_u32(&bar), 0, err, DEV_ERR_FULL_WAIT);
+}
+
+int run_bounded_wait_probe(int* err_word, cudaStream_t stream) {
+  bounded_wait_probe_kernel<<<1, 32, 0, stream>>>(err_word);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
 int launch_silu_rows(__half* out, const __half* ab, int m, int f, cudaStream_t stream) {
   LCU_REQUIRE(f % 8 == 0 && (((uintptr_t)out | (uintptr_t)ab) & 15) == 0, "silu_rows: rows of %d elements are not 16-byte vectors", f);
   const size_t n = (size_t)m * (f / 8);

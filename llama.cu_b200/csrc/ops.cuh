@@ -25,6 +25,8 @@ int launch_rope_scatter(__half* q, const __half* k_new, const __half* v_new, __h
 
 // out = half(silu(float(a)) * float(b)) element-wise
 int launch_silu(__half* out, const __half* a, const __half* b, size_t n, cudaStream_t stream);
+// one warp waiting on an mbarrier that never completes: the wait expires (about a second) and stores its code in *err_word
+int run_bounded_wait_probe(int* err_word, cudaStream_t stream);
 // rows of [a | b]: out[r][j] = silu(ab[r][j]) * ab[r][f + j] for the fused w1|w3 prompt product
 int launch_silu_rows(__half* out, const __half* ab, int m, int f, cudaStream_t stream);
 

@@ -269,3 +269,22 @@ def test_logits_head_first_maximum_and_ties(lcu):
     flat = np.full(1000, f16(0.25), np.uint16)
     tok3, _ = lcu.logits_head(flat, 1.0)
     assert tok3 == 0
+
+
+def test_bounded_wait_reports_and_leaves_the_context_usable(lcu):
+    """Every mbarrier wait in the kernels is bounded.  A probe kernel waits on a barrier that nothing completes: the
+    wait runs out (about a second), the kernel ends, the host gets status 4 with the device code, and the next
+    operation on the same context works."""
+    import ctypes as C
+    import time
+    code = C.c_int(0)
+    t0 = time.perf_counter()
+    rc = lcu.lib.lcu_selftest_bounded_wait(C.byref(code))
+    dt = time.perf_counter() - t0
+    assert rc == 4 and code.value == 0x101, (rc, hex(code.value))
+    assert b"bounded wait" in lcu.lib.lcu_last_error()
+    assert 0.3 < dt < 10.0, dt
+    x = f16(np.ones((1, 256)))
+    w = f16(np.full((64, 256), 0.5))
+    y = lcu.matmul_nt(x, w)
+    assert (f32(y) == 128.0).all()
