@@ -304,9 +304,11 @@ struct context_impl {
   int* h_stage = nullptr;                // pinned: [0] position, [1] zero, [2] token read-back
   short* h_ids = nullptr;                // pinned token staging [context_len]
   cudaEvent_t t0 = nullptr, t1 = nullptr;
-  cudaGraphExec_t graph = nullptr;
+  // two captured decode steps: [0] for positions whose attention slices stay within the register-path kernel's
+  // 64 rows per CTA, [1] for longer contexts (streaming attention kernel); the host knows the position of every step
+  cudaGraphExec_t graph[2] = {nullptr, nullptr};
   bool graph_failed = false;
-  bool warmed = false;                   // the first decode step runs un-captured (one-time kernel attribute set-up)
+  bool warmed_variant[2] = {false, false};
   int last_row = 0;                      // row of x that holds the last token's residual stream
 
   gpu_state& first() { return gpus.front(); }
@@ -319,17 +321,18 @@ struct context_impl {
   gemv_params params_w2(int l);
   gemv_params params_out(int row);
   int enqueue_hop(int from, int to, int m_rows);
-  int enqueue_decode_step();
+  int enqueue_decode_step(int long_ctx);
   int enqueue_prefill(int m_rows);
-  int build_graph();
-  int run_decode_step();
+  int build_graph(int variant);
+  int run_decode_step(int n_keys);
   int stage_inputs(const short* tokens, int n);
 };
 
 context::~context() {
   if (!impl) return;
   context_impl& c = *impl;
-  if (c.graph) cudaGraphExecDestroy(c.graph);
+  for (int v = 0; v < 2; ++v)
+    if (c.graph[v]) cudaGraphExecDestroy(c.graph[v]);
   for (size_t i = 0; i < c.gpus.size(); ++i) {
     device_guard g(c.gpus[i].device);
     cudaDeviceSynchronize();
@@ -555,7 +558,7 @@ gemv_params context_impl::params_out(int row) {
   return a;
 }
 
-int context_impl::enqueue_decode_step() {
+int context_impl::enqueue_decode_step(int long_ctx) {
   const model_params& p = m->params;
   const int d = p.dim, hd = d / p.n_heads, bs = p.q_type ? p.quantization_block_size : 0;
   const int pdl = opt.use_pdl;
@@ -591,7 +594,8 @@ int context_impl::enqueue_decode_step() {
     at.out = g.att; at.ldo = d;
     at.pos = g.state;
     at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd; at.err = g.state + 3;
-    LCU_TRY(launch_attention(at, 1, opt.attn_cluster, opt.context_len, g.stream, pdl));
+    // max_T sizes the kernel's shared memory and picks its variant: up to 64 rows per CTA the register-path kernel
+    LCU_TRY(launch_attention(at, 1, opt.attn_cluster, long_ctx ? opt.context_len : std::min(opt.context_len, 64 * opt.attn_cluster), g.stream, pdl));
     LCU_TRY(launch_gemv(params_wo(l), EPI_PLAIN, g.stream, pdl));   // wo + residual (llama_cu.cu:1174)
     LCU_TRY(launch_gemv(params_w13(l), EPI_SILU, g.stream, pdl));   // RMSNorm + w1|w3 + SiLU gate (llama_cu.cu:1176-1183)
     LCU_TRY(launch_gemv(params_w2(l), EPI_PLAIN, g.stream, pdl));   // w2 + residual (llama_cu.cu:1185)
@@ -712,7 +716,7 @@ int context_impl::enqueue_prefill(int m_rows) {
   return LCU_OK;
 }
 
-int context_impl::build_graph() {
+int context_impl::build_graph(int variant) {
   gpu_state& g0 = first();
   device_guard dg(g0.device);
   cudaGraph_t graph = nullptr;
@@ -720,42 +724,43 @@ int context_impl::build_graph() {
     cudaGetLastError();
     return LCU_ERR_CUDA;
   }
-  int rc = enqueue_decode_step();
+  int rc = enqueue_decode_step(variant);
   cudaError_t e = cudaStreamEndCapture(g0.stream, &graph);
   if (rc != LCU_OK || e != cudaSuccess || graph == nullptr) {
     if (graph) cudaGraphDestroy(graph);
     cudaGetLastError();
     return rc ? rc : LCU_ERR_CUDA;
   }
-  e = cudaGraphInstantiate(&this->graph, graph, 0);
+  e = cudaGraphInstantiate(&this->graph[variant], graph, 0);
   cudaGraphDestroy(graph);
   if (e != cudaSuccess) {
     cudaGetLastError();
-    this->graph = nullptr;
+    this->graph[variant] = nullptr;
     set_last_error("cudaGraphInstantiate: %s", cudaGetErrorString(e));
     return LCU_ERR_CUDA;
   }
   return LCU_OK;
 }
 
-int context_impl::run_decode_step() {
-  if (!warmed) {
-    warmed = true;
-    return enqueue_decode_step();
+int context_impl::run_decode_step(int n_keys) {
+  const int variant = n_keys > 64 * opt.attn_cluster ? 1 : 0;
+  if (!warmed_variant[variant]) {  // first use of a variant runs un-captured (function attributes, tensor maps, ...)
+    warmed_variant[variant] = true;
+    return enqueue_decode_step(variant);
   }
-  if (opt.use_graph && !graph && !graph_failed) {
-    if (build_graph() != LCU_OK) {
+  if (opt.use_graph && !graph[variant] && !graph_failed) {
+    if (build_graph(variant) != LCU_OK) {
       graph_failed = true;
       fprintf(stderr, "llama_cu_b200: CUDA graph capture of the decode step failed (%s); launching kernels directly\n",
               last_error());
     }
   }
-  if (graph) {
+  if (graph[variant]) {
     device_guard dg(first().device);
-    LCU_CUDA(cudaGraphLaunch(graph, first().stream));
+    LCU_CUDA(cudaGraphLaunch(graph[variant], first().stream));
     return LCU_OK;
   }
-  return enqueue_decode_step();
+  return enqueue_decode_step(variant);
 }
 
 // position word (and a zeroed step counter) to every stage, token ids to stage 0
@@ -794,7 +799,7 @@ int context::next_token(const short* tokens, int n, int* token_out) {
     LCU_REQUIRE(tokens[i] >= 0 && (uint32_t)tokens[i] < c.m->params.n_vocab, "next_token: token id %d outside the vocabulary", tokens[i]);
   LCU_TRY(c.stage_inputs(tokens, n));
   if (n == 1)
-    LCU_TRY(c.run_decode_step());
+    LCU_TRY(c.run_decode_step(c.start_pos + 1));
   else
     LCU_TRY(c.enqueue_prefill(n));
   c.last_row = n == 1 ? 0 : n - 1;
@@ -818,7 +823,7 @@ int context::decode_chained(short first_token, int n_steps, short* tokens_out, f
   LCU_TRY(c.stage_inputs(&first_token, 1));
   device_guard dg(c.first().device);
   LCU_CUDA(cudaEventRecord(c.t0, c.first().stream));
-  for (int i = 0; i < n_steps; ++i) LCU_TRY(c.run_decode_step());
+  for (int i = 0; i < n_steps; ++i) LCU_TRY(c.run_decode_step(c.start_pos + i + 1));
   LCU_CUDA(cudaEventRecord(c.t1, c.first().stream));
   LCU_CUDA(cudaMemcpyAsync(c.h_ids, c.log, (size_t)n_steps * 2, cudaMemcpyDeviceToHost, c.first().stream));
   LCU_CUDA(cudaMemcpyAsync(c.h_stage + 2, c.last().state + 2, 8, cudaMemcpyDeviceToHost, c.first().stream));
