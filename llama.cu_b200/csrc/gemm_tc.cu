@@ -13,8 +13,11 @@
 //             tcgen05.commit on its `empty` mbarrier; a last commit signals the epilogue;
 //   warps 2-5 - epilogue: each warp reads its 32-lane quadrant of the accumulator with tcgen05.ld
 //             (32 columns at a time), adds beta * out, rounds to half and stores 64-byte row pieces.
-// No multicast, no clusters.  Every mbarrier wait is bounded: on expiry the kernel records a code in
-// the error word, skips ahead and still frees its tensor memory.
+// Two kernels share these roles: gemm_tc_kernel (one SM per tile, optionally a cluster of 2 or 4 CTAs that
+// splits K and reduces through distributed shared memory - for few rows) and gemm_tc_pair_kernel (two SMs per
+// 256-row tile with tcgen05.mma.cta_group::2, persistent, two accumulators in tensor memory - for many rows).
+// No TMA multicast anywhere.  Every mbarrier wait is bounded: on expiry the kernel records a code in the error
+// word, skips ahead and still frees its tensor memory.
 #include <cuda.h>
 
 #include <mutex>
