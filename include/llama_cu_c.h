@@ -89,7 +89,8 @@ int lcu_rope_scatter_static(void* q_dev, const void* k_new_dev, const void* v_ne
 /* matmul_qk + softmax_rows + matmul_qkv, llama_cu.cu:400-531 (launches at 1163-1171), fused:
  * q [m][dim] rotated, caches head-major as above holding positions 0 .. pos0+m-1; out [m][dim].
  * cluster = 1, 2, 4, 8: one thread-block cluster of that many CTAs per (row, head), the decode kernel;
- * cluster = 0: 64-row query tiles on tensor cores, the prompt kernel. */
+ * cluster = 0: 64-row query tiles on warp-level tensor-core instructions (one fused kernel);
+ * cluster = -1: the prompt path on tcgen05 (scores to a temporary fp16 buffer, softmax, probabilities x V). */
 int lcu_attention(void* out_dev, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev, int pos0, int m, int dim,
                   int n_heads, int ctx_len, int cluster, void* stream);
 /* softmax_rows with temperature on the logits + the host-side first-maximum search,

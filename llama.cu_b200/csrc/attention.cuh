@@ -30,4 +30,9 @@ void attention_set_stream_mode(int mode);
 // Prompt rows: 64-row query tiles on tensor cores (attention_prefill.cu); same arithmetic, no clusters.
 int launch_attention_prefill(const attn_params& p, int m, int max_T, cudaStream_t stream);
 
+// Prompt rows on tcgen05 (attention_tc.cu): scores to a [heads][m_cap][round_up(ctx_len, 128)] fp16 buffer, softmax in
+// place, probabilities times V.  attention_tc_scratch_halves gives the buffer size in elements.
+size_t attention_tc_scratch_halves(int n_heads, int m_cap, int ctx_len);
+int launch_attention_tc(const attn_params& p, int m, int max_T, __half* scores, int m_cap, cudaStream_t stream);
+
 }  // namespace lcu

@@ -1,0 +1,329 @@
+// Prompt attention on tcgen05: the reference's three-step chain (matmul_qk -> softmax_rows -> matmul_qkv,
+// llama_cu.cu:400-531) with both contractions on the 5th-generation tensor cores.
+//
+//   1. attn_qk_kernel   S[h][r][t] = half( (q_r . k_t) / sqrtf(head_dim) )    128 x 128 tiles, K = head_dim, tiles above
+//                       the causal diagonal are skipped; Q and K tiles arrive by 3-D TMA (heads are one coordinate)
+//   2. attn_softmax_kernel  P = softmax over t <= pos0 + r of every row, in place, with the reference's summation order
+//                       (256 strided partial sums, xor trees); columns after the row's last key up to the end of its
+//                       row tile's key range are zeroed so that step 3 can multiply whole key blocks
+//   3. attn_pv_kernel   out[r][h*hd + j] = half( sum_t float(P[h][r][t]) float(v[t][j]) )   A = P (K-major, from the
+//                       score buffer), B = V read as it lies in the cache ([t][j]: an MN-major operand), K loop over the
+//                       64-key blocks up to the row tile's causal limit
+//
+// The score / probability buffer [heads][rows][keys] lives in HBM as in the reference (fp16, written once, read twice);
+// the rounding points are the reference's.  Every mbarrier wait is bounded.
+#include "attention.cuh"
+#include "tc_common.cuh"
+
+namespace lcu {
+namespace {
+
+constexpr int AT_BM = 128;   // query rows per tile
+constexpr int AT_BN = 128;   // keys per score tile
+constexpr int AT_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+
+struct attn_tc_params {
+  __half* scores;     // [heads][m_cap][t_cap]
+  __half* out;        // [m][ldo]
+  int ldo;
+  const int* pos;     // device scalar: position of query row 0 (nullptr: pos_value)
+  int pos_value;
+  int m, m_cap, t_cap, n_heads;
+  int* err;
+};
+
+// ------------------------------------------------------------------------------------------------ 1. scores
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS) attn_qk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                                             const attn_tc_params p) {
+  constexpr int NKB = HD / 64;  // 64-wide k-blocks of the head dimension, all loaded at once
+  constexpr uint32_t TILE_BYTES = 128 * 64 * 2;
+  constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * NKB * TILE_BYTES);  // [0] operands landed, [1] accumulator ready
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * AT_BN, m0 = blockIdx.y * AT_BM, head = blockIdx.z;
+  const int pos0 = p.pos ? *p.pos : p.pos_value;
+  if (n0 > pos0 + m0 + AT_BM - 1) return;  // every key of this tile lies in the future of every row of the tile
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bars[0]), 1);
+    mbar_init(smem_u32(&bars[1]), 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)AT_BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t full = smem_u32(&bars[0]);
+      mbar_arrive_expect_tx(full, 2 * NKB * TILE_BYTES);
+      for (int kb = 0; kb < NKB; ++kb) {
+        tma_load_3d(base + kb * TILE_BYTES, &map_q, kb * 64, head, m0, full);                 // [128 rows][64] of this head
+        tma_load_3d(base + (NKB + kb) * TILE_BYTES, &map_k, kb * 64, n0, head, full);         // [128 keys][64]
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      if (mbar_wait(smem_u32(&bars[0]), 0, p.err, DEV_ERR_FULL_WAIT)) {
+        tc_fence_after();
+#pragma unroll
+        for (int kb = 0; kb < NKB; ++kb) {
+          const uint64_t a_desc = smem_desc_sw128(base + kb * TILE_BYTES), b_desc = smem_desc_sw128(base + (NKB + kb) * TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0);
+        }
+      }
+      tc_commit(smem_u32(&bars[1]));
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = m0 + quad * 32 + lane;
+    const bool ok = mbar_wait(smem_u32(&bars[1]), 0, p.err, DEV_ERR_TMEM_WAIT);
+    tc_fence_after();
+    if (__all_sync(0xffffffffu, ok && *(volatile int*)p.err == 0)) {
+      const float scale_div = sqrtf((float)HD);
+      __half* srow = p.scores + ((size_t)head * p.m_cap + row) * p.t_cap + n0;
+#pragma unroll 1
+      for (int c = 0; c < AT_BN; c += 32) {
+        uint32_t r[32];
+        tc_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.m) {
+          __align__(16) __half2 h[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) h[i] = __floats2half2_rn(__uint_as_float(r[2 * i]) / scale_div, __uint_as_float(r[2 * i + 1]) / scale_div);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(srow + c)[i] = reinterpret_cast<const uint4*>(h)[i];
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)AT_BN) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ 2. softmax
+// One block per (row, head); the reference's softmax_rows (llama_cu.cu:433-499) with temperature 1 over the row's
+// causal prefix, its order of summation included.
+__global__ void __launch_bounds__(256) attn_softmax_kernel(const attn_tc_params p) {
+  const int r = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pos0 = p.pos ? *p.pos : p.pos_value;
+  const int L = pos0 + r + 1;                                                     // keys this row sees
+  const int m0 = (r / AT_BM) * AT_BM;
+  const int k_end = min(p.t_cap, ((pos0 + m0 + AT_BM + 63) / 64) * 64);           // key range step 3 walks for this row tile
+  __half* row = p.scores + ((size_t)head * p.m_cap + r) * p.t_cap;
+  __shared__ float s_warp[8];
+  __shared__ float s_b[2];
+  float mx = -CUDART_INF_F;
+  for (int i = tid; i < L; i += 256) mx = fmaxf(mx, __half2float(row[i]));
+  mx = warp_max(mx);
+  if (lane == 0) s_warp[warp] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float t = s_warp[0];
+    for (int w = 1; w < 8; ++w) t = fmaxf(t, s_warp[w]);
+    s_b[0] = t;
+  }
+  __syncthreads();
+  mx = s_b[0];
+  float s = 0.f;
+  for (int i = tid; i < L; i += 256) s += expf(__half2float(row[i]) - mx);  // thread t: elements t, t + 256, ... in order
+  s = warp_sum(s);
+  if (lane == 0) s_warp[warp] = s;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < 8 ? s_warp[lane] : 0.f;
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) s_b[1] = t;
+  }
+  __syncthreads();
+  const float sum = s_b[1];
+  for (int i = tid; i < k_end; i += 256) row[i] = i < L ? __float2half(expf(__half2float(row[i]) - mx) / sum) : __ushort_as_half(0);
+}
+
+// ------------------------------------------------------------------------------------------------ 3. P . V
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS, 1) attn_pv_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_v,
+                                                                const attn_tc_params p, int nstages) {
+  constexpr int ND = HD / 64;                       // 64-wide blocks of the head dimension (the operand's N atoms)
+  constexpr uint32_t A_BYTES = AT_BM * 64 * 2;      // P: 128 rows x 64 keys
+  constexpr uint32_t V_ATOM = 64 * 64 * 2;          // V: 64 keys x 64 dims
+  constexpr uint32_t STAGE = A_BYTES + ND * V_ATOM;
+  // fp32 accumulate, fp16 operands, A K-major, B MN-major (bit 16), N = HD, M = 128
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)nstages * STAGE);  // full[8], empty[8], accumulator ready
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * AT_BM, head = blockIdx.y;
+  const int pos0 = p.pos ? *p.pos : p.pos_value;
+  const int nk = min(p.t_cap, ((pos0 + m0 + AT_BM + 63) / 64) * 64) / 64;  // 64-key blocks up to this row tile's causal limit
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < nstages; ++i) {
+      mbar_init(smem_u32(&bars[i]), 1);
+      mbar_init(smem_u32(&bars[8 + i]), 1);
+    }
+    mbar_init(smem_u32(&bars[16]), 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(HD < 32 ? 32 : HD)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nk; ++kb) {
+        const int s = kb % nstages, use = kb / nstages;
+        if (use > 0 && !mbar_wait(smem_u32(&bars[8 + s]), (use - 1) & 1, p.err, DEV_ERR_EMPTY_WAIT)) break;
+        const uint32_t full = smem_u32(&bars[s]);
+        const uint32_t dst = base + (uint32_t)s * STAGE;
+        mbar_arrive_expect_tx(full, STAGE);
+        tma_load_3d(dst, &map_p, kb * 64, m0, head, full);  // probabilities [128 rows][64 keys]
+        for (int j = 0; j < ND; ++j) tma_load_3d(dst + A_BYTES + j * V_ATOM, &map_v, j * 64, kb * 64, head, full);  // V [64 keys][64 dims]
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < nk && ok; ++kb) {
+        const int s = kb % nstages, use = kb / nstages;
+        ok = mbar_wait(smem_u32(&bars[s]), use & 1, p.err, DEV_ERR_FULL_WAIT);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = base + (uint32_t)s * STAGE;
+        const uint64_t a_desc = smem_desc_sw128(a_addr);
+        const uint64_t b_desc = smem_desc_sw128_mn(a_addr + A_BYTES, V_ATOM);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // 16 keys per instruction: 32 bytes along A's rows, two 8-key groups (2 x 1024 bytes) of V
+          tc_mma_f16(tmem_base, a_desc + 2 * k, b_desc + (uint64_t)(k * 2048 >> 4), IDESC, (kb | k) != 0);
+        tc_commit(smem_u32(&bars[8 + s]));
+      }
+      tc_commit(smem_u32(&bars[16]));
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = m0 + quad * 32 + lane;
+    const bool ok = mbar_wait(smem_u32(&bars[16]), 0, p.err, DEV_ERR_TMEM_WAIT);
+    tc_fence_after();
+    if (__all_sync(0xffffffffu, ok && *(volatile int*)p.err == 0)) {
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t r[32];
+        tc_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.m) {
+          __align__(16) __half2 h[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) h[i] = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+          __half* o = p.out + (size_t)row * p.ldo + head * HD + c;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(o)[i] = reinterpret_cast<const uint4*>(h)[i];
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(HD < 32 ? 32 : HD)) : "memory");
+  }
+}
+
+template <int HD>
+int launch_tc_hd(const attn_params& p, int m, int max_T, __half* scores, int m_cap, int t_cap, cudaStream_t stream) {
+  CUtensorMap map_q, map_k, map_p, map_v;
+  const uint64_t H = (uint64_t)p.n_heads, ctx = (uint64_t)p.ctx_len;
+  {
+    // q rows [m][ldq], head h at column h * HD: dims (HD, heads, rows)
+    const uint64_t dims[3] = {(uint64_t)HD, H, (uint64_t)m}, strides[2] = {(uint64_t)HD * 2, (uint64_t)p.ldq * 2};
+    const uint32_t box[3] = {64, 1, 128};
+    int rc = tc_encode_map(&map_q, p.q, 3, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    // caches [heads][ctx][HD]: dims (HD, positions, heads)
+    const uint64_t dims[3] = {(uint64_t)HD, ctx, H}, strides[2] = {(uint64_t)HD * 2, ctx * HD * 2};
+    const uint32_t box_k[3] = {64, 128, 1}, box_v[3] = {64, 64, 1};
+    int rc = tc_encode_map(&map_k, p.k_cache, 3, dims, strides, box_k);
+    if (rc) return rc;
+    rc = tc_encode_map(&map_v, p.v_cache, 3, dims, strides, box_v);
+    if (rc) return rc;
+  }
+  {
+    // scores / probabilities [heads][m_cap][t_cap]: dims (keys, rows, heads)
+    const uint64_t dims[3] = {(uint64_t)t_cap, (uint64_t)m_cap, H}, strides[2] = {(uint64_t)t_cap * 2, (uint64_t)m_cap * t_cap * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    int rc = tc_encode_map(&map_p, scores, 3, dims, strides, box);
+    if (rc) return rc;
+  }
+  attn_tc_params q{};
+  q.scores = scores; q.out = p.out; q.ldo = p.ldo; q.pos = p.pos; q.pos_value = p.pos_value;
+  q.m = m; q.m_cap = m_cap; q.t_cap = t_cap; q.n_heads = p.n_heads; q.err = p.err;
+  static bool attr_done[16] = {};
+  int dev = 0;
+  LCU_CUDA(cudaGetDevice(&dev));
+  constexpr size_t QK_SMEM = 2 * (HD / 64) * 128 * 64 * 2 + 1024 + 64;
+  constexpr size_t PV_STAGE = 128 * 64 * 2 + (HD / 64) * 64 * 64 * 2;
+  const int nstages = 6;
+  const size_t pv_smem = nstages * PV_STAGE + 1024 + 256;
+  if (dev < 16 && !attr_done[dev]) {
+    LCU_CUDA(cudaFuncSetAttribute(attn_qk_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QK_SMEM));
+    LCU_CUDA(cudaFuncSetAttribute(attn_pv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem));
+    attr_done[dev] = true;
+  }
+  const int m_tiles = (m + AT_BM - 1) / AT_BM, t_tiles = (max_T + AT_BN - 1) / AT_BN;
+  attn_qk_kernel<HD><<<dim3(t_tiles, m_tiles, p.n_heads), AT_THREADS, QK_SMEM, stream>>>(map_q, map_k, q);
+  LCU_CUDA(cudaGetLastError());
+  attn_softmax_kernel<<<dim3(m, p.n_heads), 256, 0, stream>>>(q);
+  LCU_CUDA(cudaGetLastError());
+  attn_pv_kernel<HD><<<dim3(m_tiles, p.n_heads), AT_THREADS, pv_smem, stream>>>(map_p, map_v, q, nstages);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+}  // namespace
+
+size_t attention_tc_scratch_halves(int n_heads, int m_cap, int ctx_len) {
+  const size_t t_cap = ((size_t)ctx_len + 127) / 128 * 128;
+  return (size_t)n_heads * m_cap * t_cap;
+}
+
+int launch_attention_tc(const attn_params& p, int m, int max_T, __half* scores, int m_cap, cudaStream_t stream) {
+  LCU_REQUIRE(m >= 1 && m <= m_cap && p.n_heads >= 1, "attention: %d rows do not fit the score buffer (%d)", m, m_cap);
+  LCU_REQUIRE(max_T >= 1 && max_T <= p.ctx_len, "attention: %d positions exceed the context length %d", max_T, p.ctx_len);
+  LCU_REQUIRE(p.err != nullptr && scores != nullptr, "attention: the tensor-core path needs an error word and a score buffer");
+  LCU_REQUIRE(p.ldq % 8 == 0 && p.ldo % 8 == 0 && ((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.out & 15) == 0, "attention: rows must be 16-byte aligned");
+  const int t_cap = (p.ctx_len + 127) / 128 * 128;
+  if (p.head_dim == 128) return launch_tc_hd<128>(p, m, max_T, scores, m_cap, t_cap, stream);
+  if (p.head_dim == 64) return launch_tc_hd<64>(p, m, max_T, scores, m_cap, t_cap, stream);
+  LCU_REQUIRE(false, "attention: head_dim %d not supported (64 or 128)", p.head_dim);
+}
+
+}  // namespace lcu

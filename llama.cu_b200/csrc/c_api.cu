@@ -272,6 +272,16 @@ int lcu_attention(void* out_dev, const void* q_dev, const void* k_cache_dev, con
   at.head_dim = dim / n_heads;
   at.err = scratch_err();
   if (cluster == 0) return launch_attention_prefill(at, m, pos0 + m, (cudaStream_t)stream);
+  if (cluster == -1) {  // tcgen05 path; this stand-alone entry owns no scratch, so the score buffer lives for the call only
+    const size_t halves = attention_tc_scratch_halves(n_heads, m, ctx_len);
+    __half* scores = nullptr;
+    LCU_CUDA(cudaMalloc(&scores, halves * 2));
+    cudaMemsetAsync(scores, 0, halves * 2, (cudaStream_t)stream);
+    int rc = launch_attention_tc(at, m, pos0 + m, scores, m, (cudaStream_t)stream);
+    cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(scores);
+    return rc;
+  }
   return launch_attention(at, m, cluster, pos0 + m, (cudaStream_t)stream, 0);
 }
 int lcu_logits_head(void* probs_dev, const void* logits_dev, int n_vocab, float temperature, int* token_host, void* stream) {

@@ -24,6 +24,7 @@
 #include <unordered_map>
 
 #include "gemm_tc.cuh"
+#include "tc_common.cuh"
 
 namespace lcu {
 namespace {
@@ -31,50 +32,6 @@ namespace {
 constexpr int BM = 128;      // output rows (tokens) per tile = TMEM lanes
 constexpr int BK = 64;       // K per stage: 64 halves = one 128-byte swizzled row
 constexpr int TC_THREADS = 192;
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-               "l"(map), "r"(x), "r"(y), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// 32 lanes x 32 columns of fp32: thread t of the warp gets row (quadrant base + t), 32 consecutive columns
-__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-
-// shared-memory matrix descriptor of a K-major tile stored as 128-byte swizzled rows:
-// start address (16-byte units), leading byte offset 1 (unused for swizzled K-major), stride byte offset
-// 1024 (eight 128-byte rows form one swizzle atom), descriptor version 1, layout type 2 = 128-byte swizzle
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
 
 // half(acc + beta * previous) for 32 consecutive outputs of one row (64 bytes, 16-byte aligned)
 __device__ __forceinline__ void store_row_piece(__half* o, const float (&acc)[32], float beta) {
@@ -537,6 +494,24 @@ int launch_pair(__half* out, const __half* lhs, int ldx, const __half* w, int m,
 }
 
 }  // namespace
+
+int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+  encode_fn enc;
+  int rc = get_encoder(&enc);
+  if (rc) return rc;
+  LCU_REQUIRE(rank == 2 || rank == 3, "tensor map: rank %d not supported", rank);
+  cuuint64_t d[3], st[2];
+  cuuint32_t b[3], es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    if (i > 0) st[i - 1] = strides_bytes[i - 1];
+  }
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  LCU_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (rank %d) failed with code %d", rank, (int)r);
+  return LCU_OK;
+}
 
 bool gemm_tc_supported(int m, int N, int K, int ldx, const void* lhs, const void* w, const void* out) {
   return m >= 1 && N % 32 == 0 && K % BK == 0 && ldx % 8 == 0 && ((uintptr_t)lhs & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
