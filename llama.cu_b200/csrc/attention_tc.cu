@@ -1,17 +1,19 @@
 // Prompt attention on tcgen05: the reference's three-step chain (matmul_qk -> softmax_rows -> matmul_qkv,
 // llama_cu.cu:400-531) with both contractions on the 5th-generation tensor cores.
 //
-//   1. attn_qk_kernel   S[h][r][t] = half( (q_r . k_t) / sqrtf(head_dim) )    128 x 128 tiles, K = head_dim, tiles above
-//                       the causal diagonal are skipped; Q and K tiles arrive by 3-D TMA (heads are one coordinate)
-//   2. attn_softmax_kernel  P = softmax over t <= pos0 + r of every row, in place, with the reference's summation order
-//                       (256 strided partial sums, xor trees); columns after the row's last key up to the end of its
-//                       row tile's key range are zeroed so that step 3 can multiply whole key blocks
+//   1. attn_qk_kernel   S[h][r][t] = half( (q_r . k_t) / sqrtf(head_dim) )    128 x 128 tiles, K = head_dim, key tiles
+//                       above the causal diagonal are not visited; Q and K tiles arrive by 3-D TMA (heads are one coordinate)
+//   2. attn_softmax_kernel  P = softmax over t <= pos0 + r of every row, in place (one warp per row, the row held in
+//                       registers); columns after the row's last key up to the end of its row tile's key range are
+//                       zeroed so that step 3 can multiply whole key blocks
 //   3. attn_pv_kernel   out[r][h*hd + j] = half( sum_t float(P[h][r][t]) float(v[t][j]) )   A = P (K-major, from the
 //                       score buffer), B = V read as it lies in the cache ([t][j]: an MN-major operand), K loop over the
 //                       64-key blocks up to the row tile's causal limit
 //
 // The score / probability buffer [heads][rows][keys] lives in HBM as in the reference (fp16, written once, read twice);
 // the rounding points are the reference's.  Every mbarrier wait is bounded.
+#include <algorithm>
+
 #include "attention.cuh"
 #include "tc_common.cuh"
 
@@ -33,30 +35,45 @@ struct attn_tc_params {
 };
 
 // ------------------------------------------------------------------------------------------------ 1. scores
+// One CTA per (128-row tile, head), persistent over the key tiles up to the tile's causal limit: Q is loaded once,
+// K tiles stream through a ring, two accumulators in tensor memory let the epilogue of one key tile (8 warps: scale,
+// round to half, store) run under the loads and MMAs of the next.
+constexpr int QK_THREADS = 320;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2-9: epilogue
+constexpr int QK_STAGES = 3;
+
 template <int HD>
-__global__ void __launch_bounds__(AT_THREADS) attn_qk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                                                             const attn_tc_params p) {
-  constexpr int NKB = HD / 64;  // 64-wide k-blocks of the head dimension, all loaded at once
+__global__ void __launch_bounds__(QK_THREADS, 1) attn_qk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                                                const attn_tc_params p, int t_tiles) {
+  constexpr int NKB = HD / 64;  // 64-wide k-blocks of the head dimension
   constexpr uint32_t TILE_BYTES = 128 * 64 * 2;
+  constexpr uint32_t OPERAND = NKB * TILE_BYTES;  // one 128 x HD operand
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * NKB * TILE_BYTES);  // [0] operands landed, [1] accumulator ready
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  // [0] Q landed, [1..3] K stage landed, [4..6] K stage free, [7..8] accumulator ready, [9..10] accumulator drained
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (1 + QK_STAGES) * OPERAND);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * AT_BN, m0 = blockIdx.y * AT_BM, head = blockIdx.z;
+  const int m0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * AT_BM, head = blockIdx.y;  // long row tiles first
   const int pos0 = p.pos ? *p.pos : p.pos_value;
-  if (n0 > pos0 + m0 + AT_BM - 1) return;  // every key of this tile lies in the future of every row of the tile
+  const int n_tiles = min(t_tiles, (pos0 + m0 + AT_BM + AT_BN - 1) / AT_BN);       // key tiles that hold a visible key
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bars[0]), 1);
-    mbar_init(smem_u32(&bars[1]), 1);
+    for (int i = 0; i < QK_STAGES; ++i) {
+      mbar_init(smem_u32(&bars[1 + i]), 1);
+      mbar_init(smem_u32(&bars[4 + i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars[7 + i]), 1);
+      mbar_init(smem_u32(&bars[9 + i]), 8);
+    }
     fence_mbar_init();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)AT_BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * AT_BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -66,38 +83,55 @@ __global__ void __launch_bounds__(AT_THREADS) attn_qk_kernel(const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
-      const uint32_t full = smem_u32(&bars[0]);
-      mbar_arrive_expect_tx(full, 2 * NKB * TILE_BYTES);
-      for (int kb = 0; kb < NKB; ++kb) {
-        tma_load_3d(base + kb * TILE_BYTES, &map_q, kb * 64, head, m0, full);                 // [128 rows][64] of this head
-        tma_load_3d(base + (NKB + kb) * TILE_BYTES, &map_k, kb * 64, n0, head, full);         // [128 keys][64]
+      mbar_arrive_expect_tx(smem_u32(&bars[0]), OPERAND);
+      for (int kb = 0; kb < NKB; ++kb) tma_load_3d(base + kb * TILE_BYTES, &map_q, kb * 64, head, m0, smem_u32(&bars[0]));  // [128 rows][64] of this head
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % QK_STAGES, use = j / QK_STAGES;
+        if (use > 0 && !mbar_wait(smem_u32(&bars[4 + s]), (use - 1) & 1, p.err, DEV_ERR_EMPTY_WAIT)) break;
+        const uint32_t full = smem_u32(&bars[1 + s]);
+        mbar_arrive_expect_tx(full, OPERAND);
+        for (int kb = 0; kb < NKB; ++kb) tma_load_3d(base + (1 + s) * OPERAND + kb * TILE_BYTES, &map_k, kb * 64, j * AT_BN, head, full);  // [128 keys][64]
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      if (mbar_wait(smem_u32(&bars[0]), 0, p.err, DEV_ERR_FULL_WAIT)) {
+      bool ok = mbar_wait(smem_u32(&bars[0]), 0, p.err, DEV_ERR_FULL_WAIT);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % QK_STAGES, b = j & 1;
+        ok = mbar_wait(smem_u32(&bars[9 + b]), ((uint32_t)(j >> 1) & 1u) ^ 1u, p.err, DEV_ERR_TMEM_WAIT);  // accumulator b drained
+        ok = ok && mbar_wait(smem_u32(&bars[1 + s]), (uint32_t)(j / QK_STAGES) & 1u, p.err, DEV_ERR_FULL_WAIT);
+        if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int kb = 0; kb < NKB; ++kb) {
-          const uint64_t a_desc = smem_desc_sw128(base + kb * TILE_BYTES), b_desc = smem_desc_sw128(base + (NKB + kb) * TILE_BYTES);
+          const uint64_t a_desc = smem_desc_sw128(base + kb * TILE_BYTES), b_desc = smem_desc_sw128(base + (1 + s) * OPERAND + kb * TILE_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0);
+          for (int k = 0; k < 4; ++k) tc_mma_f16(tmem_base + (uint32_t)(b * AT_BN), a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0);
         }
+        tc_commit(smem_u32(&bars[4 + s]));
+        tc_commit(smem_u32(&bars[7 + b]));
       }
-      tc_commit(smem_u32(&bars[1]));
+      if (!ok) {  // let the epilogue warps leave
+        tc_commit(smem_u32(&bars[7]));
+        tc_commit(smem_u32(&bars[8]));
+      }
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3, chalf = (warp - 2) >> 2;  // TMEM lane quadrant of this warp; it takes 64 of the 128 columns
     const int row = m0 + quad * 32 + lane;
-    const bool ok = mbar_wait(smem_u32(&bars[1]), 0, p.err, DEV_ERR_TMEM_WAIT);
-    tc_fence_after();
-    if (__all_sync(0xffffffffu, ok && *(volatile int*)p.err == 0)) {
-      const float scale_div = sqrtf((float)HD);
-      __half* srow = p.scores + ((size_t)head * p.m_cap + row) * p.t_cap + n0;
+    const float scale_div = sqrtf((float)HD);
+    bool go = true;
+    for (int j = 0; j < n_tiles && go; ++j) {
+      const int b = j & 1;
+      const bool ok = mbar_wait(smem_u32(&bars[7 + b]), (uint32_t)(j >> 1) & 1u, p.err, DEV_ERR_TMEM_WAIT);
+      tc_fence_after();
+      go = __all_sync(0xffffffffu, ok && *(volatile int*)p.err == 0);
+      if (!go) break;
+      __half* srow = p.scores + ((size_t)head * p.m_cap + row) * p.t_cap + j * AT_BN;
 #pragma unroll 1
-      for (int c = 0; c < AT_BN; c += 32) {
+      for (int c = chalf * 64; c < chalf * 64 + 64; c += 32) {
         uint32_t r[32];
-        tc_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
+        tc_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * AT_BN + c), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < p.m) {
           __align__(16) __half2 h[16];
@@ -107,6 +141,9 @@ __global__ void __launch_bounds__(AT_THREADS) attn_qk_kernel(const __grid_consta
           for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(srow + c)[i] = reinterpret_cast<const uint4*>(h)[i];
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[9 + b]));
     }
   }
   tc_fence_before();
@@ -114,47 +151,103 @@ __global__ void __launch_bounds__(AT_THREADS) attn_qk_kernel(const __grid_consta
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)AT_BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * AT_BN)) : "memory");
   }
 }
 
 // ------------------------------------------------------------------------------------------------ 2. softmax
-// One block per (row, head); the reference's softmax_rows (llama_cu.cu:433-499) with temperature 1 over the row's
-// causal prefix, its order of summation included.
+// One warp per (row, head): the row (up to SM_VEC x 256 keys) is read once into registers as 16-byte vectors, the
+// maximum and the exp-sum are warp reductions, the probabilities are written back in place.  Arithmetic of the
+// reference's softmax_rows (llama_cu.cu:433-499) with temperature 1 over the row's causal prefix: max, e^(x - max),
+// sum, e^(x - max) / sum rounded to half; the sum is taken in a different order than its 256-thread tree.
+constexpr int SM_VEC_MAX = 16;  // vectors of 8 keys per lane: rows of up to 4096 keys
+// SM_VEC (4, 8 or 16) is picked from the longest row of the call: fewer registers, more rows in flight per SM
+template <int SM_VEC>
 __global__ void __launch_bounds__(256) attn_softmax_kernel(const attn_tc_params p) {
-  const int r = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + warp, head = blockIdx.y;
+  if (r >= p.m) return;
   const int pos0 = p.pos ? *p.pos : p.pos_value;
   const int L = pos0 + r + 1;                                                     // keys this row sees
   const int m0 = (r / AT_BM) * AT_BM;
   const int k_end = min(p.t_cap, ((pos0 + m0 + AT_BM + 63) / 64) * 64);           // key range step 3 walks for this row tile
   __half* row = p.scores + ((size_t)head * p.m_cap + r) * p.t_cap;
-  __shared__ float s_warp[8];
-  __shared__ float s_b[2];
+  uint4 v[SM_VEC];
   float mx = -CUDART_INF_F;
-  for (int i = tid; i < L; i += 256) mx = fmaxf(mx, __half2float(row[i]));
+#pragma unroll
+  for (int j = 0; j < SM_VEC; ++j) {
+    const int i0 = (j * 32 + lane) * 8;
+    v[j] = make_uint4(0, 0, 0, 0);
+    if (i0 < L) v[j] = *reinterpret_cast<const uint4*>(row + i0);
+  }
+  // whole vectors take the unpredicated path; only the vector that holds the row's last key checks every element
+#pragma unroll
+  for (int j = 0; j < SM_VEC; ++j) {
+    const int i0 = (j * 32 + lane) * 8;
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
+    if (i0 + 8 <= L) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h2[e]);
+        mx = fmaxf(mx, fmaxf(f.x, f.y));
+      }
+    } else if (i0 < L) {
+      const __half* h = reinterpret_cast<const __half*>(&v[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (i0 + e < L) mx = fmaxf(mx, __half2float(h[e]));
+    }
+  }
   mx = warp_max(mx);
-  if (lane == 0) s_warp[warp] = mx;
-  __syncthreads();
-  if (tid == 0) {
-    float t = s_warp[0];
-    for (int w = 1; w < 8; ++w) t = fmaxf(t, s_warp[w]);
-    s_b[0] = t;
+  // e^(x - max) as 2^((x - max) log2 e): one multiplication and the hardware exponential (2 ulp) instead of expf's
+  // longer sequence (1 ulp); every element is exponentiated twice here, so this is what bounds the kernel
+  auto ex = [&](float x) { return exp2f((x - mx) * 1.4426950408889634f); };
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < SM_VEC; ++j) {
+    const int i0 = (j * 32 + lane) * 8;
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
+    if (i0 + 8 <= L) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h2[e]);
+        sum0 += ex(f.x);
+        sum1 += ex(f.y);
+      }
+    } else if (i0 < L) {
+      const __half* h = reinterpret_cast<const __half*>(&v[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (i0 + e < L) sum0 += ex(__half2float(h[e]));
+    }
   }
-  __syncthreads();
-  mx = s_b[0];
-  float s = 0.f;
-  for (int i = tid; i < L; i += 256) s += expf(__half2float(row[i]) - mx);  // thread t: elements t, t + 256, ... in order
-  s = warp_sum(s);
-  if (lane == 0) s_warp[warp] = s;
-  __syncthreads();
-  if (warp == 0) {
-    float t = lane < 8 ? s_warp[lane] : 0.f;
-    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (lane == 0) s_b[1] = t;
+  const float sum = warp_sum(sum0 + sum1);
+  const float rsum = __frcp_rn(sum);
+  // e / sum as one multiplication and a residual correction (RN(e / sum) in all but vanishingly rare cases)
+  auto prob = [&](float x) {
+    const float e = ex(x), q = e * rsum;
+    return fmaf(fmaf(-q, sum, e), rsum, q);
+  };
+#pragma unroll
+  for (int j = 0; j < SM_VEC; ++j) {
+    const int i0 = (j * 32 + lane) * 8;
+    if (i0 >= k_end) continue;  // probabilities, then zeros from the row's last key to the end of the row tile's key range
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
+    __align__(16) __half2 o[4];
+    if (i0 + 8 <= L) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h2[e]);
+        o[e] = __floats2half2_rn(prob(f.x), prob(f.y));
+      }
+    } else {
+      const __half* h = reinterpret_cast<const __half*>(&v[j]);
+      __half* oh = reinterpret_cast<__half*>(o);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) oh[e] = i0 + e < L ? __float2half(prob(__half2float(h[e]))) : __ushort_as_half(0);
+    }
+    *reinterpret_cast<uint4*>(row + i0) = *reinterpret_cast<const uint4*>(o);
   }
-  __syncthreads();
-  const float sum = s_b[1];
-  for (int i = tid; i < k_end; i += 256) row[i] = i < L ? __float2half(expf(__half2float(row[i]) - mx) / sum) : __ushort_as_half(0);
 }
 
 // ------------------------------------------------------------------------------------------------ 3. P . V
@@ -289,7 +382,7 @@ int launch_tc_hd(const attn_params& p, int m, int max_T, __half* scores, int m_c
   static bool attr_done[16] = {};
   int dev = 0;
   LCU_CUDA(cudaGetDevice(&dev));
-  constexpr size_t QK_SMEM = 2 * (HD / 64) * 128 * 64 * 2 + 1024 + 64;
+  constexpr size_t QK_SMEM = (size_t)(1 + QK_STAGES) * (HD / 64) * 128 * 64 * 2 + 1024 + 128;
   constexpr size_t PV_STAGE = 128 * 64 * 2 + (HD / 64) * 64 * 64 * 2;
   const int nstages = 6;
   const size_t pv_smem = nstages * PV_STAGE + 1024 + 256;
@@ -299,9 +392,15 @@ int launch_tc_hd(const attn_params& p, int m, int max_T, __half* scores, int m_c
     attr_done[dev] = true;
   }
   const int m_tiles = (m + AT_BM - 1) / AT_BM, t_tiles = (max_T + AT_BN - 1) / AT_BN;
-  attn_qk_kernel<HD><<<dim3(t_tiles, m_tiles, p.n_heads), AT_THREADS, QK_SMEM, stream>>>(map_q, map_k, q);
+  attn_qk_kernel<HD><<<dim3(m_tiles, p.n_heads), QK_THREADS, QK_SMEM, stream>>>(map_q, map_k, q, t_tiles);
   LCU_CUDA(cudaGetLastError());
-  attn_softmax_kernel<<<dim3(m, p.n_heads), 256, 0, stream>>>(q);
+  const int k_max = std::min(t_cap, (max_T + 63) / 64 * 64);  // longest key range a row's probabilities cover
+  if (k_max <= 4 * 256)
+    attn_softmax_kernel<4><<<dim3((m + 7) / 8, p.n_heads), 256, 0, stream>>>(q);
+  else if (k_max <= 8 * 256)
+    attn_softmax_kernel<8><<<dim3((m + 7) / 8, p.n_heads), 256, 0, stream>>>(q);
+  else
+    attn_softmax_kernel<16><<<dim3((m + 7) / 8, p.n_heads), 256, 0, stream>>>(q);
   LCU_CUDA(cudaGetLastError());
   attn_pv_kernel<HD><<<dim3(m_tiles, p.n_heads), AT_THREADS, pv_smem, stream>>>(map_p, map_v, q, nstages);
   LCU_CUDA(cudaGetLastError());
@@ -318,6 +417,7 @@ size_t attention_tc_scratch_halves(int n_heads, int m_cap, int ctx_len) {
 int launch_attention_tc(const attn_params& p, int m, int max_T, __half* scores, int m_cap, cudaStream_t stream) {
   LCU_REQUIRE(m >= 1 && m <= m_cap && p.n_heads >= 1, "attention: %d rows do not fit the score buffer (%d)", m, m_cap);
   LCU_REQUIRE(max_T >= 1 && max_T <= p.ctx_len, "attention: %d positions exceed the context length %d", max_T, p.ctx_len);
+  LCU_REQUIRE(p.ctx_len <= SM_VEC_MAX * 256, "attention: the tensor-core path holds rows of up to %d keys", SM_VEC_MAX * 256);
   LCU_REQUIRE(p.err != nullptr && scores != nullptr, "attention: the tensor-core path needs an error word and a score buffer");
   LCU_REQUIRE(p.ldq % 8 == 0 && p.ldo % 8 == 0 && ((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.out & 15) == 0, "attention: rows must be 16-byte aligned");
   const int t_cap = (p.ctx_len + 127) / 128 * 128;

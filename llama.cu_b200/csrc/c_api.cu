@@ -110,6 +110,8 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "prefill_u8_deq_min_rows") prefill_tuning_ref().u8_deq_min_rows = value;
   else if (k == "attn_stream") attention_set_stream_mode(value);
   else if (k == "prefill_fuse") prefill_tuning_ref().fuse = value;
+  else if (k == "prefill_attn_tc") prefill_tuning_ref().attn_tc = value;
+  else if (k == "prefill_attn_tc_min_rows") prefill_tuning_ref().attn_tc_min_rows = value;
   else if (k == "prefill_attn_tiles") prefill_tuning_ref().attn_tiles = value;
   else if (k == "prefill_tc_split") prefill_tuning_ref().tc_split = value;
   else if (k == "prefill_tc_pair") prefill_tuning_ref().tc_pair = value;

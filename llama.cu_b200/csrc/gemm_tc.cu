@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <string>
 #include <unordered_map>
 
 #include "gemm_tc.cuh"
@@ -496,10 +497,23 @@ int launch_pair(__half* out, const __half* lhs, int ldx, const __half* w, int m,
 }  // namespace
 
 int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+  LCU_REQUIRE(rank == 2 || rank == 3, "tensor map: rank %d not supported", rank);
+  // encoded maps are kept (a map depends on address, shape and box only)
+  static std::mutex mu;
+  static std::unordered_map<std::string, CUtensorMap> cache;
+  std::string key(reinterpret_cast<const char*>(&ptr), sizeof ptr);
+  key.append(reinterpret_cast<const char*>(dims), sizeof(uint64_t) * rank);
+  key.append(reinterpret_cast<const char*>(strides_bytes), sizeof(uint64_t) * (rank - 1));
+  key.append(reinterpret_cast<const char*>(box), sizeof(uint32_t) * rank);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *map = it->second;
+    return LCU_OK;
+  }
   encode_fn enc;
   int rc = get_encoder(&enc);
   if (rc) return rc;
-  LCU_REQUIRE(rank == 2 || rank == 3, "tensor map: rank %d not supported", rank);
   cuuint64_t d[3], st[2];
   cuuint32_t b[3], es[3] = {1, 1, 1};
   for (int i = 0; i < rank; ++i) {
@@ -510,6 +524,8 @@ int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* d
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   LCU_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (rank %d) failed with code %d", rank, (int)r);
+  if (cache.size() >= 8192) cache.clear();
+  cache.emplace(std::move(key), *map);
   return LCU_OK;
 }
 

@@ -282,6 +282,7 @@ struct gpu_state {
   size_t arena_bytes = 0;
   __half *x = nullptr, *norm = nullptr, *q = nullptr, *kn = nullptr, *vn = nullptr, *att = nullptr;
   __half *h1 = nullptr, *h3 = nullptr, *hs = nullptr;
+  __half* scores = nullptr;  // prompt attention on tcgen05: [heads][context_len][round_up(context_len, 128)] scores / probabilities
   __half* deq = nullptr;  // u8 models: the dequantized matrix (or stack of matrices) of the prompt GEMM in flight
   size_t deq_halves = 0;
   float2* rope = nullptr;
@@ -392,6 +393,9 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     const size_t o_h1 = cv.take(ctxl * f * 2), o_h3 = cv.take(ctxl * f * 2), o_hs = cv.take(ctxl * f * 2);
     const size_t deq_halves = p.q_type ? std::max((size_t)2 * f * d, (size_t)3 * d * d) : 0;  // room for the stacked w1|w3 or wq|wk|wv
     const size_t o_deq = cv.take(deq_halves * 2);
+    // score buffer of the tcgen05 prompt attention (contexts up to 4096 positions; longer ones use the fused kernel)
+    const size_t score_halves = opt.context_len <= 4096 ? attention_tc_scratch_halves(p.n_heads, opt.context_len, opt.context_len) : 0;
+    const size_t o_scores = cv.take(score_halves * 2);
     const size_t o_rope = cv.take(ctxl * (hd / 2) * sizeof(float2));
     const size_t o_state = cv.take(64);
     const size_t o_ids = cv.take(ctxl * 2), o_log = cv.take(ctxl * 2);
@@ -409,6 +413,7 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     g.h1 = (__half*)(b + o_h1);
     g.h3 = (__half*)(b + o_h3);
     g.hs = (__half*)(b + o_hs);
+    g.scores = score_halves ? (__half*)(b + o_scores) : nullptr;
     g.deq = deq_halves ? (__half*)(b + o_deq) : nullptr;
     g.deq_halves = deq_halves;
     g.rope = (float2*)(b + o_rope);
@@ -673,7 +678,9 @@ int context_impl::enqueue_prefill(int m_rows) {
     at.out = g.att; at.ldo = d;
     at.pos = g.state;
     at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd; at.err = g.state + 3;
-    if (prefill_tuning_ref().attn_tiles)
+    if (pt.attn_tc && g.scores != nullptr && m_rows >= pt.attn_tc_min_rows)
+      LCU_TRY(launch_attention_tc(at, m_rows, start_pos + m_rows, g.scores, opt.context_len, g.stream));
+    else if (pt.attn_tiles)
       LCU_TRY(launch_attention_prefill(at, m_rows, start_pos + m_rows, g.stream));
     else
       LCU_TRY(launch_attention(at, m_rows, 1, start_pos + m_rows, g.stream, 0));

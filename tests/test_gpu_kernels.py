@@ -198,7 +198,9 @@ def test_rope_scatter(lcu):
 @pytest.mark.parametrize("m,T0,H,cluster", [(1, 0, 2, 1), (1, 1, 2, 8), (1, 37, 2, 4), (1, 383, 4, 8), (1, 2047, 2, 8), (7, 5, 2, 1),
                                             (16, 0, 3, 1), (1, 100, 2, 2),
                                             # cluster 0 = the prompt kernel (64-row query tiles on tensor cores)
-                                            (7, 5, 2, 0), (64, 0, 2, 0), (65, 37, 1, 0), (200, 0, 2, 0), (130, 300, 2, 0), (1, 77, 2, 0)])
+                                            (7, 5, 2, 0), (64, 0, 2, 0), (65, 37, 1, 0), (200, 0, 2, 0), (130, 300, 2, 0), (1, 77, 2, 0),
+                                            # cluster -1 = the prompt path on tcgen05 (scores, softmax, probabilities x V)
+                                            (7, 5, 2, -1), (128, 0, 1, -1), (200, 0, 2, -1), (130, 300, 2, -1), (512, 0, 4, -1), (1, 77, 2, -1)])
 def test_attention_against_oracle(lcu, m, T0, H, cluster):
     rng = np.random.default_rng(T0 + m)
     dim = H * 128
@@ -239,7 +241,7 @@ def test_attention_streaming_kernel_gives_the_same_bits(lcu, T0, H, hd, cluster)
     assert np.abs(f32(outs[1]) - f32(oo)).max() <= 4e-3
 
 
-@pytest.mark.parametrize("m,T0,cluster", [(1, 50, 4), (70, 9, 0)])
+@pytest.mark.parametrize("m,T0,cluster", [(1, 50, 4), (70, 9, 0), (70, 9, -1), (300, 100, -1)])
 def test_attention_head_dim_64(lcu, m, T0, cluster):
     rng = np.random.default_rng(8)
     H, dim = 4, 256
