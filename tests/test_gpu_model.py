@@ -67,6 +67,38 @@ def test_small_model_matches_oracle(lcu, bs, prompt_len):
     model.close()
 
 
+def test_long_prompt_attention_paths_against_oracle(lcu):
+    """A 300-token prompt through the tcgen05 attention path (scores, softmax, probabilities x V) and through the fused
+    warp-level kernel: both must reproduce the oracle's next-token distribution, and a decode step after either must too
+    (the KV cache they leave behind is the same)."""
+    scale = 0.08
+    cfg = dict(dim=256, multiple_of=256, n_heads=2, n_layers=3, n_vocab=1000)
+    model = lcu.Model.synthetic(block_size=0, seed=99, scale=scale, **cfg)
+    om = O.OracleModel(block_size=0, seed=99, scale=scale, context_len=320, temperature=0.8, **cfg)
+    prompt = O.synth_tokens(300, 99, lo=3, hi=1000)
+    to = om.next_token(prompt)
+    po = f32(om.probs())
+    to2 = om.next_token([to])
+    po2 = f32(om.probs())
+    try:
+        for tc in (1, 0):
+            lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc", tc))
+            lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc_min_rows", 2))
+            ctx = lcu.Context(model, context_len=320, temperature=0.8)
+            t = ctx.next_token(prompt)
+            pr = f32(ctx.probs())
+            assert np.abs(pr - po).max() <= 0.02 * po.max() + 1e-4, tc
+            ctx.next_token([to])
+            pr2 = f32(ctx.probs())
+            assert np.abs(pr2 - po2).max() <= 0.02 * po2.max() + 1e-4, tc
+            ctx.close()
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc", 1))
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc_min_rows", 768))
+    om.close()
+    model.close()
+
+
 def test_chained_decode_equals_host_loop_and_graph_equals_direct(lcu):
     model = lcu.Model.synthetic(block_size=0, seed=7, scale=0.08, **SMALL)
     prompt = O.synth_tokens(9, 7, lo=3, hi=1000)
