@@ -139,7 +139,7 @@ def measured_tensor_peak():
     return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
 
 
-def prefill_sample(lcu, ctx, cfg, ffn, profile=False):
+def prefill_sample(lcu, ctx, cfg, ffn, profile=False, PREFILL_LEN=PREFILL_LEN):
     """Prompt path: a PREFILL_LEN-token prompt through the public call (wall clock, host tokens in, token out),
     and the largest prompt GEMM alone (CUDA events) against the dense tensor peak."""
     import oracle_lib as O
@@ -318,7 +318,7 @@ def run_ours(args):
                   "frac_of_measured_peak": round(step_bytes * (K / (ms_all / 1e3)) / 1e9 / peak, 4),
                   "frac_of_nominal_8tbs": round(step_bytes * (K / (ms_all / 1e3)) / 1e9 / 8000.0, 4)}
     kps = ctx.kernels_per_step()
-    prefill = prefill_sample(lcu, ctx, cfg, ffn, args.profile == "prefill") if world == 1 and ctx_len >= PREFILL_LEN + 2 else None
+    prefill = prefill_sample(lcu, ctx, cfg, ffn, args.profile == "prefill", args.prefill_len) if world == 1 and ctx_len >= args.prefill_len + 2 else None
     ctx.close()
     model.close()
 
@@ -410,6 +410,7 @@ def main():
     ap.add_argument("--workload", default="7b-fp16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="seeded prompt length (128 for the headline configuration)")
+    ap.add_argument("--prefill-len", type=int, default=PREFILL_LEN, help="prompt length of the prefill sample (512; from 768 rows the tcgen05 attention path runs)")
     ap.add_argument("--pipeline", type=int, default=1, help="single process: split the layers evenly over this many GPUs")
     ap.add_argument("--profile", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                     help="cudaProfilerStart/Stop around the device-chained timed region (decode) or around the prompt pass and GEMM (prefill)")

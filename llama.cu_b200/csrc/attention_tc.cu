@@ -119,7 +119,13 @@ __global__ void __launch_bounds__(QK_THREADS, 1) attn_qk_kernel(const __grid_con
   } else {
     const int quad = warp & 3, chalf = (warp - 2) >> 2;  // TMEM lane quadrant of this warp; it takes 64 of the 128 columns
     const int row = m0 + quad * 32 + lane;
-    const float scale_div = sqrtf((float)HD);
+    // x / sqrt(head_dim) as one multiplication and a residual correction: RN(x / d) in all but vanishingly rare
+    // double-rounding cases (the result is rounded to half right after), a third of the division's instructions
+    const float scale_div = sqrtf((float)HD), scale_rcp = __frcp_rn(scale_div);
+    auto scaled = [&](uint32_t bits) {
+      const float x = __uint_as_float(bits), q = x * scale_rcp;
+      return fmaf(fmaf(-q, scale_div, x), scale_rcp, q);
+    };
     bool go = true;
     for (int j = 0; j < n_tiles && go; ++j) {
       const int b = j & 1;
@@ -136,7 +142,7 @@ __global__ void __launch_bounds__(QK_THREADS, 1) attn_qk_kernel(const __grid_con
         if (row < p.m) {
           __align__(16) __half2 h[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) h[i] = __floats2half2_rn(__uint_as_float(r[2 * i]) / scale_div, __uint_as_float(r[2 * i + 1]) / scale_div);
+          for (int i = 0; i < 16; ++i) h[i] = __floats2half2_rn(scaled(r[2 * i]), scaled(r[2 * i + 1]));
 #pragma unroll
           for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(srow + c)[i] = reinterpret_cast<const uint4*>(h)[i];
         }
@@ -201,7 +207,11 @@ __global__ void __launch_bounds__(256) attn_softmax_kernel(const attn_tc_params 
   mx = warp_max(mx);
   // e^(x - max) as 2^((x - max) log2 e): one multiplication and the hardware exponential (2 ulp) instead of expf's
   // longer sequence (1 ulp); every element is exponentiated twice here, so this is what bounds the kernel
-  auto ex = [&](float x) { return exp2f((x - mx) * 1.4426950408889634f); };
+  auto ex = [&](float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"((x - mx) * 1.4426950408889634f));
+    return y;
+  };
   float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
   for (int j = 0; j < SM_VEC; ++j) {

@@ -94,7 +94,7 @@ def test_long_prompt_attention_paths_against_oracle(lcu):
             ctx.close()
     finally:
         lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc", 1))
-        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc_min_rows", 768))
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc_min_rows", 384))
     om.close()
     model.close()
 
