@@ -186,22 +186,31 @@ __global__ void __launch_bounds__(256) attn_softmax_kernel(const attn_tc_params 
     v[j] = make_uint4(0, 0, 0, 0);
     if (i0 < L) v[j] = *reinterpret_cast<const uint4*>(row + i0);
   }
-  // whole vectors take the unpredicated path; only the vector that holds the row's last key checks every element
+  // The one vector that holds the row's last key gets its tail overwritten with -inf (maximum ignores it, 2^(-inf) = 0,
+  // probability 0), so that every pass below works on whole vectors without per-element checks.
+  {
+    const int jb = (L - 1) >> 8, lb = ((L - 1) >> 3) & 31, keep = ((L - 1) & 7) + 1;
+    if (lane == lb && keep < 8) {
+#pragma unroll
+      for (int j = 0; j < SM_VEC; ++j)
+        if (j == jb) {
+          __half* h = reinterpret_cast<__half*>(&v[j]);
+#pragma unroll
+          for (int e = 1; e < 8; ++e)
+            if (e >= keep) h[e] = __ushort_as_half(0xfc00);
+        }
+    }
+  }
 #pragma unroll
   for (int j = 0; j < SM_VEC; ++j) {
     const int i0 = (j * 32 + lane) * 8;
-    const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
-    if (i0 + 8 <= L) {
+    if (i0 < L) {
+      const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 f = __half22float2(h2[e]);
         mx = fmaxf(mx, fmaxf(f.x, f.y));
       }
-    } else if (i0 < L) {
-      const __half* h = reinterpret_cast<const __half*>(&v[j]);
-#pragma unroll
-      for (int e = 0; e < 8; ++e)
-        if (i0 + e < L) mx = fmaxf(mx, __half2float(h[e]));
     }
   }
   mx = warp_max(mx);
@@ -216,19 +225,14 @@ __global__ void __launch_bounds__(256) attn_softmax_kernel(const attn_tc_params 
 #pragma unroll
   for (int j = 0; j < SM_VEC; ++j) {
     const int i0 = (j * 32 + lane) * 8;
-    const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
-    if (i0 + 8 <= L) {
+    if (i0 < L) {
+      const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 f = __half22float2(h2[e]);
         sum0 += ex(f.x);
         sum1 += ex(f.y);
       }
-    } else if (i0 < L) {
-      const __half* h = reinterpret_cast<const __half*>(&v[j]);
-#pragma unroll
-      for (int e = 0; e < 8; ++e)
-        if (i0 + e < L) sum0 += ex(__half2float(h[e]));
     }
   }
   const float sum = warp_sum(sum0 + sum1);
@@ -242,19 +246,17 @@ __global__ void __launch_bounds__(256) attn_softmax_kernel(const attn_tc_params 
   for (int j = 0; j < SM_VEC; ++j) {
     const int i0 = (j * 32 + lane) * 8;
     if (i0 >= k_end) continue;  // probabilities, then zeros from the row's last key to the end of the row tile's key range
-    const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
     __align__(16) __half2 o[4];
-    if (i0 + 8 <= L) {
+    if (i0 < L) {
+      const __half2* h2 = reinterpret_cast<const __half2*>(&v[j]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 f = __half22float2(h2[e]);
         o[e] = __floats2half2_rn(prob(f.x), prob(f.y));
       }
     } else {
-      const __half* h = reinterpret_cast<const __half*>(&v[j]);
-      __half* oh = reinterpret_cast<__half*>(o);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) oh[e] = i0 + e < L ? __float2half(prob(__half2float(h[e]))) : __ushort_as_half(0);
+      for (int e = 0; e < 4; ++e) o[e] = __floats2half2_rn(0.f, 0.f);
     }
     *reinterpret_cast<uint4*>(row + i0) = *reinterpret_cast<const uint4*>(o);
   }
