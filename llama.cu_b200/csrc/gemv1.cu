@@ -142,7 +142,13 @@ __device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const
   const uint32_t M = 0x64646464u;  // bytes -> halves 1024 + q
   // a row's last chunk may be short; its length is a multiple of the block size, so a 128-byte pair is valid or not as a whole
   const bool ok = FULL || (sp << 7) < vb;
-  float t[4][4];
+  // the correction term is the start value of one accumulator chain: sum - 1151.5 * sum(x) costs no instruction of its own
+  float negcorr = 0.f;
+  if (ok) {
+    const float2 xs2 = *reinterpret_cast<const float2*>(xs64 + ci * (CHUNK_K / 64) + g * NSTEPS + 2 * sp);
+    negcorr = -1151.5f * (xs2.x + xs2.y);
+  }
+  float ta[4], tb[4];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int off = (((2 * sp + h) ^ flip) << 6) + c * 16;  // odd segments take the two steps in swapped order (bank spread)
@@ -153,12 +159,13 @@ __device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const
       x0 = *reinterpret_cast<const uint4*>(xseg + 2 * off);
       x1 = *reinterpret_cast<const uint4*>(xseg + 2 * off + 16);
     }
-    float* ta = t[2 * h];
-    float* tb = t[2 * h + 1];
-    ta[0] = ta[1] = ta[2] = ta[3] = 0.f;
-    tb[0] = tb[1] = tb[2] = tb[3] = 0.f;
-    mma_16816(ta, __byte_perm(lo.x, M, 0x4140), __byte_perm(hi.x, M, 0x4140), __byte_perm(lo.x, M, 0x4342), __byte_perm(hi.x, M, 0x4342), x0.x, x0.y);
-    mma_16816(tb, __byte_perm(lo.y, M, 0x4140), __byte_perm(hi.y, M, 0x4140), __byte_perm(lo.y, M, 0x4342), __byte_perm(hi.y, M, 0x4342), x0.z, x0.w);
+    if (h == 0) {  // the block's first products start the two chains
+      mma_16816_from(ta, __byte_perm(lo.x, M, 0x4140), __byte_perm(hi.x, M, 0x4140), __byte_perm(lo.x, M, 0x4342), __byte_perm(hi.x, M, 0x4342), x0.x, x0.y, negcorr);
+      mma_16816_from(tb, __byte_perm(lo.y, M, 0x4140), __byte_perm(hi.y, M, 0x4140), __byte_perm(lo.y, M, 0x4342), __byte_perm(hi.y, M, 0x4342), x0.z, x0.w, 0.f);
+    } else {
+      mma_16816(ta, __byte_perm(lo.x, M, 0x4140), __byte_perm(hi.x, M, 0x4140), __byte_perm(lo.x, M, 0x4342), __byte_perm(hi.x, M, 0x4342), x0.x, x0.y);
+      mma_16816(tb, __byte_perm(lo.y, M, 0x4140), __byte_perm(hi.y, M, 0x4140), __byte_perm(lo.y, M, 0x4342), __byte_perm(hi.y, M, 0x4342), x0.z, x0.w);
+    }
     mma_16816(ta, __byte_perm(lo.z, M, 0x4140), __byte_perm(hi.z, M, 0x4140), __byte_perm(lo.z, M, 0x4342), __byte_perm(hi.z, M, 0x4342), x1.x, x1.y);
     mma_16816(tb, __byte_perm(lo.w, M, 0x4140), __byte_perm(hi.w, M, 0x4140), __byte_perm(lo.w, M, 0x4342), __byte_perm(hi.w, M, 0x4342), x1.z, x1.w);
   }
@@ -166,12 +173,10 @@ __device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const
   const __half* scs = reinterpret_cast<const __half*>(st + 2 * ROWB);
   const int si = (g * SEG + (sp << 7)) >> bs;
   const float sl = __half2float(scs[si]), sh = __half2float(scs[geom<2>::SC_ROW / 2 + si]);
-  const float2 xs2 = *reinterpret_cast<const float2*>(xs64 + ci * (CHUNK_K / 64) + g * NSTEPS + 2 * sp);
-  const float corr = 1151.5f * (xs2.x + xs2.y);
-  acc[0] += sl * (((t[0][0] + t[1][0]) + (t[2][0] + t[3][0])) - corr);
-  acc[1] += sl * (((t[0][1] + t[1][1]) + (t[2][1] + t[3][1])) - corr);
-  acc[2] += sh * (((t[0][2] + t[1][2]) + (t[2][2] + t[3][2])) - corr);
-  acc[3] += sh * (((t[0][3] + t[1][3]) + (t[2][3] + t[3][3])) - corr);
+  acc[0] += sl * (ta[0] + tb[0]);
+  acc[1] += sl * (ta[1] + tb[1]);
+  acc[2] += sh * (ta[2] + tb[2]);
+  acc[3] += sh * (ta[3] + tb[3]);
 }
 
 // Weight types (WT): 0 = fp16; 1 = u8, every weight rounded to half((q - 127.5) * scale) before the
