@@ -53,6 +53,7 @@ int* scratch_err() {
   if (!ptr[dev]) {
     if (cudaMalloc(&ptr[dev], 256) != cudaSuccess) return nullptr;
     cudaMemset(ptr[dev], 0, 256);
+    cudaStreamSynchronize(0);  // the kernels that get this word run on other streams
   }
   return ptr[dev];
 }
@@ -133,6 +134,7 @@ int lcu_free(void* dev) {
 }
 int lcu_memcpy_h2d(void* dev, const void* host, uint64_t bytes) {
   LCU_CUDA(cudaMemcpy(dev, host, bytes, cudaMemcpyHostToDevice));
+  LCU_CUDA(cudaStreamSynchronize(0));  // complete on return, whatever stream uses the buffer next
   return LCU_OK;
 }
 int lcu_memcpy_d2h(void* host, const void* dev, uint64_t bytes) {
@@ -141,10 +143,12 @@ int lcu_memcpy_d2h(void* host, const void* dev, uint64_t bytes) {
 }
 int lcu_memcpy_d2d(void* dst_dev, const void* src_dev, uint64_t bytes) {
   LCU_CUDA(cudaMemcpy(dst_dev, src_dev, bytes, cudaMemcpyDefault));
+  LCU_CUDA(cudaStreamSynchronize(0));
   return LCU_OK;
 }
 int lcu_memset(void* dev, int value, uint64_t bytes) {
   LCU_CUDA(cudaMemset(dev, value, bytes));
+  LCU_CUDA(cudaStreamSynchronize(0));
   return LCU_OK;
 }
 int lcu_set_device(int device) {

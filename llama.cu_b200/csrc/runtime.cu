@@ -213,7 +213,10 @@ int load_file(const std::string& path, void* dst, size_t bytes) {
     set_last_error("cannot map %s", path.c_str());
     return LCU_ERR_IO;
   }
+  // a copy from pageable memory may return while its last piece is still on the way to the device, and the
+  // contexts' streams do not wait for the default stream: finish it here
   cudaError_t e = bytes ? cudaMemcpy(dst, map, bytes, cudaMemcpyHostToDevice) : cudaSuccess;
+  if (bytes && e == cudaSuccess) e = cudaStreamSynchronize(0);
   if (bytes) munmap(map, bytes);
   if (e != cudaSuccess) {
     set_last_error("copy of %s to the device failed: %s", path.c_str(), cudaGetErrorString(e));
@@ -402,7 +405,9 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     const size_t o_logits = cv.take((size_t)p.n_vocab * 2), o_probs = cv.take((size_t)p.n_vocab * 2);
     LCU_CUDA(cudaMalloc(&g.arena, cv.off));
     g.arena_bytes = cv.off;
-    LCU_CUDA(cudaMemset(g.arena, 0, cv.off));
+    // on the context's own stream: that stream does not synchronise with the default stream, and the table kernel
+    // below writes into this arena
+    LCU_CUDA(cudaMemsetAsync(g.arena, 0, cv.off, g.stream));
     char* b = (char*)g.arena;
     g.x = (__half*)(b + o_x);
     g.norm = (__half*)(b + o_norm);
@@ -431,7 +436,7 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     for (uint32_t l = 0; l < p.n_layers; ++l) n_local += c.layer_slot[l] == (int)gi;
     const size_t per = round_up(ctxl * d * 2, ALIGN);
     LCU_CUDA(cudaMalloc(&c.kv_arenas[gi], std::max<size_t>(per * 2 * n_local, ALIGN)));
-    LCU_CUDA(cudaMemset(c.kv_arenas[gi], 0, std::max<size_t>(per * 2 * n_local, ALIGN)));
+    LCU_CUDA(cudaMemsetAsync(c.kv_arenas[gi], 0, std::max<size_t>(per * 2 * n_local, ALIGN), g.stream));
     c.kv_bytes += per * 2 * n_local;
     size_t k = 0;
     for (uint32_t l = 0; l < p.n_layers; ++l)
