@@ -397,6 +397,25 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
     float accs[NACC][4];
 #pragma unroll
     for (int a = 0; a < NACC; ++a) accs[a][0] = accs[a][1] = accs[a][2] = accs[a][3] = 0.f;
+    // u8 kernels (latency-bound): what the epilogue reads from global memory is requested now, one address for the
+    // whole warp, so that its latency passes under the row's products instead of after them.  The fp16 kernels run at
+    // the memory roofline and measured 3 % slower with the early loads; they fetch in the epilogue.
+    constexpr bool EARLY = WT != 0;
+    const int vrow = 2 * (pr0 + i);
+    __half2 prev = __half2half2(__ushort_as_half(0));
+    float2 cs = make_float2(1.f, 0.f);
+    int mat = 0, row = vrow, head = 0, j = 0;
+    auto fetch_epilogue_operands = [&]() {
+      if (EPI == EPI_PLAIN) {
+        if (p.beta != 0.f) prev = *reinterpret_cast<const __half2*>(p.out + vrow);
+      } else if (EPI == EPI_ROPE_KV) {
+        map_row<EPI_ROPE_KV>(p, vrow, mat, row);
+        head = row / p.head_dim;
+        j = row - head * p.head_dim;
+        if (mat < 2) cs = p.rope[(size_t)pos * (p.head_dim >> 1) + (j >> 1)];
+      }
+    };
+    if (EARLY) fetch_epilogue_operands();
     for (int ci = 0; ci < nchunks; ++ci) {
       mbar_wait(smem_u32(&bars[warp * MAX_SW + slot]), par, p.err, DEV_ERR_FULL_WAIT);
       const int cbytes = min(ROWB, rowbytes - ci * ROWB);
@@ -439,13 +458,13 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
     v1 = warp_sum(v1);
     if (lane == 0) {
       const int pr = pr0 + i;
-      const int vrow = 2 * pr;
+      if (!EARLY) fetch_epilogue_operands();
       if (EPI == EPI_PLAIN) {
         float a0 = v0, a1 = v1;
         __half* o = p.out + vrow;
         if (p.beta != 0.f) {
-          a0 = a0 + p.beta * __half2float(o[0]);
-          a1 = a1 + p.beta * __half2float(o[1]);
+          a0 = a0 + p.beta * __low2float(prev);
+          a1 = a1 + p.beta * __high2float(prev);
         }
         const __half2 r2 = __halves2half2(__float2half(a0), __float2half(a1));
         *reinterpret_cast<__half2*>(o) = r2;
@@ -456,12 +475,8 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
           const float val = __half2float(a);  // llama_cu.cu:536-537 on the half-rounded w1 / w3 outputs
           p.out[pr] = __float2half(val / (1.0f + expf(-val)) * __half2float(bq));
         } else {
-          int mat, row;
-          map_row<EPI_ROPE_KV>(p, vrow, mat, row);
-          const int head = row / p.head_dim, j = row - head * p.head_dim;
           __half o0 = a, o1 = bq;
-          if (mat < 2) {  // llama_cu.cu:381-387, cos/sin from the context's table
-            const float2 cs = p.rope[(size_t)pos * (p.head_dim >> 1) + (j >> 1)];
+          if (mat < 2) {  // llama_cu.cu:381-387, cos/sin from the context's table (fetched above)
             const float real = __half2float(a), imag = __half2float(bq);
             const float a_cos = cs.x, a_sin = cs.y;
             o0 = __float2half(real * a_cos - imag * a_sin);
