@@ -99,6 +99,25 @@ def test_long_prompt_attention_paths_against_oracle(lcu):
     model.close()
 
 
+def test_fresh_contexts_repeat_the_same_distribution(lcu):
+    """A context is usable the moment it is created: its zeroed arenas and its RoPE table are ordered on the context's
+    own stream.  Twenty contexts in a row, each used at once with a context length whose arenas take a while to clear,
+    must all produce the same probabilities and the same next token."""
+    model = lcu.Model.synthetic(block_size=0, seed=5, scale=0.08, **SMALL)
+    prompt = O.synth_tokens(24, 5, lo=3, hi=1000)
+    first = None
+    for _ in range(20):
+        ctx = lcu.Context(model, context_len=4096, temperature=0.8)
+        tok = ctx.next_token(prompt)
+        got = (tok, np.asarray(ctx.probs(), np.uint16).copy(), ctx.next_token([tok]))
+        ctx.close()
+        if first is None:
+            first = got
+        assert got[0] == first[0] and got[2] == first[2]
+        assert np.array_equal(got[1], first[1])
+    model.close()
+
+
 def test_chained_decode_equals_host_loop_and_graph_equals_direct(lcu):
     model = lcu.Model.synthetic(block_size=0, seed=7, scale=0.08, **SMALL)
     prompt = O.synth_tokens(9, 7, lo=3, hi=1000)
