@@ -104,6 +104,7 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "int8_factored") gemv_tuning_ref().int8_factored = value;
   else if (k == "gemv_warp_stages_int8") gemv_tuning_ref().warp_stages_int8 = value;
   else if (k == "gemv_warp_stages") gemv_tuning_ref().warp_stages = value;
+  else if (k == "gemv_consumer_warps_int8") gemv_tuning_ref().consumer_warps_int8 = value;
   else if (k == "gemv_variant") gemv_tuning_ref().variant = value;
   else if (k == "gemv_prefetch_kb") gemv_tuning_ref().prefetch_kb_per_cta = value;
   else if (k == "prefill_tc_min_rows") prefill_tuning_ref().tc_min_rows = value;

@@ -27,9 +27,9 @@
 namespace lcu {
 namespace {
 
-constexpr int NW = 4;                       // consumer warps per CTA
-constexpr int NTHREADS = (NW + 1) * 32;
-constexpr int NCONS = NW * 32;
+// Consumer warps per CTA (template parameter of the kernel): 4, or 5 for u8 kernels whose activation row leaves room
+// for two CTAs per SM only - ten consumer warps per SM instead of eight, the u8 kernels being latency-bound.
+constexpr int NW_MAX = 5;
 // Stage geometry per weight type: 4 KiB of each row per stage (measured: 2 KiB stages in a ring twice as deep lose a
 // third of the u8 throughput - the per-stage cost of the producer counts).
 template <int WT>
@@ -42,7 +42,9 @@ struct geom {
 };
 constexpr int MAX_SW = 4;                   // ring depth per warp
 constexpr int NACC = 4;                     // independent accumulator sets (no chain on one result)
-constexpr int SMEM_FIXED = 256 + 64;        // barriers: full[NW][MAX_SW], empty[NW][MAX_SW]; scratch
+constexpr int EMPTY_BASE = NW_MAX * MAX_SW;  // barriers: full[w * MAX_SW + s], empty[EMPTY_BASE + w * MAX_SW + s]
+constexpr int BAR_BYTES = 2 * EMPTY_BASE * 8;
+constexpr int SMEM_FIXED = BAR_BYTES + 64;  // barriers; scratch of the RMSNorm reduction
 
 template <int EPI>
 __device__ __forceinline__ void map_row(const gemv_params& p, int vrow, int& mat, int& row) {
@@ -185,16 +187,18 @@ __device__ __forceinline__ void step_pair_factored(float (&accs)[NACC][4], const
 // (1024 + q_k) - 1151.5 * sum_k x_k), the bytes going to the tensor core as the exact halves
 // 1024 + q (one PRMT per two weights) and the group sums of x coming from the prologue.  Mode 2 has
 // no per-weight rounding: it is closer to the exact product but is not the reference's rounding.
-template <int WT, int EPI>
-__global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p, const int sw, const int pf_bytes) {
+template <int WT, int EPI, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(const gemv_params p, const int sw, const int pf_bytes) {
+  constexpr int NCONS = NW * 32;
+  static_assert(NW >= 4 && NW <= NW_MAX, "the RMSNorm reduction uses the first four consumer warps");
   constexpr int ESZ = WT == 0 ? 2 : 1;
   constexpr int ROWB = geom<WT>::ROWB, SEG = geom<WT>::SEG, NSTEPS = geom<WT>::NSTEPS;
   constexpr int CHUNK_K = ROWB / ESZ;        // weights of one row per stage
   constexpr int STAGE_BYTES = 2 * ROWB + (WT ? 2 * geom<WT>::SC_ROW : 0);
 
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [16 + w * MAX_SW + s]
-  float* scratch = reinterpret_cast<float*>(smem + 256);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [EMPTY_BASE + w * MAX_SW + s]
+  float* scratch = reinterpret_cast<float*>(smem + BAR_BYTES);
   uint8_t* xs = smem + SMEM_FIXED;                     // activation row, K halves (u8 kernels: skewed, see xoff)
   // u8 kernels read 32 activation bytes per 16 weight bytes; with the row stored flat, the two segments of a
   // quarter warp would meet on the same banks.  The activations of every segment are therefore shifted by 16 more
@@ -219,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
   if (tid == 0) {
     for (int i = 0; i < NW * MAX_SW; ++i) {
       mbar_init(smem_u32(&bars[i]), (WT == 0 || sc_bulk) ? 1 : 33);
-      mbar_init(smem_u32(&bars[16 + i]), 1);
+      mbar_init(smem_u32(&bars[EMPTY_BASE + i]), 1);
     }
     fence_mbar_init();
   }
@@ -269,7 +273,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
         for (int w = 0; w < NW; ++w) {
           if (base + w >= npairs) continue;
           const uint32_t full = smem_u32(&bars[w * MAX_SW + slot[w]]);
-          mbar_wait(smem_u32(&bars[16 + w * MAX_SW + slot[w]]), par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
+          mbar_wait(smem_u32(&bars[EMPTY_BASE + w * MAX_SW + slot[w]]), par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
           uint8_t* st = stages + (size_t)(w * sw + slot[w]) * STAGE_BYTES;
           const uint32_t scbytes = WT != 0 ? (uint32_t)(cbytes / p.bs) * 2 : 0;  // scale bytes per row of this chunk
           if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes) + (sc_bulk ? 2 * scbytes : 0));
@@ -326,20 +330,22 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
       // xor trees inside 8 warps, xor tree over the 8 warp sums.  Each of the 128 threads here plays
       // two of the reference's threads (t and t + 128), each warp two of its warps (w and w + 4).
       auto xat = [&](int i) { return __half2float(*reinterpret_cast<const __half*>(xs + xoff(i >> 3) + (i & 7) * 2)); };
-      float s0 = 0.f, s1 = 0.f;
-      for (int i = tid; i < p.K; i += 256) {
-        float v = xat(i);
-        s0 += v * v;
-      }
-      for (int i = tid + 128; i < p.K; i += 256) {
-        float v = xat(i);
-        s1 += v * v;
-      }
-      s0 = warp_sum(s0);
-      s1 = warp_sum(s1);
-      if (lane == 0) {
-        scratch[warp] = s0;
-        scratch[warp + 4] = s1;
+      if (warp < 4) {  // (a fifth consumer warp only joins the barriers and the normalisation below)
+        float s0 = 0.f, s1 = 0.f;
+        for (int i = tid; i < p.K; i += 256) {
+          float v = xat(i);
+          s0 += v * v;
+        }
+        for (int i = tid + 128; i < p.K; i += 256) {
+          float v = xat(i);
+          s1 += v * v;
+        }
+        s0 = warp_sum(s0);
+        s1 = warp_sum(s1);
+        if (lane == 0) {
+          scratch[warp] = s0;
+          scratch[warp + 4] = s1;
+        }
       }
       bar_sync(1, NCONS);
       float t = lane < 8 ? scratch[lane] : 0.f;  // every warp repeats the last tree: no second hand-over
@@ -439,7 +445,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
         for (int s = 0; s < NSTEPS; ++s) step<WT, false>(accs, s, flip, c, g, vb, seg0, xseg, st, xs64, ci, bs_shift);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars[16 + warp * MAX_SW + slot]));
+      if (lane == 0) mbar_arrive(smem_u32(&bars[EMPTY_BASE + warp * MAX_SW + slot]));
       if (++slot == sw) {
         slot = 0;
         par ^= 1;
@@ -495,18 +501,18 @@ __global__ void __launch_bounds__(NTHREADS, 3) gemv1_kernel(const gemv_params p,
   }
 }
 
-template <int WT, int EPI>
+template <int WT, int EPI, int NW>
 int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, int grid, int sw, int pf_bytes) {
   static bool attr_done[16] = {};
   int dev = 0;
   LCU_CUDA(cudaGetDevice(&dev));
   if (dev < 16 && !attr_done[dev]) {
-    LCU_CUDA(cudaFuncSetAttribute(gemv1_kernel<WT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    LCU_CUDA(cudaFuncSetAttribute(gemv1_kernel<WT, EPI, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_done[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(NTHREADS);
+  cfg.blockDim = dim3((NW + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -514,7 +520,7 @@ int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemv1_kernel<WT, EPI>, p, sw, pf_bytes));
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemv1_kernel<WT, EPI, NW>, p, sw, pf_bytes));
   return LCU_OK;
 }
 
@@ -535,20 +541,26 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   int cps = wt == 2 ? t.ctas_per_sm_int8 : t.ctas_per_sm;
   if (cps < 1) cps = 1;
   if (cps > 3) cps = 3;
-  while (cps > 1 && fixed + (size_t)NW * 2 * stage_bytes > (size_t)(228 * 1024) / cps - 1024) --cps;
+  auto fits = [&](int warps, int stages, int ctas) { return fixed + (size_t)warps * stages * stage_bytes <= (size_t)(228 * 1024) / ctas - 1024; };
+  while (cps > 1 && !fits(4, 2, cps)) --cps;
+  // factored u8 kernels that cannot have three CTAs of four consumer warps per SM take five consumer warps per CTA
+  // when those fit (a long activation row: w2 of every model, every matrix of the larger models)
+  int nw = 4;
+  if (wt == 2 && cps < 3 && t.consumer_warps_int8 != 4 && fits(5, 2, cps)) nw = 5;
   const int want_sw = wt == 2 ? t.warp_stages_int8 : t.warp_stages;
   int sw = want_sw < 2 ? 2 : (want_sw > MAX_SW ? MAX_SW : want_sw);
-  while (sw > 2 && fixed + (size_t)NW * sw * stage_bytes > (size_t)(228 * 1024) / cps - 1024) --sw;
-  const size_t smem = fixed + (size_t)NW * sw * stage_bytes;
+  while (sw > 2 && !fits(nw, sw, cps)) --sw;
+  const size_t smem = fixed + (size_t)nw * sw * stage_bytes;
   LCU_REQUIRE(smem <= 227 * 1024, "gemv: a row of K=%d does not fit in shared memory", p.K);
   const int pairs = p.n_mats * p.rows_per_mat / 2;
   const int grid = sms * cps > pairs ? pairs : sms * cps;
   const int pf = t.prefetch_kb_per_cta * 1024;
-#define LCU_GEMV1_CASE(E)                                                     \
-  case E:                                                                     \
-    if (wt == 0) return launch_one<0, E>(p, stream, pdl, smem, grid, sw, pf); \
-    if (wt == 1) return launch_one<1, E>(p, stream, pdl, smem, grid, sw, pf); \
-    return launch_one<2, E>(p, stream, pdl, smem, grid, sw, pf);
+#define LCU_GEMV1_CASE(E)                                                                  \
+  case E:                                                                                  \
+    if (wt == 0) return launch_one<0, E, 4>(p, stream, pdl, smem, grid, sw, pf);           \
+    if (wt == 1) return launch_one<1, E, 4>(p, stream, pdl, smem, grid, sw, pf);           \
+    if (nw == 5) return launch_one<2, E, 5>(p, stream, pdl, smem, grid, sw, pf);           \
+    return launch_one<2, E, 4>(p, stream, pdl, smem, grid, sw, pf);
   switch (epilogue) {
     LCU_GEMV1_CASE(EPI_PLAIN)
     LCU_GEMV1_CASE(EPI_ROPE_KV)
