@@ -247,53 +247,66 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       slot[w] = 0;
       par[w] = 0;
     }
-    // chunks are dealt round-robin: chunk ci of the pairs base .. base+NW-1 goes to warps 0 .. NW-1
-    for (int base = 0; base < npairs; base += NW) {
+    const int full_rounds = npairs / NW, r_tail = npairs - full_rounds * NW;
+    // one stage for consumer warp w: `cbytes` bytes of both rows of a pair (lanes 0 and 1 hold the row addresses,
+    // the half warps the scale addresses) and their scales
+    auto issue = [&](const int w, const uint8_t* row_src, const __half* sc_src, const int cbytes) {
+      const uint32_t full = smem_u32(&bars[w * MAX_SW + slot[w]]);
+      mbar_wait(smem_u32(&bars[EMPTY_BASE + w * MAX_SW + slot[w]]), par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
+      uint8_t* st = stages + (size_t)(w * sw + slot[w]) * STAGE_BYTES;
+      const uint32_t scbytes = WT != 0 ? (uint32_t)(cbytes / p.bs) * 2 : 0;  // scale bytes per row of this chunk
+      if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes) + (sc_bulk ? 2 * scbytes : 0));
+      __syncwarp();
+      if (lane < 2) bulk_g2s_hint(smem_u32(st + lane * ROWB), row_src, (uint32_t)cbytes, full, pol);
+      if (WT != 0) {
+        if (sc_bulk) {  // lanes 0 and 16 copy the scale runs of rows 0 and 1
+          if ((lane & 15) == 0) bulk_g2s(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW), sc_src, scbytes, full);
+        } else {
+          const int ppr = (cbytes / p.bs) >> 1;  // 4-byte pieces per row
+          for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW + j * 4), sc_src + 2 * j);
+          cp_async_mbar_arrive_noinc(full);
+        }
+      }
+      if (++slot[w] == sw) {
+        slot[w] = 0;
+        par[w] ^= 1;
+      }
+    };
+    auto pair_sources = [&](const int pr, const uint8_t*& row_src, const __half*& sc_src) {
+      int mat, row;
+      map_row<EPI>(p, 2 * pr + (lane & 1), mat, row);
+      row_src = reinterpret_cast<const uint8_t*>(p.w[mat]) + (size_t)row * rowbytes;
+      sc_src = nullptr;
+      if (WT) {
+        int m2, r2;
+        map_row<EPI>(p, 2 * pr + (lane >> 4), m2, r2);
+        sc_src = p.sc[m2] + (size_t)r2 * (p.K / p.bs);
+      }
+    };
+    // full rounds: chunk ci of the pairs base .. base+NW-1 goes to warps 0 .. NW-1 in turn
+    for (int rd = 0; rd < full_rounds; ++rd) {
       const uint8_t* src_row[NW];
       const __half* src_sc[NW];
 #pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        src_row[w] = nullptr;
-        src_sc[w] = nullptr;
-        if (base + w < npairs) {
-          // lanes 0 and 1 copy the weight rows 0 and 1 of the pair
-          int mat, row;
-          map_row<EPI>(p, 2 * (pr0 + base + w) + (lane & 1), mat, row);
-          src_row[w] = reinterpret_cast<const uint8_t*>(p.w[mat]) + (size_t)row * rowbytes;
-          if (WT) {  // scales: lanes 0-15 serve row 0, lanes 16-31 row 1
-            int m2, r2;
-            map_row<EPI>(p, 2 * (pr0 + base + w) + (lane >> 4), m2, r2);
-            src_sc[w] = p.sc[m2] + (size_t)r2 * (p.K / p.bs);
-          }
-        }
-      }
+      for (int w = 0; w < NW; ++w) pair_sources(pr0 + rd * NW + w, src_row[w], src_sc[w]);
       for (int ci = 0; ci < nchunks; ++ci) {
         const int cbytes = min(ROWB, rowbytes - ci * ROWB);
 #pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          if (base + w >= npairs) continue;
-          const uint32_t full = smem_u32(&bars[w * MAX_SW + slot[w]]);
-          mbar_wait(smem_u32(&bars[EMPTY_BASE + w * MAX_SW + slot[w]]), par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
-          uint8_t* st = stages + (size_t)(w * sw + slot[w]) * STAGE_BYTES;
-          const uint32_t scbytes = WT != 0 ? (uint32_t)(cbytes / p.bs) * 2 : 0;  // scale bytes per row of this chunk
-          if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes) + (sc_bulk ? 2 * scbytes : 0));
-          __syncwarp();
-          if (lane < 2) bulk_g2s_hint(smem_u32(st + lane * ROWB), src_row[w] + (size_t)ci * ROWB, (uint32_t)cbytes, full, pol);
-          if (WT != 0) {
-            const __half* src = src_sc[w] + (ci * CHUNK_K) / p.bs;
-            if (sc_bulk) {  // lanes 0 and 16 copy the scale runs of rows 0 and 1 (src_sc is set per half warp)
-              if ((lane & 15) == 0) bulk_g2s(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW), src, scbytes, full);
-            } else {
-              const int ppr = (cbytes / p.bs) >> 1;  // 4-byte pieces per row
-              for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW + j * 4), src + 2 * j);
-              cp_async_mbar_arrive_noinc(full);
-            }
-          }
-          if (++slot[w] == sw) {
-            slot[w] = 0;
-            par[w] ^= 1;
-          }
-        }
+        for (int w = 0; w < NW; ++w) issue(w, src_row[w] + (size_t)ci * ROWB, WT ? src_sc[w] + (ci * CHUNK_K) / p.bs : nullptr, cbytes);
+      }
+    }
+    // tail round: the pairs left over go to warps 0 .. r_tail-1
+    if (r_tail > 0) {
+      const uint8_t* src_row[NW];
+      const __half* src_sc[NW];
+#pragma unroll
+      for (int w = 0; w < NW; ++w)
+        if (w < r_tail) pair_sources(pr0 + full_rounds * NW + w, src_row[w], src_sc[w]);
+      for (int ci = 0; ci < nchunks; ++ci) {
+        const int cbytes = min(ROWB, rowbytes - ci * ROWB);
+#pragma unroll
+        for (int w = 0; w < NW; ++w)
+          if (w < r_tail) issue(w, src_row[w] + (size_t)ci * ROWB, WT ? src_sc[w] + (ci * CHUNK_K) / p.bs : nullptr, cbytes);
       }
     }
     if (WT != 0) cp_async_wait<0>();
