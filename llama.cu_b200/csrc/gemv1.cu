@@ -51,8 +51,8 @@ __device__ __forceinline__ void map_row(const gemv_params& p, int vrow, int& mat
   if (EPI == EPI_SILU) {
     mat = vrow & 1;
     row = vrow >> 1;
-  } else if (EPI == EPI_ROPE_KV) {
-    mat = vrow / p.rows_per_mat;
+  } else if (EPI == EPI_ROPE_KV) {  // three matrices: two comparisons instead of a division
+    mat = (vrow >= p.rows_per_mat) + (vrow >= 2 * p.rows_per_mat);
     row = vrow - mat * p.rows_per_mat;
   } else {
     mat = 0;
@@ -229,8 +229,10 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
   }
   __syncthreads();
 
+  const int bs_shift = p.bs > 0 ? 31 - __clz(p.bs) : 0;  // block size is a power of two (32, 64, 128, ...)
   if (warp == NW) {
     // ------------------------------------------------------------ producer
+    // (this warp's instruction chain per stage bounds the u8 kernels: shifts, no divisions)
     const uint64_t pol = policy_evict_first();
     if (pf_bytes > 0) {  // L2 look-ahead over the first rows of this CTA
       const int rows_pf = max(1, min(pf_bytes / rowbytes, 2 * npairs));
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       const uint32_t full = smem_u32(&bars[w * MAX_SW + slot[w]]);
       mbar_wait(smem_u32(&bars[EMPTY_BASE + w * MAX_SW + slot[w]]), par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
       uint8_t* st = stages + (size_t)(w * sw + slot[w]) * STAGE_BYTES;
-      const uint32_t scbytes = WT != 0 ? (uint32_t)(cbytes / p.bs) * 2 : 0;  // scale bytes per row of this chunk
+      const uint32_t scbytes = WT != 0 ? (uint32_t)(cbytes >> bs_shift) * 2 : 0;  // scale bytes per row of this chunk
       if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes) + (sc_bulk ? 2 * scbytes : 0));
       __syncwarp();
       if (lane < 2) bulk_g2s_hint(smem_u32(st + lane * ROWB), row_src, (uint32_t)cbytes, full, pol);
@@ -262,7 +264,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
         if (sc_bulk) {  // lanes 0 and 16 copy the scale runs of rows 0 and 1
           if ((lane & 15) == 0) bulk_g2s(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW), sc_src, scbytes, full);
         } else {
-          const int ppr = (cbytes / p.bs) >> 1;  // 4-byte pieces per row
+          const int ppr = (cbytes >> bs_shift) >> 1;  // 4-byte pieces per row
           for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW + j * 4), sc_src + 2 * j);
           cp_async_mbar_arrive_noinc(full);
         }
@@ -280,7 +282,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       if (WT) {
         int m2, r2;
         map_row<EPI>(p, 2 * pr + (lane >> 4), m2, r2);
-        sc_src = p.sc[m2] + (size_t)r2 * (p.K / p.bs);
+        sc_src = p.sc[m2] + (size_t)r2 * (p.K >> bs_shift);
       }
     };
     // full rounds: chunk ci of the pairs base .. base+NW-1 goes to warps 0 .. NW-1 in turn
@@ -292,7 +294,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       for (int ci = 0; ci < nchunks; ++ci) {
         const int cbytes = min(ROWB, rowbytes - ci * ROWB);
 #pragma unroll
-        for (int w = 0; w < NW; ++w) issue(w, src_row[w] + (size_t)ci * ROWB, WT ? src_sc[w] + (ci * CHUNK_K) / p.bs : nullptr, cbytes);
+        for (int w = 0; w < NW; ++w) issue(w, src_row[w] + (size_t)ci * ROWB, WT ? src_sc[w] + ((ci * CHUNK_K) >> bs_shift) : nullptr, cbytes);
       }
     }
     // tail round: the pairs left over go to warps 0 .. r_tail-1
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
         const int cbytes = min(ROWB, rowbytes - ci * ROWB);
 #pragma unroll
         for (int w = 0; w < NW; ++w)
-          if (w < r_tail) issue(w, src_row[w] + (size_t)ci * ROWB, WT ? src_sc[w] + (ci * CHUNK_K) / p.bs : nullptr, cbytes);
+          if (w < r_tail) issue(w, src_row[w] + (size_t)ci * ROWB, WT ? src_sc[w] + ((ci * CHUNK_K) >> bs_shift) : nullptr, cbytes);
       }
     }
     if (WT != 0) cp_async_wait<0>();
@@ -405,7 +407,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
 
   const int g = lane >> 2, c = lane & 3;
   const int flip = g & 1;
-  const int bs_shift = p.bs > 0 ? 31 - __clz(p.bs) : 0;  // block size is a power of two (32, 64, 128)
   const bool diag = c == (g >> 1);
   int pos = 0;
   if (EPI == EPI_ROPE_KV) pos = *p.pos;
