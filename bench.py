@@ -50,7 +50,7 @@ WORKLOADS = {
 SEED, SCALE, PROMPT_LEN, CONTEXT_LEN, TEMPERATURE = 1234, 0.02, 128, 2048, 0.8
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
 # captures summarised in profiles/gemv_w13_7b_fp16.md and profiles/gemv_w13_7b_int8.md
-NCU_TRAFFIC_BYTES = {"7b-fp16": 180413440 + 3508736, "7b-int8": 91670016 + 3379200}
+NCU_TRAFFIC_BYTES = {"7b-fp16": 180413440 + 3508736, "7b-int8": 91672832 + 2845952}
 PREFILL_LEN = 512
 
 
