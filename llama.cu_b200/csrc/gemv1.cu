@@ -252,22 +252,25 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
     const int full_rounds = npairs / NW, r_tail = npairs - full_rounds * NW;
     // one stage for consumer warp w: `cbytes` bytes of both rows of a pair (lanes 0 and 1 hold the row addresses,
     // the half warps the scale addresses) and their scales
+    // Copies of a stage are issued by one predicated instruction: lanes 0 and 1 copy the two rows, lanes 2 and 16 the
+    // scale runs of rows 0 and 1 when those travel as bulk copies (scale addresses are held per half warp).
+    const uint32_t bars_u32 = smem_u32(bars), stages_u32 = smem_u32(stages);
+    const bool lane_sc = lane >= 2;
+    const bool lane_copies = lane < 2 || (sc_bulk && (lane == 2 || lane == 16));
+    const uint32_t lane_dst = lane_sc ? 2 * ROWB + (lane >> 4) * (WT ? geom<WT>::SC_ROW : 0) : lane * ROWB;
     auto issue = [&](const int w, const uint8_t* row_src, const __half* sc_src, const int cbytes) {
-      const uint32_t full = smem_u32(&bars[w * MAX_SW + slot[w]]);
-      mbar_wait(smem_u32(&bars[EMPTY_BASE + w * MAX_SW + slot[w]]), par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
-      uint8_t* st = stages + (size_t)(w * sw + slot[w]) * STAGE_BYTES;
+      const uint32_t full = bars_u32 + (uint32_t)(w * MAX_SW + slot[w]) * 8;
+      mbar_wait(full + EMPTY_BASE * 8, par[w] ^ 1, p.err, DEV_ERR_EMPTY_WAIT);
+      const uint32_t st = stages_u32 + (uint32_t)(w * sw + slot[w]) * STAGE_BYTES;
       const uint32_t scbytes = WT != 0 ? (uint32_t)(cbytes >> bs_shift) * 2 : 0;  // scale bytes per row of this chunk
       if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(2 * cbytes) + (sc_bulk ? 2 * scbytes : 0));
       __syncwarp();
-      if (lane < 2) bulk_g2s_hint(smem_u32(st + lane * ROWB), row_src, (uint32_t)cbytes, full, pol);
-      if (WT != 0) {
-        if (sc_bulk) {  // lanes 0 and 16 copy the scale runs of rows 0 and 1
-          if ((lane & 15) == 0) bulk_g2s(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW), sc_src, scbytes, full);
-        } else {
-          const int ppr = (cbytes >> bs_shift) >> 1;  // 4-byte pieces per row
-          for (int j = lane & 15; j < ppr; j += 16) cp_async4(smem_u32(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW + j * 4), sc_src + 2 * j);
-          cp_async_mbar_arrive_noinc(full);
-        }
+      if (lane_copies)
+        bulk_g2s_hint(st + lane_dst, lane_sc ? (const void*)sc_src : (const void*)row_src, lane_sc ? scbytes : (uint32_t)cbytes, full, pol);
+      if (WT != 0 && !sc_bulk) {
+        const int ppr = (cbytes >> bs_shift) >> 1;  // 4-byte pieces per row
+        for (int j = lane & 15; j < ppr; j += 16) cp_async4(st + 2 * ROWB + (lane >> 4) * geom<WT>::SC_ROW + j * 4, sc_src + 2 * j);
+        cp_async_mbar_arrive_noinc(full);
       }
       if (++slot[w] == sw) {
         slot[w] = 0;
@@ -387,6 +390,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       bar_sync(1, NCONS);
     }
     if (WT == 2) {  // sums of the (normalised) activations over aligned groups of 64: eight lanes per group, 16 bytes per lane
+#pragma unroll 3
       for (int grp64 = warp * 4 + (lane >> 3); grp64 < p.K / 64; grp64 += NW * 4) {
         const uint4 q = *reinterpret_cast<const uint4*>(xs + xoff(grp64 * 8 + (lane & 7)));
         const __half2* h = reinterpret_cast<const __half2*>(&q);
