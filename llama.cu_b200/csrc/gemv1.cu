@@ -423,7 +423,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
     for (int a = 0; a < NACC; ++a) accs[a][0] = accs[a][1] = accs[a][2] = accs[a][3] = 0.f;
     // u8 kernels (latency-bound): what the epilogue reads from global memory is requested now, one address for the
     // whole warp, so that its latency passes under the row's products instead of after them.  The fp16 kernels run at
-    // the memory roofline and measured 3 % slower with the early loads; they fetch in the epilogue.
+    // the memory roofline, where the early loads measured no difference; they fetch in the epilogue.
     constexpr bool EARLY = WT != 0;
     const int vrow = 2 * (pr0 + i);
     __half2 prev = __half2half2(__ushort_as_half(0));
