@@ -28,8 +28,11 @@ const char* lcu_last_error(void);
 /* llama_cu::initialize (llama_cu.cu:1525-1542): prints the device properties; returns the device count. */
 int lcu_initialize(int verbose);
 int lcu_device_count(void);
-/* llama_cu::matmul_type (llama_cu.h:65-68): 4 and 0 select the native kernels, 1 is accepted as an
- * alias (the reference's "pedantic" kernels have no separate implementation here). */
+/* llama_cu::matmul_type (llama_cu.h:65-68, llama_cu.cu:28): 4 (the reference's tensor-core kernels) and 0 (its cuBLAS
+ * path) select the sm_100a kernels.  1 selects the pedantic pair of llama_cu.cu:111-145 for every matrix product
+ * (lcu_matmul_nt_* and every product inside lcu_context_next_token): one thread per output element, terms added in
+ * index order, binary32 sum (u8 weights: binary64 terms); a context then runs single-token steps through the unfused
+ * operator sequence.  It is the on-GPU check for the fast kernels and is slow by design. */
 int lcu_set_matmul_type(int type);
 /* launch-shape knobs used for the measurements (defaults are the measured best): "gemv_stages", "gemv_ctas_per_sm",
  * "gemv_ctas_per_sm_int8", "gemv_variant", "gemv_warp_stages", "gemv_warp_stages_int8", "gemv_consumer_warps_int8", "gemv_prefetch_kb",
@@ -46,6 +49,7 @@ int lcu_memcpy_h2d(void* dev, const void* host, uint64_t bytes);
 int lcu_memcpy_d2h(void* host, const void* dev, uint64_t bytes);
 int lcu_memcpy_d2d(void* dst_dev, const void* src_dev, uint64_t bytes); /* any two devices */
 int lcu_memset(void* dev, int value, uint64_t bytes);
+int lcu_mem_info(uint64_t* free_bytes_out, uint64_t* total_bytes_out); /* cudaMemGetInfo of the current device */
 int lcu_set_device(int device);
 int lcu_synchronize(void);
 
@@ -84,7 +88,10 @@ int lcu_rope_scatter(void* q_dev, const void* k_new_dev, const void* v_new_dev, 
  * 2 MiB device array inside the library instead of a per-call allocation; (pos0 + m) * (dim / n_heads / 2)
  * must not exceed 262144 entries (4096 positions at head_dim 128) or the call is rejected.  All calls
  * share that array: calls whose kernels overlap on the GPU race.  The first call on each device resolves
- * the array's address and should be made outside stream capture.  Returns without synchronising. */
+ * the array's address, which is also what makes the CUDA runtime load the module that holds the array: that
+ * first call reserves the 2 MiB (and may synchronise), so make it at start-up - one small call per device -
+ * before HBM is exhausted and outside stream capture.  Later calls take no device memory and return without
+ * synchronising. */
 int lcu_rope_scatter_static(void* q_dev, const void* k_new_dev, const void* v_new_dev, void* k_cache_dev, void* v_cache_dev, int pos0,
                             int m, int dim, int n_heads, int ctx_len, void* stream);
 /* matmul_qk + softmax_rows + matmul_qkv, llama_cu.cu:400-531 (launches at 1163-1171), fused:
@@ -123,6 +130,15 @@ void lcu_model_free(void* model);
 uint32_t lcu_ffn_dim(uint32_t dim, uint32_t multiple_of);
 /* llama_partition::autopipe, llama_cu.cu:819-837: fills layer_gpus_out[n_layers] greedily by free memory; returns 0 if it fits */
 int lcu_partition_autopipe(const void* params40, int context_len, int* layer_gpus_out);
+/* 1 if every GPU of the map holds one contiguous run of layers (what lcu_model_create / lcu_model_load accept: the
+ * reference's forward pass asserts embedding on the first and output on the last layer's GPU, llama_cu.cu:1076-1079,
+ * and a GPU that reappears later would run the head against another stage's buffers), else 0.  Host only. */
+int lcu_partition_is_contiguous(const int* layer_gpus, int n_layers);
+/* llama_params::shared_context_memory_size / kv_cache_size (llama_cu.cu:781-808): bytes of the scratch arena
+ * lcu_context_create allocates on every GPU it uses (activations, prompt-path score and dequantization buffers, tables)
+ * and of one layer's K and V caches; lcu_partition_autopipe packs with the same figures.  Host only. */
+uint64_t lcu_context_scratch_bytes(const void* params40, int context_len);
+uint64_t lcu_context_kv_bytes_per_layer(const void* params40, int context_len);
 /* contiguous equal split over n_gpus devices (the hand-built partitions of the pipelined configurations) */
 int lcu_partition_even(int n_layers, int n_gpus, int* layer_gpus_out);
 
@@ -146,6 +162,13 @@ int lcu_context_read_probs(void* ctx, uint16_t* probs_host);
 /* residual stream row of the last token before the final norm (diagnostics) */
 int lcu_context_read_hidden(void* ctx, uint16_t* hidden_host);
 int lcu_context_kernels_per_step(void* ctx);
+
+/* ---- tokenizer (host only) ------------------------------------------------------------------- */
+/* llama_vocabulary(vocab file) + llama_vocabulary::tokenize(text, bos), llama_cu.cu:1319-1437: greedy highest-score pair
+ * merging over UTF-8 characters with byte fallback (id = byte + 3), a leading space added when the text has none, id 1
+ * first when bos != 0.  vocab file layout: extract.py:44-61.  Returns the number of ids (the first `capacity` of them are
+ * written to ids_out), or -1 if the file cannot be mapped. */
+int lcu_tokenize(const char* vocab_path, const char* text, int bos, int16_t* ids_out, int capacity);
 
 /* ---- measurement ---------------------------------------------------------------------------- */
 /* Times one decode kernel class over all layers of `model` in rotation (distinct weights every

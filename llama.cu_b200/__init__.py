@@ -33,6 +33,11 @@ _SIG = {
     "lcu_memcpy_d2h": (C.c_int, [vp, vp, C.c_uint64]),
     "lcu_memcpy_d2d": (C.c_int, [vp, vp, C.c_uint64]),
     "lcu_memset": (C.c_int, [vp, C.c_int, C.c_uint64]),
+    "lcu_mem_info": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "lcu_partition_is_contiguous": (C.c_int, [vp, C.c_int]),
+    "lcu_context_scratch_bytes": (C.c_uint64, [vp, C.c_int]),
+    "lcu_context_kv_bytes_per_layer": (C.c_uint64, [vp, C.c_int]),
+    "lcu_tokenize": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, vp, C.c_int]),
     "lcu_set_device": (C.c_int, [C.c_int]),
     "lcu_synchronize": (C.c_int, []),
     "lcu_quantize_absmax_uint8": (C.c_int, [vp, vp, vp, C.c_uint64, C.c_uint64, C.c_int, vp]),

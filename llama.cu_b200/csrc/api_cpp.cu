@@ -1,4 +1,5 @@
 // The llama_cu:: C++ classes of include/llama_cu.h on top of the internal runtime.
+#define LLAMA_CU_IMPLEMENTATION
 #include "../../include/llama_cu.h"
 
 #include <fcntl.h>
@@ -12,6 +13,7 @@
 #include <cstring>
 #include <queue>
 
+#include "prefill.cuh"
 #include "runtime.cuh"
 
 namespace llama_cu {
@@ -92,6 +94,78 @@ mapped_buffer& mapped_buffer::operator=(mapped_buffer&& other) {
   return *this;
 }
 
+// ------------------------------------------------------------------ scoped_gpu, gpu_buffer (reference llama_cu.cu:691-736)
+scoped_gpu::scoped_gpu(int device) {
+  CHECK_CUDA(cudaGetDevice(&prev_device_));
+  CHECK_CUDA(cudaSetDevice(device));
+}
+scoped_gpu::~scoped_gpu() { CHECK_CUDA(cudaSetDevice(prev_device_)); }
+
+void gpu_buffer_view::copy_from(mapped_buffer const& buffer) {
+  assert(buffer.size() == size_);
+  CHECK_CUDA(cudaMemcpyAsync(dev_ptr_, buffer.data(), size_, cudaMemcpyHostToDevice));
+}
+void gpu_buffer_view::copy_from(void const* buffer, size_t size) {
+  assert(size <= size_);
+  CHECK_CUDA(cudaMemcpyAsync(dev_ptr_, buffer, size, cudaMemcpyHostToDevice));
+}
+void gpu_buffer_view::copy_to(void* buffer, size_t size) {
+  assert(size <= size_);
+  CHECK_CUDA(cudaMemcpy(buffer, dev_ptr_, size, cudaMemcpyDeviceToHost));
+}
+gpu_buffer::gpu_buffer(size_t size) {
+  CHECK_CUDA(cudaMalloc(&dev_ptr_, size ? size : 1));
+  size_ = size;
+}
+gpu_buffer::gpu_buffer(gpu_buffer&& other) : gpu_buffer_view(other.dev_ptr_, other.size_) {
+  other.dev_ptr_ = nullptr;
+  other.size_ = 0;
+}
+gpu_buffer& gpu_buffer::operator=(gpu_buffer&& other) {
+  if (this == &other) return *this;
+  if (dev_ptr_) CHECK_CUDA(cudaFree(dev_ptr_));
+  dev_ptr_ = other.dev_ptr_;
+  size_ = other.size_;
+  other.dev_ptr_ = nullptr;
+  other.size_ = 0;
+  return *this;
+}
+gpu_buffer::~gpu_buffer() {
+  if (dev_ptr_) CHECK_CUDA(cudaFree(dev_ptr_));
+}
+
+// ------------------------------------------------------------------ the operator seam (reference llama_cu.cu:1463-1523)
+namespace {
+void seam_matmul(tensor4d_view<__half>& out, tensor4d_view<__half>& lhs, lcu::dev_matrix const& w, __half beta, cudaStream_t stream) {
+  // the reference's kernels index rows densely and ignore the strides; the same contract holds here
+  assert(lhs.w == w.cols && out.w == w.rows && out.h >= lhs.h);
+  lcu::matmul_type_ref() = matmul_type;
+  if (lcu::matmul_rows(out.data(), lhs.data(), w, (int)lhs.h, __half2float(beta), lcu::device_scratch_words(), stream) != lcu::LCU_OK) {
+    fprintf(stderr, "matmul_nt: %s\n", lcu::last_error());
+    raise(SIGSEGV);  // contract violations and CUDA errors are fatal in the reference too (assert / CHECK_CUDA)
+  }
+}
+}  // namespace
+
+void matmul_nt(tensor4d_view<__half> out, tensor4d_view<__half> lhs, tensor4d_view<__half> rhs, __half beta, cudaStream_t stream) {
+  lcu::dev_matrix w;
+  w.w = rhs.data();
+  w.rows = rhs.h;
+  w.cols = rhs.w;
+  seam_matmul(out, lhs, w, beta, stream);
+}
+void matmul_nt(tensor4d_view<__half> out, tensor4d_view<__half> lhs, generic_tensor& rhs, __half beta, cudaStream_t stream) {
+  if (!rhs.is_quantized()) return matmul_nt(out, lhs, rhs.as_fp16().view(), beta, stream);
+  quantized_tensor& q = rhs.as_quantized();
+  lcu::dev_matrix w;
+  w.w = q.q_values.data();
+  w.sc = q.scales.data();
+  w.rows = q.q_values.h;
+  w.cols = q.q_values.w;
+  w.bs = q.quantization_block_size;
+  seam_matmul(out, lhs, w, beta, stream);
+}
+
 // ------------------------------------------------------------------ llama_params
 namespace {
 lcu::model_params to_internal(llama_params const& p) {
@@ -123,11 +197,10 @@ size_t llama_params::layer_size() const {
 }
 size_t llama_params::embedding_size() const { return matrix_bytes(*this, n_vocab, dim); }
 size_t llama_params::output_size() const { return matrix_bytes(*this, n_vocab, dim) + (size_t)dim * 2; }
-// activations a GPU holds for one context (no score tensor: attention is fused)
+// what a context allocates on every GPU it uses: activations for context_len rows, the prompt path's score and
+// dequantization buffers, tables (the same figure context::create and the partitioner use)
 size_t llama_params::shared_context_memory_size(size_t context_len) const {
-  const size_t d = dim, f = ffn_dim();
-  return context_len * 2 * 2 + 6 * context_len * d * 2 + 3 * context_len * f * 2 + context_len * (d / n_heads) * 4 +
-         2 * (size_t)n_vocab * 2;
+  return lcu::context_scratch_bytes(to_internal(*this), (int)context_len);
 }
 size_t llama_params::kv_cache_size(size_t context_len) const { return context_len * dim * 2 * 2; }
 
@@ -295,6 +368,7 @@ struct context_on_b200 final : public llama_context {
   size_t context_memory_usage() override { return core->memory_usage(); }
   short next_token(std::vector<short> const& new_tokens) override {
     assert(new_tokens.size() + start_pos_ <= (size_t)context_len_);  // reference llama_cu.cu:1074
+    lcu::matmul_type_ref() = matmul_type;  // the reference reads its global at every matmul (llama_cu.cu:1467, 1504)
     int token = 0;
     if (core->next_token(new_tokens.data(), (int)new_tokens.size(), &token) != lcu::LCU_OK) {
       fprintf(stderr, "%s\n", lcu::last_error());
@@ -312,3 +386,20 @@ std::unique_ptr<llama_context> llama_context::create(llama_model* model, int con
 }
 
 }  // namespace llama_cu
+
+// llama_vocabulary::tokenize for foreign-function callers (declared in llama_cu_c.h)
+extern "C" int lcu_tokenize(const char* vocab_path, const char* text, int bos, int16_t* ids_out, int capacity) {
+  if (!vocab_path || !text || (capacity > 0 && !ids_out)) {
+    lcu::set_last_error("tokenize: null argument");
+    return -1;
+  }
+  llama_cu::mapped_buffer file{std::string(vocab_path)};
+  if (!file.is_ok() || file.size() < 4) {
+    lcu::set_last_error("tokenize: cannot map vocabulary file %s", vocab_path);
+    return -1;
+  }
+  llama_cu::llama_vocabulary vocab(file);
+  const std::vector<short> ids = vocab.tokenize(text, bos != 0);
+  for (size_t i = 0; i < ids.size() && (int)i < capacity; ++i) ids_out[i] = ids[i];
+  return (int)ids.size();
+}

@@ -18,7 +18,6 @@
 using namespace lcu;
 
 namespace {
-int g_matmul_type = 4;
 context_options g_default_opts;  // "use_graph", "use_pdl", "attn_cluster" knobs apply to contexts created afterwards
 
 int require_device() {
@@ -44,19 +43,7 @@ partition make_partition(const model_params& p, const int* layer_gpus) {
   return part;
 }
 
-// small device scratch for the stand-alone operator entry points (error word etc.)
-int* scratch_err() {
-  static int* ptr[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 16) return nullptr;
-  if (!ptr[dev]) {
-    if (cudaMalloc(&ptr[dev], 256) != cudaSuccess) return nullptr;
-    cudaMemset(ptr[dev], 0, 256);
-    cudaStreamSynchronize(0);  // the kernels that get this word run on other streams
-  }
-  return ptr[dev];
-}
+int* scratch_err() { return device_scratch_words(); }
 }  // namespace
 
 extern "C" {
@@ -92,7 +79,7 @@ int lcu_initialize(int verbose) {
 
 int lcu_set_matmul_type(int type) {
   LCU_REQUIRE(type == 0 || type == 1 || type == 4, "matmul_type %d is not one of 0, 1, 4", type);
-  g_matmul_type = type;
+  matmul_type_ref() = type;
   return LCU_OK;
 }
 
@@ -152,6 +139,14 @@ int lcu_memset(void* dev, int value, uint64_t bytes) {
   LCU_CUDA(cudaStreamSynchronize(0));
   return LCU_OK;
 }
+int lcu_mem_info(uint64_t* free_bytes_out, uint64_t* total_bytes_out) {
+  NEED_DEVICE();
+  size_t f = 0, t = 0;
+  LCU_CUDA(cudaMemGetInfo(&f, &t));
+  if (free_bytes_out) *free_bytes_out = f;
+  if (total_bytes_out) *total_bytes_out = t;
+  return LCU_OK;
+}
 int lcu_set_device(int device) {
   LCU_CUDA(cudaSetDevice(device));
   return LCU_OK;
@@ -188,11 +183,11 @@ int lcu_quantize_host(uint8_t* q_host, uint16_t* scales_host, const uint16_t* in
   const size_t n = h * w;
   __half *d_in = nullptr, *d_sc = nullptr, *d_dq = nullptr;
   uint8_t* d_q = nullptr;
-  LCU_CUDA(cudaMalloc(&d_in, n * 2 + 16));
-  LCU_CUDA(cudaMalloc(&d_q, n + 16));
-  LCU_CUDA(cudaMalloc(&d_sc, n / bs * 2 + 16));
   int rc = LCU_OK;
-  cudaError_t e = cudaMemcpy(d_in, in_host, n * 2, cudaMemcpyHostToDevice);
+  cudaError_t e = cudaMalloc(&d_in, n * 2 + 16);
+  if (e == cudaSuccess) e = cudaMalloc(&d_q, n + 16);
+  if (e == cudaSuccess) e = cudaMalloc(&d_sc, n / bs * 2 + 16);
+  if (e == cudaSuccess) e = cudaMemcpy(d_in, in_host, n * 2, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) rc = launch_quantize_absmax_uint8(d_q, d_sc, d_in, h, w, bs, 0);
   if (!rc && e == cudaSuccess) e = cudaMemcpy(q_host, d_q, n, cudaMemcpyDeviceToHost);
   if (!rc && e == cudaSuccess) e = cudaMemcpy(scales_host, d_sc, n / bs * 2, cudaMemcpyDeviceToHost);
@@ -371,6 +366,21 @@ int lcu_partition_autopipe(const void* params40, int context_len, int* layer_gpu
   if (rc) return rc;
   memcpy(layer_gpus_out, lg.data(), lg.size() * sizeof(int));
   return LCU_OK;
+}
+int lcu_partition_is_contiguous(const int* layer_gpus, int n_layers) {
+  if (!layer_gpus || n_layers < 1) return 0;
+  return partition_is_contiguous(std::vector<int>(layer_gpus, layer_gpus + n_layers)) ? 1 : 0;
+}
+uint64_t lcu_context_scratch_bytes(const void* params40, int context_len) {
+  model_params p;
+  memcpy(&p, params40, sizeof(p));
+  if (p.dim == 0 || p.n_heads == 0 || p.multiple_of == 0 || context_len < 1) return 0;
+  return context_scratch_bytes(p, context_len);
+}
+uint64_t lcu_context_kv_bytes_per_layer(const void* params40, int context_len) {
+  model_params p;
+  memcpy(&p, params40, sizeof(p));
+  return context_kv_bytes_per_layer(p, context_len);
 }
 int lcu_partition_even(int n_layers, int n_gpus, int* layer_gpus_out) {
   LCU_REQUIRE(n_layers >= 1 && n_gpus >= 1 && n_gpus <= n_layers, "partition: %d layers over %d GPUs", n_layers, n_gpus);

@@ -91,7 +91,7 @@ int model::save_dir(const std::string& dir) {
     int dev = 0;
     rc = find_tensor(s.name, 0, &ptr, &bytes, &dev);
     if (rc) return rc;
-    cudaSetDevice(dev);
+    device_guard dg(dev);  // the tensor's GPU for the copy; the caller's current device is left as it was
     const std::string base = dir + "/" + s.name;
     if (s.cols == 0) {
       rc = save_device(base + ".weight__" + std::to_string(s.rows), ptr, bytes, host);
@@ -123,9 +123,15 @@ int quantize_dir(const std::string& in_dir, const std::string& out_dir, int bs) 
   __half* d_in = nullptr;
   uint8_t* d_q = nullptr;
   __half* d_sc = nullptr;
-  LCU_CUDA(cudaMalloc(&d_in, max_elems * 2));
-  LCU_CUDA(cudaMalloc(&d_q, max_elems));
-  LCU_CUDA(cudaMalloc(&d_sc, max_elems / bs * 2));
+  cudaError_t ea = cudaMalloc(&d_in, max_elems * 2);
+  if (ea == cudaSuccess) ea = cudaMalloc(&d_q, max_elems);
+  if (ea == cudaSuccess) ea = cudaMalloc(&d_sc, max_elems / bs * 2);
+  if (ea != cudaSuccess) {  // nothing stays allocated when one of the three fails
+    cudaFree(d_in);
+    cudaFree(d_q);
+    cudaFree(d_sc);
+    LCU_CUDA(ea);
+  }
   for (const named_shape& s : shapes_of(p)) {
     const std::string ib = in_dir + "/" + s.name, ob = out_dir + "/" + s.name;
     if (s.cols == 0) {  // norm vectors are copied verbatim (transform.cu:198-218)
@@ -158,11 +164,14 @@ int quantize_dir(const std::string& in_dir, const std::string& out_dir, int bs) 
 int autopipe(const model_params& p, int context_len, std::vector<int>& layer_gpus) {
   int ndev = 0;
   LCU_CUDA(cudaGetDeviceCount(&ndev));
-  const size_t d = p.dim, f = ffn_dim_of(p), v = p.n_vocab, ctx = context_len;
+  const size_t d = p.dim, f = ffn_dim_of(p), v = p.n_vocab;
   const size_t bs = p.q_type ? p.quantization_block_size : 0;
   auto mat = [&](size_t r, size_t c) { return bs ? r * c + r * (c / bs) * 2 : r * c * 2; };
-  const size_t layer_bytes = 4 * mat(d, d) + 2 * mat(f, d) + mat(d, f) + 2 * d * 2 + 2 * ctx * d * 2;  // weights + norms + K,V cache
-  const size_t scratch = 6 * ctx * d * 2 + 3 * ctx * f * 2 + v * 8 + (64u << 20);                      // per-GPU activations + margin
+  const size_t layer_bytes = 4 * mat(d, d) + 2 * mat(f, d) + mat(d, f) + 2 * d * 2 + 9 * 256  // weights + norms (256-byte aligned)
+                             + context_kv_bytes_per_layer(p, context_len);                    // + K and V cache of the layer
+  // what context::create allocates on every GPU it uses (activations, the prompt path's score and dequantization
+  // buffers, tables) + a margin for the CUDA context's own growth (graphs, module loading)
+  const size_t scratch = context_scratch_bytes(p, context_len) + (64u << 20);
   const size_t embed_bytes = mat(v, d), out_bytes = mat(v, d) + d * 2;
   layer_gpus.clear();
   int gpu = 0;

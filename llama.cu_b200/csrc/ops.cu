@@ -62,9 +62,9 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(__half* out, const __half
 }
 
 // ------------------------------------------------------------------ RoPE (llama_cu.cu:368-389)
-__global__ void rope_table_kernel(float2* table, int ctx_len, int head_dim, float theta) {
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void rope_table_kernel(float2* table, int ctx_len, int head_dim, float theta, int first_pos) {
   const int half_dim = head_dim >> 1;
+  const int idx = first_pos * half_dim + blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= ctx_len * half_dim) return;
   const int pos = idx / half_dim, i = idx - pos * half_dim;
   const int head_c = 2 * i;
@@ -389,9 +389,10 @@ int launch_rms_norm(__half* out, const __half* in, const __half* weight, int row
   return LCU_OK;
 }
 
-int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cudaStream_t stream) {
-  const int n = ctx_len * (head_dim / 2);
-  rope_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(table, ctx_len, head_dim, theta);
+int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cudaStream_t stream, int first_pos) {
+  const int n = (ctx_len - first_pos) * (head_dim / 2);
+  if (n <= 0) return LCU_OK;
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(table, ctx_len, head_dim, theta, first_pos);
   LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }
@@ -446,6 +447,53 @@ int launch_silu_rows(__half* out, const __half* ab, int m, int f, cudaStream_t s
   LCU_REQUIRE(f % 8 == 0 && (((uintptr_t)out | (uintptr_t)ab) & 15) == 0, "silu_rows: rows of %d elements are not 16-byte vectors", f);
   const size_t n = (size_t)m * (f / 8);
   silu_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(out, ab, m, f);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+// ------------------------------------------------------------------ matmul_type 1: the pedantic product
+// The reference keeps a pair of deliberately plain kernels as "a trivial reference point for optimized kernels"
+// (llama_cu.cu:110-145) and runs them when matmul_type == 1.  Same contract here: one thread owns one output element
+// and adds its K terms strictly in index order.  fp16 weights: binary32 running sum (a product of two halves is exact
+// in binary32).  u8 weights: every term x * (q - 127.5) * scale is formed in binary64 - the reference's 127.5 literal is
+// a double - added to the running sum in binary64, and the sum is rounded back to binary32 after each addition.
+__global__ void __launch_bounds__(256) pedantic_matmul_f16_kernel(__half* out, const __half* lhs, const __half* w, int m, int k, int n, float beta) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)m * n) return;
+  const __half* x = lhs + (idx / n) * (size_t)k;
+  const __half* wr = w + (idx % n) * (size_t)k;
+  float acc = 0.f;
+  for (const __half* end = x + k; x != end; ++x, ++wr) acc = __fmaf_rn(__half2float(*x), __half2float(*wr), acc);
+  out[idx] = __float2half(beta == 0.f ? acc : __fmaf_rn(beta, __half2float(out[idx]), acc));
+}
+__global__ void __launch_bounds__(256) pedantic_matmul_u8_kernel(__half* out, const __half* lhs, const uint8_t* q, const __half* scales, int m, int k,
+                                                                 int n, int bs, float beta) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)m * n) return;
+  const size_t row = idx % n;
+  const __half* x = lhs + (idx / n) * (size_t)k;
+  const uint8_t* qr = q + row * (size_t)k;
+  const __half* sr = scales + row * (size_t)(k / bs);
+  float acc = 0.f;
+  for (int b = 0; b < k / bs; ++b) {
+    const double scale = (double)__half2float(sr[b]);
+    for (int i = b * bs; i < (b + 1) * bs; ++i) {
+      const double term = __dmul_rn(__dmul_rn((double)__half2float(x[i]), (double)(float)qr[i] - 127.5), scale);
+      acc = (float)__dadd_rn((double)acc, term);
+    }
+  }
+  out[idx] = __float2half(beta == 0.f ? acc : __fmaf_rn(beta, __half2float(out[idx]), acc));
+}
+
+int launch_matmul_nt_pedantic(__half* out, const __half* lhs, const void* w, const __half* scales, int bs, int m, int k, int n, float beta,
+                              cudaStream_t stream) {
+  LCU_REQUIRE(m >= 1 && k >= 1 && n >= 1, "matmul_nt (pedantic): empty shape %d x %d x %d", m, k, n);
+  LCU_REQUIRE(bs == 0 || (bs > 0 && k % bs == 0 && scales != nullptr), "matmul_nt (pedantic): block size %d does not divide K=%d", bs, k);
+  const unsigned grid = (unsigned)(((size_t)m * n + 255) / 256);
+  if (bs == 0)
+    pedantic_matmul_f16_kernel<<<grid, 256, 0, stream>>>(out, lhs, (const __half*)w, m, k, n, beta);
+  else
+    pedantic_matmul_u8_kernel<<<grid, 256, 0, stream>>>(out, lhs, (const uint8_t*)w, scales, m, k, n, bs, beta);
   LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }

@@ -13,8 +13,8 @@ int launch_embed(__half* x, int ldx, const void* table, const __half* scales, in
 // out[r][i] = weight[i] *h half(float(in[r][i]) * rsqrt(mean(in[r]^2) + eps))
 int launch_rms_norm(__half* out, const __half* in, const __half* weight, int rows, int dim, float eps, cudaStream_t stream);
 
-// (cos, sin) of pos / theta^(2i/head_dim) for pos < ctx_len, i < head_dim/2
-int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cudaStream_t stream);
+// (cos, sin) of pos / theta^(2i/head_dim) for first_pos <= pos < ctx_len, i < head_dim/2 (entry index pos * head_dim/2 + i)
+int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cudaStream_t stream, int first_pos = 0);
 
 // Rotates q rows in place (row r at position *pos + r), rotates the new k rows into the head-major
 // key cache and copies the new v rows into the head-major value cache.  The position of row 0 is
@@ -25,6 +25,11 @@ int launch_rope_scatter(__half* q, const __half* k_new, const __half* v_new, __h
 
 // out = half(silu(float(a)) * float(b)) element-wise
 int launch_silu(__half* out, const __half* a, const __half* b, size_t n, cudaStream_t stream);
+// matmul_type 1 (reference llama_cu.cu:111-145): out(m,n) = lhs(m,k) . w(n,k)^T + beta * out, one thread per output element,
+// terms added in index order (fp16 weights: binary32 sum; u8 weights, bs > 0: binary64 terms, sum rounded to binary32
+// after every addition).  The on-GPU fp32-accumulate check for the fast kernels; slow by design.
+int launch_matmul_nt_pedantic(__half* out, const __half* lhs, const void* w, const __half* scales, int bs, int m, int k, int n, float beta,
+                              cudaStream_t stream);
 // one warp waiting on an mbarrier that never completes: the wait expires (about a second) and stores its code in *err_word
 int run_bounded_wait_probe(int* err_word, cudaStream_t stream);
 // rows of [a | b]: out[r][j] = silu(ab[r][j]) * ab[r][f + j] for the fused w1|w3 prompt product

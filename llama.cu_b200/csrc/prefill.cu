@@ -12,10 +12,16 @@ prefill_tuning& prefill_tuning_ref() {
   return t;
 }
 
+int& matmul_type_ref() {
+  static int type = 4;
+  return type;
+}
+
 int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, float beta, int* err, cudaStream_t stream, __half* deq,
                 size_t deq_halves) {
   const int K = (int)w.cols, N = (int)w.rows;
   const prefill_tuning& pt = prefill_tuning_ref();
+  if (matmul_type_ref() == 1) return launch_matmul_nt_pedantic(out, lhs, w.w, w.sc, w.bs, m, K, N, beta, stream);
   if (w.bs == 0 && pt.tc_min_rows > 0 && m >= pt.tc_min_rows && gemm_tc_supported(m, N, K, K, lhs, w.w, out))
     return launch_gemm_tc(out, lhs, K, (const __half*)w.w, m, N, K, beta, err, stream, pt.tc_tile_n, pt.tc_pair, pt.tc_split);
   if (w.bs > 0 && deq && pt.u8_deq_min_rows > 0 && m >= pt.u8_deq_min_rows && (size_t)N * K <= deq_halves &&

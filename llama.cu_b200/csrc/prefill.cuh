@@ -20,6 +20,11 @@ struct prefill_tuning {
 };
 prefill_tuning& prefill_tuning_ref();
 
+// llama_cu::matmul_type (reference llama_cu.h:65-68, llama_cu.cu:28): 4 (the reference's tensor-core kernels) and 0 (its
+// cuBLAS path) select the sm_100a kernels of this library; 1 selects the pedantic one-thread-per-output kernels for every
+// matrix product, and a context then runs single-token steps through the unfused operator sequence of the prompt path.
+int& matmul_type_ref();
+
 // Dispatch: fp16 weights with more than 8 rows go to the tcgen05 GEMM (gemm_tc.cu); up to 8 rows, and
 // u8 weights in passes of 8 rows, go through the weight-streaming GEMV.
 // lhs and out are dense row-major ([m][K], [m][N]); err is the device error word.

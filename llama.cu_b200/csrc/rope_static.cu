@@ -7,13 +7,19 @@
 // This variant keeps the table in a fixed file-scope device array instead, so it allocates
 // nothing: no cudaMalloc, no cudaFree, no allocating library routine.
 //
-// Cost and limits: every GPU that loads the library holds the 2 MiB array until the process exits.
-// The table covers at most ROPE_STATIC_MAX_ENTRIES = 262144 (position, pair) entries, e.g. 4096
-// positions at head_dim 128; larger requests are rejected.  All calls share the one array and it
-// keeps the previous call's contents: each call rewrites the entries it is about to use, so nothing
-// has to be cleared, but two calls whose kernels overlap on the GPU (different streams) race on it.
-// The first call on a device looks the array's device address up (cudaGetSymbolAddress with that
-// device current); make that first call outside any stream capture.
+// Cost and limits: the table covers at most ROPE_STATIC_MAX_ENTRIES = 262144 (position, pair)
+// entries, e.g. 4096 positions at head_dim 128; larger requests are rejected.  All calls share the
+// one array and it keeps the previous call's contents: each call rewrites the entries of the
+// positions it is about to use, so nothing has to be cleared, but two calls whose kernels overlap
+// on the GPU (different streams) race on it.
+//
+// When the 2 MiB are taken: the array belongs to this file's device module, and the CUDA runtime
+// loads a module the first time something in it is used.  That first use is the first call on a
+// device (cudaGetSymbolAddress with that device current), so it is the FIRST CALL that reserves the
+// 2 MiB and may synchronise - not the loading of the library.  Make one call per device at start-up
+// (a one-row call is enough), before the process hands the rest of HBM to its own pool and outside
+// any stream capture; from then on the array stays until the process exits and a call takes no
+// device memory at all.
 #include "../../include/llama_cu_c.h"
 #include "ops.cuh"
 
@@ -41,6 +47,14 @@ int static_table(float2** out) {
 extern "C" int lcu_rope_scatter_static(void* q_dev, const void* k_new_dev, const void* v_new_dev, void* k_cache_dev, void* v_cache_dev,
                                        int pos0, int m, int dim, int n_heads, int ctx_len, void* stream) {
   using namespace lcu;
+  {
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) {
+      cudaGetLastError();
+      set_last_error("no CUDA device is visible: this library has no CPU path");
+      return LCU_ERR_CUDA;
+    }
+  }
   LCU_REQUIRE(n_heads >= 1 && dim >= 2 && dim % n_heads == 0 && (dim / n_heads) % 2 == 0, "rope_scatter_static: bad dim %d / n_heads %d", dim, n_heads);
   LCU_REQUIRE(m >= 1 && pos0 >= 0 && pos0 + m <= ctx_len, "rope_scatter_static: positions %d..%d outside the context length %d", pos0, pos0 + m, ctx_len);
   const int hd = dim / n_heads;
@@ -52,7 +66,7 @@ extern "C" int lcu_rope_scatter_static(void* q_dev, const void* k_new_dev, const
   float2* table = nullptr;
   int rc = static_table(&table);
   if (rc) return rc;
-  rc = launch_rope_table(table, pos0 + m, hd, 10000.0f, (cudaStream_t)stream);
+  rc = launch_rope_table(table, pos0 + m, hd, 10000.0f, (cudaStream_t)stream, pos0);  // only the rows this call reads
   if (rc) return rc;
   return launch_rope_scatter((__half*)q_dev, (const __half*)k_new_dev, (const __half*)v_new_dev, (__half*)k_cache_dev, (__half*)v_cache_dev,
                              table, nullptr, pos0, m, dim, n_heads, ctx_len, (cudaStream_t)stream);

@@ -39,18 +39,35 @@ void set_last_error(const char* fmt, ...) {
 }
 const char* last_error() { return g_err; }
 
-struct device_guard {
-  int prev = 0;
-  explicit device_guard(int dev) {
-    cudaGetDevice(&prev);
-    cudaSetDevice(dev);
+// 64 zeroed device words per GPU for the stand-alone operator entry points (word 0: error word of their kernels;
+// word 8: token of lcu_logits_head); allocated at the first use on a device
+int* device_scratch_words() {
+  static int* ptr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptr[dev]) {
+    if (cudaMalloc(&ptr[dev], 256) != cudaSuccess) return nullptr;
+    cudaMemset(ptr[dev], 0, 256);
+    cudaStreamSynchronize(0);  // the kernels that get this word run on other streams
   }
-  ~device_guard() { cudaSetDevice(prev); }
-};
+  return ptr[dev];
+}
 
 uint32_t ffn_dim_of(const model_params& p) {
   uint32_t a = p.dim * 8 / 3;
   return (a + p.multiple_of - 1) / p.multiple_of * p.multiple_of;
+}
+
+// A pipeline stage is one contiguous run of layers: the forward pass keeps the final norm and the output matrix on the
+// GPU of the last layer and hands the residual row from stage to stage, so a GPU may not reappear once it was left.
+bool partition_is_contiguous(const std::vector<int>& layer_gpus) {
+  std::vector<int> seen;
+  for (size_t i = 0; i < layer_gpus.size(); ++i) {
+    if (i > 0 && layer_gpus[i] == layer_gpus[i - 1]) continue;
+    if (std::find(seen.begin(), seen.end(), layer_gpus[i]) != seen.end()) return false;
+    seen.push_back(layer_gpus[i]);
+  }
+  return true;
 }
 
 std::vector<int> partition::used_gpus() const {
@@ -135,6 +152,8 @@ int model::create(std::unique_ptr<model>& out, const model_params& p, const part
   int ndev = 0;
   LCU_CUDA(cudaGetDeviceCount(&ndev));
   for (int g : part.layer_gpus) LCU_REQUIRE(g >= 0 && g < ndev, "model: partition names GPU %d but %d are visible", g, ndev);
+  LCU_REQUIRE(partition_is_contiguous(part.layer_gpus),
+              "model: partition returns to a GPU after leaving it; every GPU must hold one contiguous range of layers");
 
   auto m = std::make_unique<model>();
   m->params = p;
@@ -277,6 +296,37 @@ int model::fill_synthetic(uint64_t seed, float scale) {
 }
 
 // ------------------------------------------------------------------ context
+namespace {
+// Offsets of everything a context keeps in its per-GPU scratch arena.  One function sizes the arena for
+// context::create, for the memory-based partitioner and for llama_params::shared_context_memory_size.
+struct scratch_layout {
+  size_t o_x, o_norm, o_q, o_kn, o_vn, o_att, o_h1, o_h3, o_hs, o_deq, o_scores, o_rope, o_state, o_ids, o_log, o_logits, o_probs;
+  size_t deq_halves, score_halves, total;
+};
+scratch_layout scratch_layout_of(const model_params& p, uint32_t ffn, int context_len) {
+  const size_t ctxl = context_len, d = p.dim, f = ffn, hd = p.dim / p.n_heads;
+  scratch_layout s{};
+  carve cv;
+  s.o_x = cv.take(ctxl * d * 2); s.o_norm = cv.take(ctxl * d * 2); s.o_q = cv.take(ctxl * d * 2);
+  s.o_kn = cv.take(ctxl * d * 2); s.o_vn = cv.take(ctxl * d * 2); s.o_att = cv.take(ctxl * d * 2);
+  s.o_h1 = cv.take(ctxl * f * 2); s.o_h3 = cv.take(ctxl * f * 2); s.o_hs = cv.take(ctxl * f * 2);
+  s.deq_halves = p.q_type ? std::max((size_t)2 * f * d, (size_t)3 * d * d) : 0;  // room for the stacked w1|w3 or wq|wk|wv
+  s.o_deq = cv.take(s.deq_halves * 2);
+  // score buffer of the tcgen05 prompt attention (contexts up to 4096 positions; longer ones use the fused kernel)
+  s.score_halves = context_len <= 4096 ? attention_tc_scratch_halves(p.n_heads, context_len, context_len) : 0;
+  s.o_scores = cv.take(s.score_halves * 2);
+  s.o_rope = cv.take(ctxl * (hd / 2) * sizeof(float2));
+  s.o_state = cv.take(64);
+  s.o_ids = cv.take(ctxl * 2); s.o_log = cv.take(ctxl * 2);
+  s.o_logits = cv.take((size_t)p.n_vocab * 2); s.o_probs = cv.take((size_t)p.n_vocab * 2);
+  s.total = cv.off;
+  return s;
+}
+}  // namespace
+
+size_t context_scratch_bytes(const model_params& p, int context_len) { return scratch_layout_of(p, ffn_dim_of(p), context_len).total; }
+size_t context_kv_bytes_per_layer(const model_params& p, int context_len) { return 2 * round_up((size_t)context_len * p.dim * 2, ALIGN); }
+
 struct gpu_state {
   int device = 0;
   cudaStream_t stream = nullptr;
@@ -363,7 +413,7 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
   context_impl& c = *ctx->impl;
   c.m = m;
   c.opt = opt;
-  const size_t ctxl = opt.context_len, d = p.dim, f = m->ffn;
+  const size_t ctxl = opt.context_len, d = p.dim;
   const std::vector<int> used = m->part.used_gpus();
   c.gpus.resize(used.size());
   c.kv_arenas.assign(used.size(), nullptr);
@@ -390,19 +440,13 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     LCU_CUDA(cudaEventCreateWithFlags(&g.ev, cudaEventDisableTiming));
     // scratch arena: activations for up to context_len rows, rope table, state words,
     // and (first / last GPU) token ids, logits, probabilities, token log
+    const scratch_layout sl = scratch_layout_of(p, m->ffn, opt.context_len);
+    const size_t o_x = sl.o_x, o_norm = sl.o_norm, o_q = sl.o_q, o_kn = sl.o_kn, o_vn = sl.o_vn, o_att = sl.o_att;
+    const size_t o_h1 = sl.o_h1, o_h3 = sl.o_h3, o_hs = sl.o_hs, o_deq = sl.o_deq, o_scores = sl.o_scores, o_rope = sl.o_rope;
+    const size_t o_state = sl.o_state, o_ids = sl.o_ids, o_log = sl.o_log, o_logits = sl.o_logits, o_probs = sl.o_probs;
+    const size_t deq_halves = sl.deq_halves, score_halves = sl.score_halves;
     carve cv;
-    const size_t o_x = cv.take(ctxl * d * 2), o_norm = cv.take(ctxl * d * 2), o_q = cv.take(ctxl * d * 2);
-    const size_t o_kn = cv.take(ctxl * d * 2), o_vn = cv.take(ctxl * d * 2), o_att = cv.take(ctxl * d * 2);
-    const size_t o_h1 = cv.take(ctxl * f * 2), o_h3 = cv.take(ctxl * f * 2), o_hs = cv.take(ctxl * f * 2);
-    const size_t deq_halves = p.q_type ? std::max((size_t)2 * f * d, (size_t)3 * d * d) : 0;  // room for the stacked w1|w3 or wq|wk|wv
-    const size_t o_deq = cv.take(deq_halves * 2);
-    // score buffer of the tcgen05 prompt attention (contexts up to 4096 positions; longer ones use the fused kernel)
-    const size_t score_halves = opt.context_len <= 4096 ? attention_tc_scratch_halves(p.n_heads, opt.context_len, opt.context_len) : 0;
-    const size_t o_scores = cv.take(score_halves * 2);
-    const size_t o_rope = cv.take(ctxl * (hd / 2) * sizeof(float2));
-    const size_t o_state = cv.take(64);
-    const size_t o_ids = cv.take(ctxl * 2), o_log = cv.take(ctxl * 2);
-    const size_t o_logits = cv.take((size_t)p.n_vocab * 2), o_probs = cv.take((size_t)p.n_vocab * 2);
+    cv.off = sl.total;
     LCU_CUDA(cudaMalloc(&g.arena, cv.off));
     g.arena_bytes = cv.off;
     // on the context's own stream: that stream does not synchronise with the default stream, and the table kernel
@@ -470,15 +514,40 @@ int context::tokens_left() const { return impl->opt.context_len - impl->start_po
 int context::position() const { return impl->start_pos; }
 int context::kernels_per_step() const { return 1 + 5 * (int)impl->m->params.n_layers + 2; }
 
+// Error words of all stages (every stage's kernels report into their own GPU's word).  A word that is set is
+// cleared here, so that one expired wait is reported once and the context stays usable.
 int context::device_error() {
   int worst = 0;
   for (auto& g : impl->gpus) {
     int e = 0;
     device_guard dg(g.device);
     if (cudaMemcpy(&e, g.state + 3, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (e) worst = e;
+    if (e) {
+      worst = e;
+      if (cudaMemset(g.state + 3, 0, 4) != cudaSuccess) return -1;
+    }
   }
   return worst;
+}
+
+// After the step's stream has been synchronised: the last stage's word came back with the token (h_stage[3]); with
+// more than one stage the other stages' words are read as well.
+static int finish_step(context& ctx, const char* who) {
+  context_impl& c = *ctx.impl;
+  int code = c.h_stage[3];
+  if (code != 0 || c.gpus.size() > 1) {
+    const int all = ctx.device_error();
+    if (all < 0) {
+      set_last_error("%s: cannot read the device error words", who);
+      return LCU_ERR_CUDA;
+    }
+    if (all) code = all;
+  }
+  if (code != 0) {
+    set_last_error("%s: a kernel gave up on a bounded wait (device error 0x%x)", who, code);
+    return LCU_ERR_DEVICE_WAIT;
+  }
+  return LCU_OK;
 }
 
 // residual stream hand-off between pipeline stages: m_rows x dim halves over NVLink
@@ -653,7 +722,8 @@ int context_impl::enqueue_prefill(int m_rows) {
     const bool rows_stacked = g.kn == g.q + (size_t)opt.context_len * d && g.vn == g.kn + (size_t)opt.context_len * d &&
                               g.h3 == g.h1 + (size_t)opt.context_len * f;
     // u8 weights: the same, with the matrices expanded to fp16 one after the other into the scratch buffer
-    const bool fuse_u8 = pt.fuse && bs > 0 && rows_stacked && pt.u8_deq_min_rows > 0 && m_rows >= pt.u8_deq_min_rows && g.deq != nullptr;
+    const bool pedantic = matmul_type_ref() == 1;  // u8 weights then stay u8 all the way into the pedantic kernel
+    const bool fuse_u8 = !pedantic && pt.fuse && bs > 0 && rows_stacked && pt.u8_deq_min_rows > 0 && m_rows >= pt.u8_deq_min_rows && g.deq != nullptr;
     const bool fuse = pt.fuse && bs == 0 && m_rows > 8 && rows_stacked;
     const bool qkv_stacked = fuse_u8 || (fuse && (char*)L.wk.w == (char*)L.wq.w + (size_t)d * d * 2 && (char*)L.wv.w == (char*)L.wk.w + (size_t)d * d * 2);
     const int ldq = qkv_stacked ? 3 * d : d;
@@ -714,7 +784,12 @@ int context_impl::enqueue_prefill(int m_rows) {
     gpu_state& g = last();
     device_guard dg(g.device);
     // only the last row's logits are used (llama_cu.cu:1194-1195)
-    LCU_TRY(launch_gemv(params_out(m_rows - 1), EPI_PLAIN, g.stream, 0));
+    if (matmul_type_ref() == 1) {
+      LCU_TRY(launch_rms_norm(g.norm, g.x + (size_t)(m_rows - 1) * d, m->norm, 1, d, p.norm_eps, g.stream));
+      LCU_TRY(matmul_rows(logits, g.norm, m->output, 1, 0.f, g.state + 3, g.stream));
+    } else {
+      LCU_TRY(launch_gemv(params_out(m_rows - 1), EPI_PLAIN, g.stream, 0));
+    }
     head_params h{};
     h.logits = logits; h.probs = probs; h.n_vocab = p.n_vocab; h.temperature = opt.temperature;
     h.token_out = g.state + 2; h.next_ids = nullptr;
@@ -810,7 +885,7 @@ int context::next_token(const short* tokens, int n, int* token_out) {
   for (int i = 0; i < n; ++i)
     LCU_REQUIRE(tokens[i] >= 0 && (uint32_t)tokens[i] < c.m->params.n_vocab, "next_token: token id %d outside the vocabulary", tokens[i]);
   LCU_TRY(c.stage_inputs(tokens, n));
-  if (n == 1)
+  if (n == 1 && matmul_type_ref() != 1)  // (the pedantic matmul type has no fused decode kernels: it takes the operator sequence below)
     LCU_TRY(c.run_decode_step(c.start_pos + 1));
   else
     LCU_TRY(c.enqueue_prefill(n));
@@ -818,10 +893,7 @@ int context::next_token(const short* tokens, int n, int* token_out) {
   device_guard dg(c.first().device);
   LCU_CUDA(cudaMemcpyAsync(c.h_stage + 2, c.last().state + 2, 8, cudaMemcpyDeviceToHost, c.first().stream));
   LCU_CUDA(cudaStreamSynchronize(c.first().stream));
-  if (c.h_stage[3] != 0) {
-    set_last_error("next_token: a kernel gave up on a bounded wait (device error 0x%x)", c.h_stage[3]);
-    return LCU_ERR_DEVICE_WAIT;
-  }
+  LCU_TRY(finish_step(*this, "next_token"));
   c.start_pos += n;
   *token_out = c.h_stage[2];
   return LCU_OK;
@@ -832,6 +904,7 @@ int context::decode_chained(short first_token, int n_steps, short* tokens_out, f
   LCU_REQUIRE(n_steps >= 1 && n_steps + c.start_pos <= c.opt.context_len, "decode_chained: %d steps at position %d exceed the context length %d",
               n_steps, c.start_pos, c.opt.context_len);
   LCU_REQUIRE(first_token >= 0 && (uint32_t)first_token < c.m->params.n_vocab, "decode_chained: token id %d outside the vocabulary", first_token);
+  LCU_REQUIRE(matmul_type_ref() != 1, "decode_chained: matmul_type 1 runs host-driven steps only (lcu_context_next_token)");
   LCU_TRY(c.stage_inputs(&first_token, 1));
   device_guard dg(c.first().device);
   LCU_CUDA(cudaEventRecord(c.t0, c.first().stream));
@@ -840,10 +913,7 @@ int context::decode_chained(short first_token, int n_steps, short* tokens_out, f
   LCU_CUDA(cudaMemcpyAsync(c.h_ids, c.log, (size_t)n_steps * 2, cudaMemcpyDeviceToHost, c.first().stream));
   LCU_CUDA(cudaMemcpyAsync(c.h_stage + 2, c.last().state + 2, 8, cudaMemcpyDeviceToHost, c.first().stream));
   LCU_CUDA(cudaStreamSynchronize(c.first().stream));
-  if (c.h_stage[3] != 0) {
-    set_last_error("decode_chained: a kernel gave up on a bounded wait (device error 0x%x)", c.h_stage[3]);
-    return LCU_ERR_DEVICE_WAIT;
-  }
+  LCU_TRY(finish_step(*this, "decode_chained"));
   c.start_pos += n_steps;
   c.last_row = 0;
   memcpy(tokens_out, c.h_ids, (size_t)n_steps * 2);
@@ -889,7 +959,6 @@ int context::bench_kernel(int which, int reps, float* ms_per_launch, uint64_t* b
   };
   gpu_state& g = c.gpus[stage];
   device_guard dg(g.device);
-  const int saved_pos = c.start_pos;
   c.h_stage[0] = 0;
   c.h_stage[1] = 0;
   LCU_CUDA(cudaMemcpyAsync(g.state, c.h_stage, 8, cudaMemcpyHostToDevice, g.stream));
@@ -915,7 +984,9 @@ int context::bench_kernel(int which, int reps, float* ms_per_launch, uint64_t* b
   *ms_per_launch = ms / reps;
   gemv_params a0 = params_of(0, epi);
   *bytes_per_launch = gemv_algorithmic_bytes(a0, epi);
-  c.start_pos = saved_pos;
+  // the launches above wrote position 0 of the K/V caches and the q / residual scratch rows: whatever the context held
+  // is gone, so it is left cleared
+  c.start_pos = 0;
   return LCU_OK;
 }
 

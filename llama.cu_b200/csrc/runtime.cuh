@@ -9,6 +9,20 @@
 
 namespace lcu {
 
+// makes `dev` the current device for the lifetime of the object, then restores the previous one
+struct device_guard {
+  int prev = 0;
+  explicit device_guard(int dev) {
+    cudaGetDevice(&prev);
+    cudaSetDevice(dev);
+  }
+  ~device_guard() { cudaSetDevice(prev); }
+  device_guard(const device_guard&) = delete;
+  device_guard& operator=(const device_guard&) = delete;
+};
+
+int* device_scratch_words();  // 64 zeroed ints on the current device (error word of the stand-alone operators)
+
 #pragma pack(push, 1)
 // The 40-byte `params` file of a weight directory (reference llama_cu.h:280-291, extract.py:30-41).
 struct model_params {
@@ -40,6 +54,9 @@ struct partition {
   int output_gpu() const { return layer_gpus.back(); }
   std::vector<int> used_gpus() const;  // in order of first use
 };
+
+// true when every GPU holds one contiguous run of layers (a GPU does not reappear after another one was used)
+bool partition_is_contiguous(const std::vector<int>& layer_gpus);
 
 struct dev_matrix {
   void* w = nullptr;       // fp16 [rows][cols] or u8 [rows][cols]
@@ -87,6 +104,10 @@ int quantize_dir(const std::string& in_dir, const std::string& out_dir, int bs);
 // greedy fill of the visible GPUs by free memory (reference llama_cu.cu:819-880); layer_gpus gets
 // n_layers entries; fails if the model does not fit
 int autopipe(const model_params& p, int context_len, std::vector<int>& layer_gpus);
+
+// bytes of the scratch arena a context allocates on every GPU it uses, and of one layer's K and V caches
+size_t context_scratch_bytes(const model_params& p, int context_len);
+size_t context_kv_bytes_per_layer(const model_params& p, int context_len);
 
 struct context_options {
   int context_len = 2048;

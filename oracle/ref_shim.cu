@@ -343,6 +343,85 @@ int ref_model_tensor(void* model, const char* name, int which, void** dev_ptr, u
   return 0;
 }
 
+}  // extern "C"
+
+// ---- seeded synthetic weights, generated on the device inside this library --------------------
+// The benchmark's reference arm must not map the product library, so the generator the product
+// uses for its synthetic models is restated here (test infrastructure; same recipe, same bits):
+// one Philox4x32-10 block per element keyed by the seed, counter = (element index, FNV-1a of the
+// tensor name), the eight 16-bit lanes summed (Irwin-Hall) and scaled to unit variance, times
+// `scale`, rounded to half.  Norm vectors are 1.0.  u8 models: each matrix is generated in fp16 and
+// quantized with the reference's own quantizer kernel (ref_quantize_device, transform.cu:28-72).
+__global__ void shim_synth_kernel(half* out, size_t n, uint64_t seed, uint64_t stream_id, float scale) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    uint32_t c0 = (uint32_t)i, c1 = (uint32_t)(i >> 32), c2 = (uint32_t)stream_id, c3 = (uint32_t)(stream_id >> 32);
+    uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    for (int r = 0; r < 10; ++r) {
+      const uint64_t p0 = (uint64_t)0xD2511F53u * c0, p1 = (uint64_t)0xCD9E8D57u * c2;
+      const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0, n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1;
+      c0 = n0; c1 = (uint32_t)p1; c2 = n2; c3 = (uint32_t)p0;
+      k0 += 0x9E3779B9u;
+      k1 += 0xBB67AE85u;
+    }
+    const int sum = (int)(c0 & 0xffffu) + (int)(c0 >> 16) + (int)(c1 & 0xffffu) + (int)(c1 >> 16) + (int)(c2 & 0xffffu) + (int)(c2 >> 16) +
+                    (int)(c3 & 0xffffu) + (int)(c3 >> 16);
+    const float z = __fmul_rn((float)(sum - 262140), 0x1.3988e2p-16f);
+    out[i] = __float2half(__fmul_rn(z, scale));
+  }
+}
+__global__ void shim_fill_kernel(half* out, size_t n, half v) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = v;
+}
+extern "C" int ref_quantize_device(void* q_dev, void* scales_dev, const void* in_dev, uint64_t h, uint64_t w, int bs);
+
+extern "C" int ref_model_fill_synthetic(void* model, uint64_t seed, float scale) {
+  auto* hnd = (ref_model_handle*)model;
+  llama_model_impl* m = hnd->impl();
+  const llama_params& p = m->params;
+  std::vector<std::string> names = {"tok_embeddings", "output", "norm"};
+  for (uint32_t i = 0; i < p.n_layers; ++i)
+    for (const char* t : {"attention_norm", "ffn_norm", "attention.wq", "attention.wk", "attention.wv", "attention.wo", "feed_forward.w1",
+                          "feed_forward.w2", "feed_forward.w3"})
+      names.push_back("layers." + std::to_string(i) + "." + t);
+  for (const std::string& name : names) {
+    tensor4d<half>* vec = nullptr;
+    generic_tensor* g = find_matrix(m, name, &vec);
+    int dev = m->partition.output_gpu;
+    if (name == "tok_embeddings") dev = m->partition.embedding_gpu;
+    if (name.rfind("layers.", 0) == 0) dev = m->partition.layer_gpus[atoi(name.c_str() + 7)];
+    scoped_gpu sg(dev);
+    if (vec) {
+      shim_fill_kernel<<<64, 256>>>(vec->data(), vec->size(), __float2half(1.0f));
+      continue;
+    }
+    if (!g) return 1;
+    uint64_t sid = 0xcbf29ce484222325ull;  // FNV-1a of the tensor name
+    for (unsigned char ch : name) sid = (sid ^ ch) * 0x100000001b3ull;
+    if (g->is_fp16()) {
+      shim_synth_kernel<<<148 * 32, 256>>>(g->as_fp16().data(), g->as_fp16().size(), seed, sid, scale);
+    } else {
+      quantized_tensor& q = g->as_quantized();
+      tensor4d<half> tmp(1, 1, q.q_values.h, q.q_values.w);
+      shim_synth_kernel<<<148 * 32, 256>>>(tmp.data(), tmp.size(), seed, sid, scale);
+      if (ref_quantize_device(q.q_values.data(), q.scales.data(), tmp.data(), q.q_values.h, q.q_values.w, q.quantization_block_size)) return 1;
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  }
+  return cudaGetLastError() != cudaSuccess;
+}
+
+// llama_vocabulary::tokenize (llama_cu.cu:1344-1437) on a vocab file in extract.py's layout (44-61).
+// Returns the number of ids (at most cap are written), or -1 if the file cannot be mapped.
+extern "C" int ref_tokenize(const char* vocab_path, const char* text, int bos, int16_t* out, int cap) {
+  mapped_buffer buf{std::string(vocab_path)};
+  if (!buf.is_ok()) return -1;
+  llama_vocabulary vocab(buf);
+  std::vector<short> ids = vocab.tokenize(text, bos != 0);
+  for (int i = 0; i < (int)ids.size() && i < cap; ++i) out[i] = ids[i];
+  return (int)ids.size();
+}
+
+extern "C" {
 // llama_model::load on a weight directory (llama_cu.cu:987-997); params are read from <dir>/params
 void* ref_model_load(const char* dir, const int* layer_gpus) {
   mapped_buffer pb(std::string(dir) + "/params");

@@ -51,7 +51,7 @@ def test_host_side_shapes_and_partitions():
     assert lcu.lib.lcu_partition_even(2, 4, lg.ctypes.data_as(C.c_void_p)) != 0
     assert b"partition" in lcu.lib.lcu_last_error()
     assert len(lcu.pack_params(4096, 256, 32, 32, 32000)) == 40
-    assert lcu.lib.lcu_set_matmul_type(3) != 0 and lcu.lib.lcu_set_matmul_type(4) == 0
+    assert lcu.lib.lcu_set_matmul_type(3) != 0 and lcu.lib.lcu_set_matmul_type(1) == 0 and lcu.lib.lcu_set_matmul_type(4) == 0
 
 
 def test_oracle_is_not_linked_into_the_product():
@@ -65,12 +65,54 @@ def test_oracle_is_not_linked_into_the_product():
                 assert "oracle" not in src.lower().replace("oracle/liboracle", "") or f == "__init__.py" and "oracle" not in src, f
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/main.cpp"), reason="reference sources not present")
+def test_partition_must_be_contiguous():
+    """A GPU may not reappear after another one was used: the head runs on the last layer's GPU and the residual row is
+    handed from stage to stage, so [0, 1, 0] would run the head against another stage's buffers."""
+    lcu = load_package()
+    ok = lambda lg: lcu.lib.lcu_partition_is_contiguous(np.asarray(lg, np.int32).ctypes.data_as(C.c_void_p), len(lg))
+    assert ok([0, 0, 0]) == 1 and ok([0, 0, 1, 1, 3]) == 1 and ok([2, 2, 0, 1]) == 1
+    assert ok([0, 1, 0]) == 0 and ok([0, 0, 1, 1, 0, 0]) == 0 and ok([1, 0, 2, 0]) == 0
+
+
+@pytest.mark.parametrize("name,dim,heads,layers,bs", [("7B", 4096, 32, 32, 0), ("7B-u8", 4096, 32, 32, 128), ("13B", 5120, 40, 40, 0),
+                                                      ("65B-u8", 8192, 64, 80, 128)])
+def test_context_scratch_figure_counts_every_buffer(name, dim, heads, layers, bs):
+    """One function sizes the per-GPU scratch arena for the context, the memory-based partitioner and
+    llama_params::shared_context_memory_size.  It must cover the activations, the score buffer of the tcgen05 prompt
+    attention (heads x ctx x round_up(ctx, 128) halves) and, for u8 models, the dequantization buffer."""
+    lcu = load_package()
+    ctx = 2048
+    ffn = lcu.lib.lcu_ffn_dim(dim, 256)
+    raw = lcu.pack_params(dim, 256, heads, layers, 32000, 1e-6, bs)
+    got = lcu.lib.lcu_context_scratch_bytes(raw, ctx)
+    activations = 6 * ctx * dim * 2 + 3 * ctx * ffn * 2
+    scores = heads * ctx * ((ctx + 127) // 128 * 128) * 2
+    deq = max(2 * ffn * dim, 3 * dim * dim) * 2 if bs else 0
+    tables = ctx * (dim // heads // 2) * 8 + 2 * 32000 * 2 + 2 * ctx * 2
+    assert activations + scores + deq + tables <= got <= activations + scores + deq + tables + 64 * 256, name
+    assert lcu.lib.lcu_context_kv_bytes_per_layer(raw, ctx) == 2 * ctx * dim * 2
+
+
+REF = os.environ.get("REF", os.environ.get("LLAMA_CU_REFERENCE", "/root/reference"))
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "transform.cu")), reason="reference sources not present")
+def test_reference_transform_tool_builds_against_the_new_header_and_library(tmp_path):
+    """The reference's transform.cu uses the LLAMA_CU_IMPLEMENTATION half of its header (tensor4d, gpu_buffer, generic_tensor,
+    CHECK_CUDA, RETURN_UNLESS): unmodified, it must compile against include/llama_cu.h and link with the new library."""
+    exe = tmp_path / "transform"
+    r = subprocess.run(["nvcc", "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "include"),
+                        os.path.join(REF, "transform.cu"), "-o", str(exe), "-L", os.path.join(ROOT, "llama.cu_b200"), "-lllama_cu_b200"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "main.cpp")), reason="reference sources not present")
 def test_reference_main_compiles_against_the_new_header(tmp_path):
     """Drop-in proof at the source level: the reference's own client builds against include/llama_cu.h."""
     exe = tmp_path / "llama_cu_main"
     cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
-    r = subprocess.run([cxx, "-std=c++17", "-I", os.path.join(ROOT, "include"), "/root/reference/main.cpp", "-o", str(exe),
+    r = subprocess.run([cxx, "-std=c++17", "-I", os.path.join(ROOT, "include"), os.path.join(REF, "main.cpp"), "-o", str(exe),
                         "-L", os.path.join(ROOT, "llama.cu_b200"), "-lllama_cu_b200",
                         "-Wl,-rpath," + os.path.join(ROOT, "llama.cu_b200")], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-2000:]

@@ -21,8 +21,16 @@ GOLD = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "
 CFG = dict(dim=4096, n_heads=32, n_layers=32, n_vocab=32000)
 
 
-@pytest.mark.parametrize("bs", [0, 128])
-def test_7b_tokens_against_reference(lcu, bs):
+@pytest.fixture
+def u8_mode(lcu, request):
+    lcu.check(lcu.lib.lcu_set_tuning(b"int8_factored", request.param))
+    yield request.param
+    lcu.check(lcu.lib.lcu_set_tuning(b"int8_factored", 1))
+
+
+@pytest.mark.parametrize("bs,u8_mode", [(0, 1), (128, 1), (128, 0)], indirect=["u8_mode"])
+def test_7b_tokens_against_reference(lcu, bs, u8_mode, record_property):
+    """u8_mode 1 = the default decode GEMV (scale factored out per block), 0 = the reference's per-weight rounding."""
     ref = np.array(GOLD[f"tokens_bs{bs}_t4"])
     margin = np.array(GOLD[f"top1_bs{bs}_t4"]) - np.array(GOLD[f"top2_bs{bs}_t4"])
     prompt = O.synth_tokens(128, 1234)
@@ -41,6 +49,11 @@ def test_7b_tokens_against_reference(lcu, bs):
     for i in range(256):
         forced.append(ctx.next_token([int(ref[i])]))
     agree = np.array(forced) == ref
+    # the figures a regression would move: where the free run leaves the reference's, and the teacher-forced agreement
+    print(f"7B bs={bs} int8_factored={u8_mode}: free run identical for {diverge} steps (reference margin there "
+          f"{margin[diverge] if diverge < len(ref) else float('nan'):.2e}), teacher-forced top-1 agreement {int(agree.sum())}/{len(agree)}")
+    record_property("free_run_steps", diverge)
+    record_property("teacher_forced_agreement", f"{int(agree.sum())}/{len(agree)}")
     assert agree.mean() >= 0.95, agree.mean()
     assert (margin[~agree] <= 5e-4).all(), margin[~agree]  # median margin is 1.2e-3; mismatches only where the reference itself is undecided
     # determinism: the chained run repeats bit for bit

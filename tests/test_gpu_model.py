@@ -24,10 +24,21 @@ def run_tokens(ctx, prompt, steps):
     return toks
 
 
-@pytest.mark.parametrize("bs,prompt_len", [(0, 12), (128, 12), (0, 40), (128, 40)])
-def test_small_model_matches_oracle(lcu, bs, prompt_len):
+@pytest.fixture
+def u8_mode(lcu, request):
+    """int8_factored for the duration of a test: 1 = scale factored out per block (default), 0 = every weight rounded to
+    half before the product, as the reference's tensor-core kernel does (llama_cu.cu:287-289)."""
+    lcu.check(lcu.lib.lcu_set_tuning(b"int8_factored", request.param))
+    yield request.param
+    lcu.check(lcu.lib.lcu_set_tuning(b"int8_factored", 1))
+
+
+@pytest.mark.parametrize("bs,prompt_len,u8_mode", [(0, 12, 1), (128, 12, 1), (0, 40, 1), (128, 40, 1), (128, 12, 0), (128, 40, 0), (64, 12, 0),
+                                                   (64, 12, 1), (32, 12, 1)], indirect=["u8_mode"])
+def test_small_model_matches_oracle(lcu, bs, prompt_len, u8_mode):
     """12-token prompts go through the multi-row GEMV passes; 40-token prompts through the tcgen05 GEMM (u8 weights
-    expanded to fp16 first) and the tiled prompt attention."""
+    expanded to fp16 first) and the tiled prompt attention.  u8 models run in both weight modes of the decode GEMV and
+    with every supported block size."""
     scale = 0.08
     model = lcu.Model.synthetic(block_size=bs, seed=1234, scale=scale, **SMALL)
     ctx = lcu.Context(model, context_len=64, temperature=0.8)
@@ -215,8 +226,8 @@ def test_quantize_model_dir_matches_in_memory_quantizer(lcu, tmp_path):
 
 
 @pytest.mark.skipif(not R.available(), reason="reference library not built")
-@pytest.mark.parametrize("bs", [0, 128])
-def test_small_model_against_reference_forward(lcu, bs):
+@pytest.mark.parametrize("bs,u8_mode", [(0, 1), (128, 1), (128, 0)], indirect=["u8_mode"])
+def test_small_model_against_reference_forward(lcu, bs, u8_mode):
     cfg = dict(dim=512, n_heads=4, n_layers=4, n_vocab=2000)
     model = lcu.Model.synthetic(block_size=bs, seed=1234, scale=0.06, **cfg)
     ctx = lcu.Context(model, context_len=128, temperature=0.8)
