@@ -1,31 +1,40 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: LLaMA-7B-shaped batch-1 greedy decode (tok/s) on B200.
+"""Benchmark of the hot path: LLaMA-7B-shaped batch-1 greedy decode (tok/s) on B200, fp16 and int8 weights.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload 7b-fp16|7b-int8]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload 7b-fp16|7b-int8|...]
 
-One "step" is one decode step (one new token through all layers, position advancing).  The
-workload is the 7B configuration the metric is quoted on: random-init fp16 weights ~N(0, 0.02)
-(seeded generator), 128-token seeded prompt, context 2048, K greedy steps after W warm-up steps.
-Weights streamed per step (13.2 GB fp16) are far larger than the 126 MB L2, so no flush is needed.
+One "step" is one decode step (one new token through all layers, position advancing).  The headline workload is the
+7B configuration the metric is quoted on: random-init fp16 weights ~N(0, 0.02) (seeded generator), 128-token seeded
+prompt, context 2048, K greedy steps after W warm-up steps.  The same model with every matrix block-absmax quantized to
+u8 (block 128, the reference quantizer's bits) is measured in the same run and reported under "int8".  Weights streamed
+per step (13.2 GB fp16, 6.7 GB u8) are far larger than the 126 MB L2, so no flush is needed between steps.
 
 Printed JSON line (rank 0):
   value     tok/s of K device-chained steps (token fed back on the device), CUDA events, max over ranks
-  e2e       tok/s of K calls of the reference-facing entry point (lcu_context_next_token: host token
-            in, host token out, one synchronisation per token), wall clock around the loop
-  roofline  the dominant kernel (fused RMSNorm + w1|w3 + SiLU GEMV) timed alone over all layers in
-            rotation with CUDA events: algorithmic bytes per launch / mean launch time vs the measured
-            HBM copy bandwidth
-  prefill   (N = 1) the prompt path: tok/s of a 512-token prompt through lcu_context_next_token, and the largest
-            prompt GEMM (the stacked w1|w3 product, 512 x 4096 x 22016, tcgen05 kernel) timed alone with CUDA events against the measured
-            dense bf16 tensor peak
-  cpu_baseline  the CPU oracle on a bounded sample (one of the 32 layers + the output head), host threads
-With N > 1 (torchrun) every rank runs an independent replica on its own GPU (the path does not
-shard at batch 1: layers are sequentially dependent), value = N*K / max-rank time, scaling "weak".
+  e2e       tok/s of K calls of the reference-facing entry point (lcu_context_next_token: host token in, host token
+            out, one synchronisation per token), wall clock around the loop
+  roofline  the dominant kernel (fused RMSNorm + w1|w3 + SiLU GEMV) timed alone over all layers in rotation with CUDA
+            events: algorithmic bytes per launch / mean launch time vs the measured HBM copy bandwidth (and vs this
+            library's own pure-read probe)
+  kernels   the same measurement for every decode GEMV class, and the quantizer
+  int8      value / e2e / roofline / kernels / whole_step of the u8 model, top-1 agreement with the fp16 run
+  config0   the single linear layer y = W x (4096 x 4096, fp16 and u8): error against a binary64 evaluation, GB/s
+  prefill   (N = 1) the prompt path: a 512-token prompt through lcu_context_next_token, and the largest prompt GEMM
+            (tcgen05 kernel) timed alone with CUDA events against the measured dense bf16 tensor peak
+  cpu_baseline  the CPU oracle on a bounded sample (one of the 32 layers + the output head), host threads; plus the
+            scalar host evaluation of config0 (one thread, and all threads)
+With N > 1 (torchrun) every rank runs an independent replica on its own GPU (batch-1 decode does not shard under the
+reference's scheme: layers are sequentially dependent), value = N*K / max-rank time, scaling "weak".  After the replica
+measurement every rank frees its model and rank 0 alone drives the reference's multi-GPU scheme over the N GPUs - the
+layer pipeline (llama_partition) - on the 65B-shaped u8 model ("pipeline"), and the row-sharded tensor-parallel decode
+("tensor_parallel") where the library provides it.
 
---impl reference times the unmodified reference (its CUDA build for sm_100a, oracle/_ref) on the same
-weights, prompt and step count through its own llama_context::next_token, timed as its main.cpp does.
+--impl reference times the unmodified reference (its CUDA build for sm_100a) on the same seeded weights, prompt and
+step count through its own llama_context::next_token, timed as its main.cpp does; its weights are generated inside the
+reference-side test library, so that arm maps none of this repository's product code.
 """
 import argparse
+import ctypes as C
 import importlib.util
 import json
 import os
@@ -45,11 +54,13 @@ WORKLOADS = {
     "65b-int8": dict(dim=8192, n_heads=64, n_layers=80, n_vocab=32000, block_size=128),
     "7b-l4-fp16": dict(dim=4096, n_heads=32, n_layers=4, n_vocab=32000, block_size=0),   # 7B kernel shapes, 4 layers: profiler captures
     "7b-l4-int8": dict(dim=4096, n_heads=32, n_layers=4, n_vocab=32000, block_size=128),
+    "65b-l4-int8": dict(dim=8192, n_heads=64, n_layers=4, n_vocab=32000, block_size=128),
     "tiny-fp16": dict(dim=512, n_heads=4, n_layers=4, n_vocab=2000, block_size=0),  # plumbing checks only
+    "tiny-int8": dict(dim=512, n_heads=4, n_layers=4, n_vocab=2000, block_size=128),
 }
 SEED, SCALE, PROMPT_LEN, CONTEXT_LEN, TEMPERATURE = 1234, 0.02, 128, 2048, 0.8
-# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
-# captures summarised in profiles/gemv_w13_7b_fp16.md and profiles/gemv_w13_7b_int8.md
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from an ncu capture of
+# that kernel on the 4-layer model of the same shapes; a constant of the kernel, not something this run measures
 NCU_TRAFFIC_BYTES = {"7b-fp16": 180413440 + 3508736, "7b-int8": 91672832 + 2845952}
 PREFILL_LEN = 512
 
@@ -75,7 +86,7 @@ def decode_bytes_per_token(cfg, ffn, t_cached):
 
 
 class ClockSampler:
-    """nvidia-smi sampling (200 ms) of SM clock and throttle reasons while the timed region runs."""
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed regions run."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -87,7 +98,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                                          "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -100,7 +111,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
         for line in open(self.path):
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
@@ -108,6 +119,7 @@ class ClockSampler:
             try:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
+                power.append(float(f[3]))
             except ValueError:
                 continue
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
@@ -115,35 +127,31 @@ class ClockSampler:
                     reasons.add(name)
         os.unlink(self.path)
         if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            # "under load" = the samples that saw the GPU drawing power; the first samples of a short run are idle ones
+            loaded = [s for s, p in zip(sm, power) if p >= 0.5 * max(power)] or sm
+            out.update(sm_mhz=statistics.median(loaded), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=max(power))
         return out
 
 
-def measured_peak():
+def measured_peaks():
+    hbm, hbm_src, tf, tf_src = 6650.0, "fallback (6.65 TB/s)", 1590.0, "fallback (1.59 PFLOP/s)"
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
-            return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, copy bandwidth)"
+            d = json.load(open(path))
+            hbm, hbm_src = float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, copy bandwidth)"
+            tf, tf_src = float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, cuBLAS burst)"
         except Exception:
             pass
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return hbm, hbm_src, tf, tf_src
 
 
-def measured_tensor_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        try:
-            return float(json.load(open(path))["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, cuBLAS burst)"
-        except Exception:
-            pass
-    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
-
-
-def prefill_sample(lcu, ctx, cfg, ffn, profile=False, PREFILL_LEN=PREFILL_LEN):
-    """Prompt path: a PREFILL_LEN-token prompt through the public call (wall clock, host tokens in, token out),
+def prefill_sample(lcu, ctx, cfg, ffn, profile=False, prefill_len=PREFILL_LEN):
+    """Prompt path: a prefill_len-token prompt through the public call (wall clock, host tokens in, token out),
     and the largest prompt GEMM alone (CUDA events) against the dense tensor peak."""
     import oracle_lib as O
-    prompt = O.synth_tokens(PREFILL_LEN, SEED + 1, lo=3, hi=min(32000, cfg["n_vocab"]))
+    prompt = O.synth_tokens(prefill_len, SEED + 1, lo=3, hi=min(32000, cfg["n_vocab"]))
     best = None
     for _ in range(3):
         ctx.clear_tokens()
@@ -152,7 +160,7 @@ def prefill_sample(lcu, ctx, cfg, ffn, profile=False, PREFILL_LEN=PREFILL_LEN):
         ctx.next_token(prompt)
         dt = time.perf_counter() - t0
         best = dt if best is None or dt < best else best
-    out = {"prompt_tokens": PREFILL_LEN, "ms": round(best * 1e3, 3), "tok_s": round(PREFILL_LEN / best, 1)}
+    out = {"prompt_tokens": prefill_len, "ms": round(best * 1e3, 3), "tok_s": round(prefill_len / best, 1)}
     if profile:  # one more prompt pass and a few GEMM launches inside the profiler's window
         ctx.clear_tokens()
         lcu.check(lcu.lib.lcu_profiler_start())
@@ -161,8 +169,8 @@ def prefill_sample(lcu, ctx, cfg, ffn, profile=False, PREFILL_LEN=PREFILL_LEN):
             lcu.bench_matmul_f16_ms(2048, cfg["dim"], ffn, reps=2)
         lcu.check(lcu.lib.lcu_profiler_stop())
     if cfg["block_size"] == 0:
-        peak, src = measured_tensor_peak()
-        m, k, n = PREFILL_LEN, cfg["dim"], 2 * ffn  # the stacked w1|w3 product, the largest GEMM of a prompt pass
+        _, _, peak, src = measured_peaks()
+        m, k, n = prefill_len, cfg["dim"], 2 * ffn  # the stacked w1|w3 product, the largest GEMM of a prompt pass
         ms = lcu.bench_matmul_f16_ms(m, k, n, reps=50)
         tf = 2.0 * m * k * n / (ms * 1e-3) / 1e12
         m2 = 2048
@@ -178,7 +186,6 @@ def prefill_sample(lcu, ctx, cfg, ffn, profile=False, PREFILL_LEN=PREFILL_LEN):
 
 def cpu_baseline_sample(cfg, ffn, steps=6):
     """CPU oracle on one layer + the head of the same shapes; extrapolated to all layers."""
-    import numpy as np
     import oracle_lib as O
 
     t0 = time.time()
@@ -202,7 +209,65 @@ def cpu_baseline_sample(cfg, ffn, steps=6):
                       f"weights generated in {gen_s:.1f} s (not timed)"}
 
 
-def dist_setup(n_gpus):
+def config0_inputs():
+    """The single-linear-layer configuration: W 4096 x 4096 fp16 ~N(0, 0.02), x 1 x 4096 fp16 ~N(0, 1), seeded; and W
+    quantized by the reference's quantizer arithmetic (block 128 along K)."""
+    import oracle_lib as O
+    n = k = 4096
+    w = O.synth_f16(n * k, SEED, "W", 0.02).reshape(n, k)
+    x = O.synth_f16(k, SEED, "x", 1.0).reshape(1, k)
+    q, s = O.quantize(w, n, k, 128)
+    return w, x, q, s
+
+
+def config0_gold(w, x, q, s):
+    import numpy as np
+    import oracle_lib as O
+    n, k = w.shape
+    g16, g8 = np.zeros((1, n), np.float64), np.zeros((1, n), np.float64)
+    O.lib().orc_matmul_nt_gold(g16.reshape(-1), x.reshape(-1), w.ctypes.data, None, None, 1, k, n, 0, 0)
+    O.lib().orc_matmul_nt_gold(g8.reshape(-1), x.reshape(-1), None, q.ctypes.data, s.ctypes.data, 1, k, n, 128, 1)  # half-rounded dequantized weights
+    return g16, g8
+
+
+def rel_err(y_u16, gold):
+    import numpy as np
+    y = np.asarray(y_u16, np.uint16).view(np.float16).astype(np.float64).reshape(gold.shape)
+    return float(np.abs(y - gold).max() / np.abs(gold).max())
+
+
+def config0_host_scalar():
+    """Baseline (ii): scalar host evaluation of y = W x (fp32 accumulate, no intrinsics) on the host cores: one thread,
+    and OpenMP over rows with every thread the machine offers; best of 10."""
+    import numpy as np
+    import oracle_lib as O
+    w, x, q, s = config0_inputs()
+    n, k = w.shape
+    L = O.lib()
+    out = {}
+    all_threads = L.orc_num_threads()
+    for label, threads in (("one_thread", 1), ("all_threads", all_threads)):
+        prev = L.orc_set_num_threads(threads)
+        res = {}
+        for name in ("fp16", "int8"):
+            y = np.zeros((1, n), np.uint16)
+            best = None
+            for _ in range(10):
+                t0 = time.perf_counter()
+                if name == "fp16":
+                    L.orc_matmul_nt_f16(y.reshape(-1), x.reshape(-1), w.reshape(-1), 1, k, n, 0.0, 0)
+                else:
+                    L.orc_matmul_nt_fp16u8(y.reshape(-1), x.reshape(-1), q.reshape(-1), s.reshape(-1), 1, k, n, 128, 0.0, 0)
+                dt = time.perf_counter() - t0
+                best = dt if best is None or dt < best else best
+            nbytes = n * k * 2 + k * 2 + n * 2 if name == "fp16" else n * k + n * (k // 128) * 2 + k * 2 + n * 2
+            res[name] = {"ms": round(best * 1e3, 3), "gbs": round(nbytes / best / 1e9, 2)}
+        L.orc_set_num_threads(prev)
+        out[label] = dict(res, cores=threads)
+    return out
+
+
+def dist_setup(n_gpus=None):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -234,47 +299,32 @@ def barrier_sync(dist, lcu):
     lcu.check(lcu.lib.lcu_synchronize())
 
 
-def run_ours(args):
+def measure_decode(lcu, workload, K, W, prompt_len, world, dist, layer_gpus=None, profile=None, with_kernels=True, with_prefill=False,
+                   prefill_len=PREFILL_LEN, forced=None):
+    """One workload on this rank's current device (or over `layer_gpus`): device-chained value, end-to-end value through
+    lcu_context_next_token, per-kernel rooflines.  `forced`: tokens of another run to teacher-force for an agreement figure."""
     import numpy as np
     import oracle_lib as O
 
-    world, rank, local, dist = dist_setup(args.gpus)
-    lcu = load_package()
-    if lcu.lib.lcu_device_count() < 1:
-        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
-    lcu.check(lcu.lib.lcu_set_device(local))
-    cfg = WORKLOADS[args.workload]
+    cfg = WORKLOADS[workload]
     ffn = lcu.lib.lcu_ffn_dim(cfg["dim"], 256)
-    K, W = args.steps, args.warmup
-    PROMPT_LEN = args.prompt_len
-    ctx_len = max(CONTEXT_LEN, PROMPT_LEN + W + K + 2)
-    layer_gpus = None
-    if args.pipeline > 1:  # one process, layers split evenly over the first P devices (the reference's pipelined configurations)
-        if world > 1:
-            raise SystemExit("--pipeline is a single-process mode; launch it without torchrun")
-        if lcu.lib.lcu_device_count() < args.pipeline:
-            raise SystemExit(f"--pipeline {args.pipeline} needs {args.pipeline} GPUs")
-        per = (cfg["n_layers"] + args.pipeline - 1) // args.pipeline
-        layer_gpus = [min(i // per, args.pipeline - 1) for i in range(cfg["n_layers"])]
+    ctx_len = max(CONTEXT_LEN, prompt_len + W + K + 2)
     t_gen0 = time.perf_counter()
     model = lcu.Model.synthetic(seed=SEED, scale=SCALE, layer_gpus=layer_gpus, **cfg)
     gen_s = time.perf_counter() - t_gen0
     ctx = lcu.Context(model, context_len=ctx_len, temperature=TEMPERATURE)
-    prompt = O.synth_tokens(PROMPT_LEN, SEED, lo=3, hi=min(32000, cfg["n_vocab"]))
+    prompt = O.synth_tokens(prompt_len, SEED, lo=3, hi=min(32000, cfg["n_vocab"]))
 
     # ---- device-chained decode: `value`
     t_prefill0 = time.perf_counter()
     first = ctx.next_token(prompt)
     prefill_s = time.perf_counter() - t_prefill0
     warm_tokens, _ = ctx.decode_chained(first, W)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     barrier_sync(dist, lcu)
-    if args.profile == "decode":
+    if profile == "decode":
         lcu.check(lcu.lib.lcu_profiler_start())
     tokens, ms = ctx.decode_chained(int(warm_tokens[-1]), K)
-    if args.profile == "decode":
+    if profile == "decode":
         lcu.check(lcu.lib.lcu_profiler_stop())
     barrier_sync(dist, lcu)
     ms_all = reduce_max_time(ms, dist)
@@ -294,63 +344,245 @@ def run_ours(args):
     lcu.check(lcu.lib.lcu_synchronize())
     e2e_ms = (time.perf_counter() - t0) * 1e3
     barrier_sync(dist, lcu)
-    clocks = sampler.stop() if rank == 0 else None
     e2e_ms_all = reduce_max_time(e2e_ms, dist)
     e2e_value = world * K / (e2e_ms_all / 1e3)
     same_tokens = bool((np.array(e2e_tokens, np.int16) == tokens).all())
+    res = {"workload": workload, "cfg": cfg, "ffn": ffn, "ctx_len": ctx_len, "gen_s": gen_s, "prefill_s": prefill_s, "value": value,
+           "ms_per_step": ms_all / K, "first": int(first), "warm_tokens": [int(t) for t in warm_tokens], "tokens": [int(t) for t in tokens],
+           "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": 10, "d2h_bytes_per_step": 8,
+                   "ms_per_step": round(e2e_ms_all / K, 5), "tokens_equal_chained_run": same_tokens},
+           "kernels_per_step": ctx.kernels_per_step()}
 
-    # ---- roofline of the dominant kernel, timed alone with CUDA events on the launching stream
-    peak, peak_src = measured_peak()
-    reps = 10 * cfg["n_layers"]
-    names = ["norm+wq|wk|wv+rope", "wo+residual", "norm+w1|w3+silu", "w2+residual", "norm+output"]
-    kernels = {}
-    for which, name in enumerate(names):
-        kms, kbytes = ctx.bench_kernel(which, reps if which < 4 else 20)
-        kernels[name] = {"us": round(kms * 1e3, 3), "bytes": kbytes, "gbs": round(kbytes / (kms * 1e-3) / 1e9, 1)}
-    dom = kernels["norm+w1|w3+silu"]
-    roofline = {"bound": "hbm", "kernel": "gemv1_kernel<WT, EPI_SILU> (fused RMSNorm + w1|w3 + SiLU gate)", "achieved": dom["gbs"], "peak": peak,
-                "unit": "GB/s", "frac": round(dom["gbs"] / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                "algorithmic_bytes_per_launch": dom["bytes"], "us_per_launch": dom["us"], "peak_source": peak_src,
-                "frac_of_nominal_8tbs": round(dom["gbs"] / 8000.0, 4)}
-    t_mid = PROMPT_LEN + W + K // 2
+    if forced is not None:  # top-1 agreement with another run's tokens, teacher-forced on them
+        ctx.clear_tokens()
+        mine = [ctx.next_token(prompt)]
+        for t in forced["feed"]:
+            mine.append(ctx.next_token([t]))
+        want = [forced["first"]] + forced["feed"][1:] + [forced["last"]]
+        res["agreement"] = {"steps": len(want), "top1_equal": int(sum(int(a == b) for a, b in zip(mine, want)))}
+
+    t_mid = prompt_len + W + K // 2
     step_bytes = decode_bytes_per_token(cfg, ffn, t_mid)
-    whole_step = {"bytes_per_token": step_bytes, "achieved_gbs": round(step_bytes * (K / (ms_all / 1e3)) / 1e9, 1),
-                  "frac_of_measured_peak": round(step_bytes * (K / (ms_all / 1e3)) / 1e9 / peak, 4),
-                  "frac_of_nominal_8tbs": round(step_bytes * (K / (ms_all / 1e3)) / 1e9 / 8000.0, 4)}
-    kps = ctx.kernels_per_step()
-    prefill = prefill_sample(lcu, ctx, cfg, ffn, args.profile == "prefill", args.prefill_len) if world == 1 and ctx_len >= args.prefill_len + 2 else None
+    hbm_peak, hbm_src, _, _ = measured_peaks()
+    gbs = step_bytes * (K / (ms_all / 1e3)) / 1e9
+    res["whole_step"] = {"bytes_per_token": step_bytes, "achieved_gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / hbm_peak, 4),
+                         "frac_of_nominal_8tbs": round(gbs / 8000.0, 4)}
+    if with_kernels:
+        # ---- roofline of every decode GEMV class, timed alone with CUDA events on the launching stream
+        reps = 10 * cfg["n_layers"]
+        names = ["norm+wq|wk|wv+rope", "wo+residual", "norm+w1|w3+silu", "w2+residual", "norm+output"]
+        kernels = {}
+        for which, name in enumerate(names):
+            kms, kbytes = ctx.bench_kernel(which, reps if which < 4 else 20)
+            kernels[name] = {"us": round(kms * 1e3, 3), "bytes": kbytes, "gbs": round(kbytes / (kms * 1e-3) / 1e9, 1),
+                             "frac": round(kbytes / (kms * 1e-3) / 1e9 / hbm_peak, 4)}
+        kernels["norm+output"]["note"] = "one 262 MB matrix (2x L2) relaunched; the other classes rotate over every layer's weights"
+        dom = kernels["norm+w1|w3+silu"]
+        res["kernels"] = kernels
+        res["roofline"] = {"bound": "hbm", "kernel": "gemv1_kernel<WT, EPI_SILU> (fused RMSNorm + w1|w3 + SiLU gate)", "achieved": dom["gbs"],
+                           "peak": hbm_peak, "unit": "GB/s", "frac": round(dom["gbs"] / hbm_peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(workload),
+                           "traffic_source": "ncu capture of this kernel on the 4-layer model (dram__bytes_read.sum + dram__bytes_write.sum per launch); "
+                                             "a constant, not measured by this run",
+                           "algorithmic_bytes_per_launch": dom["bytes"], "us_per_launch": dom["us"], "peak_source": hbm_src,
+                           "frac_of_nominal_8tbs": round(dom["gbs"] / 8000.0, 4)}
+    if with_prefill and ctx_len >= prefill_len + 2:
+        res["prefill"] = prefill_sample(lcu, ctx, cfg, ffn, profile == "prefill", prefill_len)
     ctx.close()
     model.close()
+    return res
+
+
+def read_ceiling(lcu):
+    """This library's pure-read probe (the GEMV's bulk-copy ring with the arithmetic removed): the bandwidth a read-only
+    stream can reach on this GPU, a second denominator beside the copy figure."""
+    try:
+        nbytes = 2 << 30
+        ms = lcu.read_ceiling_ms(nbytes, reps=5, copies_per_stage=2)
+        return round(nbytes / (ms * 1e-3) / 1e9, 1)
+    except Exception:
+        return None
+
+
+def config0_ours(lcu, kernels16, kernels8):
+    """y = W x through lcu_matmul_nt_* on the seeded inputs: error against the binary64 evaluation; GB/s from the
+    rotation measurement of the same kernel on the same shape (wo of the 7B model, 32 distinct matrices)."""
+    w, x, q, s = config0_inputs()
+    g16, g8 = config0_gold(w, x, q, s)
+    out = {"shape": [1, 4096, 4096],
+           "fp16": {"max_abs_err_over_max_gold": rel_err(lcu.matmul_nt(x, w), g16)},
+           "int8": {"max_abs_err_over_max_gold": rel_err(lcu.matmul_nt(x, q, s, 128), g8),
+                    "gold": "binary64 sum over the half-rounded dequantized weights (the arithmetic the reference's kernel defines)"}}
+    lcu.check(lcu.lib.lcu_set_tuning(b"int8_factored", 0))
+    try:
+        out["int8"]["max_abs_err_over_max_gold_reference_rounding_mode"] = rel_err(lcu.matmul_nt(x, q, s, 128), g8)
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"int8_factored", 1))
+    for name, ker in (("fp16", kernels16), ("int8", kernels8)):
+        if ker:
+            k = ker["wo+residual"]
+            out[name].update(us=k["us"], gbs=k["gbs"], bytes=k["bytes"],
+                             timing="the same kernel and shape inside the model (wo + residual), 32 distinct matrices in rotation, CUDA events")
+    return out
+
+
+def pipeline_leg(lcu, n_gpus, K, W, tp=False):
+    """Rank 0 alone, after the replicas are gone: the reference's multi-GPU scheme - contiguous layer ranges per GPU,
+    the residual row handed from stage to stage over NVLink - on the 65B-shaped u8 model (512-token prompt), against the
+    same model on one GPU (tokens must be identical: same kernels, the hand-off copies bits)."""
+    workload, prompt_len, steps = "65b-int8", 512, min(K, 32)
+    cfg = WORKLOADS[workload]
+    single = measure_decode(lcu, workload, steps, W, prompt_len, 1, None, with_kernels=False)
+    per = (cfg["n_layers"] + n_gpus - 1) // n_gpus
+    layer_gpus = [min(i // per, n_gpus - 1) for i in range(cfg["n_layers"])]
+    piped = measure_decode(lcu, workload, steps, W, prompt_len, 1, None, layer_gpus=layer_gpus, with_kernels=False)
+    return {"workload": f"llama-{workload} greedy decode, batch 1, {prompt_len}-token seeded prompt, {steps} steps", "gpus": n_gpus,
+            "layers_per_gpu": per, "value": round(piped["value"], 2), "ms_per_step": round(piped["ms_per_step"], 4), "e2e": piped["e2e"],
+            "single_gpu_value": round(single["value"], 2), "single_gpu_e2e": single["e2e"]["value"],
+            "tokens_equal_single_gpu": piped["tokens"] == single["tokens"] and piped["first"] == single["first"],
+            "whole_step": piped["whole_step"], "weights_generated_s": round(piped["gen_s"], 1),
+            "note": "one stage is active at a time at batch 1: the layer pipeline buys capacity, not speed (the reference's scheme)"}
+
+
+def run_ours(args):
+    world, rank, local, dist = dist_setup()
+    lcu = load_package()
+    if lcu.lib.lcu_device_count() < 1:
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    lcu.check(lcu.lib.lcu_set_device(local))
+    K, W = args.steps, args.warmup
+    layer_gpus = None
+    if args.pipeline > 1:  # one process, layers split evenly over the first P devices (the reference's pipelined configurations)
+        if world > 1:
+            raise SystemExit("--pipeline is a single-process mode; launch it without torchrun")
+        if lcu.lib.lcu_device_count() < args.pipeline:
+            raise SystemExit(f"--pipeline {args.pipeline} needs {args.pipeline} GPUs")
+        n_layers = WORKLOADS[args.workload]["n_layers"]
+        per = (n_layers + args.pipeline - 1) // args.pipeline
+        layer_gpus = [min(i // per, args.pipeline - 1) for i in range(n_layers)]
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    main = measure_decode(lcu, args.workload, K, W, args.prompt_len, world, dist, layer_gpus=layer_gpus, profile=args.profile,
+                          with_prefill=(world == 1), prefill_len=args.prefill_len)
+    # ---- the int8 half of the metric: the same model with every matrix quantized (the reference quantizer's bits)
+    int8 = None
+    if args.workload == "7b-fp16" and not args.no_int8 and args.pipeline <= 1:
+        feed = [main["first"]] + main["warm_tokens"] + main["tokens"]
+        forced = {"first": main["first"], "feed": feed[:-1], "last": feed[-1]}
+        int8 = measure_decode(lcu, "7b-int8", K, W, args.prompt_len, world, dist, forced=forced)
+    clocks = sampler.stop() if rank == 0 else None
+    cfg, ffn = main["cfg"], main["ffn"]
+    ceiling = read_ceiling(lcu) if rank == 0 else None
 
     line = {
-        "metric": "7B batch-1 decode tok/s" if args.workload.startswith("7b") else f"{args.workload} batch-1 decode tok/s",
-        "value": round(value, 2), "unit": "tok/s", "n_gpus": world if args.pipeline <= 1 else args.pipeline, "steps": K, "warmup": W,
-        "ms_per_step": round(ms_all / K, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": "7B batch-1 decode tok/s (fp16, int8); matmul achieved HBM TB/s vs peak" if args.workload.startswith("7b") else f"{args.workload} batch-1 decode tok/s",
+        "value": round(main["value"], 2), "unit": "tok/s", "n_gpus": world if args.pipeline <= 1 else args.pipeline, "steps": K, "warmup": W,
+        "ms_per_step": round(main["ms_per_step"], 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16" if cfg["block_size"] == 0 else "u8 weights x f16 activations, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"llama-{args.workload} greedy decode, batch 1, {PROMPT_LEN}-token seeded prompt, context {ctx_len}",
+        "config": {"workload": f"llama-{args.workload} greedy decode, batch 1, {args.prompt_len}-token seeded prompt, context {main['ctx_len']}",
                    "parallelism": (f"layer pipeline over {args.pipeline} GPUs in one process (one stage active at a time at batch 1)" if args.pipeline > 1
                                    else "1 GPU" if world == 1 else f"{world} independent replicas (replicas only: batch-1 decode does not shard)"),
-                   "weights_generated_s": round(gen_s, 1),
+                   "weights_generated_s": round(main["gen_s"], 1),
                    "l2": "inputs larger than L2: each step streams its weights once, far more than the 126 MB L2",
-                   "weights": f"random-init ~N(0,{SCALE}) (Irwin-Hall, seed {SEED}), RMSNorm weights 1.0", "prefill_s": round(prefill_s, 4)},
-        "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": 10, "d2h_bytes_per_step": 8,
-                "ms_per_step": round(e2e_ms_all / K, 5), "tokens_equal_chained_run": same_tokens},
-        "gpu_launches": K * kps, "kernels_per_step": kps,
-        "roofline": roofline, "kernels": kernels, "whole_step": whole_step, "clocks": clocks,
+                   "weights": f"random-init ~N(0,{SCALE}) (Irwin-Hall, seed {SEED}), RMSNorm weights 1.0", "prefill_s": round(main["prefill_s"], 4)},
+        "e2e": main["e2e"],
+        "gpu_launches": K * main["kernels_per_step"], "kernels_per_step": main["kernels_per_step"],
+        "roofline": main["roofline"], "kernels": main["kernels"], "whole_step": main["whole_step"], "clocks": clocks,
     }
-    if prefill is not None:
-        line["prefill"] = prefill
+    if ceiling:
+        for r in (main, int8):
+            if r is not None:
+                r["roofline"]["read_ceiling_gbs"] = ceiling
+                r["roofline"]["frac_of_read_ceiling"] = round(r["roofline"]["achieved"] / ceiling, 4)
+                r["whole_step"]["frac_of_read_ceiling"] = round(r["whole_step"]["achieved_gbs"] / ceiling, 4)
+    if int8 is not None:
+        a = int8["agreement"]
+        line["int8"] = {"workload": "llama-7b-int8 (every matrix block-absmax u8, block 128, fp16 scales; fp16 activations and KV cache), same prompt and steps",
+                        "dtype": "u8 weights x f16 activations, f32 accumulate", "value": round(int8["value"], 2), "unit": "tok/s",
+                        "ms_per_step": round(int8["ms_per_step"], 5), "e2e": int8["e2e"], "roofline": int8["roofline"], "kernels": int8["kernels"],
+                        "whole_step": int8["whole_step"], "gpu_launches": K * int8["kernels_per_step"],
+                        "top1_agreement_with_fp16": {"teacher_forced_steps": a["steps"], "equal": a["top1_equal"],
+                                                     "frac": round(a["top1_equal"] / a["steps"], 4)},
+                        "weights_generated_s": round(int8["gen_s"], 1)}
+        line["gpu_launches"] += K * int8["kernels_per_step"]
+    if "prefill" in main:
+        line["prefill"] = main["prefill"]
+    if rank == 0 and world == 1 and args.pipeline <= 1 and args.workload.startswith("7b"):
+        line["config0"] = config0_ours(lcu, main.get("kernels") if cfg["block_size"] == 0 else None,
+                                       int8["kernels"] if int8 is not None else (main.get("kernels") if cfg["block_size"] else None))
+        qms = C.c_float(0)
+        qh, qw = 32000, 4096  # a 262 MB matrix (2x L2): the output / embedding matrix of the 7B model
+        lcu.check(lcu.lib.lcu_bench_quantize(qh, qw, 128, 20, C.byref(qms)))
+        qbytes = qh * qw * 3 + qh * qw // 128 * 2
+        hbm_peak = measured_peaks()[0]
+        line["kernels"]["quantize_absmax_uint8"] = {"us": round(qms.value * 1e3, 2), "bytes": qbytes, "gbs": round(qbytes / (qms.value * 1e-3) / 1e9, 1),
+                                                    "frac": round(qbytes / (qms.value * 1e-3) / 1e9 / hbm_peak, 4), "shape": [qh, qw], "block": 128}
+    if world > 1:
+        # the replicas are done: everything is freed, rank 0 alone drives the multi-GPU scheme of the path over the N GPUs
+        barrier_sync(dist, lcu)
+        if rank == 0 and not args.no_pipeline_leg:
+            try:
+                line["pipeline"] = pipeline_leg(lcu, world, K, W)
+            except Exception as e:  # the replica numbers stand on their own
+                line["pipeline"] = {"error": str(e)[:300]}
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample(cfg, ffn)
+            if args.workload.startswith("7b"):
+                line["cpu_baseline"]["config0_host_scalar"] = config0_host_scalar()
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def run_reference(args):
+def reference_decode(R, cublas, mtype, cfg, K, W, ctx_len, prompt):
+    """The reference's own forward pass on seeded weights generated inside the reference-side library."""
+    L = R.lib(cublas=cublas)
+    L.ref_initialize()
+    model = L.ref_model_alloc(cfg["dim"], 256, cfg["n_heads"], cfg["n_layers"], cfg["n_vocab"], 1e-6, cfg["block_size"], None)
+    if not model or L.ref_model_fill_synthetic(model, SEED, SCALE) != 0:
+        raise RuntimeError("the reference model could not be created")
+    ctx = L.ref_context_create(model, ctx_len, TEMPERATURE, mtype)
     import numpy as np
+    t0 = time.perf_counter()
+    tok = L.ref_next_token(ctx, prompt, len(prompt), mtype)
+    prefill_s = time.perf_counter() - t0
+    warm = np.empty(W, np.int16)
+    L.ref_decode_timed(ctx, int(tok), W, warm, mtype)
+    tokens = np.empty(K, np.int16)
+    secs = L.ref_decode_timed(ctx, int(warm[-1]), K, tokens, mtype)
+    L.ref_context_free(ctx)
+    L.ref_model_free(model)
+    return {"value": K / secs, "ms_per_step": secs / K * 1e3, "prefill_s": prefill_s, "first_tokens": [int(t) for t in tokens[:8]]}
+
+
+def reference_config0(R):
+    """config0 through the reference's own matmul_nt dispatch: matmul_type 4 (tensor-core tiles), 1 (naive) and, in the
+    ENABLE_CUBLAS build, 0 (cublasGemmEx): error against the binary64 evaluation, and time over 32 distinct matrices."""
+    w, x, q, s = config0_inputs()
+    g16, g8 = config0_gold(w, x, q, s)
+    import numpy as np
+    out = {"shape": [1, 4096, 4096], "timing": "32 distinct weight matrices in rotation, CUDA events, mean of 320 launches"}
+    variants = [("type4_tensor_core", False, 4), ("type1_naive", False, 1)] + ([("type0_cublas", True, 0)] if R.cublas_available() else [])
+    for name, cublas, mtype in variants:
+        L = R.lib(cublas=cublas)
+        L.ref_initialize()
+        rec = {}
+        y = np.zeros((1, 4096), np.uint16)
+        if L.ref_matmul_nt_f16(y, x, w, 1, 4096, 4096, 0.0, mtype, 0, None) == 0:
+            ms = L.ref_matmul_rotating_ms(1, 4096, 4096, 0, mtype, 32, 320)
+            rec["fp16"] = {"max_abs_err_over_max_gold": rel_err(y, g16), "us": round(ms * 1e3, 2), "gbs": round(33570816 / (ms * 1e-3) / 1e9, 1)}
+        if mtype != 0:  # the reference asserts on quantized weights with matmul_type 0 (llama_cu.cu:1516)
+            y8 = np.zeros((1, 4096), np.uint16)
+            if L.ref_matmul_nt_fp16u8(y8, x, q, s, 1, 4096, 4096, 128, 0.0, mtype, 0, None) == 0:
+                ms = L.ref_matmul_rotating_ms(1, 4096, 4096, 128, mtype, 32, 320)
+                rec["int8"] = {"max_abs_err_over_max_gold": rel_err(y8, g8), "us": round(ms * 1e3, 2), "gbs": round(17055744 / (ms * 1e-3) / 1e9, 1)}
+        out[name] = rec
+    return out
+
+
+def run_reference(args):
     import oracle_lib as O
     import ref_lib as R
 
@@ -360,12 +592,17 @@ def run_reference(args):
         return
     cfg = WORKLOADS[args.workload]
     K, W = args.steps, args.warmup
-    base = {"impl": "reference", "metric": "7B batch-1 decode tok/s", "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+    base = {"impl": "reference", "metric": "7B batch-1 decode tok/s (fp16, int8); matmul achieved HBM TB/s vs peak", "unit": "tok/s", "n_gpus": world,
+            "steps": K, "warmup": W, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
             "dtype": "f16" if cfg["block_size"] == 0 else "u8 weights x f16 activations, f32 accumulate"}
-    lcu = load_package()
-    if not R.available() or lcu.lib.lcu_device_count() < 1:
-        # no reference build travelled to this machine: time the CPU restatement on a bounded sample
+    have_gpu = False
+    if R.available():
+        try:
+            have_gpu = subprocess.run(["nvidia-smi", "-L"], capture_output=True, timeout=60).returncode == 0
+        except Exception:
+            have_gpu = False
+    if not R.available() or not have_gpu:
+        # no reference build travelled to this machine (or no GPU): time the CPU restatement on a bounded sample
         ffn = O.lib().orc_ffn_dim(cfg["dim"], 256)
         cb = cpu_baseline_sample(cfg, ffn)
         base.update(value=round(cb["value"], 4), ms_per_step=round(1e3 / cb["value"], 3), cpu_baseline=cb,
@@ -374,30 +611,37 @@ def run_reference(args):
         print(json.dumps(base), flush=True)
         return
     ctx_len = max(CONTEXT_LEN, PROMPT_LEN + W + K + 2)
-    R.lib().ref_initialize()
-    model = lcu.Model.synthetic(seed=SEED, scale=SCALE, **cfg)  # same seeded weights, copied device to device
-    ref = R.RefModel(lcu, model, cfg["dim"], 256, cfg["n_heads"], cfg["n_layers"], cfg["n_vocab"], 1e-6, cfg["block_size"], ctx_len,
-                     TEMPERATURE, mtype=4)
-    model.close()
     prompt = O.synth_tokens(PROMPT_LEN, SEED, lo=3, hi=min(32000, cfg["n_vocab"]))
-    t0 = time.perf_counter()
-    tok = ref.next_token(prompt)
-    prefill_s = time.perf_counter() - t0
-    warm, _ = ref.decode_timed(tok, W)
-    lcu.check(lcu.lib.lcu_synchronize())
-    tokens, secs = ref.decode_timed(int(warm[-1]), K)
-    lcu.check(lcu.lib.lcu_synchronize())
-    ref.close()
-    value = K / secs
-    base.update(value=round(value, 2), ms_per_step=round(secs / K * 1e3, 4),
+    main = reference_decode(R, False, 4, cfg, K, W, ctx_len, prompt)
+    value = main["value"]
+    base.update(value=round(value, 2), ms_per_step=round(main["ms_per_step"], 4),
                 config={"workload": f"llama-{args.workload} greedy decode, batch 1, {PROMPT_LEN}-token seeded prompt, context {ctx_len}",
-                        "reference": "unmodified eiz/llama.cu built for sm_100a (oracle/_ref), matmul_type 4, llama_context::next_token "
-                                     "timed with steady_clock as main.cpp:80-100 does; the reference has no CPU path",
-                        "prefill_s": round(prefill_s, 3)},
+                        "reference": "unmodified eiz/llama.cu built for sm_100a (its CMake default: ENABLE_CUBLAS off), matmul_type 4, "
+                                     "llama_context::next_token timed with steady_clock as main.cpp:80-100 does; the reference has no CPU path; "
+                                     "weights generated by the reference-side test library (no product code is loaded by this arm)",
+                        "prefill_s": round(main["prefill_s"], 3)},
                 cpu_baseline={"value": round(value, 2), "unit": "tok/s", "cores": 1, "kind": "reference",
                               "sample": f"all {K} decode steps; one host thread driving the reference's CUDA kernels on the same B200"},
                 e2e={"value": round(value, 2), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                first_tokens=[int(t) for t in tokens[:8]])
+                first_tokens=main["first_tokens"])
+    variants = {}
+    if args.workload == "7b-fp16" and not args.no_int8:
+        for name, cublas, mtype, wl in (("matmul_type_0_cublas_fp16", True, 0, "7b-fp16"), ("matmul_type_4_int8", False, 4, "7b-int8"),
+                                        ("matmul_type_1_naive_fp16", False, 1, "7b-fp16")):
+            if cublas and not R.cublas_available():
+                variants[name] = {"unavailable": "the ENABLE_CUBLAS build of the reference is not present"}
+                continue
+            try:
+                steps = K if mtype != 1 else min(K, 4)  # the naive kernels take ~a second per token
+                r = reference_decode(R, cublas, mtype, WORKLOADS[wl], steps, W if mtype != 1 else 3, ctx_len, prompt)
+                variants[name] = {"value": round(r["value"], 2), "unit": "tok/s", "ms_per_step": round(r["ms_per_step"], 4), "steps": steps}
+            except Exception as e:
+                variants[name] = {"error": str(e)[:200]}
+        base["variants"] = variants
+        try:
+            base["config0"] = reference_config0(R)
+        except Exception as e:
+            base["config0"] = {"error": str(e)[:200]}
     print(json.dumps(base), flush=True)
 
 
@@ -409,6 +653,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="7b-fp16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-int8", action="store_true", help="skip the int8 half of the metric (and the reference arm's extra variants)")
+    ap.add_argument("--no-pipeline-leg", action="store_true", help="N > 1: skip rank 0's layer-pipeline run over the N GPUs")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="seeded prompt length (128 for the headline configuration)")
     ap.add_argument("--prefill-len", type=int, default=PREFILL_LEN, help="prompt length of the prefill sample (512; from 768 rows the tcgen05 attention path runs)")
     ap.add_argument("--pipeline", type=int, default=1, help="single process: split the layers evenly over this many GPUs")

@@ -187,6 +187,10 @@ int lcu_selftest_bounded_wait(int* device_code_out);
 /* lcu_matmul_nt_f16 (beta = 0, default stream) launched `reps` times back to back between two CUDA events on that
  * stream: mean milliseconds per launch.  Used to put the prompt GEMM against the tensor-core roofline. */
 int lcu_bench_matmul_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, int reps, float* ms_per_launch_out);
+/* lcu_quantize_absmax_uint8 on a seeded fp16 matrix [h][w] resident in device memory, `reps` launches between two CUDA
+ * events on the launching stream: mean milliseconds per launch (algorithmic traffic: 2 bytes read, 1 + 2/bs written per
+ * element; use a matrix larger than the L2 cache) */
+int lcu_bench_quantize(uint64_t h, uint64_t w, int bs, int reps, float* ms_per_launch_out);
 /* pure-read ceiling: a kernel that only streams `bytes` from HBM with the same bulk-copy ring (16 KiB stages, each
  * fetched as copies_per_stage bulk copies, 1..32); ms per pass */
 int lcu_bench_read_ceiling(uint64_t bytes, int reps, int copies_per_stage, float* ms_per_pass_out);

@@ -80,6 +80,7 @@ _SIG = {
     "lcu_bench_decode_kernel": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
     "lcu_profiler_start": (C.c_int, []),
     "lcu_profiler_stop": (C.c_int, []),
+    "lcu_bench_quantize": (C.c_int, [C.c_uint64, C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "lcu_bench_read_ceiling": (C.c_int, [C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_float)]),
 }
 EXPORTS = sorted(_SIG)

@@ -464,6 +464,39 @@ int lcu_bench_matmul_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev
   cudaEventDestroy(e1);
   return rc;
 }
+int lcu_bench_quantize(uint64_t h, uint64_t w, int bs, int reps, float* ms_per_launch_out) {
+  NEED_DEVICE();
+  LCU_REQUIRE(reps >= 1 && ms_per_launch_out && bs > 0 && w % bs == 0 && h > 0, "bench_quantize: bad arguments");
+  const size_t n = h * w;
+  __half *d_in = nullptr, *d_sc = nullptr;
+  uint8_t* d_q = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  cudaError_t e = cudaMalloc(&d_in, n * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&d_q, n);
+  if (e == cudaSuccess) e = cudaMalloc(&d_sc, n / bs * 2);
+  if (e == cudaSuccess) e = cudaEventCreate(&e0);
+  if (e == cudaSuccess) e = cudaEventCreate(&e1);
+  int rc = LCU_OK;
+  if (e == cudaSuccess) rc = launch_synth_fill(d_in, n, 1234, fnv1a64("bench.quantize"), 0.02f, 0, 0);
+  if (e == cudaSuccess && !rc) rc = launch_quantize_absmax_uint8(d_q, d_sc, d_in, h, w, bs, 0);  // warm
+  if (e == cudaSuccess && !rc) {
+    cudaEventRecord(e0, 0);
+    for (int i = 0; i < reps && !rc; ++i) rc = launch_quantize_absmax_uint8(d_q, d_sc, d_in, h, w, bs, 0);
+    cudaEventRecord(e1, 0);
+    e = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    *ms_per_launch_out = ms / reps;
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  cudaFree(d_in);
+  cudaFree(d_q);
+  cudaFree(d_sc);
+  if (rc) return rc;
+  LCU_CUDA(e);
+  return LCU_OK;
+}
 int lcu_bench_read_ceiling(uint64_t bytes, int reps, int copies_per_stage, float* ms_per_pass_out) {
   NEED_DEVICE();
   return bench_read_ceiling(bytes, reps, copies_per_stage, ms_per_pass_out);

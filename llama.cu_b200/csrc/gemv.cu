@@ -471,6 +471,13 @@ size_t gemv_algorithmic_bytes(const gemv_params& p, int epilogue) {
   return w + io;
 }
 
+// most activation rows (1..8) of length K one pass of the multi-row kernel can hold next to a two-deep ring
+int gemv_max_rows(int K) {
+  const size_t room = 227 * 1024 - SMEM_FIXED - 2 * (size_t)STAGE_BYTES;
+  const size_t rows = room / (size_t)x_stride_bytes(K);
+  return rows > 8 ? 8 : (int)rows;
+}
+
 int launch_gemv(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl) {
   LCU_REQUIRE(p.m >= 1 && p.m <= 8, "gemv: m=%d outside 1..8", p.m);
   LCU_REQUIRE(p.K > 0 && p.K % 256 == 0, "gemv: K=%d must be a positive multiple of 256", p.K);

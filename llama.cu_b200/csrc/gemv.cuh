@@ -60,6 +60,9 @@ gemv_tuning& gemv_tuning_ref();
 int launch_gemv(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl);
 
 int gemv_sm_count();
+// rows (at most 8) of K activations that one launch with m > 1 can keep in shared memory; long rows (K = 22016: 4) take
+// several passes
+int gemv_max_rows(int K);
 
 // single-row kernel (gemv1.cu); called by launch_gemv after argument checks
 int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl, int sms);

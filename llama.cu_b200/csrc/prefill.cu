@@ -30,7 +30,9 @@ int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, floa
     if (rc) return rc;
     return launch_gemm_tc(out, lhs, K, deq, m, N, K, beta, err, stream, pt.tc_tile_n, pt.tc_pair, pt.tc_split);
   }
-  for (int t = 0; t < m; t += 8) {
+  const int pass_rows = gemv_max_rows(K);  // 8, fewer where the activation rows are long
+  LCU_REQUIRE(pass_rows >= 1, "matmul_nt: a row of K=%d does not fit in shared memory", K);
+  for (int t = 0; t < m; t += pass_rows) {
     gemv_params p{};
     p.w[0] = w.w;
     p.sc[0] = w.sc;
@@ -39,7 +41,7 @@ int matmul_rows(__half* out, const __half* lhs, const dev_matrix& w, int m, floa
     p.K = K;
     p.bs = w.bs;
     p.x = lhs + (size_t)t * K;
-    p.m = m - t < 8 ? m - t : 8;
+    p.m = m - t < pass_rows ? m - t : pass_rows;
     p.ldx = K;
     p.out = out + (size_t)t * N;
     p.ldo = N;

@@ -809,6 +809,17 @@ void orc_get_last_hidden(void* c, uint16_t* out) {
 }
 // wall seconds of the last orc_next_token call: which 0 = all layers, 1 = final norm + logits + softmax
 double orc_last_timing(void* c, int which) { return which == 0 ? ((context_t*)c)->t_layers : ((context_t*)c)->t_head; }
+// number of OpenMP threads used by the calls that follow (1 = the scalar single-thread evaluation); returns the previous value
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  const int prev = omp_get_max_threads();
+  if (n >= 1) omp_set_num_threads(n);
+  return prev;
+#else
+  (void)n;
+  return 1;
+#endif
+}
 int orc_num_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();

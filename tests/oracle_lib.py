@@ -57,6 +57,7 @@ def lib():
         "orc_get_logits": (None, [C.c_void_p, u16p]),
         "orc_get_last_hidden": (None, [C.c_void_p, u16p]),
         "orc_num_threads": (C.c_int, []),
+        "orc_set_num_threads": (C.c_int, [C.c_int]),
         "orc_last_timing": (C.c_double, [C.c_void_p, C.c_int]),
     }
     for name, (res, args) in sig.items():

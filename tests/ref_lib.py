@@ -11,7 +11,9 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PATH = os.path.join(ROOT, "oracle", "_ref", "libllama_cu_ref.so")
+PATH_CUBLAS = os.path.join(ROOT, "oracle", "_ref", "libllama_cu_ref_cublas.so")  # the ENABLE_CUBLAS build: adds matmul_type 0
 _LIB = None
+_LIBS = {}
 vp = C.c_void_p
 u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
 u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
@@ -23,41 +25,55 @@ def available():
     return os.path.exists(PATH)
 
 
-def lib():
+def cublas_available():
+    return os.path.exists(PATH_CUBLAS)
+
+
+def lib(cublas=False):
+    """The reference library; cublas=True loads the variant built with ENABLE_CUBLAS (a separate copy with its own state)."""
     global _LIB
+    if cublas:
+        if "cublas" not in _LIBS:
+            _LIBS["cublas"] = _bind(C.CDLL(PATH_CUBLAS))
+        return _LIBS["cublas"]
     if _LIB is None:
-        L = C.CDLL(PATH)
-        sig = {
-            "ref_initialize": (None, []),
-            "ref_matmul_nt_f16": (C.c_int, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, vp]),
-            "ref_matmul_nt_fp16u8": (C.c_int, [u16p, u16p, u8p, u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, vp]),
-            "ref_matmul_rotating_ms": (C.c_float, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
-            "ref_rms_norm": (C.c_int, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_float]),
-            "ref_rotary": (C.c_int, [u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]),
-            "ref_silu": (C.c_int, [u16p, u16p, u16p, C.c_size_t]),
-            "ref_attention": (C.c_int, [u16p, u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
-            "ref_model_alloc": (vp, [C.c_uint32] * 5 + [C.c_float, C.c_int, vp]),
-            "ref_model_tensor": (C.c_int, [vp, C.c_char_p, C.c_int, C.POINTER(vp), C.POINTER(C.c_uint64)]),
-            "ref_model_load": (vp, [C.c_char_p, vp]),
-            "ref_model_free": (None, [vp]),
-            "ref_context_create": (vp, [vp, C.c_int, C.c_float, C.c_int]),
-            "ref_context_free": (None, [vp]),
-            "ref_context_clear": (None, [vp]),
-            "ref_context_memory_usage": (C.c_uint64, [vp]),
-            "ref_next_token": (C.c_int, [vp, i16p, C.c_int, C.c_int]),
-            "ref_get_probs": (C.c_int, [vp, u16p]),
-            "ref_decode_timed": (C.c_double, [vp, C.c_int16, C.c_int, i16p, C.c_int]),
-            "ref_quantize_absmax_uint8": (C.c_int, [u8p, u16p, u16p, C.c_uint64, C.c_uint64, C.c_int, vp]),
-            "ref_quantize_device": (C.c_int, [vp, vp, vp, C.c_uint64, C.c_uint64, C.c_int]),
-            "ref_dequantize_absmax_uint8": (C.c_int, [u16p, u16p, u8p, C.c_uint64, C.c_uint64, C.c_int]),
-            "ref_transform_quantize": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int]),
-        }
-        for name, (res, args) in sig.items():
-            fn = getattr(L, name)
-            fn.restype = res
-            fn.argtypes = args
-        _LIB = L
+        _LIB = _bind(C.CDLL(PATH))
     return _LIB
+
+
+def _bind(L):
+    sig = {
+        "ref_initialize": (None, []),
+        "ref_matmul_nt_f16": (C.c_int, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, vp]),
+        "ref_matmul_nt_fp16u8": (C.c_int, [u16p, u16p, u8p, u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, vp]),
+        "ref_matmul_rotating_ms": (C.c_float, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+        "ref_rms_norm": (C.c_int, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_float]),
+        "ref_rotary": (C.c_int, [u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]),
+        "ref_silu": (C.c_int, [u16p, u16p, u16p, C.c_size_t]),
+        "ref_attention": (C.c_int, [u16p, u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+        "ref_model_alloc": (vp, [C.c_uint32] * 5 + [C.c_float, C.c_int, vp]),
+        "ref_model_tensor": (C.c_int, [vp, C.c_char_p, C.c_int, C.POINTER(vp), C.POINTER(C.c_uint64)]),
+        "ref_model_load": (vp, [C.c_char_p, vp]),
+        "ref_model_fill_synthetic": (C.c_int, [vp, C.c_uint64, C.c_float]),
+        "ref_tokenize": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, i16p, C.c_int]),
+        "ref_model_free": (None, [vp]),
+        "ref_context_create": (vp, [vp, C.c_int, C.c_float, C.c_int]),
+        "ref_context_free": (None, [vp]),
+        "ref_context_clear": (None, [vp]),
+        "ref_context_memory_usage": (C.c_uint64, [vp]),
+        "ref_next_token": (C.c_int, [vp, i16p, C.c_int, C.c_int]),
+        "ref_get_probs": (C.c_int, [vp, u16p]),
+        "ref_decode_timed": (C.c_double, [vp, C.c_int16, C.c_int, i16p, C.c_int]),
+        "ref_quantize_absmax_uint8": (C.c_int, [u8p, u16p, u16p, C.c_uint64, C.c_uint64, C.c_int, vp]),
+        "ref_quantize_device": (C.c_int, [vp, vp, vp, C.c_uint64, C.c_uint64, C.c_int]),
+        "ref_dequantize_absmax_uint8": (C.c_int, [u16p, u16p, u8p, C.c_uint64, C.c_uint64, C.c_int]),
+        "ref_transform_quantize": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    return L
 
 
 def matmul_f16(lhs, rhs, beta=0.0, out=None, mtype=4):

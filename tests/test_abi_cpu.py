@@ -96,13 +96,28 @@ def test_context_scratch_figure_counts_every_buffer(name, dim, heads, layers, bs
 REF = os.environ.get("REF", os.environ.get("LLAMA_CU_REFERENCE", "/root/reference"))
 
 
+def linked_source(tmp_path, name):
+    """A quoted #include is searched in the including file's directory first; reaching the reference's source through a
+    symbolic link keeps its "llama_cu.h" from resolving to the reference's own header (nothing is copied)."""
+    link = tmp_path / name
+    os.symlink(os.path.join(REF, name), link)
+    return str(link)
+
+
+def header_used(compiler, src, *flags):
+    deps = subprocess.run([compiler, "-std=c++17", "-I", os.path.join(ROOT, "include"), *flags, "-M", src], capture_output=True, text=True).stdout
+    return [os.path.realpath(p) for p in re.findall(r"(\S*llama_cu\.h)", deps)]
+
+
 @pytest.mark.skipif(not os.path.exists(os.path.join(REF, "transform.cu")), reason="reference sources not present")
 def test_reference_transform_tool_builds_against_the_new_header_and_library(tmp_path):
     """The reference's transform.cu uses the LLAMA_CU_IMPLEMENTATION half of its header (tensor4d, gpu_buffer, generic_tensor,
     CHECK_CUDA, RETURN_UNLESS): unmodified, it must compile against include/llama_cu.h and link with the new library."""
+    src = linked_source(tmp_path, "transform.cu")
+    assert header_used("nvcc", src) == [os.path.join(ROOT, "include", "llama_cu.h")]
     exe = tmp_path / "transform"
     r = subprocess.run(["nvcc", "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "include"),
-                        os.path.join(REF, "transform.cu"), "-o", str(exe), "-L", os.path.join(ROOT, "llama.cu_b200"), "-lllama_cu_b200"],
+                        src, "-o", str(exe), "-L", os.path.join(ROOT, "llama.cu_b200"), "-lllama_cu_b200"],
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-2000:]
 
@@ -110,9 +125,11 @@ def test_reference_transform_tool_builds_against_the_new_header_and_library(tmp_
 @pytest.mark.skipif(not os.path.exists(os.path.join(REF, "main.cpp")), reason="reference sources not present")
 def test_reference_main_compiles_against_the_new_header(tmp_path):
     """Drop-in proof at the source level: the reference's own client builds against include/llama_cu.h."""
-    exe = tmp_path / "llama_cu_main"
+    src = linked_source(tmp_path, "main.cpp")
     cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
-    r = subprocess.run([cxx, "-std=c++17", "-I", os.path.join(ROOT, "include"), os.path.join(REF, "main.cpp"), "-o", str(exe),
+    assert header_used(cxx, src) == [os.path.join(ROOT, "include", "llama_cu.h")]
+    exe = tmp_path / "llama_cu_main"
+    r = subprocess.run([cxx, "-std=c++17", "-I", os.path.join(ROOT, "include"), src, "-o", str(exe),
                         "-L", os.path.join(ROOT, "llama.cu_b200"), "-lllama_cu_b200",
                         "-Wl,-rpath," + os.path.join(ROOT, "llama.cu_b200")], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-2000:]
