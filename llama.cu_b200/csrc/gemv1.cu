@@ -28,8 +28,9 @@ namespace lcu {
 namespace {
 
 // Consumer warps per CTA (template parameter of the kernel): 4, or 5 for u8 kernels whose activation row leaves room
-// for two CTAs per SM only - ten consumer warps per SM instead of eight, the u8 kernels being latency-bound.
-constexpr int NW_MAX = 5;
+// for two CTAs per SM only - ten consumer warps per SM instead of eight, the u8 kernels being latency-bound; 6 and 8
+// serve the one-CTA-per-SM shape, which leaves half of an SM's shared memory and registers to the kernel that follows.
+constexpr int NW_MAX = 8;
 // Stage geometry per weight type: 4 KiB of each row per stage (measured: 2 KiB stages in a ring twice as deep lose a
 // third of the u8 throughput - the per-stage cost of the producer counts).
 template <int WT>
@@ -559,12 +560,19 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   int cps = wt == 2 ? t.ctas_per_sm_int8 : t.ctas_per_sm;
   if (cps < 1) cps = 1;
   if (cps > 3) cps = 3;
-  auto fits = [&](int warps, int stages, int ctas) { return fixed + (size_t)warps * stages * stage_bytes <= (size_t)(228 * 1024) / ctas - 1024; };
+  // smem_cap_kb > 0 bounds a CTA's shared memory below its fair share of the SM (113 = half an SM: the CTAs of the next
+  // kernel of a programmatic-dependent chain then fit beside this one's and fill their rings while it still runs)
+  const size_t cap = t.smem_cap_kb > 0 ? (size_t)t.smem_cap_kb * 1024 : (size_t)228 * 1024;
+  auto fits = [&](int warps, int stages, int ctas) {
+    const size_t need = fixed + (size_t)warps * stages * stage_bytes;
+    return need <= (size_t)(228 * 1024) / ctas - 1024 && need <= cap;
+  };
   while (cps > 1 && !fits(4, 2, cps)) --cps;
   // factored u8 kernels that cannot have three CTAs of four consumer warps per SM take five consumer warps per CTA
   // when those fit (a long activation row: w2 of every model, every matrix of the larger models)
   int nw = 4;
   if (wt == 2 && cps < 3 && t.consumer_warps_int8 != 4 && fits(5, 2, cps)) nw = 5;
+  if ((t.consumer_warps == 5 || t.consumer_warps == 6 || t.consumer_warps == 8) && fits(t.consumer_warps, 2, cps)) nw = t.consumer_warps;
   const int want_sw = wt == 2 ? t.warp_stages_int8 : t.warp_stages;
   int sw = want_sw < 2 ? 2 : (want_sw > MAX_SW ? MAX_SW : want_sw);
   while (sw > 2 && !fits(nw, sw, cps)) --sw;
@@ -573,18 +581,23 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   const int pairs = p.n_mats * p.rows_per_mat / 2;
   const int grid = sms * cps > pairs ? pairs : sms * cps;
   const int pf = t.prefetch_kb_per_cta * 1024;
+#define LCU_GEMV1_NW(WTV, E)                                                               \
+  if (nw == 5) return launch_one<WTV, E, 5>(p, stream, pdl, smem, grid, sw, pf);           \
+  if (nw == 6) return launch_one<WTV, E, 6>(p, stream, pdl, smem, grid, sw, pf);           \
+  if (nw == 8) return launch_one<WTV, E, 8>(p, stream, pdl, smem, grid, sw, pf);           \
+  return launch_one<WTV, E, 4>(p, stream, pdl, smem, grid, sw, pf);
 #define LCU_GEMV1_CASE(E)                                                                  \
   case E:                                                                                  \
-    if (wt == 0) return launch_one<0, E, 4>(p, stream, pdl, smem, grid, sw, pf);           \
-    if (wt == 1) return launch_one<1, E, 4>(p, stream, pdl, smem, grid, sw, pf);           \
-    if (nw == 5) return launch_one<2, E, 5>(p, stream, pdl, smem, grid, sw, pf);           \
-    return launch_one<2, E, 4>(p, stream, pdl, smem, grid, sw, pf);
+    if (wt == 0) { LCU_GEMV1_NW(0, E) }                                                    \
+    if (wt == 1) { LCU_GEMV1_NW(1, E) }                                                    \
+    LCU_GEMV1_NW(2, E)
   switch (epilogue) {
     LCU_GEMV1_CASE(EPI_PLAIN)
     LCU_GEMV1_CASE(EPI_ROPE_KV)
     LCU_GEMV1_CASE(EPI_SILU)
   }
 #undef LCU_GEMV1_CASE
+#undef LCU_GEMV1_NW
   LCU_REQUIRE(false, "gemv: unknown epilogue %d", epilogue);
 }
 
