@@ -19,6 +19,7 @@ Printed JSON line (rank 0):
   kernels   the same measurement for every decode GEMV class, and the quantizer
   int8      value / e2e / roofline / kernels / whole_step of the u8 model, top-1 agreement with the fp16 run
   config0   the single linear layer y = W x (4096 x 4096, fp16 and u8): error against a binary64 evaluation, GB/s
+  loader    (N = 1) lcu_model_load of a saved 2.1 GB weight directory: staged pinned copies vs the reference's mapped pageable copy
   prefill   (N = 1) the prompt path: a 512-token prompt through lcu_context_next_token, and the largest prompt GEMM
             (tcgen05 kernel) timed alone with CUDA events against the measured dense bf16 tensor peak
   cpu_baseline  the CPU oracle on a bounded sample (one of the 32 layers + the output head), host threads; plus the
@@ -279,7 +280,15 @@ def dist_setup(n_gpus=None):
             torch.cuda.set_device(local)
         dist_mod.init_process_group(backend="nccl" if torch.cuda.is_available() else "gloo")
         dist = dist_mod
+        # a second group on the host: ranks that only have to wait (while rank 0 drives all GPUs) must not park a
+        # spinning NCCL kernel on a GPU that rank 0 is measuring
+        dist.host_group = dist_mod.new_group(backend="gloo")
     return world, rank, local, dist
+
+
+def host_barrier(dist):
+    if dist is not None:
+        dist.barrier(group=dist.host_group)
 
 
 def reduce_max_time(ms, dist, device=None):
@@ -425,6 +434,36 @@ def config0_ours(lcu, kernels16, kernels8):
     return out
 
 
+def loader_sample(lcu):
+    """lcu_model_load on a saved weight directory (the 7B shapes, 4 layers + embedding + output matrix: 2.1 GB of files in
+    the page cache): the staged loader (two pinned buffers, asynchronous copies overlapping parallel file reads) against
+    the reference's way (a file mapping handed to one blocking pageable copy per tensor, llama_cu.cu:699-702)."""
+    import shutil
+    base = "/dev/shm" if os.path.isdir("/dev/shm") and shutil.disk_usage("/dev/shm").free > (6 << 30) else tempfile.gettempdir()
+    d = tempfile.mkdtemp(prefix="lcu_loader_", dir=base)
+    out = {"where": base}
+    try:
+        model = lcu.Model.synthetic(seed=SEED, scale=SCALE, **WORKLOADS["7b-l4-fp16"])
+        model.save(d)
+        nbytes = model.weight_bytes()
+        model.close()
+        for name, staged in (("mapped_pageable", 0), ("staged_pinned", 1)):
+            lcu.check(lcu.lib.lcu_set_tuning(b"loader_staged", staged))
+            best = None
+            for _ in range(2):
+                t0 = time.perf_counter()
+                m = lcu.Model.load(d)
+                dt = time.perf_counter() - t0
+                m.close()
+                best = dt if best is None or dt < best else best
+            out[name] = {"s": round(best, 3), "gbs": round(nbytes / best / 1e9, 2)}
+        out["bytes"] = nbytes
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"loader_staged", 1))
+        shutil.rmtree(d, ignore_errors=True)
+    return out
+
+
 def pipeline_leg(lcu, n_gpus, K, W, tp=False):
     """Rank 0 alone, after the replicas are gone: the reference's multi-GPU scheme - contiguous layer ranges per GPU,
     the residual row handed from stage to stage over NVLink - on the 65B-shaped u8 model (512-token prompt), against the
@@ -517,14 +556,21 @@ def run_ours(args):
         hbm_peak = measured_peaks()[0]
         line["kernels"]["quantize_absmax_uint8"] = {"us": round(qms.value * 1e3, 2), "bytes": qbytes, "gbs": round(qbytes / (qms.value * 1e-3) / 1e9, 1),
                                                     "frac": round(qbytes / (qms.value * 1e-3) / 1e9 / hbm_peak, 4), "shape": [qh, qw], "block": 128}
+    if rank == 0 and world == 1 and args.pipeline <= 1 and args.workload.startswith("7b") and not args.no_loader:
+        try:
+            line["loader"] = loader_sample(lcu)
+        except Exception as e:
+            line["loader"] = {"error": str(e)[:200]}
     if world > 1:
         # the replicas are done: everything is freed, rank 0 alone drives the multi-GPU scheme of the path over the N GPUs
         barrier_sync(dist, lcu)
+        host_barrier(dist)
         if rank == 0 and not args.no_pipeline_leg:
             try:
                 line["pipeline"] = pipeline_leg(lcu, world, K, W)
             except Exception as e:  # the replica numbers stand on their own
                 line["pipeline"] = {"error": str(e)[:300]}
+        host_barrier(dist)  # the other ranks wait here on the host, their GPUs idle
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample(cfg, ffn)
@@ -532,7 +578,7 @@ def run_ours(args):
                 line["cpu_baseline"]["config0_host_scalar"] = config0_host_scalar()
         print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.barrier()
+        host_barrier(dist)
         dist.destroy_process_group()
 
 
@@ -654,6 +700,7 @@ def main():
     ap.add_argument("--workload", default="7b-fp16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-int8", action="store_true", help="skip the int8 half of the metric (and the reference arm's extra variants)")
+    ap.add_argument("--no-loader", action="store_true", help="skip the weight-directory loader sample")
     ap.add_argument("--no-pipeline-leg", action="store_true", help="N > 1: skip rank 0's layer-pipeline run over the N GPUs")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="seeded prompt length (128 for the headline configuration)")
     ap.add_argument("--prefill-len", type=int, default=PREFILL_LEN, help="prompt length of the prefill sample (512; from 768 rows the tcgen05 attention path runs)")

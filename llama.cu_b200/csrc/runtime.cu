@@ -19,8 +19,10 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstring>
+#include <thread>
 
 #include "attention.cuh"
 #include "gemv.cuh"
@@ -213,8 +215,9 @@ int model::find_tensor(const std::string& name, int which, void** ptr, size_t* b
 }
 
 namespace {
-// copies a whole file of exactly `bytes` bytes into device memory
-int load_file(const std::string& path, void* dst, size_t bytes) {
+// copies a whole file of exactly `bytes` bytes into device memory: the reference's way (llama_cu.cu:699-702, 929-971),
+// a file mapping handed to one blocking copy from pageable memory.  Kept as the baseline of the loader measurement.
+int load_file_mapped(const std::string& path, void* dst, size_t bytes) {
   int fd = open(path.c_str(), O_RDONLY);
   if (fd < 0) {
     set_last_error("cannot open %s", path.c_str());
@@ -243,23 +246,152 @@ int load_file(const std::string& path, void* dst, size_t bytes) {
   }
   return LCU_OK;
 }
+
+// Staged loader: files are read in pieces into two pinned buffers; while one piece travels to the device
+// (cudaMemcpyAsync on the loader's stream, one copy per piece) the next one is read from the file.  One loader per
+// GPU of the partition; finish() waits for the last copies.
+struct staged_loader {
+  static constexpr size_t PIECE = (size_t)64 << 20;
+  static constexpr int READERS = 8;
+  int device = 0;
+  void* pin[2] = {nullptr, nullptr};
+  cudaEvent_t done[2] = {nullptr, nullptr};
+  bool in_flight[2] = {false, false};
+  cudaStream_t stream = nullptr;
+  int cur = 0;
+
+  int init(int dev) {
+    device = dev;
+    device_guard g(dev);
+    LCU_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      LCU_CUDA(cudaMallocHost(&pin[i], PIECE));
+      LCU_CUDA(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming));
+    }
+    return LCU_OK;
+  }
+  ~staged_loader() {
+    device_guard g(device);
+    if (stream) cudaStreamSynchronize(stream);
+    for (int i = 0; i < 2; ++i) {
+      if (pin[i]) cudaFreeHost(pin[i]);
+      if (done[i]) cudaEventDestroy(done[i]);
+    }
+    if (stream) cudaStreamDestroy(stream);
+  }
+  int copy_file(const std::string& path, void* dst, size_t bytes) {
+    int fd = open(path.c_str(), O_RDONLY);
+    if (fd < 0) {
+      set_last_error("cannot open %s", path.c_str());
+      return LCU_ERR_IO;
+    }
+    struct stat st;
+    if (fstat(fd, &st) != 0 || (size_t)st.st_size != bytes) {
+      close(fd);
+      set_last_error("%s: expected %zu bytes, file has %lld", path.c_str(), bytes, (long long)st.st_size);
+      return LCU_ERR_IO;
+    }
+#ifdef POSIX_FADV_SEQUENTIAL
+    posix_fadvise(fd, 0, 0, POSIX_FADV_SEQUENTIAL);
+#endif
+    device_guard g(device);
+    for (size_t off = 0; off < bytes;) {
+      const size_t n = std::min(PIECE, bytes - off);
+      if (in_flight[cur]) {  // the buffer's previous piece must have left it
+        if (cudaEventSynchronize(done[cur]) != cudaSuccess) {
+          close(fd);
+          set_last_error("copy of %s to the device failed", path.c_str());
+          return LCU_ERR_CUDA;
+        }
+        in_flight[cur] = false;
+      }
+      // the piece is read by several threads at once (a single reader copies out of the page cache at a fraction of
+      // what the host-to-device link takes)
+      const int n_readers = n >= ((size_t)4 << 20) ? READERS : 1;
+      const size_t share = (n / n_readers + 4095) & ~(size_t)4095;
+      std::atomic<int> failed{0};
+      auto read_range = [&](size_t lo, size_t hi) {
+        while (lo < hi) {
+          const ssize_t r = pread(fd, (char*)pin[cur] + lo, hi - lo, (off_t)(off + lo));
+          if (r <= 0) {
+            failed = 1;
+            return;
+          }
+          lo += (size_t)r;
+        }
+      };
+      std::vector<std::thread> readers;
+      for (int t = 1; t < n_readers; ++t) readers.emplace_back(read_range, std::min(n, t * share), std::min(n, (t + 1) * share));
+      read_range(0, std::min(n, share));
+      for (auto& th : readers) th.join();
+      if (failed) {
+        close(fd);
+        set_last_error("short read from %s", path.c_str());
+        return LCU_ERR_IO;
+      }
+      cudaError_t e = cudaMemcpyAsync((char*)dst + off, pin[cur], n, cudaMemcpyHostToDevice, stream);
+      if (e == cudaSuccess) e = cudaEventRecord(done[cur], stream);
+      if (e != cudaSuccess) {
+        close(fd);
+        set_last_error("copy of %s to the device failed: %s", path.c_str(), cudaGetErrorString(e));
+        return LCU_ERR_CUDA;
+      }
+      in_flight[cur] = true;
+      cur ^= 1;
+      off += n;
+    }
+    close(fd);
+    return LCU_OK;
+  }
+  int finish() {
+    device_guard g(device);
+    LCU_CUDA(cudaStreamSynchronize(stream));
+    in_flight[0] = in_flight[1] = false;
+    return LCU_OK;
+  }
+};
+
+int g_loader_staged = 1;
 }  // namespace
 
+void set_loader_staged(int on) { g_loader_staged = on; }
+
 int model::load_dir(const std::string& dir) {
+  std::vector<std::unique_ptr<staged_loader>> loaders;  // one per GPU that holds tensors
+  auto loader_for = [&](int dev, staged_loader*& out) {
+    for (auto& l : loaders)
+      if (l->device == dev) {
+        out = l.get();
+        return (int)LCU_OK;
+      }
+    loaders.push_back(std::make_unique<staged_loader>());
+    out = loaders.back().get();
+    return out->init(dev);
+  };
   for (auto& s : enumerate(*this)) {
     device_guard g(s.device);
+    staged_loader* ld = nullptr;
+    if (g_loader_staged) {
+      int rc = loader_for(s.device, ld);
+      if (rc) return rc;
+    }
+    auto load = [&](const std::string& path, void* dst, size_t bytes) { return ld ? ld->copy_file(path, dst, bytes) : load_file_mapped(path, dst, bytes); };
     const std::string base = dir + "/" + s.name;
     int rc;
     if (s.mat) {
       const std::string dims = std::to_string(s.mat->rows) + "_" + std::to_string(s.mat->cols);
-      rc = load_file(base + ".weight__" + dims, s.mat->w, s.mat->weight_bytes());
+      rc = load(base + ".weight__" + dims, s.mat->w, s.mat->weight_bytes());
       if (rc == LCU_OK && s.mat->bs)
-        rc = load_file(base + ".scale__" + std::to_string(s.mat->rows) + "_" + std::to_string(s.mat->cols / s.mat->bs), s.mat->sc,
-                       s.mat->scale_bytes());
+        rc = load(base + ".scale__" + std::to_string(s.mat->rows) + "_" + std::to_string(s.mat->cols / s.mat->bs), s.mat->sc,
+                  s.mat->scale_bytes());
     } else {
-      rc = load_file(base + ".weight__" + std::to_string(s.len), *s.vec, s.len * 2);
+      rc = load(base + ".weight__" + std::to_string(s.len), *s.vec, s.len * 2);
     }
     if (rc != LCU_OK) return rc;
+  }
+  for (auto& l : loaders) {
+    int rc = l->finish();
+    if (rc) return rc;
   }
   return LCU_OK;
 }

@@ -97,6 +97,10 @@ struct model {
   int save_dir(const std::string& dir);
 };
 
+// weight-directory loader: 1 (default) = pieces through two pinned buffers with asynchronous copies overlapping the file
+// reads; 0 = the reference's way, a file mapping handed to one blocking copy from pageable memory (llama_cu.cu:699-702)
+void set_loader_staged(int on);
+
 // `transform quantize` (reference transform.cu:220-263): fp16 weight directory -> uint8 weight
 // directory, one tensor at a time on the current device
 int quantize_dir(const std::string& in_dir, const std::string& out_dir, int bs);

@@ -187,6 +187,16 @@ def test_weight_directory_round_trip(lcu, tmp_path, bs):
     again = lcu.Model.load(d)
     for name in ("tok_embeddings", "layers.2.feed_forward.w3", "norm"):
         assert (again.tensor_host(name, 0, np.uint8) == model.tensor_host(name, 0, np.uint8)).all()
+    # the reference's way of loading (file mapping + one pageable copy per tensor) is kept as the loader's baseline
+    lcu.check(lcu.lib.lcu_set_tuning(b"loader_staged", 0))
+    try:
+        mapped = lcu.Model.load(d)
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"loader_staged", 1))
+    for name in ("tok_embeddings", "output", "layers.0.attention.wq", "layers.2.feed_forward.w3", "norm"):
+        for which in ((0, 1) if bs and not name.endswith("norm") else (0,)):
+            assert (mapped.tensor_host(name, which, np.uint8) == again.tensor_host(name, which, np.uint8)).all()
+    mapped.close()
     prompt = O.synth_tokens(10, 11, lo=3, hi=1000)
     c1, c2 = lcu.Context(model, 32, 0.8), lcu.Context(again, 32, 0.8)
     assert run_tokens(c1, prompt, 6) == run_tokens(c2, prompt, 6)
