@@ -482,6 +482,67 @@ def pipeline_leg(lcu, n_gpus, K, W, tp=False):
             "note": "one stage is active at a time at batch 1: the layer pipeline buys capacity, not speed (the reference's scheme)"}
 
 
+def tensor_parallel_leg(lcu, n_gpus, K, W):
+    """Rank 0 alone: the row-sharded tensor-parallel decoder (lcu_tp_*) on the 65B-shaped u8 model over the N GPUs, against
+    the same model on one GPU fed the same tokens one at a time (tokens must be identical: every output element is
+    computed by the same code in the same order)."""
+    import oracle_lib as O
+    workload, prompt_len, steps = "65b-int8", 128, min(K, 32)
+    cfg = WORKLOADS[workload]
+    ffn = lcu.lib.lcu_ffn_dim(cfg["dim"], 256)
+    ctx_len = max(512, prompt_len + W + steps + 2)
+    prompt = O.synth_tokens(prompt_len, SEED, lo=3, hi=32000)
+    # one GPU, token by token (the decode kernels)
+    model = lcu.Model.synthetic(seed=SEED, scale=SCALE, **cfg)
+    ctx = lcu.Context(model, context_len=ctx_len, temperature=TEMPERATURE)
+    t = None
+    for tok in prompt:
+        t = ctx.next_token([int(tok)])
+    warm, _ = ctx.decode_chained(t, W)
+    ref_tokens, ref_ms = ctx.decode_chained(int(warm[-1]), steps)
+    ref_first = t
+    ctx.close()
+    model.close()
+    t0 = time.perf_counter()
+    tp = lcu.TensorParallel(n_gpus, context_len=ctx_len, temperature=TEMPERATURE, seed=SEED, scale=SCALE, **cfg)
+    gen_s = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    first = tp.next_token(prompt)
+    prompt_s = time.perf_counter() - t0
+    warm, _ = tp.decode_chained(first, W)
+    tokens, ms = tp.decode_chained(int(warm[-1]), steps)
+    # end to end: host token in, host token out
+    tp.clear_tokens()
+    tok = tp.next_token(prompt)
+    for _ in range(W):
+        tok = tp.next_token([tok])
+    t0 = time.perf_counter()
+    e2e_tokens = []
+    for _ in range(steps):
+        tok = tp.next_token([tok])
+        e2e_tokens.append(tok)
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    per_gpu = tp.weight_bytes_per_gpu()
+    kps = tp.kernels_per_step()
+    tp.close()
+    hbm_peak = measured_peaks()[0]
+    step_bytes = decode_bytes_per_token(cfg, ffn, prompt_len + W + steps // 2)
+    per_gpu_step = step_bytes / n_gpus
+    ms_step = ms / steps
+    ideal_ms = ref_ms / steps / n_gpus
+    return {"workload": f"llama-{workload} greedy decode, batch 1, {prompt_len}-token seeded prompt (fed as single-token steps), {steps} steps",
+            "gpus": n_gpus, "value": round(steps / (ms / 1e3), 2), "ms_per_step": round(ms_step, 4),
+            "e2e": {"value": round(steps / (e2e_ms / 1e3), 2), "unit": "tok/s", "h2d_bytes_per_step": 6 * n_gpus, "d2h_bytes_per_step": 8 + 4 * n_gpus,
+                    "ms_per_step": round(e2e_ms / steps, 4), "tokens_equal_chained_run": [int(x) for x in e2e_tokens] == [int(x) for x in tokens]},
+            "single_gpu_value": round(steps / (ref_ms / 1e3), 2), "speedup_over_one_gpu": round((ref_ms / steps) / ms_step, 3),
+            "tokens_equal_single_gpu": int(first) == int(ref_first) and [int(x) for x in tokens] == [int(x) for x in ref_tokens],
+            "weight_bytes_per_gpu": per_gpu, "per_gpu_hbm_gbs": round(per_gpu_step / (ms_step * 1e-3) / 1e9, 1),
+            "per_gpu_frac_of_measured_peak": round(per_gpu_step / (ms_step * 1e-3) / 1e9 / hbm_peak, 4),
+            "exchange_and_launch_overhead_us_per_layer": round((ms_step - ideal_ms) * 1e3 / cfg["n_layers"], 2),
+            "kernels_per_step_all_gpus": kps, "prompt_s": round(prompt_s, 2), "weights_generated_s": round(gen_s, 1),
+            "exchange": "peer stores from the GEMV epilogues over NVLink + flag words with bounded waits; 4 exchanges per layer (16-44 KB rows)"}
+
+
 def run_ours(args):
     world, rank, local, dist = dist_setup()
     lcu = load_package()
@@ -570,6 +631,11 @@ def run_ours(args):
                 line["pipeline"] = pipeline_leg(lcu, world, K, W)
             except Exception as e:  # the replica numbers stand on their own
                 line["pipeline"] = {"error": str(e)[:300]}
+        if rank == 0 and not args.no_pipeline_leg:
+            try:
+                line["tensor_parallel"] = tensor_parallel_leg(lcu, world, K, W)
+            except Exception as e:
+                line["tensor_parallel"] = {"error": str(e)[:300]}
         host_barrier(dist)  # the other ranks wait here on the host, their GPUs idle
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
@@ -705,12 +771,16 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="seeded prompt length (128 for the headline configuration)")
     ap.add_argument("--prefill-len", type=int, default=PREFILL_LEN, help="prompt length of the prefill sample (512; from 768 rows the tcgen05 attention path runs)")
     ap.add_argument("--pipeline", type=int, default=1, help="single process: split the layers evenly over this many GPUs")
+    ap.add_argument("--tp", type=int, default=0, help="single process: only the tensor-parallel leg (65B-shaped u8 model) over this many GPUs")
     ap.add_argument("--profile", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                     help="cudaProfilerStart/Stop around the device-chained timed region (decode) or around the prompt pass and GEMM (prefill)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.tp > 1:
+        lcu = load_package()
+        print(json.dumps({"tensor_parallel": tensor_parallel_leg(lcu, args.tp, args.steps, args.warmup)}), flush=True)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -164,6 +164,30 @@ int lcu_context_read_probs(void* ctx, uint16_t* probs_host);
 int lcu_context_read_hidden(void* ctx, uint16_t* hidden_host);
 int lcu_context_kernels_per_step(void* ctx);
 
+/* ---- tensor-parallel decode (one process, 2 / 4 / 8 GPUs of one box) ---------------------------- */
+/* No counterpart in the reference: its only multi-GPU scheme is the layer pipeline (llama_partition, llama_cu.cu:810-880,
+ * 1099-1114), which keeps one GPU busy at a time at batch 1.  Here every GPU holds a run of rows of every layer matrix and
+ * of the output matrix (whole heads of wq / wk / wv) and streams only those from its HBM; the slices of each activation row
+ * travel as peer stores over NVLink from the GEMV epilogues, ordered by flag words with bounded waits (status 4 if a wait
+ * expires).  Every output element is computed exactly as on one GPU, so tokens and probabilities equal those of an
+ * lcu_context fed the same tokens one at a time.  n_heads, the ffn dim and n_vocab must split evenly
+ * (lcu_tp_check_split, host only).  gpus: n_gpus device indices, NULL = 0 .. n_gpus-1.  A prompt runs as single-token steps. */
+int lcu_tp_check_split(const void* params40, int n_gpus);
+int lcu_tp_create(const void* params40, const int* gpus, int n_gpus, int context_len, float temperature, void** tp_out);
+/* the values lcu_model_fill_synthetic gives the whole model, generated shard by shard */
+int lcu_tp_fill_synthetic(void* tp, uint64_t seed, float scale);
+/* every GPU reads its rows of every tensor file of a weight directory (llama_cu.cu:929-984 layout) */
+int lcu_tp_load(void* tp, const char* dir);
+/* llama_context::next_token / the chained loop / probabilities / clear_tokens / tokens_left, as for lcu_context_* */
+int lcu_tp_next_token(void* tp, const int16_t* tokens_host, int n_tokens, int* token_out);
+int lcu_tp_decode_chained(void* tp, int16_t first_token, int n_steps, int16_t* tokens_host_out, float* ms_out);
+int lcu_tp_read_probs(void* tp, uint16_t* probs_host);
+void lcu_tp_clear_tokens(void* tp);
+int lcu_tp_tokens_left(void* tp);
+int lcu_tp_kernels_per_step(void* tp);
+uint64_t lcu_tp_weight_bytes_per_gpu(void* tp);
+void lcu_tp_free(void* tp);
+
 /* ---- tokenizer (host only) ------------------------------------------------------------------- */
 /* llama_vocabulary(vocab file) + llama_vocabulary::tokenize(text, bos), llama_cu.cu:1319-1437: greedy highest-score pair
  * merging over UTF-8 characters with byte fallback (id = byte + 3), a leading space added when the text has none, id 1

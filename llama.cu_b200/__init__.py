@@ -77,6 +77,18 @@ _SIG = {
     "lcu_context_read_probs": (C.c_int, [vp, vp]),
     "lcu_context_read_hidden": (C.c_int, [vp, vp]),
     "lcu_context_kernels_per_step": (C.c_int, [vp]),
+    "lcu_tp_check_split": (C.c_int, [vp, C.c_int]),
+    "lcu_tp_create": (C.c_int, [vp, vp, C.c_int, C.c_int, C.c_float, C.POINTER(vp)]),
+    "lcu_tp_fill_synthetic": (C.c_int, [vp, C.c_uint64, C.c_float]),
+    "lcu_tp_load": (C.c_int, [vp, C.c_char_p]),
+    "lcu_tp_next_token": (C.c_int, [vp, vp, C.c_int, C.POINTER(C.c_int)]),
+    "lcu_tp_decode_chained": (C.c_int, [vp, C.c_int16, C.c_int, vp, C.POINTER(C.c_float)]),
+    "lcu_tp_read_probs": (C.c_int, [vp, vp]),
+    "lcu_tp_clear_tokens": (None, [vp]),
+    "lcu_tp_tokens_left": (C.c_int, [vp]),
+    "lcu_tp_kernels_per_step": (C.c_int, [vp]),
+    "lcu_tp_weight_bytes_per_gpu": (C.c_uint64, [vp]),
+    "lcu_tp_free": (None, [vp]),
     "lcu_bench_decode_kernel": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_uint64)]),
     "lcu_profiler_start": (C.c_int, []),
     "lcu_profiler_stop": (C.c_int, []),
@@ -350,6 +362,56 @@ class Context:
     def close(self):
         if self.handle:
             lib.lcu_context_free(self.handle)
+            self.handle = None
+
+
+class TensorParallel:
+    """Row-sharded model + context over several GPUs of one box (lcu_tp_*): the same calls as Context."""
+
+    def __init__(self, n_gpus, dim, n_heads, n_layers, n_vocab, multiple_of=256, norm_eps=1e-6, block_size=0, context_len=2048,
+                 temperature=0.9, gpus=None, seed=None, scale=0.02, path=None):
+        self.n_vocab = n_vocab
+        self.handle = vp()
+        g = None if gpus is None else _ptr(np.ascontiguousarray(gpus, np.int32))
+        check(lib.lcu_tp_create(pack_params(dim, multiple_of, n_heads, n_layers, n_vocab, norm_eps, block_size), g, n_gpus, context_len,
+                                temperature, C.byref(self.handle)))
+        if path is not None:
+            check(lib.lcu_tp_load(self.handle, path.encode()))
+        elif seed is not None:
+            check(lib.lcu_tp_fill_synthetic(self.handle, seed, scale))
+
+    def next_token(self, tokens):
+        t = np.ascontiguousarray(np.asarray(tokens, np.int16))
+        out = C.c_int(0)
+        check(lib.lcu_tp_next_token(self.handle, _ptr(t), len(t), C.byref(out)))
+        return out.value
+
+    def decode_chained(self, first_token, n_steps):
+        toks = np.empty(n_steps, np.int16)
+        ms = C.c_float(0)
+        check(lib.lcu_tp_decode_chained(self.handle, int(first_token), n_steps, _ptr(toks), C.byref(ms)))
+        return toks, ms.value
+
+    def probs(self):
+        out = np.empty(self.n_vocab, np.uint16)
+        check(lib.lcu_tp_read_probs(self.handle, _ptr(out)))
+        return out
+
+    def clear_tokens(self):
+        lib.lcu_tp_clear_tokens(self.handle)
+
+    def tokens_left(self):
+        return lib.lcu_tp_tokens_left(self.handle)
+
+    def kernels_per_step(self):
+        return lib.lcu_tp_kernels_per_step(self.handle)
+
+    def weight_bytes_per_gpu(self):
+        return lib.lcu_tp_weight_bytes_per_gpu(self.handle)
+
+    def close(self):
+        if self.handle:
+            lib.lcu_tp_free(self.handle)
             self.handle = None
 
 

@@ -14,6 +14,7 @@
 #include "ops.cuh"
 #include "prefill.cuh"
 #include "runtime.cuh"
+#include "tp.cuh"
 
 using namespace lcu;
 
@@ -416,6 +417,43 @@ int lcu_context_decode_chained(void* ctx, int16_t first_token, int n_steps, int1
 int lcu_context_read_probs(void* ctx, uint16_t* probs_host) { return ((context*)ctx)->read_probs((__half*)probs_host); }
 int lcu_context_read_hidden(void* ctx, uint16_t* hidden_host) { return ((context*)ctx)->read_hidden((__half*)hidden_host); }
 int lcu_context_kernels_per_step(void* ctx) { return ((context*)ctx)->kernels_per_step(); }
+
+// ---- tensor-parallel decode
+int lcu_tp_check_split(const void* params40, int n_gpus) {
+  model_params p;
+  memcpy(&p, params40, sizeof(p));
+  return tp_check_split(p, n_gpus);
+}
+int lcu_tp_create(const void* params40, const int* gpus, int n_gpus, int context_len, float temperature, void** tp_out) {
+  NEED_DEVICE();
+  LCU_REQUIRE(params40 && tp_out && n_gpus >= 1 && n_gpus <= 8, "tp_create: bad arguments");
+  model_params p;
+  memcpy(&p, params40, sizeof(p));
+  int ids[8];
+  for (int i = 0; i < n_gpus; ++i) ids[i] = gpus ? gpus[i] : i;
+  context_options opt = g_default_opts;
+  opt.context_len = context_len;
+  opt.temperature = temperature;
+  std::unique_ptr<tp_decoder> d;
+  int rc = tp_decoder::create(d, p, ids, n_gpus, opt);
+  if (rc) return rc;
+  *tp_out = d.release();
+  return LCU_OK;
+}
+int lcu_tp_fill_synthetic(void* tp, uint64_t seed, float scale) { return ((tp_decoder*)tp)->fill_synthetic(seed, scale); }
+int lcu_tp_load(void* tp, const char* dir) { return ((tp_decoder*)tp)->load_dir(dir); }
+int lcu_tp_next_token(void* tp, const int16_t* tokens_host, int n_tokens, int* token_out) {
+  return ((tp_decoder*)tp)->next_token(tokens_host, n_tokens, token_out);
+}
+int lcu_tp_decode_chained(void* tp, int16_t first_token, int n_steps, int16_t* tokens_host_out, float* ms_out) {
+  return ((tp_decoder*)tp)->decode_chained(first_token, n_steps, tokens_host_out, ms_out);
+}
+int lcu_tp_read_probs(void* tp, uint16_t* probs_host) { return ((tp_decoder*)tp)->read_probs((__half*)probs_host); }
+void lcu_tp_clear_tokens(void* tp) { ((tp_decoder*)tp)->clear_tokens(); }
+int lcu_tp_tokens_left(void* tp) { return ((tp_decoder*)tp)->tokens_left(); }
+int lcu_tp_kernels_per_step(void* tp) { return ((tp_decoder*)tp)->kernels_per_step(); }
+uint64_t lcu_tp_weight_bytes_per_gpu(void* tp) { return ((tp_decoder*)tp)->weight_bytes_per_gpu(); }
+void lcu_tp_free(void* tp) { delete (tp_decoder*)tp; }
 
 // ---- measurement
 int lcu_bench_decode_kernel(void* ctx, int which, int reps, float* ms_per_launch_out, uint64_t* bytes_per_launch_out) {

@@ -39,7 +39,21 @@ struct gemv_params {
   int ctx_len;
   int head_dim;
   int* err;  // device error word
+  // ---- tensor-parallel decode (m == 1; all zero on a single GPU).  Every GPU streams its own rows of the matrix and
+  // owns the matching slice of the output vector; `out` and the peer pointers are pre-offset to that slice.
+  __half* peer_out[7];     // EPI_PLAIN / EPI_SILU: every result is also stored into these buffers of other GPUs (peer stores)
+  int n_peer_out;
+  int* peer_flag[7];       // this GPU's flag word on each GPU that waits for the slice; written once all stores are out
+  int n_peer_flag;
+  int* done_count;         // local counter that finds the last consumer warp of the launch (zero between launches)
+  const int* wait_flags;   // local flag words of the n_wait GPUs whose slices the activation row needs
+  int n_wait;
+  int wait_id;             // the prologue waits until every wait_flags[i] >= *seq * 1024 + wait_id
+  int exchange_id;         // the value published is *seq * 1024 + exchange_id
+  const int* seq;          // device scalar: number of the decode step in flight (monotonic over the context's life)
 };
+
+constexpr int TP_EXCHANGES_PER_STEP = 1024;  // bound of the exchange ids of one decode step
 
 // Launch-shape knobs (defaults chosen by measurement; exposed for experiments)
 struct gemv_tuning {

@@ -333,16 +333,22 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
   }
   pdl_wait();
   if (npairs > 0) {
+    if (p.n_wait > 0) {
+      // tensor-parallel: parts of the activation row come from other GPUs (peer stores into this GPU's memory); wait
+      // for their flags, then read the row past the L1 cache (it may hold lines of the buffer's previous contents)
+      if (tid < p.n_wait) flag_wait_at_least(p.wait_flags + tid, *p.seq * TP_EXCHANGES_PER_STEP + p.wait_id, p.err);
+      bar_sync(1, NCONS);
+    }
     uint4 xv[NVEC];
 #pragma unroll
     for (int j = 0; j < NVEC; ++j) {
       const int i = tid + j * NCONS;
       if (i < vec) {
-        xv[j] = *reinterpret_cast<const uint4*>(p.x + i * 8);
+        xv[j] = __ldcg(reinterpret_cast<const uint4*>(p.x + i * 8));
         *reinterpret_cast<uint4*>(xs + xoff(i)) = xv[j];
       }
     }
-    for (int i = tid + NVEC * NCONS; i < vec; i += NCONS) *reinterpret_cast<uint4*>(xs + xoff(i)) = *reinterpret_cast<const uint4*>(p.x + i * 8);
+    for (int i = tid + NVEC * NCONS; i < vec; i += NCONS) *reinterpret_cast<uint4*>(xs + xoff(i)) = __ldcg(reinterpret_cast<const uint4*>(p.x + i * 8));
     bar_sync(1, NCONS);
     if (p.norm_w != nullptr) {
       // RMSNorm with the reference's summation order (llama_cu.cu:72-106): 256 strided partial sums,
@@ -494,11 +500,14 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
         const __half2 r2 = __halves2half2(__float2half(a0), __float2half(a1));
         *reinterpret_cast<__half2*>(o) = r2;
         if (p.out_peer) *reinterpret_cast<__half2*>(p.out_peer + vrow) = r2;  // peer store over NVLink
+        for (int q = 0; q < p.n_peer_out; ++q) *reinterpret_cast<__half2*>(p.peer_out[q] + vrow) = r2;  // tensor-parallel: into every GPU's row
       } else {
         const __half a = __float2half(v0), bq = __float2half(v1);  // the matmul's own output rounding
         if (EPI == EPI_SILU) {
           const float val = __half2float(a);  // llama_cu.cu:536-537 on the half-rounded w1 / w3 outputs
-          p.out[pr] = __float2half(val / (1.0f + expf(-val)) * __half2float(bq));
+          const __half gated = __float2half(val / (1.0f + expf(-val)) * __half2float(bq));
+          p.out[pr] = gated;
+          for (int q = 0; q < p.n_peer_out; ++q) p.peer_out[q][pr] = gated;
         } else {
           __half o0 = a, o1 = bq;
           if (mat < 2) {  // llama_cu.cu:381-387, cos/sin from the context's table (fetched above)
@@ -516,6 +525,19 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
           }
         }
       }
+    }
+  }
+  // tensor-parallel: the last consumer warp of the launch to get here publishes this GPU's slice.  Lane 0 of every warp
+  // made all of that warp's stores, so its system-scope fence orders them before its count; the last counter sees
+  // every other warp's count, fences again and writes the flags (peer stores into the waiting GPUs' memory).
+  if (p.done_count != nullptr && lane == 0) {
+    __threadfence_system();
+    const int total = (int)gridDim.x * NW;
+    if (atomicAdd(p.done_count, 1) == total - 1) {
+      atomicExch(p.done_count, 0);  // (the next launch counts from zero; its warps arrive after this kernel has ended)
+      __threadfence_system();
+      const int stamp = *p.seq * TP_EXCHANGES_PER_STEP + p.exchange_id;
+      for (int q = 0; q < p.n_peer_flag; ++q) st_release_sys(p.peer_flag[q], stamp);
     }
   }
 }

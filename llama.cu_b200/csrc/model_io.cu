@@ -81,6 +81,7 @@ std::vector<named_shape> shapes_of(const model_params& p) {
 }  // namespace
 
 int model::save_dir(const std::string& dir) {
+  LCU_REQUIRE(tp_size == 1, "model: a tensor-parallel shard cannot be saved as a weight directory");
   mkdir(dir.c_str(), 0777);
   std::vector<char> host;
   int rc = write_file(dir + "/params", &params, sizeof(params));

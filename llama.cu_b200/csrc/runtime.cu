@@ -97,19 +97,27 @@ struct tensor_slot {  // one named tensor of the weight directory
   __half** vec;       // norm vector
   size_t len;         // vector length
   int device;
+  size_t full_rows = 0;  // rows of the whole matrix as named in the weight directory
+  size_t row0 = 0;       // first of them held by this model (a tensor-parallel shard holds full_rows / tp_size rows)
 };
 
 std::vector<tensor_slot> enumerate(model& m) {
   const model_params& p = m.params;
   std::vector<tensor_slot> out;
-  auto mat = [&](const std::string& name, dev_matrix& d, size_t rows, size_t cols, int dev) {
-    d.rows = rows;
+  // every layer matrix and the output matrix are split by rows over the tensor-parallel ranks; the embedding table
+  // (one row is read per token) stays whole on every rank
+  auto mat = [&](const std::string& name, dev_matrix& d, size_t rows, size_t cols, int dev, bool sharded = true) {
+    const size_t local = sharded ? rows / m.tp_size : rows;
+    d.rows = local;
     d.cols = cols;
     d.bs = p.q_type ? p.quantization_block_size : 0;
-    out.push_back({name, &d, nullptr, 0, dev});
+    tensor_slot t{name, &d, nullptr, 0, dev};
+    t.full_rows = rows;
+    t.row0 = sharded ? local * m.tp_rank : 0;
+    out.push_back(t);
   };
   auto vec = [&](const std::string& name, __half*& v, size_t len, int dev) { out.push_back({name, nullptr, &v, len, dev}); };
-  mat("tok_embeddings", m.tok_embeddings, p.n_vocab, p.dim, m.part.embedding_gpu());
+  mat("tok_embeddings", m.tok_embeddings, p.n_vocab, p.dim, m.part.embedding_gpu(), false);
   for (uint32_t i = 0; i < p.n_layers; ++i) {
     layer_weights& L = m.layers[i];
     const int dev = m.part.layer_gpus[i];
@@ -137,7 +145,7 @@ model::~model() {
   }
 }
 
-int model::create(std::unique_ptr<model>& out, const model_params& p, const partition& part) {
+int model::create(std::unique_ptr<model>& out, const model_params& p, const partition& part, int tp_rank, int tp_size) {
   LCU_REQUIRE(p.magic == PARAMS_MAGIC && p.fourcc == PARAMS_FOURCC, "model: bad magic in params");
   LCU_REQUIRE(p.dim > 0 && p.n_heads > 0 && p.n_layers > 0 && p.n_vocab > 0 && p.multiple_of > 0, "model: empty dimension in params");
   LCU_REQUIRE(p.dim % p.n_heads == 0, "model: dim %u not divisible by n_heads %u", p.dim, p.n_heads);
@@ -157,10 +165,19 @@ int model::create(std::unique_ptr<model>& out, const model_params& p, const part
   LCU_REQUIRE(partition_is_contiguous(part.layer_gpus),
               "model: partition returns to a GPU after leaving it; every GPU must hold one contiguous range of layers");
 
+  LCU_REQUIRE(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, "model: tensor-parallel rank %d of %d", tp_rank, tp_size);
+  if (tp_size > 1) {
+    LCU_REQUIRE(p.n_heads % tp_size == 0, "model: %u heads do not split over %d GPUs", p.n_heads, tp_size);
+    LCU_REQUIRE((ffn / tp_size) * tp_size == ffn && (ffn / tp_size) % 2 == 0 && (p.n_vocab / tp_size) * tp_size == p.n_vocab &&
+                    (p.n_vocab / tp_size) % 2 == 0,
+                "model: ffn dim %u and vocabulary %u must split into even row counts over %d GPUs", ffn, p.n_vocab, tp_size);
+  }
   auto m = std::make_unique<model>();
   m->params = p;
   m->ffn = ffn;
   m->part = part;
+  m->tp_rank = tp_rank;
+  m->tp_size = tp_size;
   m->layers.resize(p.n_layers);
   auto slots = enumerate(*m);
   // size and carve one arena per GPU
@@ -217,29 +234,30 @@ int model::find_tensor(const std::string& name, int which, void** ptr, size_t* b
 namespace {
 // copies a whole file of exactly `bytes` bytes into device memory: the reference's way (llama_cu.cu:699-702, 929-971),
 // a file mapping handed to one blocking copy from pageable memory.  Kept as the baseline of the loader measurement.
-int load_file_mapped(const std::string& path, void* dst, size_t bytes) {
+// (`file_bytes` is the size the whole file must have; [file_off, file_off + bytes) is the part that is loaded)
+int load_file_mapped(const std::string& path, void* dst, size_t bytes, size_t file_off, size_t file_bytes) {
   int fd = open(path.c_str(), O_RDONLY);
   if (fd < 0) {
     set_last_error("cannot open %s", path.c_str());
     return LCU_ERR_IO;
   }
   struct stat st;
-  if (fstat(fd, &st) != 0 || (size_t)st.st_size != bytes) {
+  if (fstat(fd, &st) != 0 || (size_t)st.st_size != file_bytes) {
     close(fd);
-    set_last_error("%s: expected %zu bytes, file has %lld", path.c_str(), bytes, (long long)st.st_size);
+    set_last_error("%s: expected %zu bytes, file has %lld", path.c_str(), file_bytes, (long long)st.st_size);
     return LCU_ERR_IO;
   }
-  void* map = bytes ? mmap(nullptr, bytes, PROT_READ, MAP_PRIVATE, fd, 0) : nullptr;
+  void* map = file_bytes ? mmap(nullptr, file_bytes, PROT_READ, MAP_PRIVATE, fd, 0) : nullptr;
   close(fd);
-  if (bytes && map == MAP_FAILED) {
+  if (file_bytes && map == MAP_FAILED) {
     set_last_error("cannot map %s", path.c_str());
     return LCU_ERR_IO;
   }
   // a copy from pageable memory may return while its last piece is still on the way to the device, and the
   // contexts' streams do not wait for the default stream: finish it here
-  cudaError_t e = bytes ? cudaMemcpy(dst, map, bytes, cudaMemcpyHostToDevice) : cudaSuccess;
+  cudaError_t e = bytes ? cudaMemcpy(dst, (const char*)map + file_off, bytes, cudaMemcpyHostToDevice) : cudaSuccess;
   if (bytes && e == cudaSuccess) e = cudaStreamSynchronize(0);
-  if (bytes) munmap(map, bytes);
+  if (file_bytes) munmap(map, file_bytes);
   if (e != cudaSuccess) {
     set_last_error("copy of %s to the device failed: %s", path.c_str(), cudaGetErrorString(e));
     return LCU_ERR_CUDA;
@@ -279,16 +297,16 @@ struct staged_loader {
     }
     if (stream) cudaStreamDestroy(stream);
   }
-  int copy_file(const std::string& path, void* dst, size_t bytes) {
+  int copy_file(const std::string& path, void* dst, size_t bytes, size_t file_off, size_t file_bytes) {
     int fd = open(path.c_str(), O_RDONLY);
     if (fd < 0) {
       set_last_error("cannot open %s", path.c_str());
       return LCU_ERR_IO;
     }
     struct stat st;
-    if (fstat(fd, &st) != 0 || (size_t)st.st_size != bytes) {
+    if (fstat(fd, &st) != 0 || (size_t)st.st_size != file_bytes) {
       close(fd);
-      set_last_error("%s: expected %zu bytes, file has %lld", path.c_str(), bytes, (long long)st.st_size);
+      set_last_error("%s: expected %zu bytes, file has %lld", path.c_str(), file_bytes, (long long)st.st_size);
       return LCU_ERR_IO;
     }
 #ifdef POSIX_FADV_SEQUENTIAL
@@ -312,7 +330,7 @@ struct staged_loader {
       std::atomic<int> failed{0};
       auto read_range = [&](size_t lo, size_t hi) {
         while (lo < hi) {
-          const ssize_t r = pread(fd, (char*)pin[cur] + lo, hi - lo, (off_t)(off + lo));
+          const ssize_t r = pread(fd, (char*)pin[cur] + lo, hi - lo, (off_t)(file_off + off + lo));
           if (r <= 0) {
             failed = 1;
             return;
@@ -375,17 +393,21 @@ int model::load_dir(const std::string& dir) {
       int rc = loader_for(s.device, ld);
       if (rc) return rc;
     }
-    auto load = [&](const std::string& path, void* dst, size_t bytes) { return ld ? ld->copy_file(path, dst, bytes) : load_file_mapped(path, dst, bytes); };
+    auto load = [&](const std::string& path, void* dst, size_t bytes, size_t file_off, size_t file_bytes) {
+      return ld ? ld->copy_file(path, dst, bytes, file_off, file_bytes) : load_file_mapped(path, dst, bytes, file_off, file_bytes);
+    };
     const std::string base = dir + "/" + s.name;
     int rc;
     if (s.mat) {
-      const std::string dims = std::to_string(s.mat->rows) + "_" + std::to_string(s.mat->cols);
-      rc = load(base + ".weight__" + dims, s.mat->w, s.mat->weight_bytes());
+      // files carry the whole matrix (and are named after its shape); a tensor-parallel shard reads its run of rows
+      const size_t wrow = s.mat->bs ? s.mat->cols : s.mat->cols * 2, srow = s.mat->bs ? (s.mat->cols / s.mat->bs) * 2 : 0;
+      const std::string dims = std::to_string(s.full_rows) + "_" + std::to_string(s.mat->cols);
+      rc = load(base + ".weight__" + dims, s.mat->w, s.mat->weight_bytes(), s.row0 * wrow, s.full_rows * wrow);
       if (rc == LCU_OK && s.mat->bs)
-        rc = load(base + ".scale__" + std::to_string(s.mat->rows) + "_" + std::to_string(s.mat->cols / s.mat->bs), s.mat->sc,
-                  s.mat->scale_bytes());
+        rc = load(base + ".scale__" + std::to_string(s.full_rows) + "_" + std::to_string(s.mat->cols / s.mat->bs), s.mat->sc,
+                  s.mat->scale_bytes(), s.row0 * srow, s.full_rows * srow);
     } else {
-      rc = load(base + ".weight__" + std::to_string(s.len), *s.vec, s.len * 2);
+      rc = load(base + ".weight__" + std::to_string(s.len), *s.vec, s.len * 2, 0, s.len * 2);
     }
     if (rc != LCU_OK) return rc;
   }
@@ -406,13 +428,14 @@ int model::fill_synthetic(uint64_t seed, float scale) {
     }
     const size_t n = s.mat->rows * s.mat->cols;
     const uint64_t sid = fnv1a64(s.name.c_str());
+    const uint64_t first = (uint64_t)s.row0 * s.mat->cols;  // a shard holds a run of whole rows: the same values the whole matrix has there
     if (s.mat->bs == 0) {
-      int rc = launch_synth_fill((__half*)s.mat->w, n, seed, sid, scale, 0, 0);
+      int rc = launch_synth_fill((__half*)s.mat->w, n, seed, sid, scale, first, 0);
       if (rc) return rc;
     } else {
       __half* tmp = nullptr;
       LCU_CUDA(cudaMalloc(&tmp, n * 2));
-      int rc = launch_synth_fill(tmp, n, seed, sid, scale, 0, 0);
+      int rc = launch_synth_fill(tmp, n, seed, sid, scale, first, 0);
       if (!rc) rc = launch_quantize_absmax_uint8((uint8_t*)s.mat->w, s.mat->sc, tmp, s.mat->rows, s.mat->cols, s.mat->bs, 0);
       cudaError_t e = cudaDeviceSynchronize();
       cudaFree(tmp);

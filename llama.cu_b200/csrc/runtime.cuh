@@ -82,10 +82,13 @@ struct model {
   std::vector<layer_weights> layers;
   std::vector<std::pair<int, void*>> arenas;  // (device, base) one allocation per GPU
   size_t weight_bytes_total = 0;
+  // tensor-parallel shard: rows [tp_rank, tp_rank + 1) * rows / tp_size of every layer matrix and of the output matrix
+  // (whole heads of wq / wk / wv); norm vectors and the embedding table are whole.  tp_size 1 = the whole model.
+  int tp_rank = 0, tp_size = 1;
 
   ~model();
   // allocates all tensors (uninitialised) according to params and the partition
-  static int create(std::unique_ptr<model>& out, const model_params& p, const partition& part);
+  static int create(std::unique_ptr<model>& out, const model_params& p, const partition& part, int tp_rank = 0, int tp_size = 1);
   // reads a weight directory in the reference's layout (llama_cu.cu:929-984)
   int load_dir(const std::string& dir);
   // fills every tensor with seeded synthetic data (matrices ~ scale * z, norm weights 1.0); a

@@ -65,6 +65,19 @@ def test_oracle_is_not_linked_into_the_product():
                 assert "oracle" not in src.lower().replace("oracle/liboracle", "") or f == "__init__.py" and "oracle" not in src, f
 
 
+def test_tensor_parallel_split_rules():
+    """Row shards need whole heads per GPU and even row counts of the ffn and output matrices: the three model sizes of
+    the configurations split over 2, 4 and 8 GPUs; uneven splits are refused on the host."""
+    lcu = load_package()
+    for dim, heads in ((4096, 32), (5120, 40), (8192, 64)):
+        raw = lcu.pack_params(dim, 256, heads, 2, 32000)
+        for n in (2, 4, 8):
+            assert lcu.lib.lcu_tp_check_split(raw, n) == 0, (dim, n, lcu.lib.lcu_last_error())
+        assert lcu.lib.lcu_tp_check_split(raw, 3) != 0
+    assert lcu.lib.lcu_tp_check_split(lcu.pack_params(5120, 256, 40, 2, 32000), 16) != 0
+    assert lcu.lib.lcu_tp_check_split(lcu.pack_params(512, 256, 4, 2, 2001), 2) != 0 and b"vocabulary" in lcu.lib.lcu_last_error()
+
+
 def test_partition_must_be_contiguous():
     """A GPU may not reappear after another one was used: the head runs on the last layer's GPU and the residual row is
     handed from stage to stage, so [0, 1, 0] would run the head against another stage's buffers."""
