@@ -35,7 +35,7 @@ int lcu_device_count(void);
  * operator sequence.  It is the on-GPU check for the fast kernels and is slow by design. */
 int lcu_set_matmul_type(int type);
 /* launch-shape knobs used for the measurements (defaults are the measured best): "gemv_stages", "gemv_ctas_per_sm",
- * "gemv_ctas_per_sm_int8", "gemv_variant", "gemv_warp_stages", "gemv_warp_stages_int8", "gemv_consumer_warps", "gemv_smem_cap_kb", "gemv_consumer_warps_int8", "gemv_prefetch_kb",
+ * "gemv_ctas_per_sm_int8", "gemv_variant", "gemv_warp_stages", "gemv_warp_stages_int8", "gemv_consumer_warps_int8", "gemv_prefetch_kb",
  * "int8_factored" (0 = round every dequantized weight to half as the reference does), "prefill_tc_min_rows",
  * "prefill_tc_tile_n", "prefill_tc_pair", "prefill_tc_split", "prefill_u8_deq_min_rows", "prefill_fuse", "prefill_attn_tc",
  * "prefill_attn_tc_min_rows", "prefill_attn_tiles", "attn_stream",

@@ -92,8 +92,6 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "int8_factored") gemv_tuning_ref().int8_factored = value;
   else if (k == "gemv_warp_stages_int8") gemv_tuning_ref().warp_stages_int8 = value;
   else if (k == "gemv_warp_stages") gemv_tuning_ref().warp_stages = value;
-  else if (k == "gemv_consumer_warps") gemv_tuning_ref().consumer_warps = value;
-  else if (k == "gemv_smem_cap_kb") gemv_tuning_ref().smem_cap_kb = value;
   else if (k == "gemv_consumer_warps_int8") gemv_tuning_ref().consumer_warps_int8 = value;
   else if (k == "gemv_variant") gemv_tuning_ref().variant = value;
   else if (k == "gemv_prefetch_kb") gemv_tuning_ref().prefetch_kb_per_cta = value;

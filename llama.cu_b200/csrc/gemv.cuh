@@ -64,8 +64,6 @@ struct gemv_tuning {
   int int8_factored = 1;  // u8 weights: 1 = scale factored out of 64-weight groups (fast), 0 = the reference's per-weight rounding
   int warp_stages = 3;  // gemv1.cu: ring depth of every consumer warp (8 KiB per stage)
   int warp_stages_int8 = 3;  // same for the factored u8 kernel
-  int consumer_warps = 0;  // gemv1.cu, any weight type: 0 = automatic (4, or 5 as below), 5 / 6 / 8 = that many consumer warps per CTA when they fit
-  int smem_cap_kb = 0;     // gemv1.cu: upper bound on a CTA's shared memory in KiB (0 = its share of the SM)
   int consumer_warps_int8 = 0;  // factored u8 kernel: 0 = five consumer warps per CTA where three CTAs/SM do not fit, 4 = always four
   int prefetch_kb_per_cta = 32;  // L2 look-ahead issued by each CTA's producer at kernel start
 };

@@ -28,9 +28,8 @@ namespace lcu {
 namespace {
 
 // Consumer warps per CTA (template parameter of the kernel): 4, or 5 for u8 kernels whose activation row leaves room
-// for two CTAs per SM only - ten consumer warps per SM instead of eight, the u8 kernels being latency-bound; 6 and 8
-// serve the one-CTA-per-SM shape, which leaves half of an SM's shared memory and registers to the kernel that follows.
-constexpr int NW_MAX = 8;
+// for two CTAs per SM only - ten consumer warps per SM instead of eight, the u8 kernels being latency-bound.
+constexpr int NW_MAX = 5;
 // Stage geometry per weight type: 4 KiB of each row per stage (measured: 2 KiB stages in a ring twice as deep lose a
 // third of the u8 throughput - the per-stage cost of the producer counts).
 template <int WT>
@@ -199,7 +198,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
 
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [EMPTY_BASE + w * MAX_SW + s]
-  float* scratch = reinterpret_cast<float*>(smem + BAR_BYTES);
+  float* scratch = reinterpret_cast<float*>(smem + BAR_BYTES);  // [8] floats of the RMSNorm reduction, then the activation row's barrier
+  const uint32_t xbar = smem_u32(smem + BAR_BYTES + 32);
   uint8_t* xs = smem + SMEM_FIXED;                     // activation row, K halves (u8 kernels: skewed, see xoff)
   // u8 kernels read 32 activation bytes per 16 weight bytes; with the row stored flat, the two segments of a
   // quarter warp would meet on the same banks.  The activations of every segment are therefore shifted by 16 more
@@ -207,7 +207,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
   auto xoff = [](int vec_index) { return WT == 0 ? vec_index * 16 : (vec_index + (vec_index >> (geom<WT>::SEG_SHIFT - 3))) * 16; };
   const int xbytes = WT == 0 ? p.K * 2 : p.K * 2 + (p.K >> geom<WT>::SEG_SHIFT) * 16 + 16;
   float* xs64 = reinterpret_cast<float*>(xs + ((xbytes + 127) & ~127));  // sums of x over aligned groups of 64
-  uint8_t* stages = reinterpret_cast<uint8_t*>(xs64) + ((p.K / 64 * 4 + 127) & ~127);  // [NW][sw][STAGE_BYTES]
+  // norm weights beyond what the consumers hold in registers (rows longer than NVEC * 8 * consumer threads) are staged here
+  uint8_t* nws = reinterpret_cast<uint8_t*>(xs64) + ((p.K / 64 * 4 + 127) & ~127);
+  uint8_t* stages = nws + (p.norm_w != nullptr && p.K > 4096 ? (((p.K - 4096) * 2 + 127) & ~127) : 0);  // [NW][sw][STAGE_BYTES]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   pdl_launch_dependents();
@@ -226,6 +228,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       mbar_init(smem_u32(&bars[i]), (WT == 0 || sc_bulk) ? 1 : 33);
       mbar_init(smem_u32(&bars[EMPTY_BASE + i]), 1);
     }
+    mbar_init(xbar, 1);
     fence_mbar_init();
   }
   __syncthreads();
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
 
   // -------------------------------------------------------------- consumers
   // The norm weights do not depend on the previous kernel: their loads are in flight while this one waits for it.
-  constexpr int NVEC = 4;  // 16-byte vectors per thread kept in registers (covers K <= 4096)
+  constexpr int NVEC = 4;  // 16-byte vectors of norm weights per thread kept in registers (covers K <= 4096 with four warps)
   const int vec = p.K >> 3;
   uint4 nw[NVEC];
   if (p.norm_w != nullptr && npairs > 0) {
@@ -330,26 +333,28 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       const int i = tid + j * NCONS;
       nw[j] = i < vec ? *reinterpret_cast<const uint4*>(p.norm_w + i * 8) : make_uint4(0, 0, 0, 0);
     }
+    // the rest of a long row's norm weights: asynchronous 16-byte copies into shared memory, no registers held
+    for (int i = tid + NVEC * NCONS; i < vec; i += NCONS) cp_async16(smem_u32(nws) + (uint32_t)(i - NVEC * NCONS) * 16, p.norm_w + i * 8);
+    cp_async_commit();
   }
   pdl_wait();
   if (npairs > 0) {
-    if (p.n_wait > 0) {
-      // tensor-parallel: parts of the activation row come from other GPUs (peer stores into this GPU's memory); wait
-      // for their flags, then read the row past the L1 cache (it may hold lines of the buffer's previous contents)
-      if (tid < p.n_wait) flag_wait_at_least(p.wait_flags + tid, *p.seq * TP_EXCHANGES_PER_STEP + p.wait_id, p.err);
-      bar_sync(1, NCONS);
-    }
-    uint4 xv[NVEC];
-#pragma unroll
-    for (int j = 0; j < NVEC; ++j) {
-      const int i = tid + j * NCONS;
-      if (i < vec) {
-        xv[j] = __ldcg(reinterpret_cast<const uint4*>(p.x + i * 8));
-        *reinterpret_cast<uint4*>(xs + xoff(i)) = xv[j];
+    // The activation row comes in as bulk copies of one 512-element segment each (one trip to L2 whatever the row
+    // length; per-thread loads paid a round trip per batch of four vectors, several microseconds for rows of 8192 and
+    // more).  Bulk copies read through L2, which also is where another GPU's peer stores land.
+    if (warp == 0) {
+      if (p.n_wait > 0) {
+        // tensor-parallel: parts of the row come from other GPUs; wait for their flags first
+        if (lane < p.n_wait) flag_wait_at_least(p.wait_flags + lane, *p.seq * TP_EXCHANGES_PER_STEP + p.wait_id, p.err);
+        __syncwarp();
       }
+      if (lane == 0) mbar_arrive_expect_tx(xbar, (uint32_t)p.K * 2);
+      __syncwarp();
+      const int nseg = (p.K + 511) >> 9;
+      for (int sg = lane; sg < nseg; sg += 32)
+        bulk_g2s(smem_u32(xs + xoff(sg * 64)), p.x + sg * 512, (uint32_t)min(1024, (p.K - sg * 512) * 2), xbar);
     }
-    for (int i = tid + NVEC * NCONS; i < vec; i += NCONS) *reinterpret_cast<uint4*>(xs + xoff(i)) = __ldcg(reinterpret_cast<const uint4*>(p.x + i * 8));
-    bar_sync(1, NCONS);
+    mbar_wait(xbar, 0, p.err, DEV_ERR_FULL_WAIT);
     if (p.norm_w != nullptr) {
       // RMSNorm with the reference's summation order (llama_cu.cu:72-106): 256 strided partial sums,
       // xor trees inside 8 warps, xor tree over the 8 warp sums.  Each of the 128 threads here plays
@@ -390,10 +395,12 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
 #pragma unroll
       for (int j = 0; j < NVEC; ++j) {
         const int i = tid + j * NCONS;
-        if (i < vec) *reinterpret_cast<uint4*>(xs + xoff(i)) = norm8(xv[j], nw[j]);
+        if (i < vec) *reinterpret_cast<uint4*>(xs + xoff(i)) = norm8(*reinterpret_cast<const uint4*>(xs + xoff(i)), nw[j]);
       }
+      cp_async_wait<0>();  // (each thread reads back the staged norm weights it copied itself)
       for (int i = tid + NVEC * NCONS; i < vec; i += NCONS)
-        *reinterpret_cast<uint4*>(xs + xoff(i)) = norm8(*reinterpret_cast<const uint4*>(xs + xoff(i)), *reinterpret_cast<const uint4*>(p.norm_w + i * 8));
+        *reinterpret_cast<uint4*>(xs + xoff(i)) =
+            norm8(*reinterpret_cast<const uint4*>(xs + xoff(i)), *reinterpret_cast<const uint4*>(nws + (size_t)(i - NVEC * NCONS) * 16));
       bar_sync(1, NCONS);
     }
     if (WT == 2) {  // sums of the (normalised) activations over aligned groups of 64: eight lanes per group, 16 bytes per lane
@@ -528,16 +535,16 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
     }
   }
   // tensor-parallel: the last consumer warp of the launch to get here publishes this GPU's slice.  Lane 0 of every warp
-  // made all of that warp's stores, so its system-scope fence orders them before its count; the last counter sees
-  // every other warp's count, fences again and writes the flags (peer stores into the waiting GPUs' memory).
+  // made all of that warp's stores, so its system-scope release fence orders them before its count; the last counter
+  // sees every other warp's count, fences again and writes the flags (peer stores into the waiting GPUs' memory).
   if (p.done_count != nullptr && lane == 0) {
-    __threadfence_system();
+    fence_acq_rel_sys();
     const int total = (int)gridDim.x * NW;
     if (atomicAdd(p.done_count, 1) == total - 1) {
       atomicExch(p.done_count, 0);  // (the next launch counts from zero; its warps arrive after this kernel has ended)
-      __threadfence_system();
+      fence_acq_rel_sys();
       const int stamp = *p.seq * TP_EXCHANGES_PER_STEP + p.exchange_id;
-      for (int q = 0; q < p.n_peer_flag; ++q) st_release_sys(p.peer_flag[q], stamp);
+      for (int q = 0; q < p.n_peer_flag; ++q) st_relaxed_sys(p.peer_flag[q], stamp);
     }
   }
 }
@@ -576,25 +583,19 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   const size_t stage_bytes = wt == 2 ? 2 * geom<2>::ROWB + 2 * geom<2>::SC_ROW : wt == 1 ? 2 * geom<1>::ROWB + 2 * geom<1>::SC_ROW : 2 * geom<0>::ROWB;
   const int seg_shift = wt == 2 ? geom<2>::SEG_SHIFT : geom<1>::SEG_SHIFT;
   const size_t xbytes = wt == 0 ? (size_t)p.K * 2 : (size_t)p.K * 2 + ((size_t)p.K >> seg_shift) * 16 + 16;  // u8: skewed activation row
-  const size_t fixed = SMEM_FIXED + ((xbytes + 127) & ~(size_t)127) + (((size_t)p.K / 64 * 4 + 127) & ~(size_t)127);
+  const size_t nw_stage = p.norm_w != nullptr && p.K > 4096 ? ((((size_t)p.K - 4096) * 2 + 127) & ~(size_t)127) : 0;
+  const size_t fixed = SMEM_FIXED + ((xbytes + 127) & ~(size_t)127) + (((size_t)p.K / 64 * 4 + 127) & ~(size_t)127) + nw_stage;
   // CTAs per SM: as many as asked for that still fit with a two-deep ring per warp (the factored u8 kernel is
   // latency-bound and compiled for three); then the deepest ring that keeps them resident
   int cps = wt == 2 ? t.ctas_per_sm_int8 : t.ctas_per_sm;
   if (cps < 1) cps = 1;
   if (cps > 3) cps = 3;
-  // smem_cap_kb > 0 bounds a CTA's shared memory below its fair share of the SM (113 = half an SM: the CTAs of the next
-  // kernel of a programmatic-dependent chain then fit beside this one's and fill their rings while it still runs)
-  const size_t cap = t.smem_cap_kb > 0 ? (size_t)t.smem_cap_kb * 1024 : (size_t)228 * 1024;
-  auto fits = [&](int warps, int stages, int ctas) {
-    const size_t need = fixed + (size_t)warps * stages * stage_bytes;
-    return need <= (size_t)(228 * 1024) / ctas - 1024 && need <= cap;
-  };
+  auto fits = [&](int warps, int stages, int ctas) { return fixed + (size_t)warps * stages * stage_bytes <= (size_t)(228 * 1024) / ctas - 1024; };
   while (cps > 1 && !fits(4, 2, cps)) --cps;
   // factored u8 kernels that cannot have three CTAs of four consumer warps per SM take five consumer warps per CTA
   // when those fit (a long activation row: w2 of every model, every matrix of the larger models)
   int nw = 4;
   if (wt == 2 && cps < 3 && t.consumer_warps_int8 != 4 && fits(5, 2, cps)) nw = 5;
-  if ((t.consumer_warps == 5 || t.consumer_warps == 6 || t.consumer_warps == 8) && fits(t.consumer_warps, 2, cps)) nw = t.consumer_warps;
   const int want_sw = wt == 2 ? t.warp_stages_int8 : t.warp_stages;
   int sw = want_sw < 2 ? 2 : (want_sw > MAX_SW ? MAX_SW : want_sw);
   while (sw > 2 && !fits(nw, sw, cps)) --sw;
@@ -603,23 +604,18 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   const int pairs = p.n_mats * p.rows_per_mat / 2;
   const int grid = sms * cps > pairs ? pairs : sms * cps;
   const int pf = t.prefetch_kb_per_cta * 1024;
-#define LCU_GEMV1_NW(WTV, E)                                                               \
-  if (nw == 5) return launch_one<WTV, E, 5>(p, stream, pdl, smem, grid, sw, pf);           \
-  if (nw == 6) return launch_one<WTV, E, 6>(p, stream, pdl, smem, grid, sw, pf);           \
-  if (nw == 8) return launch_one<WTV, E, 8>(p, stream, pdl, smem, grid, sw, pf);           \
-  return launch_one<WTV, E, 4>(p, stream, pdl, smem, grid, sw, pf);
 #define LCU_GEMV1_CASE(E)                                                                  \
   case E:                                                                                  \
-    if (wt == 0) { LCU_GEMV1_NW(0, E) }                                                    \
-    if (wt == 1) { LCU_GEMV1_NW(1, E) }                                                    \
-    LCU_GEMV1_NW(2, E)
+    if (wt == 0) return launch_one<0, E, 4>(p, stream, pdl, smem, grid, sw, pf);           \
+    if (wt == 1) return launch_one<1, E, 4>(p, stream, pdl, smem, grid, sw, pf);           \
+    if (nw == 5) return launch_one<2, E, 5>(p, stream, pdl, smem, grid, sw, pf);           \
+    return launch_one<2, E, 4>(p, stream, pdl, smem, grid, sw, pf);
   switch (epilogue) {
     LCU_GEMV1_CASE(EPI_PLAIN)
     LCU_GEMV1_CASE(EPI_ROPE_KV)
     LCU_GEMV1_CASE(EPI_SILU)
   }
 #undef LCU_GEMV1_CASE
-#undef LCU_GEMV1_NW
   LCU_REQUIRE(false, "gemv: unknown epilogue %d", epilogue);
 }
 

@@ -66,11 +66,12 @@ __global__ void __launch_bounds__(256) tp_publish_kernel(const uint4* src, peer_
     const uint4 v = src[i];
     for (int q = 0; q < peers.n_dst; ++q) peers.dst[q][i] = v;
   }
-  __threadfence_system();
+  fence_acq_rel_sys();
   __syncthreads();
   if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
     const int stamp = *seq * TP_EXCHANGES_PER_STEP + exchange_id;
-    for (int q = 0; q < peers.n_flag; ++q) st_release_sys(peers.flag[q], stamp);
+    for (int q = 0; q < peers.n_flag; ++q) st_relaxed_sys(peers.flag[q], stamp);
   }
 }
 
