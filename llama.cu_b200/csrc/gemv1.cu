@@ -339,22 +339,42 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
   }
   pdl_wait();
   if (npairs > 0) {
-    // The activation row comes in as bulk copies of one 512-element segment each (one trip to L2 whatever the row
-    // length; per-thread loads paid a round trip per batch of four vectors, several microseconds for rows of 8192 and
-    // more).  Bulk copies read through L2, which also is where another GPU's peer stores land.
-    if (warp == 0) {
+    // Rows that fit the consumers' registers (NVEC vectors per thread: K <= 4096 with four warps) are loaded by the
+    // threads themselves and stay in registers for the normalisation.  Longer rows come in as bulk copies of one
+    // 512-element segment each: one trip to L2 whatever the row length, where per-thread loads paid a round trip per
+    // batch of vectors - several microseconds for rows of 8192 and more.  Both read past L1 (L2 is where another GPU's
+    // peer stores land).
+    const bool row_in_regs = vec <= NVEC * NCONS;
+    uint4 xv[NVEC];
+    if (row_in_regs) {
       if (p.n_wait > 0) {
         // tensor-parallel: parts of the row come from other GPUs; wait for their flags first
-        if (lane < p.n_wait) flag_wait_at_least(p.wait_flags + lane, *p.seq * TP_EXCHANGES_PER_STEP + p.wait_id, p.err);
-        __syncwarp();
+        if (tid < p.n_wait) flag_wait_at_least(p.wait_flags + tid, (unsigned long long)(*p.seq - 1) * p.wait_per_step[tid] + p.wait_count[tid], p.err);
+        bar_sync(1, NCONS);
       }
-      if (lane == 0) mbar_arrive_expect_tx(xbar, (uint32_t)p.K * 2);
-      __syncwarp();
-      const int nseg = (p.K + 511) >> 9;
-      for (int sg = lane; sg < nseg; sg += 32)
-        bulk_g2s(smem_u32(xs + xoff(sg * 64)), p.x + sg * 512, (uint32_t)min(1024, (p.K - sg * 512) * 2), xbar);
+#pragma unroll
+      for (int j = 0; j < NVEC; ++j) {
+        const int i = tid + j * NCONS;
+        if (i < vec) {
+          xv[j] = __ldcg(reinterpret_cast<const uint4*>(p.x + i * 8));
+          *reinterpret_cast<uint4*>(xs + xoff(i)) = xv[j];
+        }
+      }
+      bar_sync(1, NCONS);
+    } else {
+      if (warp == 0) {
+        if (p.n_wait > 0) {
+          if (lane < p.n_wait) flag_wait_at_least(p.wait_flags + lane, (unsigned long long)(*p.seq - 1) * p.wait_per_step[lane] + p.wait_count[lane], p.err);
+          __syncwarp();
+        }
+        if (lane == 0) mbar_arrive_expect_tx(xbar, (uint32_t)p.K * 2);
+        __syncwarp();
+        const int nseg = (p.K + 511) >> 9;
+        for (int sg = lane; sg < nseg; sg += 32)
+          bulk_g2s(smem_u32(xs + xoff(sg * 64)), p.x + sg * 512, (uint32_t)min(1024, (p.K - sg * 512) * 2), xbar);
+      }
+      mbar_wait(xbar, 0, p.err, DEV_ERR_FULL_WAIT);
     }
-    mbar_wait(xbar, 0, p.err, DEV_ERR_FULL_WAIT);
     if (p.norm_w != nullptr) {
       // RMSNorm with the reference's summation order (llama_cu.cu:72-106): 256 strided partial sums,
       // xor trees inside 8 warps, xor tree over the 8 warp sums.  Each of the 128 threads here plays
@@ -395,7 +415,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
 #pragma unroll
       for (int j = 0; j < NVEC; ++j) {
         const int i = tid + j * NCONS;
-        if (i < vec) *reinterpret_cast<uint4*>(xs + xoff(i)) = norm8(*reinterpret_cast<const uint4*>(xs + xoff(i)), nw[j]);
+        if (i < vec) *reinterpret_cast<uint4*>(xs + xoff(i)) = norm8(row_in_regs ? xv[j] : *reinterpret_cast<const uint4*>(xs + xoff(i)), nw[j]);
       }
       cp_async_wait<0>();  // (each thread reads back the staged norm weights it copied itself)
       for (int i = tid + NVEC * NCONS; i < vec; i += NCONS)
@@ -534,19 +554,12 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       }
     }
   }
-  // tensor-parallel: the last consumer warp of the launch to get here publishes this GPU's slice.  Lane 0 of every warp
-  // made all of that warp's stores, so its system-scope release fence orders them before its count; the last counter
-  // sees every other warp's count, fences again and writes the flags (peer stores into the waiting GPUs' memory).
-  if (p.done_count != nullptr && lane == 0) {
-    fence_acq_rel_sys();
-    const int total = (int)gridDim.x * NW;
-    if (atomicAdd(p.done_count, 1) == total - 1) {
-      atomicExch(p.done_count, 0);  // (the next launch counts from zero; its warps arrive after this kernel has ended)
-      fence_acq_rel_sys();
-      const int stamp = *p.seq * TP_EXCHANGES_PER_STEP + p.exchange_id;
-      for (int q = 0; q < p.n_peer_flag; ++q) st_relaxed_sys(p.peer_flag[q], stamp);
-    }
-  }
+  // tensor-parallel: every consumer warp counts itself, once it is through with its row pairs, on a counter in the memory
+  // of each GPU that waits for this GPU's slice (remote reduction over NVLink, fire and forget).  Lane 0 made all of the
+  // warp's result stores itself, so the release semantics of its reduction order them before the count; a waiting
+  // kernel sees the slice complete when the counter has grown by the number of consumer warps of this launch.
+  if (p.n_peer_flag > 0 && lane == 0)
+    for (int q = 0; q < p.n_peer_flag; ++q) red_release_sys_add(p.peer_flag[q], 1ull);
 }
 
 template <int WT, int EPI, int NW>
@@ -574,8 +587,12 @@ int launch_one(const gemv_params& p, cudaStream_t stream, int pdl, size_t smem, 
 
 }  // namespace
 
-// m == 1 entry used by launch_gemv (argument checks are done there)
-int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl, int sms) {
+namespace {
+struct gemv1_config {
+  int wt, nw, sw, grid, pf;
+  size_t smem;
+};
+int configure(const gemv_params& p, int sms, gemv1_config& c) {
   const gemv_tuning& t = gemv_tuning_ref();
   const bool q = p.bs != 0;
   // weight type of the kernel: fp16; u8 with the reference's per-weight rounding; u8 with factored scales
@@ -602,8 +619,31 @@ int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stre
   const size_t smem = fixed + (size_t)nw * sw * stage_bytes;
   LCU_REQUIRE(smem <= 227 * 1024, "gemv: a row of K=%d does not fit in shared memory", p.K);
   const int pairs = p.n_mats * p.rows_per_mat / 2;
-  const int grid = sms * cps > pairs ? pairs : sms * cps;
-  const int pf = t.prefetch_kb_per_cta * 1024;
+  c.wt = wt;
+  c.nw = nw;
+  c.sw = sw;
+  c.grid = sms * cps > pairs ? pairs : sms * cps;
+  c.pf = t.prefetch_kb_per_cta * 1024;
+  c.smem = smem;
+  return LCU_OK;
+}
+}  // namespace
+
+// consumer warps of the launch launch_gemv would make for these arguments (each counts itself once on the waiting GPUs'
+// counters in tensor-parallel decode); 0 if the arguments cannot be launched
+int gemv_single_row_consumer_warps(const gemv_params& p) {
+  gemv1_config c;
+  if (configure(p, gemv_sm_count(), c) != LCU_OK) return 0;
+  return c.grid * c.nw;
+}
+
+// m == 1 entry used by launch_gemv (argument checks are done there)
+int launch_gemv_single_row(const gemv_params& p, int epilogue, cudaStream_t stream, int pdl, int sms) {
+  gemv1_config c;
+  int rc = configure(p, sms, c);
+  if (rc) return rc;
+  const int wt = c.wt, nw = c.nw, sw = c.sw, grid = c.grid, pf = c.pf;
+  const size_t smem = c.smem;
 #define LCU_GEMV1_CASE(E)                                                                  \
   case E:                                                                                  \
     if (wt == 0) return launch_one<0, E, 4>(p, stream, pdl, smem, grid, sw, pf);           \
