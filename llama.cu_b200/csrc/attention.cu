@@ -30,6 +30,23 @@ __device__ __forceinline__ void st_dsmem_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+// Tensor-parallel decode: the CTA that wrote a head's output counts itself; the last one of the launch writes this GPU's
+// flag into the memory of every GPU that waits for the attention row (system-scope fences: the storing threads' before
+// the count, the counting thread's before the flags).
+__device__ __forceinline__ void publish_when_last(const attn_params& p, int tid, int n_storing, int n_ctas) {
+  if (tid < n_storing) fence_acq_rel_sys();
+  __syncthreads();
+  if (tid == 0) {
+    fence_acq_rel_sys();
+    if (atomicAdd(p.done_count, 1) == n_ctas - 1) {
+      atomicExch(p.done_count, 0);
+      fence_acq_rel_sys();
+      const int stamp = *p.seq * p.exchanges_per_step + p.exchange_id;
+      for (int q = 0; q < p.n_peer_flag; ++q) st_relaxed_sys(p.peer_flag[q], stamp);
+    }
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) {
   constexpr int LPR = HD / 8;    // lanes that share one cached row (8 halves = 16 bytes each)
@@ -193,8 +210,12 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
   if (rank == 0 && tid < HD) {
     float s = 0.f;
     for (uint32_t r = 0; r < cs; ++r) s += rpart[r * HD + tid];
-    p.out[(size_t)qrow * p.ldo + head * HD + tid] = __float2half(s);
+    const __half o = __float2half(s);
+    const size_t at = (size_t)qrow * p.ldo + head * HD + tid;
+    p.out[at] = o;
+    for (int q = 0; q < p.n_peer_out; ++q) p.peer_out[q][at] = o;  // tensor-parallel: into every GPU's row (peer stores)
   }
+  if (rank == 0 && p.done_count != nullptr) publish_when_last(p, tid, HD, (int)(gridDim.y * gridDim.z));
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -390,8 +411,12 @@ __global__ void __launch_bounds__(AS_THREADS, 3) attn_stream_kernel(const attn_p
   if (rank == 0 && tid < HD) {
     float s = 0.f;
     for (uint32_t r = 0; r < cs; ++r) s += rpart[r * HD + tid];
-    p.out[(size_t)qrow * p.ldo + head * HD + tid] = __float2half(s);
+    const __half o = __float2half(s);
+    const size_t at = (size_t)qrow * p.ldo + head * HD + tid;
+    p.out[at] = o;
+    for (int q = 0; q < p.n_peer_out; ++q) p.peer_out[q][at] = o;  // tensor-parallel: into every GPU's row (peer stores)
   }
+  if (rank == 0 && p.done_count != nullptr) publish_when_last(p, tid, HD, (int)(gridDim.y * gridDim.z));
 }
 
 template <int HD>

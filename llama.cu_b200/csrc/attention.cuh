@@ -18,6 +18,16 @@ struct attn_params {
   int n_heads;
   int head_dim;
   int* err;               // device error word for the bounded waits of the streaming kernel (nullptr: that kernel is not used)
+  // ---- tensor-parallel decode (cluster kernels only; all zero on a single GPU): this GPU's heads are a slice of the
+  // attention row; the slice is also stored into the other GPUs' rows and then published like a GEMV's (gemv.cuh)
+  __half* peer_out[7];
+  int n_peer_out;
+  int* peer_flag[8];
+  int n_peer_flag;
+  int* done_count;        // local counter that finds the last (row, head) of the launch (zero between launches)
+  const int* seq;
+  int exchange_id;
+  int exchanges_per_step;
 };
 
 // m query rows; `cluster` CTAs (1, 2, 4 or 8) share one (row, head); max_T bounds pos + m so that

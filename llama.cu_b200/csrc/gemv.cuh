@@ -41,18 +41,19 @@ struct gemv_params {
   int* err;  // device error word
   // ---- tensor-parallel decode (m == 1; all zero on a single GPU).  Every GPU streams its own rows of the matrix and
   // owns the matching slice of the output vector; `out` and the peer pointers are pre-offset to that slice.
-  __half* peer_out[7];                  // EPI_PLAIN / EPI_SILU: every result is also stored into these buffers of other GPUs (peer stores)
+  __half* peer_out[7];     // EPI_PLAIN / EPI_SILU: every result is also stored into these buffers of other GPUs (peer stores)
   int n_peer_out;
-  unsigned long long* peer_flag[8];     // this GPU's counter on each GPU that waits for the slice: +1 per consumer warp of the launch
+  int* peer_flag[8];       // this GPU's flag word on each GPU that waits for the slice; written once all stores are out
   int n_peer_flag;
-  const unsigned long long* wait_flags; // local counters, one per source GPU, of the slices the activation row is made of
+  int* done_count;         // local counter that finds the last CTA of the launch (zero between launches)
+  const int* wait_flags;   // local flag words of the n_wait GPUs whose slices the activation row needs
   int n_wait;
-  // the prologue waits until wait_flags[i] >= (*seq - 1) * wait_per_step[i] + wait_count[i]: what source i adds to the
-  // counter in one whole decode step, and what it has added within the step once the slice is complete
-  unsigned int wait_per_step[8];
-  unsigned int wait_count[8];
-  const int* seq;                       // device scalar: number of the decode step in flight (1, 2, ... over the context's life)
+  int wait_id;             // the prologue waits until every wait_flags[i] >= *seq * 1024 + wait_id
+  int exchange_id;         // the value published is *seq * 1024 + exchange_id
+  const int* seq;          // device scalar: number of the decode step in flight (monotonic over the context's life)
 };
+
+constexpr int TP_EXCHANGES_PER_STEP = 1024;  // bound of the exchange ids of one decode step
 
 // Launch-shape knobs (defaults chosen by measurement; exposed for experiments)
 struct gemv_tuning {
@@ -77,8 +78,7 @@ int gemv_sm_count();
 // several passes
 int gemv_max_rows(int K);
 
-// consumer warps of the single-row launch these arguments lead to (tensor-parallel bookkeeping: every one of them adds 1
-// to the counters in peer_flag)
+// consumer warps of the single-row launch these arguments lead to
 int gemv_single_row_consumer_warps(const gemv_params& p);
 
 // single-row kernel (gemv1.cu); called by launch_gemv after argument checks

@@ -200,6 +200,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // full: [w * MAX_SW + s], empty: [EMPTY_BASE + w * MAX_SW + s]
   float* scratch = reinterpret_cast<float*>(smem + BAR_BYTES);  // [8] floats of the RMSNorm reduction, then the activation row's barrier
   const uint32_t xbar = smem_u32(smem + BAR_BYTES + 32);
+  int* cta_done = reinterpret_cast<int*>(smem + BAR_BYTES + 40);  // consumer warps of this CTA that are through (tensor-parallel)
   uint8_t* xs = smem + SMEM_FIXED;                     // activation row, K halves (u8 kernels: skewed, see xoff)
   // u8 kernels read 32 activation bytes per 16 weight bytes; with the row stored flat, the two segments of a
   // quarter warp would meet on the same banks.  The activations of every segment are therefore shifted by 16 more
@@ -229,6 +230,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       mbar_init(smem_u32(&bars[EMPTY_BASE + i]), 1);
     }
     mbar_init(xbar, 1);
+    *cta_done = 0;
     fence_mbar_init();
   }
   __syncthreads();
@@ -349,7 +351,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
     if (row_in_regs) {
       if (p.n_wait > 0) {
         // tensor-parallel: parts of the row come from other GPUs; wait for their flags first
-        if (tid < p.n_wait) flag_wait_at_least(p.wait_flags + tid, (unsigned long long)(*p.seq - 1) * p.wait_per_step[tid] + p.wait_count[tid], p.err);
+        if (tid < p.n_wait) flag_wait_at_least(p.wait_flags + tid, *p.seq * TP_EXCHANGES_PER_STEP + p.wait_id, p.err);
         bar_sync(1, NCONS);
       }
 #pragma unroll
@@ -364,7 +366,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
     } else {
       if (warp == 0) {
         if (p.n_wait > 0) {
-          if (lane < p.n_wait) flag_wait_at_least(p.wait_flags + lane, (unsigned long long)(*p.seq - 1) * p.wait_per_step[lane] + p.wait_count[lane], p.err);
+          if (lane < p.n_wait) flag_wait_at_least(p.wait_flags + lane, *p.seq * TP_EXCHANGES_PER_STEP + p.wait_id, p.err);
           __syncwarp();
         }
         if (lane == 0) mbar_arrive_expect_tx(xbar, (uint32_t)p.K * 2);
@@ -554,12 +556,22 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       }
     }
   }
-  // tensor-parallel: every consumer warp counts itself, once it is through with its row pairs, on a counter in the memory
-  // of each GPU that waits for this GPU's slice (remote reduction over NVLink, fire and forget).  Lane 0 made all of the
-  // warp's result stores itself, so the release semantics of its reduction order them before the count; a waiting
-  // kernel sees the slice complete when the counter has grown by the number of consumer warps of this launch.
-  if (p.n_peer_flag > 0 && lane == 0)
-    for (int q = 0; q < p.n_peer_flag; ++q) red_release_sys_add(p.peer_flag[q], 1ull);
+  // tensor-parallel: the last consumer warp of the launch to get here publishes this GPU's slice.  Lane 0 of every warp
+  // made all of that warp's stores, so its system-scope fence orders them before its count.  Warps count inside their
+  // CTA first (shared memory), the last warp of a CTA counts the CTA (global memory: a few hundred additions to one
+  // address instead of thousands), and the last CTA fences again and writes the flags into the waiting GPUs' memory.
+  if (p.done_count != nullptr && lane == 0) {
+    fence_acq_rel_sys();
+    if (atomicAdd(cta_done, 1) == NW - 1) {
+      fence_acq_rel_sys();
+      if (atomicAdd(p.done_count, 1) == (int)gridDim.x - 1) {
+        atomicExch(p.done_count, 0);  // (the next launch counts from zero; its warps arrive after this kernel has ended)
+        fence_acq_rel_sys();
+        const int stamp = *p.seq * TP_EXCHANGES_PER_STEP + p.exchange_id;
+        for (int q = 0; q < p.n_peer_flag; ++q) st_relaxed_sys(p.peer_flag[q], stamp);
+      }
+    }
+  }
 }
 
 template <int WT, int EPI, int NW>

@@ -9,15 +9,13 @@
 // single-GPU run.
 //
 // Exchange: the GEMV epilogue stores each result into its own row AND into the same place of every other GPU's row
-// (plain peer stores over NVLink; no TMA multicast, no library kernel on peer memory).  Every consumer warp of a launch,
-// once its stores are out, adds 1 to this GPU's counter in every GPU's memory (a remote reduction with release
-// semantics); the kernel that needs the whole row polls its own GPU's counters until each source has added the warps
-// of its launch (bounded: ~1 s, then the error word is set and the step ends).  All GPUs make the same launches, so
-// the host knows every count.
-// Per layer: attention output (after a small publish kernel), x after wo, the gated hidden row after w1|w3, x after w2.
+// (plain peer stores over NVLink; no TMA multicast, no library kernel on peer memory).  When the last consumer warp of a
+// launch has made its stores it publishes step * 1024 + exchange_id into a flag word in every GPU's memory; the kernel
+// that needs the whole row polls its own GPU's flag words (bounded: ~1 s, then the error word is set and the step ends).
+// Per layer: the attention output, x after wo, the gated hidden row after w1|w3, x after w2.
 // The logits slices go to GPU 0, which runs the softmax / argmax head and sends the token back to every GPU.
 // A step is captured once as a CUDA graph spanning all GPUs (fork / join by events on stream 0); inside it the GPUs are
-// ordered by the counters alone.
+// ordered by the flags alone.
 #include "tp.cuh"
 
 #include <algorithm>
@@ -48,38 +46,17 @@ struct carve {
   } while (0)
 
 // state words of a GPU: [0] position, [1] step counter of a chained run, [2] last token, [3] error word,
-// [4] number of the decode step in flight (1, 2, ...); from word 16: eight 64-bit counters, counter `src` = consumer warps
-// (and publish kernels) of GPU `src` that have delivered their part of an activation row to this GPU so far
-constexpr int ST_POS = 0, ST_STEP = 1, ST_TOKEN = 2, ST_ERR = 3, ST_SEQ = 4, ST_FLAGS = 16, ST_WORDS = 32;
-
-struct peer_list {
-  uint4* dst[TP_MAX];
-  unsigned long long* flag[TP_MAX];
-  int n_dst, n_flag;
-};
+// [4] number of the decode step in flight (monotonic), [5] "last CTA" counter of the GEMV launches, [6] of the attention launches,
+// [8 .. 15] flag words: [8 + src] = step * 1024 + id of the last exchange GPU `src` has completed
+constexpr int ST_POS = 0, ST_STEP = 1, ST_TOKEN = 2, ST_ERR = 3, ST_SEQ = 4, ST_DONE = 5, ST_FLAGS = 8, ST_WORDS = 16;
 
 __global__ void tp_begin_kernel(int* state) { state[ST_SEQ] += 1; }
 
-// copies this GPU's slice of an activation row into the same place of the other GPUs' rows, then counts itself (+1) on
-// every GPU's counter for this GPU
-__global__ void __launch_bounds__(256) tp_publish_kernel(const uint4* src, peer_list peers, int n_vec) {
+// holds the stream until the n flag words have reached step * 1024 + wait_id (the kernel behind it reads what arrived)
+__global__ void tp_wait_kernel(const int* flags, int n, const int* seq, int wait_id, int* err) {
   pdl_launch_dependents();
   pdl_wait();
-  for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
-    const uint4 v = src[i];
-    for (int q = 0; q < peers.n_dst; ++q) peers.dst[q][i] = v;
-  }
-  fence_acq_rel_sys();
-  __syncthreads();
-  if (threadIdx.x == 0)
-    for (int q = 0; q < peers.n_flag; ++q) red_release_sys_add(peers.flag[q], 1ull);
-}
-
-// holds the stream until the n counters have reached (step - 1) * per_step + count (the kernel behind it reads what arrived)
-__global__ void tp_wait_kernel(const unsigned long long* flags, int n, const int* seq, unsigned int per_step, unsigned int count, int* err) {
-  pdl_launch_dependents();
-  pdl_wait();
-  if ((int)threadIdx.x < n) flag_wait_at_least(flags + threadIdx.x, (unsigned long long)(*seq - 1) * per_step + count, err);
+  if ((int)threadIdx.x < n) flag_wait_at_least(flags + threadIdx.x, *seq * TP_EXCHANGES_PER_STEP + wait_id, err);
 }
 
 // the chosen token goes to every other GPU's id buffer (ordering to their next step: the join / fork events of the steps)
@@ -138,13 +115,7 @@ struct tp_impl {
   bool warmed[2] = {false, false}, graph_failed = false;
 
   gemv_params base(int gi, int K) const;
-  void exchange(gemv_params& a, int gi, size_t slice_off, __half* tp_gpu::*row) const;
-  void wait_for(gemv_params& a, int gi, unsigned int count) const;
-  unsigned long long* counter(int on_gpu, int src) const { return reinterpret_cast<unsigned long long*>(g[on_gpu].state + ST_FLAGS) + src; }
-  // consumer warps of the exchanging launches (the same on every GPU: same shapes, same launch rules)
-  unsigned int w_wo = 0, w_13 = 0, w_2 = 0, w_out = 0;
-  unsigned int per_layer() const { return 1 + w_wo + w_13 + w_2; }
-  unsigned int per_step(int on_gpu) const { return p.n_layers * per_layer() + (on_gpu == 0 ? w_out : 0); }
+  void exchange(gemv_params& a, int gi, size_t slice_off, __half* tp_gpu::*row, int exchange_id) const;
   int enqueue_step(int long_ctx);
   int build_graph(int variant);
   int run_step(int n_keys);
@@ -282,8 +253,8 @@ size_t tp_decoder::memory_usage() const {
 int tp_decoder::n_gpus() const { return impl->n; }
 int tp_decoder::tokens_left() const { return impl->opt.context_len - impl->start_pos; }
 void tp_decoder::clear_tokens() { impl->start_pos = 0; }
-// per GPU: begin, embed, 6 per layer (QKV, attention, publish, wo, w1|w3, w2), output rows, + on GPU 0 wait, head, token
-int tp_decoder::kernels_per_step() const { return impl->n * (3 + 6 * (int)impl->p.n_layers) + 3 + (impl->n - 1); }
+// per GPU: begin, embed, 5 per layer (QKV, attention, wo, w1|w3, w2), output rows, + on GPU 0 wait, head, token
+int tp_decoder::kernels_per_step() const { return impl->n * (3 + 5 * (int)impl->p.n_layers) + 3 + (impl->n - 1); }
 
 gemv_params tp_impl::base(int gi, int K) const {
   const tp_gpu& g = this->g[gi];
@@ -296,50 +267,27 @@ gemv_params tp_impl::base(int gi, int K) const {
   a.err = g.state + ST_ERR;
   a.pos = g.state + ST_POS;
   a.seq = g.state + ST_SEQ;
+  a.wait_flags = g.state + ST_FLAGS;
   return a;
 }
 
-// the launch starts its products once every GPU has delivered `count` units of this step (see per_step)
-void tp_impl::wait_for(gemv_params& a, int gi, unsigned int count) const {
-  a.wait_flags = counter(gi, 0);
-  a.n_wait = n;
-  for (int i = 0; i < n; ++i) {
-    a.wait_per_step[i] = per_step(gi);
-    a.wait_count[i] = count;
-  }
-}
-
-// results of this launch also go into `row` of every other GPU at element offset slice_off, and every consumer warp
-// counts itself on every GPU's counter for this GPU (this GPU's own included)
-void tp_impl::exchange(gemv_params& a, int gi, size_t slice_off, __half* tp_gpu::*row) const {
+// results of this launch also go into `row` of every other GPU at element offset slice_off, and once the launch is
+// complete every GPU (this one included) gets the flag exchange_id in its slot for this GPU
+void tp_impl::exchange(gemv_params& a, int gi, size_t slice_off, __half* tp_gpu::*row, int exchange_id) const {
   a.n_peer_out = 0;
   a.n_peer_flag = 0;
   for (int j = 0; j < n; ++j) {
     if (j != gi) a.peer_out[a.n_peer_out++] = g[j].*row + slice_off;
-    a.peer_flag[a.n_peer_flag++] = counter(j, gi);
+    a.peer_flag[a.n_peer_flag++] = g[j].state + ST_FLAGS + gi;
   }
+  a.done_count = g[gi].state + ST_DONE;
+  a.exchange_id = exchange_id;
 }
 
 int tp_impl::enqueue_step(int long_ctx) {
   const int d = p.dim, hd = d / p.n_heads, f = ffn, V = p.n_vocab, L = p.n_layers, bs = p.q_type ? p.quantization_block_size : 0;
   const int dl = d / n, fl = f / n, vl = V / n, pdl = opt.use_pdl;
-  // the counts of the exchanging launches (GPU 0's shapes stand for all)
-  {
-    const layer_weights& W = g[0].shard->layers[0];
-    gemv_params a = base(0, d);
-    a.w[0] = W.wo.w; a.n_mats = 1; a.rows_per_mat = dl;
-    w_wo = gemv_single_row_consumer_warps(a);
-    a = base(0, d);
-    a.w[0] = W.w1.w; a.n_mats = 2; a.rows_per_mat = fl; a.norm_w = W.ffn_norm;
-    w_13 = gemv_single_row_consumer_warps(a);
-    a = base(0, f);
-    a.w[0] = W.w2.w; a.n_mats = 1; a.rows_per_mat = dl;
-    w_2 = gemv_single_row_consumer_warps(a);
-    a = base(0, d);
-    a.w[0] = g[0].shard->output.w; a.n_mats = 1; a.rows_per_mat = vl; a.norm_w = g[0].shard->norm;
-    w_out = gemv_single_row_consumer_warps(a);
-    LCU_REQUIRE(w_wo && w_13 && w_2 && w_out, "tensor parallel: a matrix shard cannot be launched (%s)", last_error());
-  }
+  LCU_REQUIRE(4 * L + 2 < TP_EXCHANGES_PER_STEP, "tensor parallel: %d layers exceed the exchange numbering", L);
   // fork: the other GPUs' streams join stream 0's place in the step sequence
   {
     device_guard dg(g[0].device);
@@ -365,7 +313,7 @@ int tp_impl::enqueue_step(int long_ctx) {
       device_guard dg(me.device);
       const model& m = *me.shard;
       const layer_weights& W = m.layers[l];
-      const unsigned int c0 = (unsigned int)l * per_layer();  // units every GPU has delivered in this step before this layer
+      const int id0 = 4 * l;
       {  // RMSNorm + this GPU's heads of wq | wk | wv + RoPE + cache write (llama_cu.cu:1129-1156)
         gemv_params a = base(gi, d);
         a.w[0] = W.wq.w; a.w[1] = W.wk.w; a.w[2] = W.wv.w;
@@ -380,7 +328,10 @@ int tp_impl::enqueue_step(int long_ctx) {
         a.rope = me.rope;
         a.ctx_len = opt.context_len;
         a.head_dim = hd;
-        if (l > 0) wait_for(a, gi, c0);  // x of the previous layer's w2: slices of every GPU
+        if (l > 0) {  // x of the previous layer's w2: slices of every GPU
+          a.n_wait = n;
+          a.wait_id = id0;
+        }
         LCU_TRY(launch_gemv(a, EPI_ROPE_KV, me.stream, pdl));
       }
       {  // attention of this GPU's heads (llama_cu.cu:1161-1171), then the slice to every GPU
@@ -390,20 +341,22 @@ int tp_impl::enqueue_step(int long_ctx) {
         at.out = me.att + (size_t)gi * dl; at.ldo = dl;
         at.pos = me.state + ST_POS;
         at.ctx_len = opt.context_len; at.n_heads = p.n_heads / n; at.head_dim = hd; at.err = me.state + ST_ERR;
-        LCU_TRY(launch_attention(at, 1, opt.attn_cluster, long_ctx ? opt.context_len : std::min(opt.context_len, 64 * opt.attn_cluster), me.stream, pdl));
-        peer_list pl{};
         for (int j = 0; j < n; ++j) {
-          if (j != gi) pl.dst[pl.n_dst++] = reinterpret_cast<uint4*>(g[j].att + (size_t)gi * dl);
-          pl.flag[pl.n_flag++] = counter(j, gi);
+          if (j != gi) at.peer_out[at.n_peer_out++] = g[j].att + (size_t)gi * dl;
+          at.peer_flag[at.n_peer_flag++] = g[j].state + ST_FLAGS + gi;
         }
-        LCU_TRY(launch_small(tp_publish_kernel, 256, me.stream, pdl, reinterpret_cast<const uint4*>(me.att + (size_t)gi * dl), pl, dl / 8));
+        at.done_count = me.state + ST_DONE + 1;
+        at.seq = me.state + ST_SEQ;
+        at.exchange_id = id0 + 1;
+        at.exchanges_per_step = TP_EXCHANGES_PER_STEP;
+        LCU_TRY(launch_attention(at, 1, opt.attn_cluster, long_ctx ? opt.context_len : std::min(opt.context_len, 64 * opt.attn_cluster), me.stream, pdl));
       }
       {  // this GPU's rows of wo + residual (llama_cu.cu:1174)
         gemv_params a = base(gi, d);
         a.w[0] = W.wo.w; a.sc[0] = W.wo.sc; a.n_mats = 1; a.rows_per_mat = dl;
         a.x = me.att; a.out = me.x + (size_t)gi * dl; a.ldo = d; a.beta = 1.0f;
-        wait_for(a, gi, c0 + 1);
-        exchange(a, gi, (size_t)gi * dl, &tp_gpu::x);
+        a.n_wait = n; a.wait_id = id0 + 1;
+        exchange(a, gi, (size_t)gi * dl, &tp_gpu::x, id0 + 2);
         LCU_TRY(launch_gemv(a, EPI_PLAIN, me.stream, pdl));
       }
       {  // RMSNorm + this GPU's rows of w1 | w3 + SiLU gate (llama_cu.cu:1176-1183)
@@ -411,16 +364,16 @@ int tp_impl::enqueue_step(int long_ctx) {
         a.w[0] = W.w1.w; a.w[1] = W.w3.w; a.sc[0] = W.w1.sc; a.sc[1] = W.w3.sc;
         a.n_mats = 2; a.rows_per_mat = fl;
         a.x = me.x; a.norm_w = W.ffn_norm; a.out = me.hs + (size_t)gi * fl; a.ldo = f;
-        wait_for(a, gi, c0 + 1 + w_wo);
-        exchange(a, gi, (size_t)gi * fl, &tp_gpu::hs);
+        a.n_wait = n; a.wait_id = id0 + 2;
+        exchange(a, gi, (size_t)gi * fl, &tp_gpu::hs, id0 + 3);
         LCU_TRY(launch_gemv(a, EPI_SILU, me.stream, pdl));
       }
       {  // this GPU's rows of w2 + residual (llama_cu.cu:1185)
         gemv_params a = base(gi, f);
         a.w[0] = W.w2.w; a.sc[0] = W.w2.sc; a.n_mats = 1; a.rows_per_mat = dl;
         a.x = me.hs; a.out = me.x + (size_t)gi * dl; a.ldo = d; a.beta = 1.0f;
-        wait_for(a, gi, c0 + 1 + w_wo + w_13);
-        exchange(a, gi, (size_t)gi * dl, &tp_gpu::x);
+        a.n_wait = n; a.wait_id = id0 + 3;
+        exchange(a, gi, (size_t)gi * dl, &tp_gpu::x, id0 + 4);
         LCU_TRY(launch_gemv(a, EPI_PLAIN, me.stream, pdl));
       }
     }
@@ -433,14 +386,16 @@ int tp_impl::enqueue_step(int long_ctx) {
       gemv_params a = base(gi, d);
       a.w[0] = m.output.w; a.sc[0] = m.output.sc; a.n_mats = 1; a.rows_per_mat = vl;
       a.x = me.x; a.norm_w = m.norm; a.out = me.logits + (size_t)gi * vl; a.ldo = V;
-      wait_for(a, gi, (unsigned int)L * per_layer());
+      a.n_wait = n; a.wait_id = 4 * L;
       if (gi != 0) a.peer_out[a.n_peer_out++] = g[0].logits + (size_t)gi * vl;
-      a.peer_flag[a.n_peer_flag++] = counter(0, gi);
+      a.peer_flag[a.n_peer_flag++] = g[0].state + ST_FLAGS + gi;
+      a.done_count = me.state + ST_DONE;
+      a.exchange_id = 4 * L + 1;
       LCU_TRY(launch_gemv(a, EPI_PLAIN, me.stream, pdl));
     }
     if (gi == 0) {  // softmax(T) + first-maximum token (llama_cu.cu:1196-1209), the token to every GPU
-      LCU_TRY(launch_small(tp_wait_kernel, 32, me.stream, pdl, (const unsigned long long*)counter(0, 0), n, (const int*)(me.state + ST_SEQ), per_step(0),
-                           per_step(0), me.state + ST_ERR));
+      LCU_TRY(launch_small(tp_wait_kernel, 32, me.stream, pdl, (const int*)(me.state + ST_FLAGS), n, (const int*)(me.state + ST_SEQ), 4 * L + 1,
+                           me.state + ST_ERR));
       head_params h{};
       h.logits = me.logits; h.probs = me.probs; h.n_vocab = V; h.temperature = opt.temperature;
       h.token_out = me.state + ST_TOKEN; h.next_ids = me.ids;
@@ -543,13 +498,6 @@ int tp_impl::finish(const char* who) {
     }
   }
   if (code != 0) {
-    // the counters no longer match the step count: both start over, so that the decoder stays usable
-    for (int gi = 0; gi < n; ++gi) {
-      device_guard dg(g[gi].device);
-      cudaDeviceSynchronize();
-      cudaMemset(g[gi].state + ST_SEQ, 0, (ST_WORDS - ST_SEQ) * 4);
-      cudaDeviceSynchronize();
-    }
     set_last_error("%s: a kernel gave up on a bounded wait (device error 0x%x)", who, code);
     return LCU_ERR_DEVICE_WAIT;
   }
