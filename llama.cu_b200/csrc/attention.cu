@@ -487,6 +487,16 @@ int g_attn_stream = -1;  // -1 = streaming kernel when a CTA's slice can exceed 
 
 void attention_set_stream_mode(int mode) { g_attn_stream = mode; }
 
+// loads the decode attention kernels on the current device ahead of their first launch (see gemv_single_row_preload)
+int attention_preload() {
+  cudaFuncAttributes fa;
+  LCU_CUDA(cudaFuncGetAttributes(&fa, attn_kernel<128>));
+  LCU_CUDA(cudaFuncGetAttributes(&fa, attn_kernel<64>));
+  LCU_CUDA(cudaFuncGetAttributes(&fa, attn_stream_kernel<128>));
+  LCU_CUDA(cudaFuncGetAttributes(&fa, attn_stream_kernel<64>));
+  return LCU_OK;
+}
+
 int launch_attention(const attn_params& p, int m, int cluster, int max_T, cudaStream_t stream, int pdl) {
   LCU_REQUIRE(m >= 1 && p.n_heads >= 1, "attention: empty problem");
   LCU_REQUIRE(cluster >= 1 && cluster <= 8 && (cluster & (cluster - 1)) == 0, "attention: cluster size %d not in {1,2,4,8}", cluster);

@@ -34,6 +34,8 @@ struct attn_params {
 // shared memory can be sized without reading the device position.
 int launch_attention(const attn_params& p, int m, int cluster, int max_T, cudaStream_t stream, int pdl);
 
+int attention_preload();
+
 // -1 = rows through a shared-memory ring of bulk copies when a CTA's slice can exceed 64 rows (default), 0 = never, 1 = always
 void attention_set_stream_mode(int mode);
 

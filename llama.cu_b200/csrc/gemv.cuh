@@ -78,6 +78,8 @@ int gemv_sm_count();
 // several passes
 int gemv_max_rows(int K);
 
+// loads all single-row kernels on the current device ahead of their first launch
+int gemv_single_row_preload();
 // consumer warps of the single-row launch these arguments lead to
 int gemv_single_row_consumer_warps(const gemv_params& p);
 

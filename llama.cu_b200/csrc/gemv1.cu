@@ -641,6 +641,21 @@ int configure(const gemv_params& p, int sms, gemv1_config& c) {
 }
 }  // namespace
 
+// Loads every single-row kernel on the current device (the CUDA runtime loads a kernel at its first use; a first decode
+// step whose launches stall one after the other in that loading would leave the other GPUs of a tensor-parallel step
+// waiting far longer than their bounded waits allow).
+int gemv_single_row_preload() {
+  cudaFuncAttributes fa;
+#define LCU_PRELOAD(WTV, E, NWV) LCU_CUDA(cudaFuncGetAttributes(&fa, gemv1_kernel<WTV, E, NWV>));
+#define LCU_PRELOAD_E(E) LCU_PRELOAD(0, E, 4) LCU_PRELOAD(1, E, 4) LCU_PRELOAD(2, E, 4) LCU_PRELOAD(2, E, 5)
+  LCU_PRELOAD_E(EPI_PLAIN)
+  LCU_PRELOAD_E(EPI_ROPE_KV)
+  LCU_PRELOAD_E(EPI_SILU)
+#undef LCU_PRELOAD_E
+#undef LCU_PRELOAD
+  return LCU_OK;
+}
+
 // consumer warps of the launch launch_gemv would make for these arguments (each counts itself once on the waiting GPUs'
 // counters in tensor-parallel decode); 0 if the arguments cannot be launched
 int gemv_single_row_consumer_warps(const gemv_params& p) {

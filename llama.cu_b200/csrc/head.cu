@@ -150,6 +150,12 @@ __global__ void __cluster_dims__(HC_CLUSTER, 1, 1) __launch_bounds__(HC_THREADS)
 
 }  // namespace
 
+int head_preload() {
+  cudaFuncAttributes fa;
+  LCU_CUDA(cudaFuncGetAttributes(&fa, logits_head_cluster_kernel));
+  return LCU_OK;
+}
+
 int launch_logits_head(const head_params& p, cudaStream_t stream, int pdl) {
   const int J = (p.n_vocab + 255) / 256;
   const size_t smem = (size_t)J * 32 * sizeof(float);

@@ -622,6 +622,16 @@ int launch_synth_fill(__half* out, size_t n, uint64_t seed, uint64_t stream_id, 
   return LCU_OK;
 }
 
+// loads the small kernels of a decode step on the current device ahead of their first launch
+int ops_preload() {
+  cudaFuncAttributes fa;
+  LCU_CUDA(cudaFuncGetAttributes(&fa, embed_kernel));
+  LCU_CUDA(cudaFuncGetAttributes(&fa, bump_pos_kernel));
+  LCU_CUDA(cudaFuncGetAttributes(&fa, token_to_ids_kernel));
+  LCU_CUDA(cudaFuncGetAttributes(&fa, logits_head_kernel));
+  return LCU_OK;
+}
+
 int launch_bump_pos(int* pos, int inc, cudaStream_t stream) {
   bump_pos_kernel<<<1, 1, 0, stream>>>(pos, inc);
   LCU_CUDA(cudaGetLastError());

@@ -67,6 +67,10 @@ int launch_synth_fill(__half* out, size_t n, uint64_t seed, uint64_t stream_id, 
 int launch_fill_half(__half* out, size_t n, float value, cudaStream_t stream);
 uint64_t fnv1a64(const char* s);
 
+// load the kernels of a decode step on the current device ahead of their first launch (ops.cu, head.cu)
+int ops_preload();
+int head_preload();
+
 // pipeline helpers: *pos += inc; ids[0] = (short)*token (ids may live on a peer GPU)
 int launch_bump_pos(int* pos, int inc, cudaStream_t stream);
 int launch_token_to_ids(short* ids, const int* token, cudaStream_t stream);

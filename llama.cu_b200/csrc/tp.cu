@@ -29,6 +29,9 @@ namespace lcu {
 namespace {
 
 constexpr int TP_MAX = 8;
+// measurement switch (lcu_set_tuning "tp_debug"; results are wrong when set): 1 = kernels do not wait for the other GPUs'
+// slices, 2 = kernels neither send their slices nor publish, 4 = no peer stores of results but flags are still published
+int g_tp_debug = 0;
 constexpr size_t ALIGN = 256;
 struct carve {
   size_t off = 0;
@@ -100,6 +103,8 @@ struct tp_gpu {
 };
 
 }  // namespace
+
+void tp_set_debug(int v) { g_tp_debug = v; }
 
 struct tp_impl {
   model_params p{};
@@ -211,6 +216,18 @@ int tp_decoder::create(std::unique_ptr<tp_decoder>& out, const model_params& p, 
     g.log = (short*)(b + o_log);
     g.state = (int*)(b + o_state);
     LCU_TRY(launch_rope_table(g.rope, opt.context_len, hd, 10000.0f, g.stream));
+    // every kernel of a step is loaded on this GPU now: in the first step no launch may stall in kernel loading while
+    // the other GPUs' kernels are already waiting for this GPU's slices
+    LCU_TRY(gemv_single_row_preload());
+    LCU_TRY(attention_preload());
+    LCU_TRY(ops_preload());
+    LCU_TRY(head_preload());
+    {
+      cudaFuncAttributes fa;
+      LCU_CUDA(cudaFuncGetAttributes(&fa, tp_begin_kernel));
+      LCU_CUDA(cudaFuncGetAttributes(&fa, tp_wait_kernel));
+      LCU_CUDA(cudaFuncGetAttributes(&fa, tp_token_kernel));
+    }
     // K and V caches of this GPU's heads: [layer][K | V][local head][position][head_dim]
     const size_t per = round_up(ctxl * (d / n_gpus) * 2, ALIGN);
     g.kv_bytes = per * 2 * L;
@@ -276,8 +293,9 @@ gemv_params tp_impl::base(int gi, int K) const {
 void tp_impl::exchange(gemv_params& a, int gi, size_t slice_off, __half* tp_gpu::*row, int exchange_id) const {
   a.n_peer_out = 0;
   a.n_peer_flag = 0;
+  if (g_tp_debug & 2) return;
   for (int j = 0; j < n; ++j) {
-    if (j != gi) a.peer_out[a.n_peer_out++] = g[j].*row + slice_off;
+    if (j != gi && !(g_tp_debug & 4)) a.peer_out[a.n_peer_out++] = g[j].*row + slice_off;
     a.peer_flag[a.n_peer_flag++] = g[j].state + ST_FLAGS + gi;
   }
   a.done_count = g[gi].state + ST_DONE;
@@ -329,7 +347,7 @@ int tp_impl::enqueue_step(int long_ctx) {
         a.ctx_len = opt.context_len;
         a.head_dim = hd;
         if (l > 0) {  // x of the previous layer's w2: slices of every GPU
-          a.n_wait = n;
+          a.n_wait = (g_tp_debug & 1) ? 0 : n;
           a.wait_id = id0;
         }
         LCU_TRY(launch_gemv(a, EPI_ROPE_KV, me.stream, pdl));
@@ -341,11 +359,11 @@ int tp_impl::enqueue_step(int long_ctx) {
         at.out = me.att + (size_t)gi * dl; at.ldo = dl;
         at.pos = me.state + ST_POS;
         at.ctx_len = opt.context_len; at.n_heads = p.n_heads / n; at.head_dim = hd; at.err = me.state + ST_ERR;
-        for (int j = 0; j < n; ++j) {
-          if (j != gi) at.peer_out[at.n_peer_out++] = g[j].att + (size_t)gi * dl;
+        for (int j = 0; j < n && !(g_tp_debug & 2); ++j) {
+          if (j != gi && !(g_tp_debug & 4)) at.peer_out[at.n_peer_out++] = g[j].att + (size_t)gi * dl;
           at.peer_flag[at.n_peer_flag++] = g[j].state + ST_FLAGS + gi;
         }
-        at.done_count = me.state + ST_DONE + 1;
+        if (!(g_tp_debug & 2)) at.done_count = me.state + ST_DONE + 1;
         at.seq = me.state + ST_SEQ;
         at.exchange_id = id0 + 1;
         at.exchanges_per_step = TP_EXCHANGES_PER_STEP;
@@ -355,7 +373,7 @@ int tp_impl::enqueue_step(int long_ctx) {
         gemv_params a = base(gi, d);
         a.w[0] = W.wo.w; a.sc[0] = W.wo.sc; a.n_mats = 1; a.rows_per_mat = dl;
         a.x = me.att; a.out = me.x + (size_t)gi * dl; a.ldo = d; a.beta = 1.0f;
-        a.n_wait = n; a.wait_id = id0 + 1;
+        a.n_wait = (g_tp_debug & 1) ? 0 : n; a.wait_id = id0 + 1;
         exchange(a, gi, (size_t)gi * dl, &tp_gpu::x, id0 + 2);
         LCU_TRY(launch_gemv(a, EPI_PLAIN, me.stream, pdl));
       }
@@ -364,7 +382,7 @@ int tp_impl::enqueue_step(int long_ctx) {
         a.w[0] = W.w1.w; a.w[1] = W.w3.w; a.sc[0] = W.w1.sc; a.sc[1] = W.w3.sc;
         a.n_mats = 2; a.rows_per_mat = fl;
         a.x = me.x; a.norm_w = W.ffn_norm; a.out = me.hs + (size_t)gi * fl; a.ldo = f;
-        a.n_wait = n; a.wait_id = id0 + 2;
+        a.n_wait = (g_tp_debug & 1) ? 0 : n; a.wait_id = id0 + 2;
         exchange(a, gi, (size_t)gi * fl, &tp_gpu::hs, id0 + 3);
         LCU_TRY(launch_gemv(a, EPI_SILU, me.stream, pdl));
       }
@@ -372,7 +390,7 @@ int tp_impl::enqueue_step(int long_ctx) {
         gemv_params a = base(gi, f);
         a.w[0] = W.w2.w; a.sc[0] = W.w2.sc; a.n_mats = 1; a.rows_per_mat = dl;
         a.x = me.hs; a.out = me.x + (size_t)gi * dl; a.ldo = d; a.beta = 1.0f;
-        a.n_wait = n; a.wait_id = id0 + 3;
+        a.n_wait = (g_tp_debug & 1) ? 0 : n; a.wait_id = id0 + 3;
         exchange(a, gi, (size_t)gi * dl, &tp_gpu::x, id0 + 4);
         LCU_TRY(launch_gemv(a, EPI_PLAIN, me.stream, pdl));
       }
@@ -386,15 +404,21 @@ int tp_impl::enqueue_step(int long_ctx) {
       gemv_params a = base(gi, d);
       a.w[0] = m.output.w; a.sc[0] = m.output.sc; a.n_mats = 1; a.rows_per_mat = vl;
       a.x = me.x; a.norm_w = m.norm; a.out = me.logits + (size_t)gi * vl; a.ldo = V;
-      a.n_wait = n; a.wait_id = 4 * L;
+      a.n_wait = (g_tp_debug & 1) ? 0 : n; a.wait_id = 4 * L;
       if (gi != 0) a.peer_out[a.n_peer_out++] = g[0].logits + (size_t)gi * vl;
       a.peer_flag[a.n_peer_flag++] = g[0].state + ST_FLAGS + gi;
       a.done_count = me.state + ST_DONE;
       a.exchange_id = 4 * L + 1;
       LCU_TRY(launch_gemv(a, EPI_PLAIN, me.stream, pdl));
     }
+  }
+  // (everything the head waits for is enqueued before the head itself: the host must never sit between a waiting
+  // kernel and the launch it waits for)
+  for (int gi = n - 1; gi >= 0; --gi) {
+    tp_gpu& me = g[gi];
+    device_guard dg(me.device);
     if (gi == 0) {  // softmax(T) + first-maximum token (llama_cu.cu:1196-1209), the token to every GPU
-      LCU_TRY(launch_small(tp_wait_kernel, 32, me.stream, pdl, (const int*)(me.state + ST_FLAGS), n, (const int*)(me.state + ST_SEQ), 4 * L + 1,
+      LCU_TRY(launch_small(tp_wait_kernel, 32, me.stream, pdl, (const int*)(me.state + ST_FLAGS), (g_tp_debug & 1) ? 0 : n, (const int*)(me.state + ST_SEQ), 4 * L + 1,
                            me.state + ST_ERR));
       head_params h{};
       h.logits = me.logits; h.probs = me.probs; h.n_vocab = V; h.temperature = opt.temperature;

@@ -13,6 +13,9 @@ struct tp_impl;  // defined in tp.cu
 // the row counts of the model must split evenly over the GPUs (whole heads, even row counts); host-only check
 int tp_check_split(const model_params& p, int n_gpus);
 
+// measurement switch, see tp.cu (0 = normal operation)
+void tp_set_debug(int v);
+
 struct tp_decoder {
   ~tp_decoder();
   // allocates the row shards of the model, the K/V caches of each GPU's heads and the activation rows on the named GPUs

@@ -81,3 +81,21 @@ def test_tensor_parallel_rejects_bad_splits(lcu):
     assert lcu.lib.lcu_tp_check_split(raw, 2) == 0 and lcu.lib.lcu_tp_check_split(raw, 4) == 0
     assert lcu.lib.lcu_tp_check_split(raw, 8) != 0 and b"heads" in lcu.lib.lcu_last_error()
     assert lcu.lib.lcu_tp_check_split(raw, 1) != 0
+
+
+def test_tensor_parallel_as_the_first_work_of_a_process(lcu):
+    """The CUDA runtime loads a kernel at its first launch, and that loading may wait for the device to go idle.  A
+    tensor-parallel step whose launches stalled there, between a kernel that already waits and the launch it waits for,
+    would run into the bounded waits.  The decoder therefore loads all kernels of a step when it is created; this runs it
+    in a fresh process where nothing has been launched before."""
+    import os
+    import subprocess
+    import sys
+    if lcu.lib.lcu_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    code = ("import sys; sys.path.insert(0, %r); from conftest import load_package; lcu = load_package()\n"
+            "tp = lcu.TensorParallel(2, dim=1024, n_heads=8, n_layers=6, n_vocab=32000, block_size=128, context_len=64, temperature=0.8, seed=3, scale=0.04)\n"
+            "t = tp.next_token([5, 6, 7, 8]); ch, ms = tp.decode_chained(t, 8); print('ok', t, list(ch))\n") % here
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and r.stdout.startswith("ok"), (r.stdout[-500:], r.stderr[-1500:])
