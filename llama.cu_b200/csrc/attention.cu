@@ -30,32 +30,19 @@ __device__ __forceinline__ void st_dsmem_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
-// Tensor-parallel decode: the CTA that wrote a head's output counts itself (device-scope fences: the output is in this
-// GPU's memory); the last one of the launch copies this GPU's whole slice of the attention row into the other GPUs' rows
-// (peer stores), fences at system scope and writes this GPU's flag into the memory of every GPU that waits for the row.
-__device__ __forceinline__ void publish_when_last(const attn_params& p, int tid, int n_threads, int n_ctas) {
-  __shared__ int s_last;
-  __threadfence();
-  __syncthreads();
+// Tensor-parallel decode: the CTA that wrote a head's output (into this GPU's row and, as peer stores, into the other
+// GPUs' rows) counts itself behind a device-scope fence; the last one of the launch fences at system scope - cumulative
+// over everything counted before it - and writes this GPU's flag into the memory of every GPU that waits for the row.
+__device__ __forceinline__ void publish_when_last(const attn_params& p, int tid, int n_ctas) {
+  __syncthreads();  // the storing threads' writes are ordered before thread 0's fence
   if (tid == 0) {
     __threadfence();
-    s_last = atomicAdd(p.done_count, 1) == n_ctas - 1;
-  }
-  __syncthreads();
-  if (!s_last) return;
-  if (tid == 0) atomicExch(p.done_count, 0);
-  __threadfence();
-  const uint4* slice = reinterpret_cast<const uint4*>(p.out);
-  for (int i = tid; i < (p.slice_halves >> 3); i += n_threads) {
-    const uint4 v = __ldcg(slice + i);
-    for (int q = 0; q < p.n_peer_out; ++q) reinterpret_cast<uint4*>(p.peer_out[q])[i] = v;
-  }
-  fence_acq_rel_sys();
-  __syncthreads();
-  if (tid == 0) {
-    fence_acq_rel_sys();
-    const int stamp = *p.seq * p.exchanges_per_step + p.exchange_id;
-    for (int q = 0; q < p.n_peer_flag; ++q) st_relaxed_sys(p.peer_flag[q], stamp);
+    if (atomicAdd(p.done_count, 1) == n_ctas - 1) {
+      atomicExch(p.done_count, 0);
+      fence_acq_rel_sys();
+      const int stamp = *p.seq * p.exchanges_per_step + p.exchange_id;
+      for (int q = 0; q < p.n_peer_flag; ++q) st_relaxed_sys(p.peer_flag[q], stamp);
+    }
   }
 }
 
@@ -225,8 +212,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const attn_params p) 
     const __half o = __float2half(s);
     const size_t at = (size_t)qrow * p.ldo + head * HD + tid;
     p.out[at] = o;
+    for (int q = 0; q < p.n_peer_out; ++q) p.peer_out[q][at] = o;  // tensor-parallel: into every GPU's row (peer stores)
   }
-  if (rank == 0 && p.done_count != nullptr) publish_when_last(p, tid, ATT_THREADS, (int)(gridDim.y * gridDim.z));
+  if (rank == 0 && p.done_count != nullptr) publish_when_last(p, tid, (int)(gridDim.y * gridDim.z));
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -425,8 +413,9 @@ __global__ void __launch_bounds__(AS_THREADS, 3) attn_stream_kernel(const attn_p
     const __half o = __float2half(s);
     const size_t at = (size_t)qrow * p.ldo + head * HD + tid;
     p.out[at] = o;
+    for (int q = 0; q < p.n_peer_out; ++q) p.peer_out[q][at] = o;  // tensor-parallel: into every GPU's row (peer stores)
   }
-  if (rank == 0 && p.done_count != nullptr) publish_when_last(p, tid, ATT_THREADS, (int)(gridDim.y * gridDim.z));
+  if (rank == 0 && p.done_count != nullptr) publish_when_last(p, tid, (int)(gridDim.y * gridDim.z));
 }
 
 template <int HD>

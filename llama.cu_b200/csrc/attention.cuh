@@ -20,9 +20,8 @@ struct attn_params {
   int* err;               // device error word for the bounded waits of the streaming kernel (nullptr: that kernel is not used)
   // ---- tensor-parallel decode (cluster kernels only; all zero on a single GPU): this GPU's heads are a slice of the
   // attention row; the slice is also stored into the other GPUs' rows and then published like a GEMV's (gemv.cuh)
-  __half* peer_out[7];    // the slice out[0 .. slice_halves) (m == 1) is copied here by the last CTA of the launch
+  __half* peer_out[7];
   int n_peer_out;
-  int slice_halves;
   int* peer_flag[8];
   int n_peer_flag;
   int* done_count;        // local counter that finds the last (row, head) of the launch (zero between launches)

@@ -41,9 +41,8 @@ struct gemv_params {
   int* err;  // device error word
   // ---- tensor-parallel decode (m == 1; all zero on a single GPU).  Every GPU streams its own rows of the matrix and
   // owns the matching slice of the output vector; `out` and the peer pointers are pre-offset to that slice.
-  __half* peer_out[7];     // EPI_PLAIN / EPI_SILU: the slice `out[0 .. slice_halves)` is copied into these buffers of other GPUs
-  int n_peer_out;          // (peer stores by the last warp of the launch) before the flags are written
-  int slice_halves;        // elements of this GPU's slice of the output row (a multiple of 8)
+  __half* peer_out[7];     // EPI_PLAIN / EPI_SILU: every result is also stored into these buffers of other GPUs (peer stores)
+  int n_peer_out;
   int* peer_flag[8];       // this GPU's flag word on each GPU that waits for the slice; written once all stores are out
   int n_peer_flag;
   int* done_count;         // local counter that finds the last CTA of the launch (zero between launches)

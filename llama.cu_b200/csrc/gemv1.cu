@@ -529,11 +529,14 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
         const __half2 r2 = __halves2half2(__float2half(a0), __float2half(a1));
         *reinterpret_cast<__half2*>(o) = r2;
         if (p.out_peer) *reinterpret_cast<__half2*>(p.out_peer + vrow) = r2;  // peer store over NVLink
+        for (int q = 0; q < p.n_peer_out; ++q) *reinterpret_cast<__half2*>(p.peer_out[q] + vrow) = r2;  // tensor-parallel: into every GPU's row
       } else {
         const __half a = __float2half(v0), bq = __float2half(v1);  // the matmul's own output rounding
         if (EPI == EPI_SILU) {
           const float val = __half2float(a);  // llama_cu.cu:536-537 on the half-rounded w1 / w3 outputs
-          p.out[pr] = __float2half(val / (1.0f + expf(-val)) * __half2float(bq));
+          const __half gated = __float2half(val / (1.0f + expf(-val)) * __half2float(bq));
+          p.out[pr] = gated;
+          for (int q = 0; q < p.n_peer_out; ++q) p.peer_out[q][pr] = gated;
         } else {
           __half o0 = a, o1 = bq;
           if (mat < 2) {  // llama_cu.cu:381-387, cos/sin from the context's table (fetched above)
@@ -553,33 +556,18 @@ __global__ void __launch_bounds__((NW + 1) * 32, NW == 4 ? 3 : 2) gemv1_kernel(c
       }
     }
   }
-  // tensor-parallel: the last consumer warp of the launch to get here sends this GPU's slice of the output row to the
-  // other GPUs and publishes it.  Finding that warp costs device-scope fences only (results are in this GPU's memory):
-  // warps count inside their CTA (shared memory), the last warp of a CTA counts the CTA (global memory).  The last warp
-  // of the last CTA then copies the whole slice into the other GPUs' rows (peer stores over NVLink, 16 bytes per lane),
-  // and only its lanes pay for a system-scope fence - thousands of warps doing that serialise for more than 10 us -
-  // before lane 0 writes the flags into the waiting GPUs' memory.
-  if (p.done_count != nullptr) {
-    int last = 0;
-    if (lane == 0) {
+  // tensor-parallel: the last consumer warp of the launch to get here publishes this GPU's slice (every result went into
+  // the other GPUs' rows as a peer store in the epilogue above, made by lane 0 of its warp).  The fences widen with the
+  // counting: a warp counts itself inside its CTA behind a CTA-scope fence (shared memory), the last warp of a CTA
+  // counts the CTA behind a device-scope fence (global memory), and only the last warp of the launch pays for the
+  // system-scope fence - cumulative over everything counted before it - ahead of the flags it writes into the waiting
+  // GPUs' memory.  (A system-scope fence in every warp serialises for more than 10 us per launch.)
+  if (p.done_count != nullptr && lane == 0) {
+    __threadfence_block();
+    if (atomicAdd_block(cta_done, 1) == NW - 1) {
       __threadfence();
-      if (atomicAdd(cta_done, 1) == NW - 1) {
-        __threadfence();
-        last = atomicAdd(p.done_count, 1) == (int)gridDim.x - 1;
-      }
-    }
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (last) {
-      if (lane == 0) atomicExch(p.done_count, 0);  // (the next launch counts from zero; its warps arrive after this kernel has ended)
-      __threadfence();
-      const uint4* slice = reinterpret_cast<const uint4*>(p.out);
-      for (int i = lane; i < (p.slice_halves >> 3); i += 32) {
-        const uint4 v = __ldcg(slice + i);
-        for (int q = 0; q < p.n_peer_out; ++q) reinterpret_cast<uint4*>(p.peer_out[q])[i] = v;
-      }
-      fence_acq_rel_sys();
-      __syncwarp();
-      if (lane == 0) {
+      if (atomicAdd(p.done_count, 1) == (int)gridDim.x - 1) {
+        atomicExch(p.done_count, 0);  // (the next launch counts from zero; its warps arrive after this kernel has ended)
         fence_acq_rel_sys();
         const int stamp = *p.seq * TP_EXCHANGES_PER_STEP + p.exchange_id;
         for (int q = 0; q < p.n_peer_flag; ++q) st_relaxed_sys(p.peer_flag[q], stamp);

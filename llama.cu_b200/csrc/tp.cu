@@ -8,11 +8,12 @@
 // element is computed by the same instructions in the same order: tokens and probabilities are bit-identical to the
 // single-GPU run.
 //
-// Exchange, inside the producing kernel: the last warp of a GEMV launch (the last CTA of an attention launch) - found by
-// counting with device-scope fences only - copies this GPU's slice of the output row into the same place of every other
-// GPU's row (plain peer stores over NVLink; no TMA multicast, no library kernel on peer memory), fences at system scope
-// and writes step * 1024 + exchange_id into a flag word in every GPU's memory; the kernel that needs the whole row polls
-// its own GPU's flag words (bounded: ~1 s, then the error word is set and the step ends).
+// Exchange, inside the producing kernel: the GEMV epilogue (and the attention kernel) stores each result into its own
+// row AND into the same place of every other GPU's row (plain peer stores over NVLink; no TMA multicast, no library
+// kernel on peer memory).  The last warp of the launch - found by counting behind fences that widen from CTA to device
+// scope - fences once at system scope and writes step * 1024 + exchange_id into a flag word in every GPU's memory; the
+// kernel that needs the whole row polls its own GPU's flag words (bounded: ~1 s, then the error word is set and the
+// step ends).
 // Per layer: the attention output, x after wo, the gated hidden row after w1|w3, x after w2.
 // The logits slices go to GPU 0, which runs the softmax / argmax head and sends the token back to every GPU.
 // A step is captured once as a CUDA graph spanning all GPUs (fork / join by events on stream 0); inside it the GPUs are
@@ -294,7 +295,6 @@ gemv_params tp_impl::base(int gi, int K) const {
 void tp_impl::exchange(gemv_params& a, int gi, size_t slice_off, __half* tp_gpu::*row, int exchange_id) const {
   a.n_peer_out = 0;
   a.n_peer_flag = 0;
-  a.slice_halves = a.rows_per_mat;  // one output element per row (EPI_PLAIN) or per row pair of w1 | w3 (EPI_SILU)
   if (g_tp_debug & 2) return;
   for (int j = 0; j < n; ++j) {
     if (j != gi && !(g_tp_debug & 4)) a.peer_out[a.n_peer_out++] = g[j].*row + slice_off;
@@ -365,7 +365,6 @@ int tp_impl::enqueue_step(int long_ctx) {
           if (j != gi && !(g_tp_debug & 4)) at.peer_out[at.n_peer_out++] = g[j].att + (size_t)gi * dl;
           at.peer_flag[at.n_peer_flag++] = g[j].state + ST_FLAGS + gi;
         }
-        at.slice_halves = dl;
         if (!(g_tp_debug & 2)) at.done_count = me.state + ST_DONE + 1;
         at.seq = me.state + ST_SEQ;
         at.exchange_id = id0 + 1;
@@ -408,7 +407,6 @@ int tp_impl::enqueue_step(int long_ctx) {
       a.w[0] = m.output.w; a.sc[0] = m.output.sc; a.n_mats = 1; a.rows_per_mat = vl;
       a.x = me.x; a.norm_w = m.norm; a.out = me.logits + (size_t)gi * vl; a.ldo = V;
       a.n_wait = (g_tp_debug & 1) ? 0 : n; a.wait_id = 4 * L;
-      a.slice_halves = vl;
       if (gi != 0) a.peer_out[a.n_peer_out++] = g[0].logits + (size_t)gi * vl;
       a.peer_flag[a.n_peer_flag++] = g[0].state + ST_FLAGS + gi;
       a.done_count = me.state + ST_DONE;
