@@ -163,6 +163,23 @@ int lcu_context_read_probs(void* ctx, uint16_t* probs_host);
 /* residual stream row of the last token before the final norm (diagnostics) */
 int lcu_context_read_hidden(void* ctx, uint16_t* hidden_host);
 int lcu_context_kernels_per_step(void* ctx);
+/* The sampler the reference has commented out (llama_cu.cu:1202-1203: std::discrete_distribution over the fp16
+ * probabilities in place of the argmax), on the device.  mode 0 = greedy (default, what the reference runs), 1 = token i
+ * with probability p_i / sum(p): the cumulative sum (binary32, fixed order) is inverted at u * sum(p), u from a
+ * counter-based generator keyed by (seed, sequence length after the step), so a run repeats for the same seed.
+ * The reference draws from std::random_device and cannot be repeated; no parity of tokens is claimed in mode 1. */
+int lcu_context_set_sampling(void* ctx, int mode, uint64_t seed);
+/* the u of mode 1 for a sequence length (host only), and the same inversion as a stand-alone operator on device probabilities */
+float lcu_sampler_uniform(uint64_t seed, int index);
+int lcu_sample_token(const void* probs_dev, int n_vocab, float u, int* token_host, void* stream);
+/* Context roll-over without a new prompt pass.  The reference's client clears the context when it is full and feeds the
+ * last context_len / 2 tokens again (main.cpp:83-87).  This call keeps the last `keep` cached positions instead: values
+ * move to positions 0 .. keep-1, keys are rotated back by the dropped length (they are cached rotated), and decoding
+ * continues at position `keep`.  The kept rows still carry what they attended to before, so the continuation is not the
+ * one a fresh prompt pass over the kept tokens gives. */
+int lcu_context_rollover(void* ctx, int keep);
+/* the same move on one layer's caches ([n_heads][ctx_len][head_dim], keys rotated): rows [first, first + keep) to [0, keep) */
+int lcu_rollover(void* k_cache_dev, void* v_cache_dev, int n_heads, int ctx_len, int head_dim, int first, int keep, void* stream);
 
 /* ---- tensor-parallel decode (one process, 2 / 4 / 8 GPUs of one box) ---------------------------- */
 /* No counterpart in the reference: its only multi-GPU scheme is the layer pipeline (llama_partition, llama_cu.cu:810-880,

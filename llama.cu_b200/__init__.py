@@ -77,6 +77,11 @@ _SIG = {
     "lcu_context_read_probs": (C.c_int, [vp, vp]),
     "lcu_context_read_hidden": (C.c_int, [vp, vp]),
     "lcu_context_kernels_per_step": (C.c_int, [vp]),
+    "lcu_context_set_sampling": (C.c_int, [vp, C.c_int, C.c_uint64]),
+    "lcu_context_rollover": (C.c_int, [vp, C.c_int]),
+    "lcu_rollover": (C.c_int, [vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
+    "lcu_sampler_uniform": (C.c_float, [C.c_uint64, C.c_int]),
+    "lcu_sample_token": (C.c_int, [vp, C.c_int, C.c_float, C.POINTER(C.c_int), vp]),
     "lcu_tp_check_split": (C.c_int, [vp, C.c_int]),
     "lcu_tp_create": (C.c_int, [vp, vp, C.c_int, C.c_int, C.c_float, C.POINTER(vp)]),
     "lcu_tp_fill_synthetic": (C.c_int, [vp, C.c_uint64, C.c_float]),
@@ -353,6 +358,12 @@ class Context:
 
     def kernels_per_step(self):
         return lib.lcu_context_kernels_per_step(self.handle)
+
+    def set_sampling(self, mode, seed=0):
+        check(lib.lcu_context_set_sampling(self.handle, mode, seed))
+
+    def rollover(self, keep):
+        check(lib.lcu_context_rollover(self.handle, keep))
 
     def bench_kernel(self, which, reps):
         ms, b = C.c_float(0), C.c_uint64(0)

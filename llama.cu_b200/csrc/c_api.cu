@@ -415,6 +415,25 @@ int lcu_context_decode_chained(void* ctx, int16_t first_token, int n_steps, int1
 }
 int lcu_context_read_probs(void* ctx, uint16_t* probs_host) { return ((context*)ctx)->read_probs((__half*)probs_host); }
 int lcu_context_read_hidden(void* ctx, uint16_t* hidden_host) { return ((context*)ctx)->read_hidden((__half*)hidden_host); }
+int lcu_context_set_sampling(void* ctx, int mode, uint64_t seed) { return ((context*)ctx)->set_sampling(mode, seed); }
+int lcu_context_rollover(void* ctx, int keep) { return ((context*)ctx)->rollover(keep); }
+float lcu_sampler_uniform(uint64_t seed, int index) { return sampler_uniform(seed, index); }
+int lcu_sample_token(const void* probs_dev, int n_vocab, float u, int* token_host, void* stream) {
+  NEED_DEVICE();
+  int* d_tok = scratch_err();
+  LCU_REQUIRE(d_tok != nullptr && token_host != nullptr, "sample_token: no scratch");
+  LCU_REQUIRE(u >= 0.f && u < 1.f, "sample_token: u = %f outside [0, 1)", u);
+  int rc = launch_sample((const __half*)probs_dev, n_vocab, 0, nullptr, u, d_tok + 9, nullptr, nullptr, nullptr, 0, (cudaStream_t)stream);
+  if (rc) return rc;
+  LCU_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  LCU_CUDA(cudaMemcpy(token_host, d_tok + 9, 4, cudaMemcpyDeviceToHost));
+  return LCU_OK;
+}
+int lcu_rollover(void* k_cache_dev, void* v_cache_dev, int n_heads, int ctx_len, int head_dim, int first, int keep, void* stream) {
+  NEED_DEVICE();
+  LCU_REQUIRE(n_heads >= 1 && head_dim >= 2 && head_dim % 2 == 0, "rollover: bad head shape");
+  return launch_rollover((__half*)k_cache_dev, (__half*)v_cache_dev, n_heads, ctx_len, head_dim, first, keep, 10000.0f, (cudaStream_t)stream);
+}
 int lcu_context_kernels_per_step(void* ctx) { return ((context*)ctx)->kernels_per_step(); }
 
 // ---- tensor-parallel decode

@@ -3,6 +3,8 @@
 // functions) of the reference kernel it replaces, cited beside it.
 #include "ops.cuh"
 
+#include <algorithm>
+
 #include <math_constants.h>
 
 namespace lcu {
@@ -622,6 +624,100 @@ int launch_synth_fill(__half* out, size_t n, uint64_t seed, uint64_t stream_id, 
   return LCU_OK;
 }
 
+// ------------------------------------------------------------------ sampler
+// The reference's next_token ends in `std::discrete_distribution<short> dist(probs.begin(), probs.end()); return dist(rng_);`
+// - commented out in favour of the argmax (llama_cu.cu:1202-1209).  Same distribution here, on the device: token i
+// with probability float(p_i) / sum_j float(p_j) over the fp16 probabilities, chosen by inverting the cumulative sum at
+// u * total.  Every sum is binary32 in a fixed order (32-element chunks in index order, then the chunk sums in index
+// order), so a host restatement gives the same token for the same u.
+__device__ __host__ inline float sampler_uniform_from(uint32_t word) { return (float)(word >> 8) * 0x1p-24f; }  // [0, 1)
+
+__global__ void __launch_bounds__(1024) sample_kernel(const __half* probs, int n, uint64_t seed, const int* index_ptr, float u_given, int* token_out,
+                                                      short* next_ids, short* log, const int* step, int log_capacity) {
+  __shared__ float chunk[1024];
+  __shared__ int s_pick;
+  __shared__ float s_before, s_target;
+  const int tid = threadIdx.x;
+  const int per = (n + 1023) / 1024;  // elements per chunk
+  const int lo = tid * per, hi = min(n, lo + per);
+  float s = 0.f;
+  for (int i = lo; i < hi; ++i) s += __half2float(probs[i]);
+  chunk[tid] = s;
+  __syncthreads();
+  if (tid == 0) {
+    float u = u_given;
+    if (index_ptr != nullptr) {  // counter-based: one Philox block per (seed, index)
+      uint32_t c[4] = {(uint32_t)*index_ptr, 0u, 0x73616d70u, 0x6c657221u};
+      philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+      u = sampler_uniform_from(c[0]);
+    }
+    float total = 0.f;
+    for (int c = 0; c < 1024; ++c) total += chunk[c];
+    const float target = u * total;
+    float run = 0.f;
+    int pick = -1;
+    for (int c = 0; c < 1024; ++c) {
+      if (run + chunk[c] > target) {
+        pick = c;
+        break;
+      }
+      run += chunk[c];
+    }
+    s_pick = pick;
+    s_before = run;
+    s_target = target;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int token = -1;
+    if (s_pick >= 0) {
+      float run = s_before;
+      const int c_lo = s_pick * per, c_hi = min(n, c_lo + per);
+      for (int i = c_lo; i < c_hi; ++i) {
+        const float w = __half2float(probs[i]);
+        run += w;
+        if (run > s_target && w > 0.f) {
+          token = i;
+          break;
+        }
+      }
+    }
+    if (token < 0)  // rounding left the target at or past the total: the last token with a non-zero probability
+      for (int i = n - 1; i >= 0; --i)
+        if (__half2float(probs[i]) > 0.f) {
+          token = i;
+          break;
+        }
+    if (token < 0) token = 0;
+    if (token_out) *token_out = token;
+    if (next_ids) next_ids[0] = (short)token;
+    if (log && step && *step >= 1 && *step - 1 < log_capacity) log[*step - 1] = (short)token;  // over the head's argmax entry
+  }
+}
+
+// block rotation of cached keys for a context roll-over: key rows [first, first + keep) of every head move to positions
+// [0, keep), each pair (2i, 2i+1) rotated back by `first` positions (the angle of llama_cu.cu:375-388 with pos = -first),
+// value rows move unchanged.  One CTA per (destination position, head); in-place is safe row by row in ascending order
+// only when first > 0, so the kernel reads from the source row into registers before any thread writes the destination
+// row of another CTA is touched: rows are disjoint per CTA and destination < source.
+__global__ void rollover_kernel(__half* k_cache, __half* v_cache, int ctx_len, int head_dim, int first, float theta) {
+  const int dst = blockIdx.x, head = blockIdx.y, src = dst + first;
+  __half* kd = k_cache + ((size_t)head * ctx_len + dst) * head_dim;
+  const __half* ks = k_cache + ((size_t)head * ctx_len + src) * head_dim;
+  __half* vd = v_cache + ((size_t)head * ctx_len + dst) * head_dim;
+  const __half* vs = v_cache + ((size_t)head * ctx_len + src) * head_dim;
+  for (int i = threadIdx.x; i < head_dim / 2; i += blockDim.x) {
+    const float re = __half2float(ks[2 * i]), im = __half2float(ks[2 * i + 1]);
+    const float angle = -(float)first / powf(theta, float(2 * i) / head_dim);
+    const float c = cosf(angle), sn = sinf(angle);
+    const __half v0 = vs[2 * i], v1 = vs[2 * i + 1];
+    kd[2 * i] = __float2half(re * c - im * sn);
+    kd[2 * i + 1] = __float2half(re * sn + im * c);
+    vd[2 * i] = v0;
+    vd[2 * i + 1] = v1;
+  }
+}
+
 // loads the small kernels of a decode step on the current device ahead of their first launch
 int ops_preload() {
   cudaFuncAttributes fa;
@@ -629,6 +725,41 @@ int ops_preload() {
   LCU_CUDA(cudaFuncGetAttributes(&fa, bump_pos_kernel));
   LCU_CUDA(cudaFuncGetAttributes(&fa, token_to_ids_kernel));
   LCU_CUDA(cudaFuncGetAttributes(&fa, logits_head_kernel));
+  return LCU_OK;
+}
+
+int launch_sample(const __half* probs, int n_vocab, uint64_t seed, const int* index, float u, int* token_out, short* next_ids, short* log,
+                  const int* step, int log_capacity, cudaStream_t stream) {
+  LCU_REQUIRE(n_vocab >= 1 && probs != nullptr, "sample: empty distribution");
+  sample_kernel<<<1, 1024, 0, stream>>>(probs, n_vocab, seed, index, u, token_out, next_ids, log, step, log_capacity);
+  LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+float sampler_uniform(uint64_t seed, int index) {
+  uint32_t c[4] = {(uint32_t)index, 0u, 0x73616d70u, 0x6c657221u};
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; ++r) {  // Philox4x32-10, as philox4x32_10 on the device
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1;
+    c[0] = n0; c[1] = (uint32_t)p1; c[2] = n2; c[3] = (uint32_t)p0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return sampler_uniform_from(c[0]);
+}
+
+// Rows are processed in ascending destination order by independent CTAs; a CTA's source row (dst + first) may be the
+// destination row of a later CTA, so the move runs in waves of `first` rows: wave w moves rows [w*first, (w+1)*first),
+// whose sources [(w+1)*first, (w+2)*first) no earlier wave has written.
+int launch_rollover(__half* k_cache, __half* v_cache, int n_heads, int ctx_len, int head_dim, int first, int keep, float theta, cudaStream_t stream) {
+  LCU_REQUIRE(first >= 1 && keep >= 1 && first + keep <= ctx_len, "rollover: rows %d..%d outside the context length %d", first, first + keep, ctx_len);
+  for (int done = 0; done < keep; done += first) {
+    const int rows = std::min(first, keep - done);
+    const size_t off = (size_t)done * head_dim;  // shifts both source and destination by `done` rows
+    rollover_kernel<<<dim3(rows, n_heads), 64, 0, stream>>>(k_cache + off, v_cache + off, ctx_len, head_dim, first, theta);
+  }
+  LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }
 

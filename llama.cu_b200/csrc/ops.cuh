@@ -55,6 +55,17 @@ int launch_logits_head(const head_params& p, cudaStream_t stream, int pdl);
 // one-block version of the same computation (any vocabulary size; used when the clustered kernel does not fit)
 int launch_logits_head_single(const head_params& p, cudaStream_t stream, int pdl);
 
+// Multinomial sampling over fp16 probabilities (the reference's commented-out discrete_distribution, llama_cu.cu:1202-1203):
+// token i with probability p_i / sum(p), by inverting the cumulative sum at u * sum(p).  u comes from a counter-based
+// generator (seed, *index) when index != nullptr, else from the argument.  Writes token_out / next_ids[0] and replaces
+// the entry the logits head appended to the token log.
+int launch_sample(const __half* probs, int n_vocab, uint64_t seed, const int* index, float u, int* token_out, short* next_ids, short* log,
+                  const int* step, int log_capacity, cudaStream_t stream);
+float sampler_uniform(uint64_t seed, int index);  // the u of launch_sample for (seed, index), on the host
+// Context roll-over without a new prompt pass: cached rows [first, first + keep) of every head of one layer move to
+// [0, keep); keys are rotated back by `first` positions, values move as they are.
+int launch_rollover(__half* k_cache, __half* v_cache, int n_heads, int ctx_len, int head_dim, int first, int keep, float theta, cudaStream_t stream);
+
 // block-absmax quantizer, bit-identical to the reference's (transform.cu:28-72)
 int launch_quantize_absmax_uint8(uint8_t* q, __half* scales, const __half* in, size_t h, size_t w, int bs, cudaStream_t stream);
 int launch_dequantize_absmax_uint8(__half* out, const __half* scales, const uint8_t* q, size_t h, size_t w, int bs,

@@ -41,6 +41,12 @@ void set_last_error(const char* fmt, ...) {
 }
 const char* last_error() { return g_err; }
 
+#define LCU_TRY(expr)      \
+  do {                     \
+    int _rc = (expr);      \
+    if (_rc) return _rc;   \
+  } while (0)
+
 // 64 zeroed device words per GPU for the stand-alone operator entry points (word 0: error word of their kernels;
 // word 8: token of lcu_logits_head); allocated at the first use on a device
 int* device_scratch_words() {
@@ -667,7 +673,40 @@ size_t context::memory_usage() const {
 }
 int context::tokens_left() const { return impl->opt.context_len - impl->start_pos; }
 int context::position() const { return impl->start_pos; }
-int context::kernels_per_step() const { return 1 + 5 * (int)impl->m->params.n_layers + 2; }
+int context::kernels_per_step() const { return 1 + 5 * (int)impl->m->params.n_layers + 2 + (impl->opt.sampling ? 1 : 0); }
+
+int context::set_sampling(int mode, uint64_t seed) {
+  LCU_REQUIRE(mode == 0 || mode == 1, "set_sampling: mode %d (0 = greedy, 1 = multinomial)", mode);
+  context_impl& c = *impl;
+  c.opt.sampling = mode;
+  c.opt.sample_seed = seed;
+  for (int v = 0; v < 2; ++v)  // the captured steps hold the old choice
+    if (c.graph[v]) {
+      device_guard dg(c.first().device);
+      LCU_CUDA(cudaStreamSynchronize(c.first().stream));
+      cudaGraphExecDestroy(c.graph[v]);
+      c.graph[v] = nullptr;
+    }
+  return LCU_OK;
+}
+
+int context::rollover(int keep) {
+  context_impl& c = *impl;
+  LCU_REQUIRE(keep >= 1 && keep < c.start_pos, "rollover: keep %d of %d cached positions", keep, c.start_pos);
+  const model_params& p = c.m->params;
+  const int first = c.start_pos - keep;
+  for (uint32_t l = 0; l < p.n_layers; ++l) {
+    gpu_state& g = c.gpus[c.layer_slot[l]];
+    device_guard dg(g.device);
+    LCU_TRY(launch_rollover(c.k_cache[l], c.v_cache[l], p.n_heads, c.opt.context_len, p.dim / p.n_heads, first, keep, 10000.0f, g.stream));
+  }
+  for (auto& g : c.gpus) {
+    device_guard dg(g.device);
+    LCU_CUDA(cudaStreamSynchronize(g.stream));
+  }
+  c.start_pos = keep;
+  return LCU_OK;
+}
 
 // Error words of all stages (every stage's kernels report into their own GPU's word).  A word that is set is
 // cleared here, so that one expired wait is reported once and the context stays usable.
@@ -716,11 +755,6 @@ int context_impl::enqueue_hop(int from, int to, int m_rows) {
   return LCU_OK;
 }
 
-#define LCU_TRY(expr)      \
-  do {                     \
-    int _rc = (expr);      \
-    if (_rc) return _rc;   \
-  } while (0)
 
 // ---- kernel arguments of the decode step
 gemv_params context_impl::params_base(gpu_state& g, int K) {
@@ -844,6 +878,8 @@ int context_impl::enqueue_decode_step(int long_ctx) {
     h.token_out = g.state + 2; h.next_ids = gpus.size() == 1 ? ids : nullptr;
     h.pos = g.state; h.advance = 1; h.log = log; h.step = g.state + 1; h.log_capacity = opt.context_len;
     LCU_TRY(launch_logits_head(h, g.stream, pdl));
+    if (opt.sampling)  // the reference's discrete_distribution over the probabilities (llama_cu.cu:1202-1203) instead of the argmax
+      LCU_TRY(launch_sample(probs, p.n_vocab, opt.sample_seed, g.state, 0.f, g.state + 2, h.next_ids, log, g.state + 1, opt.context_len, g.stream));
     if (gpus.size() > 1) {
       // multi-GPU: the token returns to stage 0 (the other stages advanced their position word on the way)
       LCU_TRY(launch_token_to_ids(ids, g.state + 2, g.stream));  // peer store into stage 0's id buffer
@@ -950,6 +986,7 @@ int context_impl::enqueue_prefill(int m_rows) {
     h.token_out = g.state + 2; h.next_ids = nullptr;
     h.pos = g.state; h.advance = m_rows; h.log = nullptr; h.step = nullptr; h.log_capacity = 0;
     LCU_TRY(launch_logits_head(h, g.stream, 0));
+    if (opt.sampling) LCU_TRY(launch_sample(probs, p.n_vocab, opt.sample_seed, g.state, 0.f, g.state + 2, nullptr, nullptr, nullptr, 0, g.stream));
     if (gpus.size() > 1) {
       LCU_CUDA(cudaEventRecord(g.ev, g.stream));
       LCU_CUDA(cudaStreamWaitEvent(first().stream, g.ev, 0));

@@ -122,6 +122,8 @@ struct context_options {
   int use_graph = 1;     // replay one CUDA graph per decode step
   int use_pdl = 1;       // programmatic dependent launch between the kernels of a step
   int attn_cluster = 8;  // CTAs per (row, head) in decode attention
+  int sampling = 0;      // 0 = greedy (first maximum, what the reference runs); 1 = multinomial over the fp16 probabilities
+  uint64_t sample_seed = 0;
 };
 
 struct context_impl;  // defined in runtime.cu
@@ -145,6 +147,11 @@ struct context {
   // times one decode kernel class over all layers in rotation (see lcu_bench_decode_kernel)
   int bench_kernel(int which, int reps, float* ms_per_launch, uint64_t* bytes_per_launch);
   int device_error();                  // non-zero if a kernel gave up on a bounded wait
+  // 0 = greedy, 1 = multinomial sampling with a counter-based generator keyed by (seed, sequence length)
+  int set_sampling(int mode, uint64_t seed);
+  // Context roll-over without a new prompt pass: keeps the last `keep` cached positions (keys rotated back to
+  // positions 0 .. keep-1, values moved) and continues at position `keep`.
+  int rollover(int keep);
   std::unique_ptr<context_impl> impl;
 };
 

@@ -809,6 +809,49 @@ void orc_get_last_hidden(void* c, uint16_t* out) {
 }
 // wall seconds of the last orc_next_token call: which 0 = all layers, 1 = final norm + logits + softmax
 double orc_last_timing(void* c, int which) { return which == 0 ? ((context_t*)c)->t_layers : ((context_t*)c)->t_head; }
+// Multinomial sampling over fp16 probabilities: the distribution of the reference's commented-out
+// `std::discrete_distribution<short> dist(probs.begin(), probs.end())` (llama_cu.cu:1202-1203), token i with probability
+// p_i / sum(p), restated as the inversion of the cumulative sum at u * sum(p) with binary32 sums in a fixed order:
+// chunks of ceil(n / 1024) elements summed in index order, the chunk sums added in index order, then a running sum
+// inside the chunk that crosses the target.  Falls back to the last token with a non-zero probability.
+int orc_sample_token(const uint16_t* probs, int n, float u) {
+  init_tables();
+  const int per = (n + 1023) / 1024;
+  std::vector<float> chunk(1024, 0.f);
+  for (int c = 0; c < 1024; ++c) {
+    float s = 0.f;
+    for (int i = c * per; i < std::min(n, (c + 1) * per); ++i) s += h2f(probs[i]);
+    chunk[c] = s;
+  }
+  float total = 0.f;
+  for (int c = 0; c < 1024; ++c) total += chunk[c];
+  const float target = u * total;
+  float run = 0.f;
+  int pick = -1;
+  for (int c = 0; c < 1024; ++c) {
+    if (run + chunk[c] > target) {
+      pick = c;
+      break;
+    }
+    run += chunk[c];
+  }
+  if (pick >= 0)
+    for (int i = pick * per; i < std::min(n, (pick + 1) * per); ++i) {
+      const float w = h2f(probs[i]);
+      run += w;
+      if (run > target && w > 0.f) return i;
+    }
+  for (int i = n - 1; i >= 0; --i)
+    if (h2f(probs[i]) > 0.f) return i;
+  return 0;
+}
+// u in [0, 1) for (seed, index): word 0 of the Philox4x32-10 block with counter (index, 0, "samp", "ler!"), top 24 bits
+float orc_sampler_uniform(uint64_t seed, int index) {
+  uint32_t c[4] = {(uint32_t)index, 0u, 0x73616d70u, 0x6c657221u};
+  philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+  return (float)(c[0] >> 8) * 0x1p-24f;
+}
+
 // number of OpenMP threads used by the calls that follow (1 = the scalar single-thread evaluation); returns the previous value
 int orc_set_num_threads(int n) {
 #ifdef _OPENMP

@@ -56,6 +56,8 @@ def lib():
         "orc_get_probs": (None, [C.c_void_p, u16p]),
         "orc_get_logits": (None, [C.c_void_p, u16p]),
         "orc_get_last_hidden": (None, [C.c_void_p, u16p]),
+        "orc_sample_token": (C.c_int, [u16p, C.c_int, C.c_float]),
+        "orc_sampler_uniform": (C.c_float, [C.c_uint64, C.c_int]),
         "orc_num_threads": (C.c_int, []),
         "orc_set_num_threads": (C.c_int, [C.c_int]),
         "orc_last_timing": (C.c_double, [C.c_void_p, C.c_int]),
