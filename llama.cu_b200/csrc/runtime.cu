@@ -461,7 +461,7 @@ namespace {
 // Offsets of everything a context keeps in its per-GPU scratch arena.  One function sizes the arena for
 // context::create, for the memory-based partitioner and for llama_params::shared_context_memory_size.
 struct scratch_layout {
-  size_t o_x, o_norm, o_q, o_kn, o_vn, o_att, o_h1, o_h3, o_hs, o_deq, o_scores, o_rope, o_state, o_ids, o_log, o_logits, o_probs;
+  size_t o_x, o_norm, o_q, o_kn, o_vn, o_att, o_h1, o_h3, o_hs, o_deq, o_deq2, o_scores, o_rope, o_state, o_ids, o_log, o_logits, o_probs;
   size_t deq_halves, score_halves, total;
 };
 scratch_layout scratch_layout_of(const model_params& p, uint32_t ffn, int context_len) {
@@ -471,8 +471,11 @@ scratch_layout scratch_layout_of(const model_params& p, uint32_t ffn, int contex
   s.o_x = cv.take(ctxl * d * 2); s.o_norm = cv.take(ctxl * d * 2); s.o_q = cv.take(ctxl * d * 2);
   s.o_kn = cv.take(ctxl * d * 2); s.o_vn = cv.take(ctxl * d * 2); s.o_att = cv.take(ctxl * d * 2);
   s.o_h1 = cv.take(ctxl * f * 2); s.o_h3 = cv.take(ctxl * f * 2); s.o_hs = cv.take(ctxl * f * 2);
-  s.deq_halves = p.q_type ? std::max((size_t)2 * f * d, (size_t)3 * d * d) : 0;  // room for the stacked w1|w3 or wq|wk|wv
+  // u8 models: two buffers, each with room for the stacked w1|w3 or wq|wk|wv expanded to fp16 (one feeds the prompt GEMM
+  // in flight while the next matrix is expanded into the other)
+  s.deq_halves = p.q_type ? std::max((size_t)2 * f * d, (size_t)3 * d * d) : 0;
   s.o_deq = cv.take(s.deq_halves * 2);
+  s.o_deq2 = cv.take(s.deq_halves * 2);
   // score buffer of the tcgen05 prompt attention (contexts up to 4096 positions; longer ones use the fused kernel)
   s.score_halves = context_len <= 4096 ? attention_tc_scratch_halves(p.n_heads, context_len, context_len) : 0;
   s.o_scores = cv.take(s.score_halves * 2);
@@ -499,6 +502,11 @@ struct gpu_state {
   __half* scores = nullptr;  // prompt attention on tcgen05: [heads][context_len][round_up(context_len, 128)] scores / probabilities
   __half* deq = nullptr;  // u8 models: the dequantized matrix (or stack of matrices) of the prompt GEMM in flight
   size_t deq_halves = 0;
+  // prompt path of u8 models: matrices are expanded to fp16 one job ahead on a side stream, into two alternating buffers
+  __half* deq_buf[2] = {nullptr, nullptr};
+  cudaStream_t side = nullptr;
+  cudaEvent_t deq_done[2] = {nullptr, nullptr}, gemm_done[2] = {nullptr, nullptr};
+  long deq_issued = 0, deq_used = 0;  // jobs expanded / consumed so far (job j lives in buffer j % 2)
   float2* rope = nullptr;
   int* state = nullptr;  // [0] position, [1] step counter, [2] last token, [3] error word
 };
@@ -553,6 +561,11 @@ context::~context() {
     cudaDeviceSynchronize();
     if (c.gpus[i].arena) cudaFree(c.gpus[i].arena);
     if (i < c.kv_arenas.size() && c.kv_arenas[i]) cudaFree(c.kv_arenas[i]);
+    if (c.gpus[i].side) cudaStreamDestroy(c.gpus[i].side);
+    for (int e = 0; e < 2; ++e) {
+      if (c.gpus[i].deq_done[e]) cudaEventDestroy(c.gpus[i].deq_done[e]);
+      if (c.gpus[i].gemm_done[e]) cudaEventDestroy(c.gpus[i].gemm_done[e]);
+    }
     if (c.gpus[i].stream) cudaStreamDestroy(c.gpus[i].stream);
     if (c.gpus[i].ev) cudaEventDestroy(c.gpus[i].ev);
   }
@@ -626,6 +639,15 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     g.scores = score_halves ? (__half*)(b + o_scores) : nullptr;
     g.deq = deq_halves ? (__half*)(b + o_deq) : nullptr;
     g.deq_halves = deq_halves;
+    if (deq_halves) {
+      g.deq_buf[0] = g.deq;
+      g.deq_buf[1] = (__half*)(b + sl.o_deq2);
+      LCU_CUDA(cudaStreamCreateWithFlags(&g.side, cudaStreamNonBlocking));
+      for (int i = 0; i < 2; ++i) {
+        LCU_CUDA(cudaEventCreateWithFlags(&g.deq_done[i], cudaEventDisableTiming));
+        LCU_CUDA(cudaEventCreateWithFlags(&g.gemm_done[i], cudaEventDisableTiming));
+      }
+    }
     g.rope = (float2*)(b + o_rope);
     g.state = (int*)(b + o_state);
     if (gi == 0) c.ids = (short*)(b + o_ids);
@@ -893,6 +915,44 @@ int context_impl::enqueue_decode_step(int long_ctx) {
 int context_impl::enqueue_prefill(int m_rows) {
   const model_params& p = m->params;
   const int d = p.dim, hd = d / p.n_heads, f = m->ffn, bs = p.q_type ? p.quantization_block_size : 0;
+  // u8 weights, prompts long enough for the tcgen05 GEMM: every matrix (or stack of matrices) is expanded to fp16 - the
+  // exact values the reference's tile kernel builds in shared memory, llama_cu.cu:287-289 - on a side stream, one GEMM
+  // ahead, into two alternating buffers: the expansion streams from HBM while the GEMM before it keeps the tensor
+  // cores busy, instead of the two taking turns.  Job j of a GPU lives in buffer j % 2.
+  for (auto& g : gpus) g.deq_issued = g.deq_used = 0;
+  auto expand = [&](gpu_state& g, const dev_matrix* const* mats, int n_mats) -> int {
+    const int b = (int)(g.deq_issued % 2);
+    if (g.deq_issued >= 2) LCU_CUDA(cudaStreamWaitEvent(g.side, g.gemm_done[b], 0));  // the GEMM that read this buffer last
+    size_t off = 0;
+    for (int i = 0; i < n_mats; ++i) {
+      LCU_TRY(launch_dequantize_absmax_uint8(g.deq_buf[b] + off, mats[i]->sc, (const uint8_t*)mats[i]->w, mats[i]->rows, mats[i]->cols, bs, g.side));
+      off += mats[i]->rows * mats[i]->cols;
+    }
+    LCU_CUDA(cudaEventRecord(g.deq_done[b], g.side));
+    ++g.deq_issued;
+    return LCU_OK;
+  };
+  // job k of layer l: 0 = wq|wk|wv, 1 = wo, 2 = w1|w3, 3 = w2
+  auto expand_job = [&](gpu_state& g, uint32_t l, int k) -> int {
+    const layer_weights& W = m->layers[l];
+    const dev_matrix* qkv[3] = {&W.wq, &W.wk, &W.wv};
+    const dev_matrix* w13[2] = {&W.w1, &W.w3};
+    const dev_matrix* one[1] = {k == 1 ? &W.wo : &W.w2};
+    return k == 0 ? expand(g, qkv, 3) : k == 2 ? expand(g, w13, 2) : expand(g, one, 1);
+  };
+  // the GEMM of the oldest expanded job: waits for its expansion, runs, releases the buffer
+  auto gemm_expanded = [&](gpu_state& g, __half* out, const __half* lhs, size_t rows, size_t cols, float beta) -> int {
+    const int b = (int)(g.deq_used % 2);
+    LCU_CUDA(cudaStreamWaitEvent(g.stream, g.deq_done[b], 0));
+    dev_matrix w;
+    w.w = g.deq_buf[b];
+    w.rows = rows;
+    w.cols = cols;
+    LCU_TRY(matmul_rows(out, lhs, w, m_rows, beta, g.state + 3, g.stream));
+    LCU_CUDA(cudaEventRecord(g.gemm_done[b], g.stream));
+    ++g.deq_used;
+    return LCU_OK;
+  };
   {
     gpu_state& g = first();
     device_guard dg(g.device);
@@ -922,14 +982,12 @@ int context_impl::enqueue_prefill(int m_rows) {
       dev_matrix wqkv = L.wq;
       wqkv.rows = 3 * (size_t)d;
       if (fuse_u8) {
-        const dev_matrix* src[3] = {&L.wq, &L.wk, &L.wv};
-        for (int i = 0; i < 3; ++i)
-          LCU_TRY(launch_dequantize_absmax_uint8(g.deq + (size_t)i * d * d, src[i]->sc, (const uint8_t*)src[i]->w, d, d, bs, g.stream));
-        wqkv.w = g.deq;
-        wqkv.sc = nullptr;
-        wqkv.bs = 0;
+        if (g.deq_issued == g.deq_used) LCU_TRY(expand_job(g, l, 0));  // first layer of this GPU in this prompt: nothing was expanded ahead
+        LCU_TRY(gemm_expanded(g, g.q, g.norm, 3 * (size_t)d, d, 0.f));
+        LCU_TRY(expand_job(g, l, 1));
+      } else {
+        LCU_TRY(matmul_rows(g.q, g.norm, wqkv, m_rows, 0.f, err, g.stream));
       }
-      LCU_TRY(matmul_rows(g.q, g.norm, wqkv, m_rows, 0.f, err, g.stream));
       LCU_TRY(launch_rope_scatter(g.q, g.q + d, g.q + 2 * d, k_cache[l], v_cache[l], g.rope, g.state, 0, m_rows, d, p.n_heads, opt.context_len,
                                   g.stream, ldq));
     } else {
@@ -950,26 +1008,34 @@ int context_impl::enqueue_prefill(int m_rows) {
       LCU_TRY(launch_attention_prefill(at, m_rows, start_pos + m_rows, g.stream));
     else
       LCU_TRY(launch_attention(at, m_rows, 1, start_pos + m_rows, g.stream, 0));
-    LCU_TRY(matmul_rows(g.x, g.att, L.wo, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
+    if (fuse_u8) {
+      LCU_TRY(gemm_expanded(g, g.x, g.att, d, d, 1.0f));
+      LCU_TRY(expand_job(g, l, 2));
+    } else {
+      LCU_TRY(matmul_rows(g.x, g.att, L.wo, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
+    }
     LCU_TRY(launch_rms_norm(g.norm, g.x, L.ffn_norm, m_rows, d, p.norm_eps, g.stream));
     if (fuse_u8 || (fuse && (char*)L.w3.w == (char*)L.w1.w + (size_t)f * d * 2)) {
       dev_matrix w13 = L.w1;
       w13.rows = 2 * (size_t)f;
       if (fuse_u8) {
-        LCU_TRY(launch_dequantize_absmax_uint8(g.deq, L.w1.sc, (const uint8_t*)L.w1.w, f, d, bs, g.stream));
-        LCU_TRY(launch_dequantize_absmax_uint8(g.deq + (size_t)f * d, L.w3.sc, (const uint8_t*)L.w3.w, f, d, bs, g.stream));
-        w13.w = g.deq;
-        w13.sc = nullptr;
-        w13.bs = 0;
+        LCU_TRY(gemm_expanded(g, g.h1, g.norm, 2 * (size_t)f, d, 0.f));
+        LCU_TRY(expand_job(g, l, 3));
+      } else {
+        LCU_TRY(matmul_rows(g.h1, g.norm, w13, m_rows, 0.f, err, g.stream));
       }
-      LCU_TRY(matmul_rows(g.h1, g.norm, w13, m_rows, 0.f, err, g.stream));
       LCU_TRY(launch_silu_rows(g.hs, g.h1, m_rows, f, g.stream));
     } else {
       LCU_TRY(matmul_rows(g.h1, g.norm, L.w1, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
       LCU_TRY(matmul_rows(g.h3, g.norm, L.w3, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
       LCU_TRY(launch_silu(g.hs, g.h1, g.h3, (size_t)m_rows * f, g.stream));
     }
-    LCU_TRY(matmul_rows(g.x, g.hs, L.w2, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
+    if (fuse_u8) {
+      LCU_TRY(gemm_expanded(g, g.x, g.hs, d, f, 1.0f));
+      if (l + 1 < p.n_layers && layer_slot[l + 1] == gi) LCU_TRY(expand_job(g, l + 1, 0));  // the next layer's first job, while this GEMM runs
+    } else {
+      LCU_TRY(matmul_rows(g.x, g.hs, L.w2, m_rows, 1.0f, err, g.stream, g.deq, g.deq_halves));
+    }
   }
   {
     gpu_state& g = last();

@@ -100,7 +100,7 @@ def test_context_scratch_figure_counts_every_buffer(name, dim, heads, layers, bs
     got = lcu.lib.lcu_context_scratch_bytes(raw, ctx)
     activations = 6 * ctx * dim * 2 + 3 * ctx * ffn * 2
     scores = heads * ctx * ((ctx + 127) // 128 * 128) * 2
-    deq = max(2 * ffn * dim, 3 * dim * dim) * 2 if bs else 0
+    deq = 2 * max(2 * ffn * dim, 3 * dim * dim) * 2 if bs else 0  # two buffers: one feeds the GEMM in flight, the next matrix expands into the other
     tables = ctx * (dim // heads // 2) * 8 + 2 * 32000 * 2 + 2 * ctx * 2
     assert activations + scores + deq + tables <= got <= activations + scores + deq + tables + 64 * 256, name
     assert lcu.lib.lcu_context_kv_bytes_per_layer(raw, ctx) == 2 * ctx * dim * 2
