@@ -254,36 +254,46 @@ __global__ void __launch_bounds__(256) quantize_kernel(uint8_t* q, __half* scale
 // its eight bytes at once.  Block sizes 32 .. 256 (4 .. 32 lanes per block); n_vec = elements / 8.
 template <int LANES>
 __global__ void __launch_bounds__(256) quantize8_kernel(uint8_t* q, __half* scales, const __half* in, size_t n_vec) {
+  constexpr int UNROLL = 2;  // vectors per thread whose loads are in flight together
   const size_t stride = (size_t)gridDim.x * 256;
   const size_t n_round = (n_vec + 31) / 32 * 32;  // whole warps take part in the shuffles
-  for (size_t v = (size_t)blockIdx.x * 256 + threadIdx.x; v < n_round; v += stride) {
-    const bool valid = v < n_vec;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (valid) raw = *reinterpret_cast<const uint4*>(in + v * 8);
-    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-    float f[8];
+  for (size_t v0 = (size_t)blockIdx.x * 256 + threadIdx.x; v0 < n_round; v0 += UNROLL * stride) {
+    uint4 raw[UNROLL];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 p = __half22float2(h2[e]);
-      f[2 * e] = p.x;
-      f[2 * e + 1] = p.y;
+    for (int r = 0; r < UNROLL; ++r) {
+      const size_t v = v0 + r * stride;
+      raw[r] = v < n_vec ? *reinterpret_cast<const uint4*>(in + v * 8) : make_uint4(0, 0, 0, 0);
     }
-    float absmax_val = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) absmax_val = fmaxf(absmax_val, fabsf(f[e]));
+    for (int r = 0; r < UNROLL; ++r) {
+      const size_t v = v0 + r * stride;
+      if (v >= n_round) break;  // (warp-uniform: v and n_round are multiples of 32 apart from the lane)
+      const bool valid = v < n_vec;
+      const __half2* h2 = reinterpret_cast<const __half2*>(&raw[r]);
+      float f[8];
 #pragma unroll
-    for (int o = LANES / 2; o > 0; o >>= 1) absmax_val = fmaxf(absmax_val, __shfl_xor_sync(0xffffffffu, absmax_val, o));
-    const __half s_absmax = __float2half(absmax_val / 127.5f);
-    const float sf = __half2float(s_absmax);
-    if (!valid) continue;
-    if ((v & (LANES - 1)) == 0) scales[v / LANES] = s_absmax;
-    uint32_t lo = 0, hi = 0;
+      for (int e = 0; e < 4; ++e) {
+        const float2 p = __half22float2(h2[e]);
+        f[2 * e] = p.x;
+        f[2 * e + 1] = p.y;
+      }
+      float absmax_val = 0.f;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      lo |= (uint32_t)static_cast<uint8_t>(roundf(127.5f + f[e] / sf)) << (8 * e);
-      hi |= (uint32_t)static_cast<uint8_t>(roundf(127.5f + f[e + 4] / sf)) << (8 * e);
+      for (int e = 0; e < 8; ++e) absmax_val = fmaxf(absmax_val, fabsf(f[e]));
+#pragma unroll
+      for (int o = LANES / 2; o > 0; o >>= 1) absmax_val = fmaxf(absmax_val, __shfl_xor_sync(0xffffffffu, absmax_val, o));
+      const __half s_absmax = __float2half(absmax_val / 127.5f);
+      const float sf = __half2float(s_absmax);
+      if (!valid) continue;
+      if ((v & (LANES - 1)) == 0) scales[v / LANES] = s_absmax;
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        lo |= (uint32_t)static_cast<uint8_t>(roundf(127.5f + f[e] / sf)) << (8 * e);
+        hi |= (uint32_t)static_cast<uint8_t>(roundf(127.5f + f[e + 4] / sf)) << (8 * e);
+      }
+      *reinterpret_cast<uint2*>(q + v * 8) = make_uint2(lo, hi);
     }
-    *reinterpret_cast<uint2*>(q + v * 8) = make_uint2(lo, hi);
   }
 }
 
@@ -580,7 +590,7 @@ int launch_quantize_absmax_uint8(uint8_t* q, __half* scales, const __half* in, s
   if (vec_ok && (bs == 32 || bs == 64 || bs == 128 || bs == 256)) {
     const size_t n_vec = n_blocks * (size_t)(bs / 8);
     size_t grid8 = (n_vec + 255) / 256;
-    if (grid8 > 148 * 16) grid8 = 148 * 16;
+    if (grid8 > 148 * 8) grid8 = 148 * 8;
     if (bs == 32) quantize8_kernel<4><<<(unsigned)grid8, 256, 0, stream>>>(q, scales, in, n_vec);
     else if (bs == 64) quantize8_kernel<8><<<(unsigned)grid8, 256, 0, stream>>>(q, scales, in, n_vec);
     else if (bs == 128) quantize8_kernel<16><<<(unsigned)grid8, 256, 0, stream>>>(q, scales, in, n_vec);
