@@ -62,7 +62,7 @@ WORKLOADS = {
 SEED, SCALE, PROMPT_LEN, CONTEXT_LEN, TEMPERATURE = 1234, 0.02, 128, 2048, 0.8
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from an ncu capture of
 # that kernel on the 4-layer model of the same shapes; a constant of the kernel, not something this run measures
-NCU_TRAFFIC_BYTES = {"7b-fp16": 180413440 + 3508736, "7b-int8": 91672832 + 2845952}
+NCU_TRAFFIC_BYTES = {"7b-fp16": 180454144 + 3425792, "7b-int8": 91701248 + 2929152}
 PREFILL_LEN = 512
 
 
