@@ -642,7 +642,7 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline_sample(cfg, ffn)
             if args.workload.startswith("7b"):
                 line["cpu_baseline"]["config0_host_scalar"] = config0_host_scalar()
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         host_barrier(dist)
         dist.destroy_process_group()
@@ -695,13 +695,18 @@ def reference_config0(R):
 
 
 def run_reference(args):
+    """The reference arm (rank 0 alone; the other ranks leave without work)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    emit(reference_line(args))
+
+
+def reference_line(args):
     import oracle_lib as O
     import ref_lib as R
 
-    rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if rank != 0:
-        return
     cfg = WORKLOADS[args.workload]
     K, W = args.steps, args.warmup
     base = {"impl": "reference", "metric": "7B batch-1 decode tok/s (fp16, int8); matmul achieved HBM TB/s vs peak", "unit": "tok/s", "n_gpus": world,
@@ -720,8 +725,7 @@ def run_reference(args):
         base.update(value=round(cb["value"], 4), ms_per_step=round(1e3 / cb["value"], 3), cpu_baseline=cb,
                     config={"workload": f"llama-{args.workload} greedy decode, batch 1 (CPU restatement of the reference, bounded sample)"},
                     e2e={"value": round(cb["value"], 4), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
-        print(json.dumps(base), flush=True)
-        return
+        return base
     ctx_len = max(CONTEXT_LEN, PROMPT_LEN + W + K + 2)
     prompt = O.synth_tokens(PROMPT_LEN, SEED, lo=3, hi=min(32000, cfg["n_vocab"]))
     main = reference_decode(R, False, 4, cfg, K, W, ctx_len, prompt)
@@ -754,10 +758,23 @@ def run_reference(args):
             base["config0"] = reference_config0(R)
         except Exception as e:
             base["config0"] = {"error": str(e)[:200]}
-    print(json.dumps(base), flush=True)
+    return base
+
+
+_RESULT_FD = None
+
+
+def emit(line):
+    """Write one JSON line to the process's original stdout.  Libraries loaded by either arm print on file descriptor 1
+    (the reference's initialize() lists device properties, NCCL its version), so main() points descriptor 1 at stderr
+    for the whole run and keeps the original for the result."""
+    text = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    os.write(_RESULT_FD if _RESULT_FD is not None else 1, text)
 
 
 def main():
+    global _RESULT_FD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -777,9 +794,12 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.tp > 1:
         lcu = load_package()
-        print(json.dumps({"tensor_parallel": tensor_parallel_leg(lcu, args.tp, args.steps, args.warmup)}), flush=True)
+        emit({"tensor_parallel": tensor_parallel_leg(lcu, args.tp, args.steps, args.warmup)})
     elif args.impl == "reference":
         run_reference(args)
     else:
