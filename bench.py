@@ -177,7 +177,7 @@ def prefill_sample(lcu, ctx, cfg, ffn, profile=False, prefill_len=PREFILL_LEN):
         m2 = 2048
         ms2 = lcu.bench_matmul_f16_ms(m2, k, n, reps=20)
         tf2 = 2.0 * m2 * k * n / (ms2 * 1e-3) / 1e12
-        out["gemm_roofline"] = {"bound": "tensor", "kernel": "gemm_tc_pair_kernel (tcgen05.mma cta_group::2, TMA-fed, accumulator in TMEM)",
+        out["gemm_roofline"] = {"bound": "tensor", "kernel": "tcgen05 prompt GEMM (cta_group::2, TMA-fed, accumulators in tensor memory; whole tiles per SM pair or the last wave's K steps dealt evenly, chosen per shape)",
                                 "shape": [m, k, n], "us_per_launch": round(ms * 1e3, 2), "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s",
                                 "frac": round(tf / peak, 4), "peak_source": src,
                                 "at_2048_rows": {"shape": [m2, k, n], "us_per_launch": round(ms2 * 1e3, 2), "achieved": round(tf2, 1),

@@ -20,6 +20,7 @@
 // word, skips ahead and still frees its tensor memory.
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -529,6 +530,11 @@ int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* d
   return LCU_OK;
 }
 
+int& gemm_tc_sk_mode() {
+  static int mode = -1;
+  return mode;
+}
+
 bool gemm_tc_supported(int m, int N, int K, int ldx, const void* lhs, const void* w, const void* out) {
   return m >= 1 && N % 32 == 0 && K % BK == 0 && ldx % 8 == 0 && ((uintptr_t)lhs & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
          ((uintptr_t)out & 15) == 0;
@@ -538,6 +544,51 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
                    int force_bn, int force_pair, int force_split) {
   LCU_REQUIRE(gemm_tc_supported(m, N, K, ldx, lhs, w, out), "gemm_tc: unsupported shape m=%d N=%d K=%d ldx=%d or unaligned pointers", m, N, K, ldx);
   const int sms = gemv_sm_count();
+  // More than 128 rows: three kernels can run the product - whole tiles per SM pair (below), the kernel that deals the
+  // K steps of the last, partial wave evenly over the pairs (gemm_tc_sk.cu, 256-wide tiles), and the same with
+  // 512-wide tiles (a third less operand traffic per multiply-add, no overlap of epilogue and main loop).  Which one is
+  // fastest depends on how the tile count meets the 74 pairs; the estimates below are fitted to timings of the 7B, 13B
+  // and 65B products at 256 to 2048 rows (microseconds; picks within 2 % of the best of the three in sum).  Mode -1 =
+  // this rule; 256 / 512 force the balanced kernel with that tile width; 0 = never.
+  if (force_pair < 0 && !force_bn && m > BM) {
+    const int mode = gemm_tc_sk_mode();
+    int tile = mode > 0 ? mode : 0;
+    if (mode < 0) {
+      const long C = sms / 2, nk = K / BK, tm = (m + 2 * BM - 1) / (2 * BM);
+      auto ceil_div_l = [](long a, long b) { return (a + b - 1) / b; };
+      double whole;  // the kernels below
+      if ((m > 2 * BM || N > 8192) && N % 128 == 0) {
+        const long n256 = tm * (N / 256);
+        if (N % 256 == 0 && n256 * 4 >= C * 3) whole = ceil_div_l(n256, C) * nk * (n256 > 40 ? 0.465 : 0.40) + 5;
+        else whole = ceil_div_l(tm * (N / 128), C) * nk * 0.42 + 5;
+      } else {
+        const long n128 = (long)((m + BM - 1) / BM) * (N / 128);
+        long sp = n128 * 4 <= sms ? 4 : n128 * 2 <= sms ? 2 : 1;
+        if (nk < 8 * sp) sp = 1;
+        whole = ceil_div_l(n128 * sp, sms) * ((double)nk / sp) * 0.40 + 6;
+      }
+      auto balanced = [&](int bn) -> double {
+        if (N % bn) return 1e30;
+        const long n = tm * (N / bn), full = n / C, rest = n - full * C;
+        const double per = bn == 256 ? 0.465 : 0.80;
+        double t = full * (nk * per + (bn == 512 ? 4 : 0)) + 5;
+        if (rest) {
+          const long cs = std::min(C, std::min(rest * nk, rest * 3));
+          const double per_s = cs > 40 ? per : (bn == 256 ? 0.40 : 0.72);
+          t += (double)(rest * nk) / cs * per_s + (bn == 256 ? 14 : 26);
+        }
+        return t;
+      };
+      double best = whole;
+      const double t256 = balanced(256), t512 = N >= 2 * K ? balanced(512) : 1e30;
+      if (t256 < 0.97 * whole && t256 < best) {
+        best = t256;
+        tile = 256;
+      }
+      if (t512 < 0.97 * whole && t512 < best) tile = 512;
+    }
+    if (tile && gemm_tc_sk_supported(m, N, K, ldx, lhs, w, out, tile)) return launch_gemm_tc_sk(out, lhs, ldx, w, m, N, K, beta, err, stream, tile);
+  }
   // Large products: the two-SM kernel, with its 256-wide tile when that still gives (nearly) every SM pair a tile.
   // Up to 256 rows of a matrix with few tiles stay on the one-SM kernel, which can split K to fill the SMs.
   int pair = force_pair;

@@ -17,4 +17,14 @@ bool gemm_tc_supported(int m, int N, int K, int ldx, const void* lhs, const void
 int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream,
                    int force_bn = 0, int force_pair = -1, int force_split = -1);
 
+// Wide-tile variant with the K loop balanced over the SM pairs (gemm_tc_sk.cu): 256 x tile_n output tiles (tile_n 256 or
+// 512, dividing N), any number of rows.  Partial sums of tiles shared between pairs go through a workspace kept per
+// (device, stream) and are added in a fixed order.
+// -1 (default) = launch_gemm_tc uses it, with 256- or 512-wide tiles, where its estimate says it wins; 256 / 512 =
+// always, with that tile width, where it divides N; 0 = never
+int& gemm_tc_sk_mode();
+bool gemm_tc_sk_supported(int m, int N, int K, int ldx, const void* lhs, const void* w, const void* out, int tile_n);
+int launch_gemm_tc_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream,
+                      int tile_n);
+
 }  // namespace lcu

@@ -144,6 +144,35 @@ def test_prefill_tensor_core_gemm(lcu, m, k, n, beta, tile):
         assert np.abs(f32(y) - f32(y_gemv)).max() <= 2e-3 * scale
 
 
+@pytest.mark.parametrize("tile", [256, 512])
+@pytest.mark.parametrize("m,k,n,beta", [(129, 512, 512, 0.0), (200, 1024, 1024, 1.0), (300, 4096, 1536, 0.0), (512, 11008, 4096, 1.0),
+                                        # fewer tiles than SM pairs: every tile is shared by several pairs
+                                        (257, 2048, 512, 1.0),
+                                        # whole waves first, then the shared tiles (2 x 86 tiles for 74 pairs)
+                                        (512, 320, 22016, 0.0), (1000, 2048, 2560, 1.0)])
+def test_prefill_gemm_with_balanced_k_steps(lcu, m, k, n, beta, tile):
+    """The tcgen05 GEMM that deals the K steps of the last wave's tiles evenly over the SM pairs (partial sums through a
+    workspace, added in pair order): against the oracle's binary64-accumulated product, same tolerance as the whole-tile
+    kernel, for both tile widths; and twice in a row with equal bits (the order of the sums does not depend on timing)."""
+    if n % tile:
+        pytest.skip("tile width does not divide N")
+    rng = np.random.default_rng(m * 11 + n + tile)
+    x = f16(rng.standard_normal((m, k)))
+    w = O.synth_f16(n * k, 5, f"sk{n}x{k}", 0.05).reshape(n, k)
+    prev = f16(rng.standard_normal((m, n)))
+    yo = prev.copy()
+    L.orc_matmul_nt_f16(yo.reshape(-1), x.reshape(-1), w.reshape(-1), m, k, n, beta, 1)
+    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_sk", tile))
+    try:
+        y = lcu.matmul_nt(x, w, beta=beta, out_u16=prev)
+        y2 = lcu.matmul_nt(x, w, beta=beta, out_u16=prev)
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_sk", -1))
+    scale = max(1.0, float(np.abs(f32(yo)).max()))
+    assert np.abs(f32(y) - f32(yo)).max() <= 2e-3 * scale
+    assert np.array_equal(y, y2)
+
+
 def test_matmul_rejects_bad_shapes(lcu):
     with pytest.raises(lcu.LcuError, match="multiple of 256"):
         lcu.matmul_nt(np.zeros((1, 100), np.uint16), np.zeros((4, 100), np.uint16))
