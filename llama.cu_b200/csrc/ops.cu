@@ -63,6 +63,56 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(__half* out, const __half
   }
 }
 
+// Same arithmetic and summation order with one trip to memory: every thread brings 16-byte vectors of the row into
+// registers and into shared memory, the 256 strided partial sums of the reference are formed from shared memory, and the
+// normalised row is written from the registers.  Rows of up to 8 * 256 * RN_VEC elements, 16-byte aligned.
+constexpr int RN_VEC = 4;
+__global__ void __launch_bounds__(256) rms_norm_vec_kernel(__half* out, const __half* in, const __half* weight, int w, float eps) {
+  extern __shared__ __align__(16) uint8_t rn_row[];  // the row as halves
+  __shared__ float s_warp[8];
+  const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int vec = w >> 3;
+  const uint4* x = reinterpret_cast<const uint4*>(in + (size_t)row * w);
+  uint4 xv[RN_VEC], wv[RN_VEC];
+#pragma unroll
+  for (int j = 0; j < RN_VEC; ++j) {
+    const int i = tid + j * 256;
+    if (i < vec) {
+      xv[j] = x[i];
+      wv[j] = reinterpret_cast<const uint4*>(weight)[i];
+      reinterpret_cast<uint4*>(rn_row)[i] = xv[j];
+    }
+  }
+  __syncthreads();
+  const __half* xr = reinterpret_cast<const __half*>(rn_row);
+  float s = 0.f;
+  for (int i = tid; i < w; i += 256) {
+    const float v = __half2float(xr[i]);
+    s += v * v;
+  }
+  s = warp_sum(s);
+  if (lane == 0) s_warp[warp] = s;
+  __syncthreads();
+  float t = lane < 8 ? s_warp[lane] : 0.f;  // every warp repeats the last tree
+  for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  const float rinv = rsqrtf(__shfl_sync(0xffffffffu, t, 0) / w + eps);
+#pragma unroll
+  for (int j = 0; j < RN_VEC; ++j) {
+    const int i = tid + j * 256;
+    if (i < vec) {
+      uint4 o = xv[j];
+      __half2* o2 = reinterpret_cast<__half2*>(&o);
+      const __half2* w2 = reinterpret_cast<const __half2*>(&wv[j]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(o2[e]);
+        o2[e] = __hmul2(w2[e], __floats2half2_rn(f.x * rinv, f.y * rinv));
+      }
+      reinterpret_cast<uint4*>(out + (size_t)row * w)[i] = o;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ RoPE (llama_cu.cu:368-389)
 __global__ void rope_table_kernel(float2* table, int ctx_len, int head_dim, float theta, int first_pos) {
   const int half_dim = head_dim >> 1;
@@ -97,6 +147,37 @@ __global__ void rope_scatter_kernel(__half* q, const __half* k_new, const __half
     k_cache[dst + 1] = __float2half(real * a_sin + imag * a_cos);
   }
   *reinterpret_cast<__half2*>(v_cache + dst) = *reinterpret_cast<const __half2*>(v_new + src);
+}
+
+// Same arithmetic, eight consecutive columns (four rotation pairs, inside one head) per thread with 16-byte accesses.
+__global__ void __launch_bounds__(128) rope_scatter_vec_kernel(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
+                                                               const float2* rope, const int* pos_ptr, int pos_value, int m, int dim, int n_heads,
+                                                               int ctx_len, int ld) {
+  const int r = blockIdx.y;
+  const int c = 8 * (blockIdx.x * blockDim.x + threadIdx.x);
+  if (c >= dim) return;
+  const int hd = dim / n_heads;
+  const int head = c / hd, j = c - head * hd;
+  const int pos = (pos_ptr ? *pos_ptr : pos_value) + r;
+  const float4* tab = reinterpret_cast<const float4*>(rope + (size_t)pos * (hd >> 1) + (j >> 1));
+  const float4 t0 = tab[0], t1 = tab[1];
+  const float cs[4][2] = {{t0.x, t0.y}, {t0.z, t0.w}, {t1.x, t1.y}, {t1.z, t1.w}};
+  const size_t src = (size_t)r * ld + c;
+  const size_t dst = ((size_t)head * ctx_len + pos) * hd + j;
+  auto rotate = [&](uint4 v) {
+    __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float real = __low2float(h[e]), imag = __high2float(h[e]);
+      h[e] = __halves2half2(__float2half(real * cs[e][0] - imag * cs[e][1]), __float2half(real * cs[e][1] + imag * cs[e][0]));
+    }
+    return v;
+  };
+  const uint4 qv = *reinterpret_cast<const uint4*>(q + src), kv = *reinterpret_cast<const uint4*>(k_new + src);
+  const uint4 vv = *reinterpret_cast<const uint4*>(v_new + src);
+  *reinterpret_cast<uint4*>(q + src) = rotate(qv);
+  *reinterpret_cast<uint4*>(k_cache + dst) = rotate(kv);
+  *reinterpret_cast<uint4*>(v_cache + dst) = vv;
 }
 
 // ------------------------------------------------------------------ SiLU gate (llama_cu.cu:533-539)
@@ -434,7 +515,10 @@ int launch_embed(__half* x, int ldx, const void* table, const __half* scales, in
 }
 
 int launch_rms_norm(__half* out, const __half* in, const __half* weight, int rows, int dim, float eps, cudaStream_t stream) {
-  rms_norm_kernel<<<rows, 256, 0, stream>>>(out, in, weight, dim, eps);
+  if (dim % 8 == 0 && dim <= 8 * 256 * RN_VEC && ((((uintptr_t)out | (uintptr_t)in | (uintptr_t)weight)) & 15) == 0)
+    rms_norm_vec_kernel<<<rows, 256, (size_t)dim * 2, stream>>>(out, in, weight, dim, eps);
+  else
+    rms_norm_kernel<<<rows, 256, 0, stream>>>(out, in, weight, dim, eps);
   LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }
@@ -450,9 +534,16 @@ int launch_rope_table(float2* table, int ctx_len, int head_dim, float theta, cud
 int launch_rope_scatter(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
                         const float2* rope, const int* pos, int pos_value, int m, int dim, int n_heads, int ctx_len,
                         cudaStream_t stream, int ld) {
-  dim3 grid((dim / 2 + 127) / 128, m);
-  rope_scatter_kernel<<<grid, 128, 0, stream>>>(q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len,
-                                                ld > 0 ? ld : dim);
+  const int row_ld = ld > 0 ? ld : dim;
+  const int hd = dim / n_heads;
+  const uintptr_t all = (uintptr_t)q | (uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)rope;
+  if (hd % 8 == 0 && row_ld % 8 == 0 && (all & 15) == 0) {
+    dim3 grid((dim / 8 + 127) / 128, m);
+    rope_scatter_vec_kernel<<<grid, 128, 0, stream>>>(q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len, row_ld);
+  } else {
+    dim3 grid((dim / 2 + 127) / 128, m);
+    rope_scatter_kernel<<<grid, 128, 0, stream>>>(q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len, row_ld);
+  }
   LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }
