@@ -47,4 +47,8 @@ int launch_attention_prefill(const attn_params& p, int m, int max_T, cudaStream_
 size_t attention_tc_scratch_halves(int n_heads, int m_cap, int ctx_len);
 int launch_attention_tc(const attn_params& p, int m, int max_T, __half* scores, int m_cap, cudaStream_t stream);
 
+// Prompt rows on tcgen05 in one kernel (attention_fused.cu): scores, softmax and probabilities x V per (128-row tile,
+// head) with the scores in tensor memory and the probabilities in shared memory; no score buffer.
+int launch_attention_fused(const attn_params& p, int m, int max_T, cudaStream_t stream);
+
 }  // namespace lcu

@@ -102,6 +102,7 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "prefill_fuse") prefill_tuning_ref().fuse = value;
   else if (k == "prefill_attn_tc") prefill_tuning_ref().attn_tc = value;
   else if (k == "prefill_attn_tc_min_rows") prefill_tuning_ref().attn_tc_min_rows = value;
+  else if (k == "prefill_attn_fused_min_rows") prefill_tuning_ref().attn_fused_min_rows = value;
   else if (k == "prefill_attn_tiles") prefill_tuning_ref().attn_tiles = value;
   else if (k == "prefill_tc_split") prefill_tuning_ref().tc_split = value;
   else if (k == "prefill_tc_pair") prefill_tuning_ref().tc_pair = value;
@@ -278,6 +279,7 @@ int lcu_attention(void* out_dev, const void* q_dev, const void* k_cache_dev, con
   at.head_dim = dim / n_heads;
   at.err = scratch_err();
   if (cluster == 0) return launch_attention_prefill(at, m, pos0 + m, (cudaStream_t)stream);
+  if (cluster == -2) return launch_attention_fused(at, m, pos0 + m, (cudaStream_t)stream);  // tcgen05, one kernel
   if (cluster == -1) {  // tcgen05 path; this stand-alone entry owns no scratch, so the score buffer lives for the call only
     const size_t halves = attention_tc_scratch_halves(n_heads, m, ctx_len);
     __half* scores = nullptr;

@@ -11,9 +11,10 @@ struct prefill_tuning {
   int u8_deq_min_rows = 9;   // u8 weights: this many rows or more take a dequantization pass + the tcgen05 GEMM (0 = never);
                              // measured at 7B: 9.3 ms for any prompt of 9..47 tokens against 7..34 ms through GEMV passes
   int fuse = 1;         // fp16 prompts: wq|wk|wv and w1|w3 as one GEMM each over the stacked matrices
-  int attn_tc = 1;      // prompt attention: 1 = the tcgen05 kernels (scores through an fp16 buffer), 0 = the fused warp-level kernel
-  int attn_tc_min_rows = 384;  // rows from which the tcgen05 path is used (measured at 7B: 10.26 / 10.33 ms at 384 rows,
-                               // 15.7 / 16.7 at 1024, 33.9 / 36.9 at 2000; below, its three launches per layer cost more)
+  int attn_tc = 2;      // prompt attention: 2 = one tcgen05 kernel per layer (scores in tensor memory), 1 = three tcgen05 kernels with the
+                        // scores in an fp16 buffer (allocated by contexts created while this is 1), 0 = the fused warp-level kernel
+  int attn_tc_min_rows = 384;  // rows from which the three-kernel path is used (its three launches per layer cost more below)
+  int attn_fused_min_rows = 65;  // rows from which the one-kernel path is used (up to 64 rows: one tile of the warp-level kernel)
   int attn_tiles = 1;   // prompt attention: 1 = 64-row query tiles on tensor cores, 0 = the per-row decode kernel
   int tc_split = -1;    // one-SM kernel: -1 = split K over 2 / 4 CTAs when tiles are few, 1 / 2 / 4 = always that factor
   int tc_pair = -1;     // two-SM kernel: -1 = when m > 128, 0 = never, 128 / 256 = always with that tile width

@@ -476,8 +476,9 @@ scratch_layout scratch_layout_of(const model_params& p, uint32_t ffn, int contex
   s.deq_halves = p.q_type ? std::max((size_t)2 * f * d, (size_t)3 * d * d) : 0;
   s.o_deq = cv.take(s.deq_halves * 2);
   s.o_deq2 = cv.take(s.deq_halves * 2);
-  // score buffer of the tcgen05 prompt attention (contexts up to 4096 positions; longer ones use the fused kernel)
-  s.score_halves = context_len <= 4096 ? attention_tc_scratch_halves(p.n_heads, context_len, context_len) : 0;
+  // score buffer of the three-kernel tcgen05 prompt attention: only when that path is selected ("prefill_attn_tc" = 1);
+  // the one-kernel path (2, the default) keeps scores in tensor memory
+  s.score_halves = (prefill_tuning_ref().attn_tc == 1 && context_len <= 4096) ? attention_tc_scratch_halves(p.n_heads, context_len, context_len) : 0;
   s.o_scores = cv.take(s.score_halves * 2);
   s.o_rope = cv.take(ctxl * (hd / 2) * sizeof(float2));
   s.o_state = cv.take(64);
@@ -1002,7 +1003,9 @@ int context_impl::enqueue_prefill(int m_rows) {
     at.out = g.att; at.ldo = d;
     at.pos = g.state;
     at.ctx_len = opt.context_len; at.n_heads = p.n_heads; at.head_dim = hd; at.err = g.state + 3;
-    if (pt.attn_tc && g.scores != nullptr && m_rows >= pt.attn_tc_min_rows)
+    if (pt.attn_tc == 2 && m_rows >= pt.attn_fused_min_rows)
+      LCU_TRY(launch_attention_fused(at, m_rows, start_pos + m_rows, g.stream));
+    else if (pt.attn_tc == 1 && g.scores != nullptr && m_rows >= pt.attn_tc_min_rows)
       LCU_TRY(launch_attention_tc(at, m_rows, start_pos + m_rows, g.scores, opt.context_len, g.stream));
     else if (pt.attn_tiles)
       LCU_TRY(launch_attention_prefill(at, m_rows, start_pos + m_rows, g.stream));

@@ -91,15 +91,22 @@ def test_partition_must_be_contiguous():
                                                       ("65B-u8", 8192, 64, 80, 128)])
 def test_context_scratch_figure_counts_every_buffer(name, dim, heads, layers, bs):
     """One function sizes the per-GPU scratch arena for the context, the memory-based partitioner and
-    llama_params::shared_context_memory_size.  It must cover the activations, the score buffer of the tcgen05 prompt
-    attention (heads x ctx x round_up(ctx, 128) halves) and, for u8 models, the dequantization buffer."""
+    llama_params::shared_context_memory_size.  It must cover the activations and, for u8 models, the dequantization
+    buffers; the score buffer (heads x ctx x round_up(ctx, 128) halves) is part of it only while the three-kernel prompt
+    attention is selected - the default one-kernel path keeps scores in tensor memory."""
     lcu = load_package()
     ctx = 2048
     ffn = lcu.lib.lcu_ffn_dim(dim, 256)
     raw = lcu.pack_params(dim, 256, heads, layers, 32000, 1e-6, bs)
     got = lcu.lib.lcu_context_scratch_bytes(raw, ctx)
     activations = 6 * ctx * dim * 2 + 3 * ctx * ffn * 2
-    scores = heads * ctx * ((ctx + 127) // 128 * 128) * 2
+    scores = 0
+    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc", 1))
+    try:
+        with_scores = lcu.lib.lcu_context_scratch_bytes(raw, ctx)
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc", 2))
+    assert with_scores - got >= heads * ctx * ((ctx + 127) // 128 * 128) * 2
     deq = 2 * max(2 * ffn * dim, 3 * dim * dim) * 2 if bs else 0  # two buffers: one feeds the GEMM in flight, the next matrix expands into the other
     tables = ctx * (dim // heads // 2) * 8 + 2 * 32000 * 2 + 2 * ctx * 2
     assert activations + scores + deq + tables <= got <= activations + scores + deq + tables + 64 * 256, name

@@ -229,7 +229,10 @@ def test_rope_scatter(lcu):
                                             # cluster 0 = the prompt kernel (64-row query tiles on tensor cores)
                                             (7, 5, 2, 0), (64, 0, 2, 0), (65, 37, 1, 0), (200, 0, 2, 0), (130, 300, 2, 0), (1, 77, 2, 0),
                                             # cluster -1 = the prompt path on tcgen05 (scores, softmax, probabilities x V)
-                                            (7, 5, 2, -1), (128, 0, 1, -1), (200, 0, 2, -1), (130, 300, 2, -1), (512, 0, 4, -1), (1, 77, 2, -1)])
+                                            (7, 5, 2, -1), (128, 0, 1, -1), (200, 0, 2, -1), (130, 300, 2, -1), (512, 0, 4, -1), (1, 77, 2, -1),
+                                            # cluster -2 = the same path in one kernel (scores in tensor memory, no score buffer)
+                                            (7, 5, 2, -2), (128, 0, 1, -2), (200, 0, 2, -2), (130, 300, 2, -2), (512, 0, 4, -2), (1, 77, 2, -2),
+                                            (129, 127, 2, -2), (1000, 24, 2, -2), (300, 1700, 1, -2)])
 def test_attention_against_oracle(lcu, m, T0, H, cluster):
     rng = np.random.default_rng(T0 + m)
     dim = H * 128
@@ -270,7 +273,7 @@ def test_attention_streaming_kernel_gives_the_same_bits(lcu, T0, H, hd, cluster)
     assert np.abs(f32(outs[1]) - f32(oo)).max() <= 4e-3
 
 
-@pytest.mark.parametrize("m,T0,cluster", [(1, 50, 4), (70, 9, 0), (70, 9, -1), (300, 100, -1)])
+@pytest.mark.parametrize("m,T0,cluster", [(1, 50, 4), (70, 9, 0), (70, 9, -1), (300, 100, -1), (70, 9, -2), (300, 100, -2)])
 def test_attention_head_dim_64(lcu, m, T0, cluster):
     rng = np.random.default_rng(8)
     H, dim = 4, 256

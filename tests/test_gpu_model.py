@@ -79,8 +79,8 @@ def test_small_model_matches_oracle(lcu, bs, prompt_len, u8_mode):
 
 
 def test_long_prompt_attention_paths_against_oracle(lcu):
-    """A 300-token prompt through the tcgen05 attention path (scores, softmax, probabilities x V) and through the fused
-    warp-level kernel: both must reproduce the oracle's next-token distribution, and a decode step after either must too
+    """A 300-token prompt through the one-kernel tcgen05 attention (2), the three-kernel tcgen05 path with its score buffer
+    (1) and the fused warp-level kernel (0): all must reproduce the oracle's next-token distribution, and a decode step after either must too
     (the KV cache they leave behind is the same)."""
     scale = 0.08
     cfg = dict(dim=256, multiple_of=256, n_heads=2, n_layers=3, n_vocab=1000)
@@ -92,7 +92,7 @@ def test_long_prompt_attention_paths_against_oracle(lcu):
     to2 = om.next_token([to])
     po2 = f32(om.probs())
     try:
-        for tc in (1, 0):
+        for tc in (2, 1, 0):
             lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc", tc))
             lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc_min_rows", 2))
             ctx = lcu.Context(model, context_len=320, temperature=0.8)
@@ -104,7 +104,7 @@ def test_long_prompt_attention_paths_against_oracle(lcu):
             assert np.abs(pr2 - po2).max() <= 0.02 * po2.max() + 1e-4, tc
             ctx.close()
     finally:
-        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc", 1))
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc", 2))
         lcu.check(lcu.lib.lcu_set_tuning(b"prefill_attn_tc_min_rows", 384))
     om.close()
     model.close()
