@@ -38,7 +38,7 @@ int lcu_set_matmul_type(int type);
  * "gemv_ctas_per_sm_int8", "gemv_variant", "gemv_warp_stages", "gemv_warp_stages_int8", "gemv_consumer_warps_int8", "gemv_prefetch_kb",
  * "int8_factored" (0 = round every dequantized weight to half as the reference does), "prefill_tc_min_rows",
  * "prefill_tc_tile_n", "prefill_tc_pair", "prefill_tc_split", "prefill_tc_sk", "prefill_u8_deq_min_rows", "prefill_fuse", "prefill_attn_tc",
- * "prefill_attn_tc_min_rows", "prefill_attn_tiles", "attn_stream",
+ * "prefill_attn_tc_min_rows", "prefill_attn_fused_min_rows", "prefill_attn_tiles", "prompt_pdl", "attn_stream",
  * "use_graph", "use_pdl", "attn_cluster", "loader_staged" (lcu_model_load: 1 = pinned double-buffered asynchronous copies, 0 = a file mapping and one
  * blocking pageable copy per tensor as the reference does).  Unknown keys are rejected. */
 int lcu_set_tuning(const char* key, int value);
@@ -99,7 +99,8 @@ int lcu_rope_scatter_static(void* q_dev, const void* k_new_dev, const void* v_ne
  * q [m][dim] rotated, caches head-major as above holding positions 0 .. pos0+m-1; out [m][dim].
  * cluster = 1, 2, 4, 8: one thread-block cluster of that many CTAs per (row, head), the decode kernel;
  * cluster = 0: 64-row query tiles on warp-level tensor-core instructions (one fused kernel);
- * cluster = -1: the prompt path on tcgen05 (scores to a temporary fp16 buffer, softmax, probabilities x V). */
+ * cluster = -1: the prompt path on tcgen05 as three kernels (scores to a temporary fp16 buffer, softmax, probabilities x V);
+ * cluster = -2: the prompt path on tcgen05 as one kernel (scores in tensor memory, no buffer). */
 int lcu_attention(void* out_dev, const void* q_dev, const void* k_cache_dev, const void* v_cache_dev, int pos0, int m, int dim,
                   int n_heads, int ctx_len, int cluster, void* stream);
 /* softmax_rows with temperature on the logits + the host-side first-maximum search,

@@ -76,8 +76,6 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attn_fused_kernel(const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * FA_BM, head = blockIdx.y;  // long row tiles first
-  const int pos0 = p.pos ? *p.pos : p.pos_value;
-  const int n_tiles = min(t_tiles, (pos0 + m0 + FA_BM + FA_BN - 1) / FA_BN);       // key tiles that hold a visible key
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bars[B_Q]), 1);
@@ -102,6 +100,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attn_fused_kernel(const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // (the position word and the operands are read after this line)
+  const int pos0 = p.pos ? *p.pos : p.pos_value;
+  const int n_tiles = min(t_tiles, (pos0 + m0 + FA_BM + FA_BN - 1) / FA_BN);       // key tiles that hold a visible key
 
   if (warp == 0) {
     if (lane == 0) {
@@ -374,8 +376,7 @@ int launch_fused_hd(const attn_params& p, int m, int max_T, cudaStream_t stream)
     attr_done[dev] = true;
   }
   const int m_tiles = (m + FA_BM - 1) / FA_BM, t_tiles = (max_T + FA_BN - 1) / FA_BN;
-  attn_fused_kernel<HD><<<dim3(m_tiles, p.n_heads), FA_THREADS, SMEM, stream>>>(map_q, map_k, map_v, q, t_tiles);
-  LCU_CUDA(cudaGetLastError());
+  LCU_CUDA(launch_after(attn_fused_kernel<HD>, dim3(m_tiles, p.n_heads), dim3(FA_THREADS), SMEM, stream, map_q, map_k, map_v, q, t_tiles));
   return LCU_OK;
 }
 

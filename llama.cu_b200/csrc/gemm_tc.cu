@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   if (S > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");  // waited for before the first remote store
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // everything above ran under the previous kernel's tail; nothing before this line touches global memory
 
   float own[S == 1 ? 1 : CPR][32];  // epilogue warps: this CTA's partial of the columns it owns
   bool go = false;
@@ -280,6 +282,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
   cluster_sync();  // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // everything above ran under the previous kernel's tail; nothing before this line touches global memory
 
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer (both CTAs)
@@ -458,13 +462,22 @@ int launch_bn(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
   cfg.blockDim = dim3(TC_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = S;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (S > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = S;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  if (prompt_pdl()) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = S > 1 ? 1 : 0;
+  cfg.numAttrs = n_attr;
   LCU_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, S>, map_a, map_b, out, m, N, K, beta, nstages, a_box_rows, err));
   return LCU_OK;
 }
@@ -490,8 +503,8 @@ int launch_pair(__half* out, const __half* lhs, int ldx, const __half* w, int m,
   const int tiles_m = (m + 2 * BM - 1) / (2 * BM), n_tiles = tiles_m * (N / BN);
   int clusters = gemv_sm_count() / 2;
   if (clusters > n_tiles) clusters = n_tiles;
-  gemm_tc_pair_kernel<BN><<<2 * clusters, TC_THREADS, smem, stream>>>(map_a, map_b, out, m, N, K, beta, nstages, tiles_m, n_tiles, err);
-  LCU_CUDA(cudaGetLastError());
+  LCU_CUDA(launch_after(gemm_tc_pair_kernel<BN>, dim3(2 * clusters), dim3(TC_THREADS), smem, stream, map_a, map_b, out, m, N, K, beta, nstages, tiles_m,
+                        n_tiles, err));
   return LCU_OK;
 }
 

@@ -192,6 +192,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
   cluster_sync();  // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // everything above ran under the previous kernel's tail; nothing before this line touches global memory
 
   if (warp == 0) {
     if (lane == 0) {  // ---- TMA producer (both CTAs)
@@ -503,9 +505,8 @@ int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
   int rc = sk_get_workspace(dev, stream, (size_t)clusters * 256 * BN, clusters, &ws);
   if (rc) return rc;
   const int seq = ++ws->seq;
-  gemm_tc_sk_kernel<NB><<<2 * clusters, SK_THREADS, smem, stream>>>(map_a, map_b, map_out, m, N, K, beta, nstages, tiles_m, n_tiles, ws->partials, ws->flags,
-                                                                  seq, err);
-  LCU_CUDA(cudaGetLastError());
+  LCU_CUDA(launch_after(gemm_tc_sk_kernel<NB>, dim3(2 * clusters), dim3(SK_THREADS), smem, stream, map_a, map_b, map_out, m, N, K, beta, nstages, tiles_m,
+                        n_tiles, ws->partials, ws->flags, seq, err));
   return LCU_OK;
 }
 

@@ -38,6 +38,8 @@ __global__ void embed_kernel(__half* x, int ldx, const void* table, const __half
 // ------------------------------------------------------------------ RMSNorm (llama_cu.cu:66-107)
 // Same launch shape (one 256-thread block per row) and the same reduction order as the reference.
 __global__ void __launch_bounds__(256) rms_norm_kernel(__half* out, const __half* in, const __half* weight, int w, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const __half* x = in + (size_t)row * w;
   __shared__ float s_warp[8];
@@ -72,6 +74,8 @@ __global__ void __launch_bounds__(256) rms_norm_vec_kernel(__half* out, const __
   __shared__ float s_warp[8];
   const int row = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int vec = w >> 3;
+  pdl_launch_dependents();
+  pdl_wait();
   const uint4* x = reinterpret_cast<const uint4*>(in + (size_t)row * w);
   uint4 xv[RN_VEC], wv[RN_VEC];
 #pragma unroll
@@ -126,6 +130,8 @@ __global__ void rope_table_kernel(float2* table, int ctx_len, int head_dim, floa
 
 __global__ void rope_scatter_kernel(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
                                     const float2* rope, const int* pos_ptr, int pos_value, int m, int dim, int n_heads, int ctx_len, int ld) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.y;
   const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
   if (c >= dim) return;
@@ -153,6 +159,8 @@ __global__ void rope_scatter_kernel(__half* q, const __half* k_new, const __half
 __global__ void __launch_bounds__(128) rope_scatter_vec_kernel(__half* q, const __half* k_new, const __half* v_new, __half* k_cache, __half* v_cache,
                                                                const float2* rope, const int* pos_ptr, int pos_value, int m, int dim, int n_heads,
                                                                int ctx_len, int ld) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.y;
   const int c = 8 * (blockIdx.x * blockDim.x + threadIdx.x);
   if (c >= dim) return;
@@ -516,10 +524,9 @@ int launch_embed(__half* x, int ldx, const void* table, const __half* scales, in
 
 int launch_rms_norm(__half* out, const __half* in, const __half* weight, int rows, int dim, float eps, cudaStream_t stream) {
   if (dim % 8 == 0 && dim <= 8 * 256 * RN_VEC && ((((uintptr_t)out | (uintptr_t)in | (uintptr_t)weight)) & 15) == 0)
-    rms_norm_vec_kernel<<<rows, 256, (size_t)dim * 2, stream>>>(out, in, weight, dim, eps);
+    LCU_CUDA(launch_after(rms_norm_vec_kernel, dim3(rows), dim3(256), (size_t)dim * 2, stream, out, in, weight, dim, eps));
   else
-    rms_norm_kernel<<<rows, 256, 0, stream>>>(out, in, weight, dim, eps);
-  LCU_CUDA(cudaGetLastError());
+    LCU_CUDA(launch_after(rms_norm_kernel, dim3(rows), dim3(256), 0, stream, out, in, weight, dim, eps));
   return LCU_OK;
 }
 
@@ -539,17 +546,20 @@ int launch_rope_scatter(__half* q, const __half* k_new, const __half* v_new, __h
   const uintptr_t all = (uintptr_t)q | (uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)rope;
   if (hd % 8 == 0 && row_ld % 8 == 0 && (all & 15) == 0) {
     dim3 grid((dim / 8 + 127) / 128, m);
-    rope_scatter_vec_kernel<<<grid, 128, 0, stream>>>(q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len, row_ld);
+    LCU_CUDA(launch_after(rope_scatter_vec_kernel, grid, dim3(128), 0, stream, q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads,
+                          ctx_len, row_ld));
   } else {
     dim3 grid((dim / 2 + 127) / 128, m);
-    rope_scatter_kernel<<<grid, 128, 0, stream>>>(q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len, row_ld);
+    LCU_CUDA(launch_after(rope_scatter_kernel, grid, dim3(128), 0, stream, q, k_new, v_new, k_cache, v_cache, rope, pos, pos_value, m, dim, n_heads, ctx_len,
+                          row_ld));
   }
-  LCU_CUDA(cudaGetLastError());
   return LCU_OK;
 }
 
 // rows of [a | b] pairs: out[r][j] = silu(ab[r][j]) * ab[r][f + j], f % 8 == 0
 __global__ void __launch_bounds__(256) silu_rows_kernel(__half* out, const __half* ab, int m, int f) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int fv = f >> 3;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)m * fv) return;
@@ -587,8 +597,7 @@ int run_bounded_wait_probe(int* err_word, cudaStream_t stream) {
 int launch_silu_rows(__half* out, const __half* ab, int m, int f, cudaStream_t stream) {
   LCU_REQUIRE(f % 8 == 0 && (((uintptr_t)out | (uintptr_t)ab) & 15) == 0, "silu_rows: rows of %d elements are not 16-byte vectors", f);
   const size_t n = (size_t)m * (f / 8);
-  silu_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(out, ab, m, f);
-  LCU_CUDA(cudaGetLastError());
+  LCU_CUDA(launch_after(silu_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, out, ab, m, f));
   return LCU_OK;
 }
 

@@ -12,6 +12,11 @@ prefill_tuning& prefill_tuning_ref() {
   return t;
 }
 
+int& prompt_pdl() {
+  static int on = 1;
+  return on;
+}
+
 int& matmul_type_ref() {
   static int type = 4;
   return type;
