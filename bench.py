@@ -162,6 +162,22 @@ def prefill_sample(lcu, ctx, cfg, ffn, profile=False, prefill_len=PREFILL_LEN):
         dt = time.perf_counter() - t0
         best = dt if best is None or dt < best else best
     out = {"prompt_tokens": prefill_len, "ms": round(best * 1e3, 3), "tok_s": round(prefill_len / best, 1)}
+    # other prompt lengths that fit the context: a short prompt (time to first token) and a long one
+    other = {}
+    for n in (16, 128, 2000):
+        if n == prefill_len or n + 2 > CONTEXT_LEN:
+            continue
+        pr = O.synth_tokens(n, SEED + 2, lo=3, hi=min(32000, cfg["n_vocab"]))
+        b2 = None
+        for _ in range(3):
+            ctx.clear_tokens()
+            lcu.check(lcu.lib.lcu_synchronize())
+            t0 = time.perf_counter()
+            ctx.next_token(pr)
+            dt = time.perf_counter() - t0
+            b2 = dt if b2 is None or dt < b2 else b2
+        other[str(n)] = round(b2 * 1e3, 3)
+    out["ms_by_prompt_tokens"] = other
     if profile:  # one more prompt pass and a few GEMM launches inside the profiler's window
         ctx.clear_tokens()
         lcu.check(lcu.lib.lcu_profiler_start())
@@ -569,7 +585,7 @@ def run_ours(args):
     if args.workload == "7b-fp16" and not args.no_int8 and args.pipeline <= 1:
         feed = [main["first"]] + main["warm_tokens"] + main["tokens"]
         forced = {"first": main["first"], "feed": feed[:-1], "last": feed[-1]}
-        int8 = measure_decode(lcu, "7b-int8", K, W, args.prompt_len, world, dist, forced=forced)
+        int8 = measure_decode(lcu, "7b-int8", K, W, args.prompt_len, world, dist, forced=forced, with_prefill=(world == 1), prefill_len=args.prefill_len)
     clocks = sampler.stop() if rank == 0 else None
     cfg, ffn = main["cfg"], main["ffn"]
     ceiling = read_ceiling(lcu) if rank == 0 else None
@@ -604,6 +620,8 @@ def run_ours(args):
                         "top1_agreement_with_fp16": {"teacher_forced_steps": a["steps"], "equal": a["top1_equal"],
                                                      "frac": round(a["top1_equal"] / a["steps"], 4)},
                         "weights_generated_s": round(int8["gen_s"], 1)}
+        if "prefill" in int8:
+            line["int8"]["prefill"] = int8["prefill"]
         line["gpu_launches"] += K * int8["kernels_per_step"]
     if "prefill" in main:
         line["prefill"] = main["prefill"]
