@@ -227,6 +227,11 @@ int lcu_profiler_stop(void);
  * (LCU_ERR_DEVICE_WAIT) with the device code (0x101) in *device_code_out; the context stays usable.  No counterpart
  * in the reference (its kernels have no waits). */
 int lcu_selftest_bounded_wait(int* device_code_out);
+/* The quantizer forms q = u8(roundf(127.5f + x / scale)) (transform.cu:60-80) with a reciprocal multiply, one residual
+ * correction and trunc(v + 0.5f).  This entry compares that with the reference's IEEE division and roundf for EVERY pair
+ * (x a finite half, scale a positive finite half, |x| within the absmax that rounds to the scale) on the device and
+ * returns the number of pairs checked and the number of differing bytes (0). */
+int lcu_selftest_quantizer_arithmetic(uint64_t* checked_out, uint64_t* differences_out);
 /* lcu_matmul_nt_f16 (beta = 0, default stream) launched `reps` times back to back between two CUDA events on that
  * stream: mean milliseconds per launch.  Used to put the prompt GEMM against the tensor-core roofline. */
 int lcu_bench_matmul_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, int reps, float* ms_per_launch_out);

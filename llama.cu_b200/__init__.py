@@ -54,6 +54,7 @@ _SIG = {
     "lcu_attention": (C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "lcu_logits_head": (C.c_int, [vp, vp, C.c_int, C.c_float, C.POINTER(C.c_int), vp]),
     "lcu_selftest_bounded_wait": (C.c_int, [C.POINTER(C.c_int)]),
+    "lcu_selftest_quantizer_arithmetic": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "lcu_bench_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "lcu_synth_fill_f16": (C.c_int, [vp, C.c_uint64, C.c_uint64, C.c_char_p, C.c_float, C.c_uint64, vp]),
     "lcu_model_create": (C.c_int, [vp, vp, C.POINTER(vp)]),

@@ -489,6 +489,14 @@ int lcu_profiler_stop(void) {
   LCU_CUDA(cudaProfilerStop());
   return LCU_OK;
 }
+int lcu_selftest_quantizer_arithmetic(uint64_t* checked_out, uint64_t* differences_out) {
+  NEED_DEVICE();
+  unsigned long long a = 0, b = 0;
+  int rc = quantizer_arithmetic_check(&a, &b);
+  *checked_out = a;
+  *differences_out = b;
+  return rc;
+}
 int lcu_selftest_bounded_wait(int* device_code_out) {
   NEED_DEVICE();
   int* err = scratch_err();

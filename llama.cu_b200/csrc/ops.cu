@@ -338,6 +338,50 @@ __global__ void __launch_bounds__(256) quantize_kernel(uint8_t* q, __half* scale
   }
 }
 
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// q = u8(roundf(127.5f + x / s)) costs an IEEE division and a roundf per element - about 25 instructions, which is what
+// bounded the kernel at half the copy bandwidth.  For the inputs the quantizer can see - x a finite half, s a positive
+// finite half, |x| within the absmax that rounds to s - the same byte comes out of a reciprocal multiply with one
+// residual correction (the correctly rounded quotient) and trunc(v + 0.5f) for the non-negative v = 127.5f + quotient:
+// 7 instructions.  "The same byte" is not argued, it is checked: quantizer_check_kernel compares the two for every such
+// pair (2 x 10^9 of them) on the device, and tests/test_gpu_kernels.py requires zero differences.
+__device__ __forceinline__ uint32_t quant_byte_reference(float x, float s) { return static_cast<uint8_t>(roundf(127.5f + x / s)); }
+__device__ __forceinline__ uint32_t quant_byte_fast(float x, float s, float rcp) {
+  const float t = x * rcp;
+  const float quo = fmaf(fmaf(-t, s, x), rcp, t);
+  return static_cast<uint8_t>(127.5f + quo + 0.5f);  // (conversion truncates)
+}
+
+// every (x, s) pair of the quantizer's domain: s = positive finite half number blockIdx.x * 256 + threadIdx.x..., x every
+// finite half with |x| <= the largest absmax whose scale rounds to s.  counts[0] = pairs checked, counts[1] = differences.
+__global__ void __launch_bounds__(256) quantizer_check_kernel(unsigned long long* counts) {
+  unsigned long long checked = 0, diff = 0;
+  for (uint32_t sb = blockIdx.x + 1; sb < 0x7c00u; sb += gridDim.x) {  // bit patterns of the positive finite halves
+    const float s = __half2float(__ushort_as_half((unsigned short)sb));
+    const float rcp = __frcp_rn(s);
+    for (uint32_t xb = threadIdx.x; xb < 0x10000u; xb += 256) {
+      if ((xb & 0x7c00u) == 0x7c00u) continue;  // inf / nan
+      const __half xh = __ushort_as_half((unsigned short)xb);
+      const float x = __half2float(xh);
+      // in the domain iff a block with this absmax would get this scale
+      if (__half_as_ushort(__float2half(fabsf(x) / 127.5f)) > sb) continue;
+      ++checked;
+      if (quant_byte_reference(x, s) != quant_byte_fast(x, s, rcp)) ++diff;
+    }
+  }
+  checked = warp_sum_u64(checked);
+  diff = warp_sum_u64(diff);
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(counts, checked);
+    atomicAdd(counts + 1, diff);
+  }
+}
+
 // The same arithmetic with 16-byte loads: a thread holds eight consecutive halves in registers (read once), the
 // BS / 8 neighbouring lanes that share a block agree on the block's absmax with xor shuffles, and every thread stores
 // its eight bytes at once.  Block sizes 32 .. 256 (4 .. 32 lanes per block); n_vec = elements / 8.
@@ -366,9 +410,9 @@ __global__ void __launch_bounds__(256) quantize8_kernel(uint8_t* q, __half* scal
         f[2 * e] = p.x;
         f[2 * e + 1] = p.y;
       }
-      float absmax_val = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) absmax_val = fmaxf(absmax_val, fabsf(f[e]));
+      // absmax on the packed halves (the maximum of halves is exact in any format; NaNs are passed over as fmaxf does)
+      __half2 am2 = __hmax2(__hmax2(__habs2(h2[0]), __habs2(h2[1])), __hmax2(__habs2(h2[2]), __habs2(h2[3])));
+      float absmax_val = fmaxf(0.f, fmaxf(__low2float(am2), __high2float(am2)));
 #pragma unroll
       for (int o = LANES / 2; o > 0; o >>= 1) absmax_val = fmaxf(absmax_val, __shfl_xor_sync(0xffffffffu, absmax_val, o));
       const __half s_absmax = __float2half(absmax_val / 127.5f);
@@ -376,10 +420,19 @@ __global__ void __launch_bounds__(256) quantize8_kernel(uint8_t* q, __half* scal
       if (!valid) continue;
       if ((v & (LANES - 1)) == 0) scales[v / LANES] = s_absmax;
       uint32_t lo = 0, hi = 0;
+      if (sf > 0.f && absmax_val < CUDART_INF_F) {  // (block-uniform) the checked domain: finite values, positive scale
+        const float rcp = __frcp_rn(sf);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        lo |= (uint32_t)static_cast<uint8_t>(roundf(127.5f + f[e] / sf)) << (8 * e);
-        hi |= (uint32_t)static_cast<uint8_t>(roundf(127.5f + f[e + 4] / sf)) << (8 * e);
+        for (int e = 0; e < 4; ++e) {
+          lo |= quant_byte_fast(f[e], sf, rcp) << (8 * e);
+          hi |= quant_byte_fast(f[e + 4], sf, rcp) << (8 * e);
+        }
+      } else {  // an all-zero block (0 / 0), infinities or NaNs: the reference's own instructions
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          lo |= quant_byte_reference(f[e], sf) << (8 * e);
+          hi |= quant_byte_reference(f[e + 4], sf) << (8 * e);
+        }
       }
       *reinterpret_cast<uint2*>(q + v * 8) = make_uint2(lo, hi);
     }
@@ -702,6 +755,20 @@ int launch_quantize_absmax_uint8(uint8_t* q, __half* scales, const __half* in, s
   if (grid > 148 * 16) grid = 148 * 16;
   quantize_kernel<<<(unsigned)grid, 256, 0, stream>>>(q, scales, in, n_blocks, bs);
   LCU_CUDA(cudaGetLastError());
+  return LCU_OK;
+}
+
+int quantizer_arithmetic_check(unsigned long long* checked_out, unsigned long long* differences_out) {
+  unsigned long long* d = nullptr;
+  LCU_CUDA(cudaMalloc(&d, 16));
+  LCU_CUDA(cudaMemset(d, 0, 16));
+  quantizer_check_kernel<<<148 * 4, 256>>>(d);
+  unsigned long long h[2] = {0, 0};
+  cudaError_t e = cudaMemcpy(h, d, 16, cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  LCU_CUDA(e);
+  *checked_out = h[0];
+  *differences_out = h[1];
   return LCU_OK;
 }
 

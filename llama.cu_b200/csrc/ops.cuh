@@ -86,4 +86,8 @@ int head_preload();
 int launch_bump_pos(int* pos, int inc, cudaStream_t stream);
 int launch_token_to_ids(short* ids, const int* token, cudaStream_t stream);
 
+// compares the quantizer's fast arithmetic with the reference's (IEEE division, roundf) for every (value, scale) pair of its
+// domain on the device: number of pairs checked and number of differing bytes
+int quantizer_arithmetic_check(unsigned long long* checked_out, unsigned long long* differences_out);
+
 }  // namespace lcu

@@ -173,6 +173,18 @@ def test_prefill_gemm_with_balanced_k_steps(lcu, m, k, n, beta, tile):
     assert np.array_equal(y, y2)
 
 
+def test_quantizer_fast_arithmetic_equals_division_and_roundf_on_its_whole_domain(lcu):
+    """The quantizer forms its bytes with a reciprocal multiply, one residual correction and trunc(v + 0.5f) instead of the
+    reference's IEEE division and roundf (transform.cu:60-80).  The device compares the two for every pair the quantizer
+    can meet - every positive finite half as scale, every finite half within the absmax that rounds to it: about two
+    billion pairs - and must find no differing byte."""
+    import ctypes as C
+    checked, diff = C.c_uint64(0), C.c_uint64(0)
+    lcu.check(lcu.lib.lcu_selftest_quantizer_arithmetic(C.byref(checked), C.byref(diff)))
+    assert checked.value > 1_000_000_000
+    assert diff.value == 0
+
+
 def test_matmul_rejects_bad_shapes(lcu):
     with pytest.raises(lcu.LcuError, match="multiple of 256"):
         lcu.matmul_nt(np.zeros((1, 100), np.uint16), np.zeros((4, 100), np.uint16))
