@@ -354,7 +354,7 @@ __device__ __forceinline__ uint32_t quant_byte_reference(float x, float s) { ret
 __device__ __forceinline__ uint32_t quant_byte_fast(float x, float s, float rcp) {
   const float t = x * rcp;
   const float quo = fmaf(fmaf(-t, s, x), rcp, t);
-  return static_cast<uint8_t>(127.5f + quo + 0.5f);  // (conversion truncates)
+  return static_cast<uint8_t>(quo + 128.0f);  // trunc((127.5f + quo) + 0.5f) in one addition (conversion truncates); checked like the rest
 }
 
 // every (x, s) pair of the quantizer's domain: s = positive finite half number blockIdx.x * 256 + threadIdx.x..., x every
