@@ -149,7 +149,9 @@ def test_prefill_tensor_core_gemm(lcu, m, k, n, beta, tile):
                                         # fewer tiles than SM pairs: every tile is shared by several pairs
                                         (257, 2048, 512, 1.0),
                                         # whole waves first, then the shared tiles (2 x 86 tiles for 74 pairs)
-                                        (512, 320, 22016, 0.0), (1000, 2048, 2560, 1.0)])
+                                        (512, 320, 22016, 0.0), (1000, 2048, 2560, 1.0),
+                                        # smallest legal K and N, ragged rows
+                                        (131, 64, 512, 1.0), (515, 128, 1024, 0.0)])
 def test_prefill_gemm_with_balanced_k_steps(lcu, m, k, n, beta, tile):
     """The tcgen05 GEMM that deals the K steps of the last wave's tiles evenly over the SM pairs (partial sums through a
     workspace, added in pair order): against the oracle's binary64-accumulated product, same tolerance as the whole-tile
@@ -244,7 +246,8 @@ def test_rope_scatter(lcu):
                                             (7, 5, 2, -1), (128, 0, 1, -1), (200, 0, 2, -1), (130, 300, 2, -1), (512, 0, 4, -1), (1, 77, 2, -1),
                                             # cluster -2 = the same path in one kernel (scores in tensor memory, no score buffer)
                                             (7, 5, 2, -2), (128, 0, 1, -2), (200, 0, 2, -2), (130, 300, 2, -2), (512, 0, 4, -2), (1, 77, 2, -2),
-                                            (129, 127, 2, -2), (1000, 24, 2, -2), (300, 1700, 1, -2)])
+                                            (129, 127, 2, -2), (1000, 24, 2, -2), (300, 1700, 1, -2), (65, 0, 1, -2), (100, 1948, 1, -2),
+                                            (66, 3, 3, -2)])
 def test_attention_against_oracle(lcu, m, T0, H, cluster):
     rng = np.random.default_rng(T0 + m)
     dim = H * 128
