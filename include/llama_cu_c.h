@@ -37,7 +37,8 @@ int lcu_set_matmul_type(int type);
 /* launch-shape knobs used for the measurements (defaults are the measured best): "gemv_stages", "gemv_ctas_per_sm",
  * "gemv_ctas_per_sm_int8", "gemv_variant", "gemv_warp_stages", "gemv_warp_stages_int8", "gemv_consumer_warps_int8", "gemv_prefetch_kb",
  * "int8_factored" (0 = round every dequantized weight to half as the reference does), "prefill_tc_min_rows",
- * "prefill_tc_tile_n", "prefill_tc_pair", "prefill_tc_split", "prefill_tc_sk", "prefill_u8_deq_min_rows", "prefill_fuse", "prefill_attn_tc",
+ * "prefill_tc_tile_n", "prefill_tc_pair", "prefill_tc_split", "prefill_tc_sk", "prefill_gate_fused", "prefill_u8_deq_min_rows",
+ * "prefill_fuse", "prefill_attn_tc",
  * "prefill_attn_tc_min_rows", "prefill_attn_fused_min_rows", "prefill_attn_tiles", "prompt_pdl", "attn_stream",
  * "use_graph", "use_pdl", "attn_cluster", "loader_staged" (lcu_model_load: 1 = pinned double-buffered asynchronous copies, 0 = a file mapping and one
  * blocking pageable copy per tensor as the reference does).  Unknown keys are rejected. */
@@ -71,6 +72,13 @@ int lcu_quantize_model_dir(const char* in_dir, const char* out_dir, int bs);
 /* matmul_nt(out, lhs, rhs, beta, stream), llama_cu.cu:738-742 / 1463-1496:
  * out(m,n) = lhs(m,k) . rhs(n,k)^T + beta * out, fp16 in/out, fp32 accumulation.  No gutter rows needed. */
 int lcu_matmul_nt_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, float beta, void* stream);
+/* The feed-forward's first half as one launch: matmul_nt of lhs(m,k) with w1 and with w3 (llama_cu.cu:1180-1181; w13 =
+ * [w1; w3], (2 f, k), k a multiple of 64) and silu (llama_cu.cu:533-539, 1182-1183) on the half-rounded products: out(m,f).
+ * The same bits as lcu_matmul_nt_f16 on each matrix followed by lcu_silu.  tile = accumulator columns per output tile:
+ * 256 (f a multiple of 128; the gate runs under the next tile's main loop) or 512 (f a multiple of 256).  Prompt passes
+ * use it as the tuning key "prefill_gate_fused" says (-1 = when estimated faster, 256 / 512 = from 129 rows with that
+ * tile, 0 = never). */
+int lcu_matmul_nt_f16_gated(void* out_dev, const void* lhs_dev, const void* w13_dev, int m, int k, int f, int tile, void* stream);
 /* matmul_nt(out, lhs, generic_tensor& rhs, beta, stream) with a quantized rhs, llama_cu.cu:743-747 / 1498-1523 */
 int lcu_matmul_nt_fp16u8(void* out_dev, const void* lhs_dev, const void* q_dev, const void* scales_dev, int m, int k, int n, int bs,
                          float beta, void* stream);
@@ -232,6 +240,10 @@ int lcu_selftest_bounded_wait(int* device_code_out);
  * (x a finite half, scale a positive finite half, |x| within the absmax that rounds to the scale) on the device and
  * returns the number of pairs checked and the number of differing bytes (0). */
 int lcu_selftest_quantizer_arithmetic(uint64_t* checked_out, uint64_t* differences_out);
+/* lcu_matmul_nt_f16_gated forms silu's a / (1 + expf(-a)) (llama_cu.cu:533-539) with a refined reciprocal and one
+ * residual correction instead of the IEEE division.  This entry compares the two on the device for all 65536
+ * half-precision a (the only values the gate meets) and returns how many were compared and how many differ (0). */
+int lcu_selftest_silu_arithmetic(uint64_t* checked_out, uint64_t* differences_out);
 /* lcu_matmul_nt_f16 (beta = 0, default stream) launched `reps` times back to back between two CUDA events on that
  * stream: mean milliseconds per launch.  Used to put the prompt GEMM against the tensor-core roofline. */
 int lcu_bench_matmul_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, int m, int k, int n, int reps, float* ms_per_launch_out);

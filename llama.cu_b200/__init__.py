@@ -46,6 +46,7 @@ _SIG = {
     "lcu_quantize_host": (C.c_int, [vp, vp, vp, C.c_uint64, C.c_uint64, C.c_int, vp]),
     "lcu_quantize_model_dir": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int]),
     "lcu_matmul_nt_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, vp]),
+    "lcu_matmul_nt_f16_gated": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "lcu_matmul_nt_fp16u8": (C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, vp]),
     "lcu_rms_norm": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_float, vp]),
     "lcu_silu": (C.c_int, [vp, vp, vp, C.c_uint64, vp]),
@@ -55,6 +56,7 @@ _SIG = {
     "lcu_logits_head": (C.c_int, [vp, vp, C.c_int, C.c_float, C.POINTER(C.c_int), vp]),
     "lcu_selftest_bounded_wait": (C.c_int, [C.POINTER(C.c_int)]),
     "lcu_selftest_quantizer_arithmetic": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "lcu_selftest_silu_arithmetic": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "lcu_bench_matmul_f16": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "lcu_synth_fill_f16": (C.c_int, [vp, C.c_uint64, C.c_uint64, C.c_char_p, C.c_float, C.c_uint64, vp]),
     "lcu_model_create": (C.c_int, [vp, vp, C.POINTER(vp)]),
@@ -183,6 +185,18 @@ def dequantize(q, scales, bs):
     check(lib.lcu_dequantize_absmax_uint8(do.ptr, ds.ptr, dq.ptr, h, w, bs, None))
     check(lib.lcu_synchronize())
     return do.to_host(np.uint16, (h, w))
+
+
+def matmul_nt_gated(lhs_u16, w13_u16, tile=256):
+    """silu(lhs . w1^T) * (lhs . w3^T) on half-rounded products as one launch; w13 = [w1; w3] stacked, (2 f, k)."""
+    lhs = np.ascontiguousarray(lhs_u16, np.uint16)
+    w13 = np.ascontiguousarray(w13_u16, np.uint16)
+    m, k = lhs.shape
+    f = w13.shape[0] // 2
+    dl, dr, do = DeviceBuffer.from_host(lhs), DeviceBuffer.from_host(w13), DeviceBuffer.from_host(np.zeros((m, f), np.uint16))
+    check(lib.lcu_matmul_nt_f16_gated(do.ptr, dl.ptr, dr.ptr, m, k, f, tile, None))
+    check(lib.lcu_synchronize())
+    return do.to_host(np.uint16, (m, f))
 
 
 def matmul_nt(lhs_u16, rhs, scales=None, bs=0, beta=0.0, out_u16=None):

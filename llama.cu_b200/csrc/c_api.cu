@@ -107,6 +107,7 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "prefill_tc_split") prefill_tuning_ref().tc_split = value;
   else if (k == "prefill_tc_pair") prefill_tuning_ref().tc_pair = value;
   else if (k == "prefill_tc_sk") gemm_tc_sk_mode() = value;
+  else if (k == "prefill_gate_fused") gemm_tc_gate_mode() = value;
   else if (k == "prompt_pdl") prompt_pdl() = value;
   else if (k == "tp_debug") tp_set_debug(value);
   else if (k == "loader_staged") set_loader_staged(value);
@@ -225,6 +226,10 @@ int lcu_matmul_nt_f16(void* out_dev, const void* lhs_dev, const void* rhs_dev, i
   w.cols = k;
   w.bs = 0;
   return matmul_rows((__half*)out_dev, (const __half*)lhs_dev, w, m, beta, scratch_err(), (cudaStream_t)stream);
+}
+int lcu_matmul_nt_f16_gated(void* out_dev, const void* lhs_dev, const void* w13_dev, int m, int k, int f, int tile, void* stream) {
+  NEED_DEVICE();
+  return launch_gemm_tc_gated((__half*)out_dev, (const __half*)lhs_dev, k, (const __half*)w13_dev, m, f, k, scratch_err(), (cudaStream_t)stream, tile);
 }
 int lcu_matmul_nt_fp16u8(void* out_dev, const void* lhs_dev, const void* q_dev, const void* scales_dev, int m, int k, int n, int bs,
                          float beta, void* stream) {
@@ -493,6 +498,14 @@ int lcu_selftest_quantizer_arithmetic(uint64_t* checked_out, uint64_t* differenc
   NEED_DEVICE();
   unsigned long long a = 0, b = 0;
   int rc = quantizer_arithmetic_check(&a, &b);
+  *checked_out = a;
+  *differences_out = b;
+  return rc;
+}
+int lcu_selftest_silu_arithmetic(uint64_t* checked_out, uint64_t* differences_out) {
+  NEED_DEVICE();
+  unsigned long long a = 0, b = 0;
+  int rc = silu_arithmetic_check(&a, &b);
   *checked_out = a;
   *differences_out = b;
   return rc;

@@ -548,6 +548,60 @@ int& gemm_tc_sk_mode() {
   return mode;
 }
 
+// Estimated duration (microseconds) of an [m][K] x [N][K]^T product, m > 128, on the three kernels: whole tiles per SM
+// pair, and the balanced kernel with 256- and 512-wide tiles.  Fitted to timings of the 7B, 13B and 65B products at 256 to
+// 2048 rows (picks within 2 % of the best of the three in sum).
+static void gemm_tc_estimates(int m, int N, int K, int sms, double* whole_us, double* t256_us, double* t512_us) {
+  const long C = sms / 2, nk = K / BK, tm = (m + 2 * BM - 1) / (2 * BM);
+  auto ceil_div_l = [](long a, long b) { return (a + b - 1) / b; };
+  double whole;
+  if ((m > 2 * BM || N > 8192) && N % 128 == 0) {
+    const long n256 = tm * (N / 256);
+    if (N % 256 == 0 && n256 * 4 >= C * 3) whole = ceil_div_l(n256, C) * nk * (n256 > 40 ? 0.465 : 0.40) + 5;
+    else whole = ceil_div_l(tm * (N / 128), C) * nk * 0.42 + 5;
+  } else {
+    const long n128 = (long)((m + BM - 1) / BM) * (N / 128);
+    long sp = n128 * 4 <= sms ? 4 : n128 * 2 <= sms ? 2 : 1;
+    if (nk < 8 * sp) sp = 1;
+    whole = ceil_div_l(n128 * sp, sms) * ((double)nk / sp) * 0.40 + 6;
+  }
+  auto balanced = [&](int bn) -> double {
+    if (N % bn) return 1e30;
+    const long n = tm * (N / bn), full = n / C, rest = n - full * C;
+    const double per = bn == 256 ? 0.465 : 0.80;
+    double t = full * (nk * per + (bn == 512 ? 4 : 0)) + 5;
+    if (rest) {
+      const long cs = std::min(C, std::min(rest * nk, rest * 3));
+      const double per_s = cs > 40 ? per : (bn == 256 ? 0.40 : 0.72);
+      t += (double)(rest * nk) / cs * per_s + (bn == 256 ? 14 : 26);
+    }
+    return t;
+  };
+  *whole_us = whole;
+  *t256_us = balanced(256);
+  *t512_us = N >= 2 * K ? balanced(512) : 1e30;
+}
+
+int& gemm_tc_gate_mode() {
+  static int mode = -1;
+  return mode;
+}
+
+int gemm_tc_gated_tile(int m, int f, int K) {
+  const int mode = gemm_tc_gate_mode();
+  if (m <= BM || mode == 0) return 0;
+  if (mode > 0) return mode == 512 && f % 256 == 0 ? 512 : 256;
+  // the one launch (256 accumulator columns per tile: the gate's arithmetic runs under the next tile's main loop, so
+  // its duration is the balanced kernel's for the stacked product plus about 3 us measured, more beyond 1024 rows)
+  // against the best kernel for the stacked product plus the gate kernel's pass over the result (6 bytes per output
+  // element at about 5 TB/s, and a launch).  7B shapes: the one launch wins 4 to 8 us per layer from 129 to 1024 rows.
+  double whole, t256, t512;
+  gemm_tc_estimates(m, 2 * f, K, gemv_sm_count(), &whole, &t256, &t512);
+  const double gate_us = (double)m * f * 6.0 / 5.0e6 + 2;
+  const double one_launch = t256 + 3 + (m > 1024 ? (m - 1024) * 0.016 : 0.0);
+  return one_launch < std::min(whole, t512) + gate_us ? 256 : 0;
+}
+
 bool gemm_tc_supported(int m, int N, int K, int ldx, const void* lhs, const void* w, const void* out) {
   return m >= 1 && N % 32 == 0 && K % BK == 0 && ldx % 8 == 0 && ((uintptr_t)lhs & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
          ((uintptr_t)out & 15) == 0;
@@ -560,40 +614,15 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
   // More than 128 rows: three kernels can run the product - whole tiles per SM pair (below), the kernel that deals the
   // K steps of the last, partial wave evenly over the pairs (gemm_tc_sk.cu, 256-wide tiles), and the same with
   // 512-wide tiles (a third less operand traffic per multiply-add, no overlap of epilogue and main loop).  Which one is
-  // fastest depends on how the tile count meets the 74 pairs; the estimates below are fitted to timings of the 7B, 13B
-  // and 65B products at 256 to 2048 rows (microseconds; picks within 2 % of the best of the three in sum).  Mode -1 =
-  // this rule; 256 / 512 force the balanced kernel with that tile width; 0 = never.
+  // fastest depends on how the tile count meets the 74 pairs (gemm_tc_estimates).  Mode -1 = that rule; 256 / 512 force
+  // the balanced kernel with that tile width; 0 = never.
   if (force_pair < 0 && !force_bn && m > BM) {
     const int mode = gemm_tc_sk_mode();
     int tile = mode > 0 ? mode : 0;
     if (mode < 0) {
-      const long C = sms / 2, nk = K / BK, tm = (m + 2 * BM - 1) / (2 * BM);
-      auto ceil_div_l = [](long a, long b) { return (a + b - 1) / b; };
-      double whole;  // the kernels below
-      if ((m > 2 * BM || N > 8192) && N % 128 == 0) {
-        const long n256 = tm * (N / 256);
-        if (N % 256 == 0 && n256 * 4 >= C * 3) whole = ceil_div_l(n256, C) * nk * (n256 > 40 ? 0.465 : 0.40) + 5;
-        else whole = ceil_div_l(tm * (N / 128), C) * nk * 0.42 + 5;
-      } else {
-        const long n128 = (long)((m + BM - 1) / BM) * (N / 128);
-        long sp = n128 * 4 <= sms ? 4 : n128 * 2 <= sms ? 2 : 1;
-        if (nk < 8 * sp) sp = 1;
-        whole = ceil_div_l(n128 * sp, sms) * ((double)nk / sp) * 0.40 + 6;
-      }
-      auto balanced = [&](int bn) -> double {
-        if (N % bn) return 1e30;
-        const long n = tm * (N / bn), full = n / C, rest = n - full * C;
-        const double per = bn == 256 ? 0.465 : 0.80;
-        double t = full * (nk * per + (bn == 512 ? 4 : 0)) + 5;
-        if (rest) {
-          const long cs = std::min(C, std::min(rest * nk, rest * 3));
-          const double per_s = cs > 40 ? per : (bn == 256 ? 0.40 : 0.72);
-          t += (double)(rest * nk) / cs * per_s + (bn == 256 ? 14 : 26);
-        }
-        return t;
-      };
+      double whole, t256, t512;
+      gemm_tc_estimates(m, N, K, sms, &whole, &t256, &t512);
       double best = whole;
-      const double t256 = balanced(256), t512 = N >= 2 * K ? balanced(512) : 1e30;
       if (t256 < 0.97 * whole && t256 < best) {
         best = t256;
         tile = 256;

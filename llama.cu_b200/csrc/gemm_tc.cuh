@@ -27,4 +27,15 @@ bool gemm_tc_sk_supported(int m, int N, int K, int ldx, const void* lhs, const v
 int launch_gemm_tc_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream,
                       int tile_n);
 
+// w1|w3 and the SiLU gate as one launch (gemm_tc_sk.cu): out[m][f] = half(silu(half(lhs . w1^T)) * half(lhs . w3^T)) with
+// w13 = [w1; w3] stacked ([2 f][K]); the same bits as the stacked product followed by the gate kernel.
+// gemm_tc_gate_mode: -1 = when the estimate favours it, 256 / 512 = from 129 rows with that many accumulator columns per
+// tile, 0 = never.  gemm_tc_gated_tile: the tile to use for this shape under that mode, 0 = run product and gate apart.
+int& gemm_tc_gate_mode();
+int gemm_tc_gated_tile(int m, int f, int K);
+bool gemm_tc_gated_supported(int m, int f, int K, int ldx, const void* lhs, const void* w13, const void* out);
+// tile_n: accumulator columns per tile (256: 128 output columns, the gate hidden under the next tile; 512: 256 output columns)
+int launch_gemm_tc_gated(__half* out, const __half* lhs, int ldx, const __half* w13, int m, int f, int K, int* err, cudaStream_t stream,
+                         int tile_n = 256);
+
 }  // namespace lcu

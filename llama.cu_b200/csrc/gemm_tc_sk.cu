@@ -142,12 +142,20 @@ struct sk_schedule {
   }
 };
 
-template <int NB>  // 256-column accumulators per tile (1: the tile is 256 x 256 and tensor memory holds two of them)
+// NB: 256-column accumulators per tile (1: the tile is 256 x 256 and tensor memory holds two of them).
+// GATE: the two halves of a tile's accumulator columns are the same BN / 2 output columns of two matrices stacked in W -
+// rows [n, n + BN / 2) and [gate_rows + n, gate_rows + n + BN / 2) - and the epilogue stores half(silu(half(a)) * half(b))
+// (llama_cu.cu:533-539 on the half-rounded products, what the separate gate kernel computes from the stored halves): w1|w3
+// and the SiLU gate as one launch, without the [rows][2 f] intermediate.  With NB = 1 each CTA of the pair loads one
+// matrix's 128 rows, and the gate's arithmetic (a division and an exponential per element on four warps) runs under the
+// next tile's main loop.
+template <int NB, bool GATE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
     gemm_tc_sk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_out, int m, int N, int K,
-                      float beta, int nstages, int tiles_m, int n_tiles, float* workspace, int* flags, int seq, int* err) {
+                      float beta, int nstages, int tiles_m, int n_tiles, float* workspace, int* flags, int seq, int* err, int gate_rows) {
   constexpr int BN = 256 * NB;
+  constexpr int BN_OUT = GATE ? BN / 2 : BN;  // output columns per tile
   constexpr uint32_t A_BYTES = SK_BM * SK_BK * 2, B_BYTES = 128 * SK_BK * 2, STAGE = A_BYTES + NB * B_BYTES;
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);  // fp32 acc, fp16 x fp16, K-major, N = 256, M = 256
   constexpr int NBUF = NB == 1 ? 2 : 1;  // accumulator buffers: the epilogue of one segment runs under the main loop of the next
@@ -201,7 +209,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
       bool ok = true;
       while (ok && sched.next(tile, kb0, kb1, split)) {
         const int m0 = (tile % tiles_m) * (2 * SK_BM) + (int)rank * SK_BM;
-        const int n0 = (tile / tiles_m) * BN + (int)rank * 128;
+        // rows of W for this CTA's 128 columns of accumulator h: n0 + h * n_step
+        const int n0 = (tile / tiles_m) * BN_OUT + (int)rank * ((GATE && NB == 1) ? gate_rows : 128);
+        const int n_step = GATE ? gate_rows : 256;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % nstages;
           const uint32_t ph = (uint32_t)(it / nstages) & 1u;
@@ -212,7 +222,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bars[s]), 2 * STAGE);
           sk_tma_load_pair(dst, &map_a, kb * SK_BK, m0, full_leader);
 #pragma unroll
-          for (int h = 0; h < NB; ++h) sk_tma_load_pair(dst + A_BYTES + h * B_BYTES, &map_b, kb * SK_BK, n0 + h * 256, full_leader);
+          for (int h = 0; h < NB; ++h) sk_tma_load_pair(dst + A_BYTES + h * B_BYTES, &map_b, kb * SK_BK, n0 + h * n_step, full_leader);
         }
       }
     }
@@ -260,7 +270,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
     bool go = true;
     for (; go && sched.next(tile, kb0, kb1, split); ++si) {
       const int row = (tile % tiles_m) * (2 * SK_BM) + trow;
-      const int n0 = (tile / tiles_m) * BN;
+      const int n0 = (tile / tiles_m) * BN_OUT;
       const int b = si % NBUF;
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN);
       const bool ok = mbar_wait(smem_u32(&bars[16 + b]), (uint32_t)(si / NBUF) & 1u, err, DEV_ERR_TMEM_WAIT);
@@ -322,10 +332,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
           }
           __syncwarp();
         }
+        // GATE: the pieces are visited as (first matrix, second matrix) pairs of the same output columns
+        auto piece_of = [](int idx) { return GATE ? (idx >> 1) + (idx & 1) * (BN / 64) : idx; };
+        uint32_t first[16];  // GATE: the half-rounded products of the first matrix for the piece in flight
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int idx = 0; idx < BN / 32; ++idx) {
+          const int piece = piece_of(idx);
           uint32_t r[32];
-          tc_ld_32x32(acc + (uint32_t)c, r);
+          tc_ld_32x32(acc + (uint32_t)(piece * 32), r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           float sum[32];
 #pragma unroll
@@ -336,7 +350,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
             for (int q = 0; q < 2; ++q)
 #pragma unroll
               for (int i = 0; i < 8; ++i) cur[q][i] = nxt[q][i];
-            if (c + 32 < BN) fetch((c >> 5) + 1);
+            if (idx + 1 < BN / 32) fetch(piece_of(idx + 1));
 #pragma unroll
             for (int q = 0; q < 2; ++q)
               if (q < n_peers) {
@@ -349,7 +363,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
                 }
               }
             for (int q = 2; q < n_peers; ++q) {
-              const float4* src = peer_piece(q, c >> 5);
+              const float4* src = peer_piece(q, piece);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float4 v = __ldcg(src + i * 256);
@@ -360,16 +374,41 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
               }
             }
           }
+          if (GATE && (idx & 1) == 0) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const __half2 h = __floats2half2_rn(sum[2 * i], sum[2 * i + 1]);
+              first[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            continue;
+          }
+          uint32_t outw[16];  // the piece's 32 output halves (beta = 0 paths)
+          if (GATE) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&first[i]));
+              const float2 bq = __half22float2(__floats2half2_rn(sum[2 * i], sum[2 * i + 1]));
+              const __half2 gt = __halves2half2(__float2half(silu_of_half(a.x) * bq.x), __float2half(silu_of_half(a.y) * bq.y));
+              outw[i] = *reinterpret_cast<const uint32_t*>(&gt);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const __half2 h = __floats2half2_rn(sum[2 * i], sum[2 * i + 1]);
+              outw[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          }
           // results go out through shared memory: the warp's 32 rows x 64 columns are stored by one bulk tensor copy
           // (rows are 44 KB apart in memory; stores of 64 bytes per thread kept the load/store unit busy for longer
           // than the tile's arithmetic left room for)
+          const int c = (GATE ? idx >> 1 : idx) * 32;  // output column of the piece within the tile
           const int chunk = c >> 6, buf = chunk & 1;
           const uint32_t sb = stg + (uint32_t)buf * 4096;
           if ((c & 32) == 0) {
-            if (beta != 0.f) {
+            if (!GATE && beta != 0.f) {
               if (lane == 0) {
                 sk_store_wait_read<0>();  // the other buffer's last store has read it: it may take the next chunk's previous values
-                if (c + 64 < BN) {
+                if (c + 64 < BN_OUT) {
                   mbar_arrive_expect_tx(prev_bar + (uint32_t)(buf ^ 1) * 8, 4096);
                   tma_load_2d(stg + (uint32_t)(buf ^ 1) * 4096, &map_out, n0 + c + 64, row0w, prev_bar + (uint32_t)(buf ^ 1) * 8);
                 }
@@ -386,18 +425,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint32_t at = rowb + ((uint32_t)((((c & 32) >> 3) + i) ^ (lane & 7)) << 4);
-            uint4 v;
-            __half2* h = reinterpret_cast<__half2*>(&v);
-            if (beta != 0.f) {
+            uint4 v = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
+            if (!GATE && beta != 0.f) {
+              __half2* h = reinterpret_cast<__half2*>(&v);
               asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(at) : "memory");
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float2 prev = __half22float2(h[e]);
                 h[e] = __floats2half2_rn(fmaf(beta, prev.x, sum[8 * i + 2 * e]), fmaf(beta, prev.y, sum[8 * i + 2 * e + 1]));
               }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(sum[8 * i + 2 * e], sum[8 * i + 2 * e + 1]);
             }
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
           }
@@ -453,6 +489,8 @@ int sk_get_workspace(int dev, cudaStream_t stream, size_t partial_floats, int n_
     // stream order)
     if (w.partials) LCU_CUDA(cudaFreeAsync(w.partials, stream));
     if (w.flags) LCU_CUDA(cudaFreeAsync(w.flags, stream));
+    partial_floats = std::max(partial_floats, w.partial_floats);  // (both only grow, whichever of the two asked for more)
+    n_flags = std::max(n_flags, w.n_flags);
     w = sk_workspace{};
     LCU_CUDA(cudaMalloc(&w.partials, partial_floats * sizeof(float)));
     LCU_CUDA(cudaMalloc(&w.flags, (size_t)n_flags * sizeof(int)));
@@ -464,9 +502,11 @@ int sk_get_workspace(int dev, cudaStream_t stream, size_t partial_floats, int n_
   return LCU_OK;
 }
 
-template <int NB>
+// GATE: w is the stack [w1; w3] of two [N][K] matrices and out is [m][N]
+template <int NB, bool GATE>
 int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream) {
   constexpr int BN = 256 * NB;
+  constexpr int BN_OUT = GATE ? BN / 2 : BN;
   CUtensorMap map_a, map_b;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)m}, strides[1] = {(uint64_t)ldx * 2};
@@ -475,7 +515,7 @@ int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
     if (rc) return rc;
   }
   {
-    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N}, strides[1] = {(uint64_t)K * 2};
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)(GATE ? 2 * N : N)}, strides[1] = {(uint64_t)K * 2};
     const uint32_t box[2] = {(uint32_t)SK_BK, 128u};
     int rc = tc_encode_map(&map_b, w, 2, dims, strides, box);
     if (rc) return rc;
@@ -495,18 +535,18 @@ int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
   int dev = 0;
   LCU_CUDA(cudaGetDevice(&dev));
   if (dev < 16 && !attr_done[dev]) {
-    LCU_CUDA(cudaFuncSetAttribute(gemm_tc_sk_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    LCU_CUDA(cudaFuncSetAttribute(gemm_tc_sk_kernel<NB, GATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_done[dev] = true;
   }
-  const int tiles_m = (m + 2 * SK_BM - 1) / (2 * SK_BM), n_tiles = tiles_m * (N / BN);
+  const int tiles_m = (m + 2 * SK_BM - 1) / (2 * SK_BM), n_tiles = tiles_m * (N / BN_OUT);
   int clusters = gemv_sm_count() / 2;
   if (clusters > n_tiles) clusters = n_tiles < 1 ? 1 : std::min<long long>(clusters, (long long)n_tiles * (K / SK_BK));
   sk_workspace* ws = nullptr;
   int rc = sk_get_workspace(dev, stream, (size_t)clusters * 256 * BN, clusters, &ws);
   if (rc) return rc;
   const int seq = ++ws->seq;
-  LCU_CUDA(launch_after(gemm_tc_sk_kernel<NB>, dim3(2 * clusters), dim3(SK_THREADS), smem, stream, map_a, map_b, map_out, m, N, K, beta, nstages, tiles_m,
-                        n_tiles, ws->partials, ws->flags, seq, err));
+  LCU_CUDA(launch_after(gemm_tc_sk_kernel<NB, GATE>, dim3(2 * clusters), dim3(SK_THREADS), smem, stream, map_a, map_b, map_out, m, N, K, beta, nstages,
+                        tiles_m, n_tiles, ws->partials, ws->flags, seq, err, GATE ? N : 0));
   return LCU_OK;
 }
 
@@ -521,7 +561,17 @@ int launch_gemm_tc_sk(__half* out, const __half* lhs, int ldx, const __half* w, 
                       int tile_n) {
   LCU_REQUIRE(gemm_tc_sk_supported(m, N, K, ldx, lhs, w, out, tile_n), "gemm_tc_sk: unsupported shape m=%d N=%d K=%d ldx=%d tile %d", m, N, K, ldx,
               tile_n);
-  return tile_n == 512 ? launch_sk<2>(out, lhs, ldx, w, m, N, K, beta, err, stream) : launch_sk<1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+  return tile_n == 512 ? launch_sk<2, false>(out, lhs, ldx, w, m, N, K, beta, err, stream) : launch_sk<1, false>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+}
+
+bool gemm_tc_gated_supported(int m, int f, int K, int ldx, const void* lhs, const void* w, const void* out) {
+  return m >= 1 && f % 128 == 0 && K % SK_BK == 0 && ldx % 8 == 0 && ((uintptr_t)lhs & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+}
+
+int launch_gemm_tc_gated(__half* out, const __half* lhs, int ldx, const __half* w13, int m, int f, int K, int* err, cudaStream_t stream, int tile_n) {
+  LCU_REQUIRE(gemm_tc_gated_supported(m, f, K, ldx, lhs, w13, out) && (tile_n == 256 || (tile_n == 512 && f % 256 == 0)),
+              "gemm_tc_gated: unsupported shape m=%d f=%d K=%d ldx=%d tile=%d", m, f, K, ldx, tile_n);
+  return tile_n == 512 ? launch_sk<2, true>(out, lhs, ldx, w13, m, f, K, 0.f, err, stream) : launch_sk<1, true>(out, lhs, ldx, w13, m, f, K, 0.f, err, stream);
 }
 
 }  // namespace lcu

@@ -758,6 +758,31 @@ int launch_quantize_absmax_uint8(uint8_t* q, __half* scales, const __half* in, s
   return LCU_OK;
 }
 
+// every half-precision a: silu_of_half against the division it replaces, bit for bit (NaN = NaN)
+__global__ void silu_check_kernel(unsigned long long* counts) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 65536u) return;
+  const float a = __half2float(__ushort_as_half((unsigned short)i));
+  const float want = a / (1.0f + expf(-a)), got = silu_of_half(a);
+  const bool same = (want != want && got != got) || __float_as_uint(want) == __float_as_uint(got);
+  atomicAdd(counts, 1ull);
+  if (!same) atomicAdd(counts + 1, 1ull);
+}
+
+int silu_arithmetic_check(unsigned long long* checked_out, unsigned long long* differences_out) {
+  unsigned long long* d = nullptr;
+  LCU_CUDA(cudaMalloc(&d, 16));
+  LCU_CUDA(cudaMemset(d, 0, 16));
+  silu_check_kernel<<<256, 256>>>(d);
+  unsigned long long h[2] = {0, 0};
+  cudaError_t e = cudaMemcpy(h, d, 16, cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  LCU_CUDA(e);
+  *checked_out = h[0];
+  *differences_out = h[1];
+  return LCU_OK;
+}
+
 int quantizer_arithmetic_check(unsigned long long* checked_out, unsigned long long* differences_out) {
   unsigned long long* d = nullptr;
   LCU_CUDA(cudaMalloc(&d, 16));

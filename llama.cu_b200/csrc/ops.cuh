@@ -89,5 +89,7 @@ int launch_token_to_ids(short* ids, const int* token, cudaStream_t stream);
 // compares the quantizer's fast arithmetic with the reference's (IEEE division, roundf) for every (value, scale) pair of its
 // domain on the device: number of pairs checked and number of differing bytes
 int quantizer_arithmetic_check(unsigned long long* checked_out, unsigned long long* differences_out);
+// silu_of_half (common.cuh) against a / (1 + expf(-a)) for all 65536 half-precision a: values compared, values that differ
+int silu_arithmetic_check(unsigned long long* checked_out, unsigned long long* differences_out);
 
 }  // namespace lcu

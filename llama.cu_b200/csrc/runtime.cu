@@ -25,6 +25,7 @@
 #include <thread>
 
 #include "attention.cuh"
+#include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "ops.cuh"
 #include "prefill.cuh"
@@ -942,14 +943,16 @@ int context_impl::enqueue_prefill(int m_rows) {
     return k == 0 ? expand(g, qkv, 3) : k == 2 ? expand(g, w13, 2) : expand(g, one, 1);
   };
   // the GEMM of the oldest expanded job: waits for its expansion, runs, releases the buffer
-  auto gemm_expanded = [&](gpu_state& g, __half* out, const __half* lhs, size_t rows, size_t cols, float beta) -> int {
+  // (gate: the buffer holds w1|w3 and out takes silu(lhs . w1^T) * (lhs . w3^T), rows = 2 f; the value is the tile width)
+  auto gemm_expanded = [&](gpu_state& g, __half* out, const __half* lhs, size_t rows, size_t cols, float beta, int gate = 0) -> int {
     const int b = (int)(g.deq_used % 2);
     LCU_CUDA(cudaStreamWaitEvent(g.stream, g.deq_done[b], 0));
     dev_matrix w;
     w.w = g.deq_buf[b];
     w.rows = rows;
     w.cols = cols;
-    LCU_TRY(matmul_rows(out, lhs, w, m_rows, beta, g.state + 3, g.stream));
+    if (gate) LCU_TRY(launch_gemm_tc_gated(out, lhs, (int)cols, g.deq_buf[b], m_rows, (int)(rows / 2), (int)cols, g.state + 3, g.stream, gate));
+    else LCU_TRY(matmul_rows(out, lhs, w, m_rows, beta, g.state + 3, g.stream));
     LCU_CUDA(cudaEventRecord(g.gemm_done[b], g.stream));
     ++g.deq_used;
     return LCU_OK;
@@ -1021,13 +1024,20 @@ int context_impl::enqueue_prefill(int m_rows) {
     if (fuse_u8 || (fuse && (char*)L.w3.w == (char*)L.w1.w + (size_t)f * d * 2)) {
       dev_matrix w13 = L.w1;
       w13.rows = 2 * (size_t)f;
+      // the tensor-core GEMM is on and no kernel is forced: w1|w3 and the gate may run as one launch (tile width, 0 = apart)
+      const bool gate_allowed = pt.tc_min_rows > 0 && m_rows >= pt.tc_min_rows && pt.tc_tile_n == 0 && pt.tc_pair < 0 && gemm_tc_sk_mode() != 0;
+      int gate_tile = gate_allowed ? gemm_tc_gated_tile(m_rows, (int)f, (int)d) : 0;
       if (fuse_u8) {
-        LCU_TRY(gemm_expanded(g, g.h1, g.norm, 2 * (size_t)f, d, 0.f));
+        if (!gemm_tc_gated_supported(m_rows, (int)f, (int)d, (int)d, g.norm, g.deq_buf[0], g.hs) || ((uintptr_t)g.deq_buf[1] & 15)) gate_tile = 0;
+        LCU_TRY(gemm_expanded(g, gate_tile ? g.hs : g.h1, g.norm, 2 * (size_t)f, d, 0.f, gate_tile));
         LCU_TRY(expand_job(g, l, 3));
+      } else if (gate_tile && gemm_tc_gated_supported(m_rows, (int)f, (int)d, (int)d, g.norm, w13.w, g.hs)) {
+        LCU_TRY(launch_gemm_tc_gated(g.hs, g.norm, (int)d, (const __half*)w13.w, m_rows, (int)f, (int)d, err, g.stream, gate_tile));
       } else {
+        gate_tile = 0;
         LCU_TRY(matmul_rows(g.h1, g.norm, w13, m_rows, 0.f, err, g.stream));
       }
-      LCU_TRY(launch_silu_rows(g.hs, g.h1, m_rows, f, g.stream));
+      if (!gate_tile) LCU_TRY(launch_silu_rows(g.hs, g.h1, m_rows, f, g.stream));
     } else {
       LCU_TRY(matmul_rows(g.h1, g.norm, L.w1, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));
       LCU_TRY(matmul_rows(g.h3, g.norm, L.w3, m_rows, 0.f, err, g.stream, g.deq, g.deq_halves));

@@ -175,6 +175,53 @@ def test_prefill_gemm_with_balanced_k_steps(lcu, m, k, n, beta, tile):
     assert np.array_equal(y, y2)
 
 
+@pytest.mark.parametrize("tile", [256, 512])
+@pytest.mark.parametrize("m,k,f", [(512, 4096, 11008), (2000, 1024, 2816), (129, 64, 256), (515, 512, 1280),
+                                   # fewer tiles than SM pairs: every tile is shared by several pairs
+                                   (700, 4096, 5632), (300, 2048, 128)])
+def test_gated_gemm_equals_the_stacked_product_followed_by_silu(lcu, m, k, f, tile):
+    """w1|w3 and the SiLU gate as one launch (both products of a tile in tensor memory, the gate in the epilogue) against
+    the two-step path the reference takes (llama_cu.cu:1180-1183): the stacked product stored as halves, then silu on
+    those halves.  Equal bits - the one launch rounds the products to half before the gate exactly as the store does -
+    when both paths add partial sums in the same order, which the balanced kernel with the same tile width guarantees."""
+    if f % (tile // 2):
+        pytest.skip("tile width does not divide the output")
+    rng = np.random.default_rng(m + 3 * f)
+    x = f16(rng.standard_normal((m, k)))
+    w13 = O.synth_f16(2 * f * k, 9, f"gate{f}x{k}", 0.05).reshape(2 * f, k)
+    # the two-step path with the same tile shape and K split: half a tile of columns of w1 beside the same of w3
+    hw = tile // 2
+    order = np.concatenate([np.concatenate([np.arange(c, c + hw), f + np.arange(c, c + hw)]) for c in range(0, f, hw)])
+    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_sk", tile))
+    try:
+        h = lcu.matmul_nt(x, np.ascontiguousarray(w13[order]))
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_sk", -1))
+    stacked = np.empty((m, 2 * f), np.uint16)
+    stacked[:, order] = h
+    want = lcu.silu(np.ascontiguousarray(stacked[:, :f]), np.ascontiguousarray(stacked[:, f:]))
+    got = lcu.matmul_nt_gated(x, w13, tile)
+    assert np.array_equal(got, want)
+    # and against the oracle's product + gate (binary64 accumulation), at the GEMM's tolerance
+    ho = np.zeros((m, 2 * f), np.uint16)
+    L.orc_matmul_nt_f16(ho.reshape(-1), x.reshape(-1), w13.reshape(-1), m, k, 2 * f, 0.0, 1)
+    a, b = np.ascontiguousarray(ho[:, :f]), np.ascontiguousarray(ho[:, f:])
+    ref = np.zeros_like(a)
+    L.orc_silu(ref.reshape(-1), a.reshape(-1), b.reshape(-1), a.size)
+    scale = max(1.0, float(np.abs(f32(ref)).max()))
+    assert np.abs(f32(got) - f32(ref)).max() <= 4e-3 * scale
+
+
+def test_gate_arithmetic_equals_the_division_for_every_half(lcu):
+    """The one-launch w1|w3 + gate forms a / (1 + expf(-a)) with a refined reciprocal instead of the IEEE division
+    (llama_cu.cu:533-539): compared on the device for all 65536 half-precision a, no differing bit."""
+    import ctypes as C
+    checked, diff = C.c_uint64(0), C.c_uint64(0)
+    lcu.check(lcu.lib.lcu_selftest_silu_arithmetic(C.byref(checked), C.byref(diff)))
+    assert checked.value == 65536
+    assert diff.value == 0
+
+
 def test_quantizer_fast_arithmetic_equals_division_and_roundf_on_its_whole_domain(lcu):
     """The quantizer forms its bytes with a reciprocal multiply, one residual correction and trunc(v + 0.5f) instead of the
     reference's IEEE division and roundf (transform.cu:60-80).  The device compares the two for every pair the quantizer

@@ -110,6 +110,34 @@ def test_long_prompt_attention_paths_against_oracle(lcu):
     model.close()
 
 
+@pytest.mark.parametrize("bs", [0, 128])
+def test_long_prompt_with_gate_in_the_gemm_epilogue_against_oracle(lcu, bs):
+    """A 300-token prompt with w1|w3 and the SiLU gate as one launch (both tile widths) and as product + gate kernel
+    (llama_cu.cu:1180-1183): each reproduces the oracle's next-token distribution, and the one-launch passes give the
+    same token as the two-step pass."""
+    scale = 0.08
+    cfg = dict(dim=256, multiple_of=256, n_heads=2, n_layers=3, n_vocab=1000)
+    model = lcu.Model.synthetic(block_size=bs, seed=77, scale=scale, **cfg)
+    om = O.OracleModel(block_size=bs, seed=77, scale=scale, context_len=320, temperature=0.8, **cfg)
+    prompt = O.synth_tokens(300, 77, lo=3, hi=1000)
+    om.next_token(prompt)
+    po = f32(om.probs())
+    tokens = []
+    try:
+        for mode in (0, 256, 512, -1):
+            lcu.check(lcu.lib.lcu_set_tuning(b"prefill_gate_fused", mode))
+            ctx = lcu.Context(model, context_len=320, temperature=0.8)
+            tokens.append(ctx.next_token(prompt))
+            pr = f32(ctx.probs())
+            assert np.abs(pr - po).max() <= 0.02 * po.max() + 1e-4, mode
+            ctx.close()
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_gate_fused", -1))
+    assert len(set(tokens)) == 1, tokens
+    om.close()
+    model.close()
+
+
 def test_fresh_contexts_repeat_the_same_distribution(lcu):
     """A context is usable the moment it is created: its zeroed arenas and its RoPE table are ordered on the context's
     own stream.  Twenty contexts in a row, each used at once with a context length whose arenas take a while to clear,
