@@ -34,6 +34,7 @@ namespace {
 constexpr int BM = 128;      // output rows (tokens) per tile = TMEM lanes
 constexpr int BK = 64;       // K per stage: 64 halves = one 128-byte swizzled row
 constexpr int TC_THREADS = 192;
+constexpr int TC_MAX_STAGES = 12;  // one-SM kernel: barrier slots for the ring
 
 // half(acc + beta * previous) for 32 consecutive outputs of one row (64 bytes, 16-byte aligned)
 __device__ __forceinline__ void store_row_piece(__half* o, const float (&acc)[32], float beta) {
@@ -69,7 +70,13 @@ template <int BN, int S>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                                                 __half* out, int m, int N, int K, float beta, int nstages, int a_box_rows,
                                                                 int* err) {
-  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
+  // A stage holds the activation box (a_box_rows rows, 2 to 16 KB) and the BN weight rows.  The MMA reads 128 operand rows
+  // from the box's address: with a short box the rest comes from whatever follows in the ring, reaches output rows >= m
+  // only, and those are never stored.  Short prompts so get up to 12 stages of weights in flight instead of 6.
+  constexpr uint32_t B_BYTES = BN * BK * 2;
+  const uint32_t A_BYTES = (uint32_t)a_box_rows * (BK * 2), STAGE = A_BYTES + B_BYTES;
+  constexpr int MAXS = TC_MAX_STAGES;
+  constexpr uint32_t TM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;  // tensor memory comes in powers of two
   // instruction descriptor: fp32 accumulate, fp16 x fp16, both K-major, N = BN, M = 128
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   constexpr int CW = BN / S;        // columns owned by each CTA of the cluster
@@ -80,8 +87,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms are 1024-byte aligned
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t red = base + (uint32_t)nstages * STAGE;  // [S-1 senders][CW/4][128 rows] float4
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)nstages * STAGE + RED_BYTES);  // full[8], empty[8], tmem_full
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)nstages * STAGE + RED_BYTES);  // full[MAXS], empty[MAXS], tmem_full
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAXS + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = S > 1 ? (int)cluster_ctarank() : 0;
@@ -92,13 +99,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   if (threadIdx.x == 0) {
     for (int i = 0; i < nstages; ++i) {
       mbar_init(smem_u32(&bars[i]), 1);
-      mbar_init(smem_u32(&bars[8 + i]), 1);
+      mbar_init(smem_u32(&bars[MAXS + i]), 1);
     }
-    mbar_init(smem_u32(&bars[16]), 1);
+    mbar_init(smem_u32(&bars[2 * MAXS]), 1);
     fence_mbar_init();
   }
   if (warp == 1) {  // tensor-memory allocation: BN fp32 columns x 128 lanes
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -116,12 +123,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     if (lane == 0) {  // ---- TMA producer
       for (int kb = 0; kb < nk; ++kb) {
         const int s = kb % nstages, use = kb / nstages;
-        if (use > 0 && !mbar_wait(smem_u32(&bars[8 + s]), (use - 1) & 1, err, DEV_ERR_EMPTY_WAIT)) break;
+        if (use > 0 && !mbar_wait(smem_u32(&bars[MAXS + s]), (use - 1) & 1, err, DEV_ERR_EMPTY_WAIT)) break;
         const uint32_t full = smem_u32(&bars[s]);
         const uint32_t dst = base + (uint32_t)s * STAGE;
-        // few rows: the activation box covers a_box_rows rows only; the rest of the 128-row operand keeps whatever
-        // shared memory held, which reaches output rows >= m only, and those are never stored
-        mbar_arrive_expect_tx(full, (uint32_t)a_box_rows * (BK * 2) + B_BYTES);
+        mbar_arrive_expect_tx(full, STAGE);
         tma_load_2d(dst, &map_a, (kb0 + kb) * BK, m0, full);
         tma_load_2d(dst + A_BYTES, &map_b, (kb0 + kb) * BK, n0, full);
       }
@@ -139,15 +144,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)  // 16 halves = 32 bytes = 2 descriptor address units per K step
           tc_mma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0);
-        tc_commit(smem_u32(&bars[8 + s]));  // the stage is free once these MMAs have read it
+        tc_commit(smem_u32(&bars[MAXS + s]));  // the stage is free once these MMAs have read it
       }
-      tc_commit(smem_u32(&bars[16]));  // accumulator complete (also on the error path: lets the epilogue leave)
+      tc_commit(smem_u32(&bars[2 * MAXS]));  // accumulator complete (also on the error path: lets the epilogue leave)
     }
   } else {
     // ---- epilogue: warp w may touch TMEM lanes 32 * (w % 4) ... + 31 only
     const int quad = warp & 3;
     const int trow = quad * 32 + lane;  // row of the tile = TMEM lane
-    const bool ok = mbar_wait(smem_u32(&bars[16]), 0, err, DEV_ERR_TMEM_WAIT);
+    const bool ok = mbar_wait(smem_u32(&bars[2 * MAXS]), 0, err, DEV_ERR_TMEM_WAIT);
     tc_fence_after();
     go = __all_sync(0xffffffffu, ok && *(volatile int*)err == 0);  // warp-uniform: tcgen05.ld is .aligned
     if (S > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // every CTA of the cluster is running
@@ -162,7 +167,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 #pragma unroll
           for (int i = 0; i < 32; ++i) own[S == 1 ? 0 : c % CPR][i] = __uint_as_float(r[i]);
           if (S == 1) {
-            if (m0 + trow < m) store_row_piece(out + (size_t)(m0 + trow) * N + n0 + c * 32, own[0], beta);
+            // (a tile width that does not divide N: the last tile's columns past N hold products with zero-filled rows)
+            if (m0 + trow < m && n0 + c * 32 < N) store_row_piece(out + (size_t)(m0 + trow) * N + n0 + c * 32, own[0], beta);
           }
         } else {
           // float4 number j4 of this row goes to ((j4 * 128 + row) * 16) so that a warp's stores are contiguous
@@ -205,7 +211,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TM_COLS) : "memory");
   }
 }
 
@@ -444,12 +450,13 @@ int launch_bn(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
   if (rc) return rc;
   rc = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN, true);
   if (rc) return rc;
-  constexpr size_t STAGE = (size_t)(BM + BN) * BK * 2;
+  const size_t STAGE = (size_t)(a_box_rows + BN) * BK * 2;
   constexpr size_t RED = S > 1 ? (size_t)(S - 1) * BM * (BN / S) * 4 : 0;
   int nstages = (int)((200 * 1024 - RED) / STAGE);
-  if (nstages > 8) nstages = 8;
+  if (nstages > TC_MAX_STAGES) nstages = TC_MAX_STAGES;
   if (nstages > K / BK) nstages = K / BK;
-  const size_t smem = nstages * STAGE + RED + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
+  // (the MMA reads BM operand rows from the last stage's box too: the slack below covers what a short box leaves out)
+  const size_t smem = nstages * STAGE + RED + (size_t)(BM - a_box_rows) * BK * 2 + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
   static bool attr_done[16] = {};
   int dev = 0;
   LCU_CUDA(cudaGetDevice(&dev));
@@ -458,7 +465,7 @@ int launch_bn(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
     attr_done[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N / BN) * S, (m + BM - 1) / BM);
+  cfg.gridDim = dim3(((N + BN - 1) / BN) * S, (m + BM - 1) / BM);
   cfg.blockDim = dim3(TC_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -616,7 +623,7 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
   // 512-wide tiles (a third less operand traffic per multiply-add, no overlap of epilogue and main loop).  Which one is
   // fastest depends on how the tile count meets the 74 pairs (gemm_tc_estimates).  Mode -1 = that rule; 256 / 512 force
   // the balanced kernel with that tile width; 0 = never.
-  if (force_pair < 0 && !force_bn && m > BM) {
+  if (force_pair < 0 && !force_bn && (m > BM || gemm_tc_sk_mode() > 0)) {
     const int mode = gemm_tc_sk_mode();
     int tile = mode > 0 ? mode : 0;
     if (mode < 0) {
@@ -645,11 +652,33 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
     LCU_REQUIRE((pair == 128 || pair == 256) && N % pair == 0, "gemm_tc: pair tile width %d does not divide N=%d", pair, N);
     return pair == 256 ? launch_pair<256>(out, lhs, ldx, w, m, N, K, beta, err, stream) : launch_pair<128>(out, lhs, ldx, w, m, N, K, beta, err, stream);
   }
-  int bn = force_bn;
+  int bn = force_bn, split = force_split;
   if (!bn) bn = N % 128 == 0 ? 128 : N % 64 == 0 ? 64 : 32;  // measured: the widest tile wins even when it leaves SMs idle
-  LCU_REQUIRE((bn == 32 || bn == 64 || bn == 128) && N % bn == 0, "gemm_tc: tile width %d does not divide N=%d", bn, N);
+  if (!force_bn && force_split < 0 && m <= BM && N % 128 == 0) {
+    // Up to 128 rows the product streams the weights once and an SM takes in about 50 GB/s whatever its tile's width, so
+    // what counts is that all SMs stream the same number of bytes: tile widths from 96 to 256 (the last tile may hang
+    // over N) and split-K for the 128-wide tile are compared by waves x max(bytes per CTA / 50 GB/s, 0.27 us per K step)
+    // + 7 us per wave, against the whole matrix at 5.8 TB/s.  7B: w1|w3 (N = 22016) takes 160-wide tiles (138 CTAs, one
+    // wave, instead of 172 in two: 51 -> 38 us), wq|wk|wv (12288) 96-wide ones (128 CTAs instead of 96).
+    const double nk = K / BK;
+    double best = 1e30;
+    const int widths[6] = {128, 96, 160, 192, 224, 256};
+    for (int i = 0; i < 6; ++i)
+      for (int sp = 1; sp <= (widths[i] == 128 ? 4 : 1); sp *= 2) {
+        if (nk < 8 * sp) continue;
+        const long ctas = (long)((N + widths[i] - 1) / widths[i]) * sp, waves = (ctas + sms - 1) / sms;
+        const double per_cta = std::max(widths[i] * 128.0 * nk / sp / 50e3, nk / sp * 0.27);
+        const double est = std::max(waves * per_cta, (double)N * K * 2 / 5.8e6) + 7.0 * waves + (sp > 1 ? 1.5 : 0.0);
+        if (est < best - 0.5) {  // (ties stay with the earlier candidate)
+          best = est;
+          bn = widths[i];
+          split = sp;
+        }
+      }
+  }
+  LCU_REQUIRE(bn % 32 == 0 && bn >= 32 && bn <= 256, "gemm_tc: tile width %d is not a multiple of 32 up to 256", bn);
+  if (bn == 128 && N % 128) split = 1;  // (the split-K clusters own whole 128-wide tiles)
   if (bn == 128) {
-    int split = force_split;
     if (split < 0) {
       const long tiles = (long)(N / 128) * ((m + BM - 1) / BM);
       split = tiles * 4 <= sms ? 4 : tiles * 2 <= sms ? 2 : 1;
@@ -660,8 +689,15 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
     if (split == 2) return launch_bn<128, 2>(out, lhs, ldx, w, m, N, K, beta, err, stream);
     return launch_bn<128, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
   }
-  if (bn == 64) return launch_bn<64, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
-  return launch_bn<32, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+  switch (bn) {
+    case 32: return launch_bn<32, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+    case 64: return launch_bn<64, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+    case 96: return launch_bn<96, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+    case 160: return launch_bn<160, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+    case 192: return launch_bn<192, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+    case 224: return launch_bn<224, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+    default: return launch_bn<256, 1>(out, lhs, ldx, w, m, N, K, beta, err, stream);
+  }
 }
 
 }  // namespace lcu

@@ -99,16 +99,17 @@ struct sk_schedule {
   int C, Cs, c, nk, full_waves, first_split_tile;  // Cs: pairs that take part in the split tiles (every one of them has a K step)
   long long U, u, u1;  // units of the split tiles: all, next of this pair, end of this pair's range
   int wave;
-  __device__ void init(int n_tiles, int nk_, int C_, int c_) {
+  __device__ void init(int n_tiles, int nk_, int C_, int c_, int share_cap) {
     C = C_;
     c = c_;
     nk = nk_;
     full_waves = n_tiles / C;
     first_split_tile = full_waves * C;
     U = (long long)(n_tiles - first_split_tile) * nk;
-    // at most three pairs per shared tile: its owner adds the other pairs' sums one after the other at the very end of
-    // the kernel, and what it reads of the first two is requested ahead
-    const long long split_pairs = (long long)(n_tiles - first_split_tile) * 3;
+    // at most share_cap pairs per shared tile (three for long prompts: the owner adds the other pairs' 256-row sums
+    // one after the other at the very end of the kernel, and what it reads of the first two is requested ahead; eight
+    // for prompts of up to 128 rows, whose sums are small)
+    const long long split_pairs = (long long)(n_tiles - first_split_tile) * share_cap;
     Cs = (int)min(min((long long)C, U), split_pairs);
     u = c < Cs ? sk_first_unit(U, c, Cs) : 0;
     u1 = c < Cs ? sk_first_unit(U, c + 1, Cs) : 0;
@@ -153,7 +154,8 @@ template <int NB, bool GATE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
     gemm_tc_sk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_out, int m, int N, int K,
-                      float beta, int nstages, int tiles_m, int n_tiles, float* workspace, int* flags, int seq, int* err, int gate_rows) {
+                      float beta, int nstages, int tiles_m, int n_tiles, float* workspace, int* flags, int seq, int* err, int gate_rows,
+                      int share_cap) {
   constexpr int BN = 256 * NB;
   constexpr int BN_OUT = GATE ? BN / 2 : BN;  // output columns per tile
   constexpr uint32_t A_BYTES = SK_BM * SK_BK * 2, B_BYTES = 128 * SK_BK * 2, STAGE = A_BYTES + NB * B_BYTES;
@@ -174,7 +176,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
   const int C = gridDim.x / 2, cluster_id = blockIdx.x / 2;
   const int nk = K / SK_BK;
   sk_schedule sched;
-  sched.init(n_tiles, nk, C, cluster_id);
+  sched.init(n_tiles, nk, C, cluster_id, share_cap);
   int tile, kb0, kb1;
   bool split;
 
@@ -280,16 +282,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
       if (kb0 > 0) {
         // the tail of a tile that another pair owns: fp32 partial sums into this pair's workspace slot
         float* slot = workspace + (size_t)cluster_id * (256 * BN);
+        // (rows past the last one are neither written here nor read by the owner: a short prompt hands over m rows, not 256)
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = 0; c < BN && row - lane < m; c += 32) {
           uint32_t r[32];
           tc_ld_32x32(acc + (uint32_t)c, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           // float4 number ((piece * 8 + i) * 256 + row): the 32 lanes of a warp store 512 contiguous bytes
           float4* dst = reinterpret_cast<float4*>(slot) + (size_t)(c >> 5) * 8 * 256 + trow;
+          if (row < m) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            dst[i * 256] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            for (int i = 0; i < 8; ++i)
+              dst[i * 256] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+          }
         }
         __threadfence();
         __syncwarp();
@@ -318,13 +323,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
           for (int q = 0; q < 2; ++q)
             if (q < n_peers) {
               const float4* src = peer_piece(q, piece);
+              if (row < m) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) nxt[q][i] = __ldcg(src + i * 256);
+                for (int i = 0; i < 8; ++i) nxt[q][i] = __ldcg(src + i * 256);
+              }
             }
         };
-        if (n_peers > 0) fetch(0);
         const int row0w = row - lane;  // first of this warp's 32 rows
-        if (beta != 0.f) {
+        const bool rows_live = row0w < m;  // a warp whose rows all lie past the last one has nothing to add or store
+        if (n_peers > 0 && rows_live) fetch(0);
+        if (beta != 0.f && rows_live) {
           if (lane == 0) {
             sk_store_wait_read<0>();
             mbar_arrive_expect_tx(prev_bar, 4096);
@@ -336,7 +344,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
         auto piece_of = [](int idx) { return GATE ? (idx >> 1) + (idx & 1) * (BN / 64) : idx; };
         uint32_t first[16];  // GATE: the half-rounded products of the first matrix for the piece in flight
 #pragma unroll 1
-        for (int idx = 0; idx < BN / 32; ++idx) {
+        for (int idx = 0; idx < BN / 32 && rows_live; ++idx) {
           const int piece = piece_of(idx);
           uint32_t r[32];
           tc_ld_32x32(acc + (uint32_t)(piece * 32), r);
@@ -362,7 +370,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
                   sum[4 * i + 3] += cur[q][i].w;
                 }
               }
-            for (int q = 2; q < n_peers; ++q) {
+            for (int q = 2; q < n_peers && row < m; ++q) {
               const float4* src = peer_piece(q, piece);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
@@ -546,7 +554,7 @@ int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
   if (rc) return rc;
   const int seq = ++ws->seq;
   LCU_CUDA(launch_after(gemm_tc_sk_kernel<NB, GATE>, dim3(2 * clusters), dim3(SK_THREADS), smem, stream, map_a, map_b, map_out, m, N, K, beta, nstages,
-                        tiles_m, n_tiles, ws->partials, ws->flags, seq, err, GATE ? N : 0));
+                        tiles_m, n_tiles, ws->partials, ws->flags, seq, err, GATE ? N : 0, m <= SK_BM ? 8 : 3));
   return LCU_OK;
 }
 

@@ -7,7 +7,7 @@ namespace lcu {
 
 struct prefill_tuning {
   int tc_min_rows = 9;  // fp16 weights: this many rows or more go to the tcgen05 GEMM (0 = never)
-  int tc_tile_n = 0;    // one-SM kernel: 0 = pick the tile width per shape; 32 / 64 / 128 forces it
+  int tc_tile_n = 0;    // one-SM kernel: 0 = pick the tile width per shape; a multiple of 32 up to 256 forces it
   int u8_deq_min_rows = 9;   // u8 weights: this many rows or more take a dequantization pass + the tcgen05 GEMM (0 = never);
                              // measured at 7B: 9.3 ms for any prompt of 9..47 tokens against 7..34 ms through GEMV passes
   int fuse = 1;         // fp16 prompts: wq|wk|wv and w1|w3 as one GEMM each over the stacked matrices

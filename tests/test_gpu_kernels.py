@@ -119,7 +119,12 @@ def test_matmul_small_shapes(lcu, m, k, n, bs, beta):
                                              (200, 1024, 256, 1.0, 64), (77, 4096, 1024, 0.0, 32), (300, 11008, 128, 0.0, 0),
                                              (257, 4096, 4096, 1.0, 0),
                                              # more pair tiles than SM pairs: the persistent loop takes several tiles per pair
-                                             (300, 256, 22016, 1.0, 0), (257, 320, 12288, 0.0, 0)])
+                                             (300, 256, 22016, 1.0, 0), (257, 320, 12288, 0.0, 0),
+                                             # tile widths that do not divide N: the last tile hangs over the matrix
+                                             (16, 512, 22016, 1.0, 160), (100, 256, 1024, 0.0, 96), (128, 512, 4096, 1.0, 224),
+                                             (33, 1024, 2560, 0.0, 192), (64, 256, 1536, 1.0, 256), (9, 64, 32, 0.0, 96),
+                                             # the widths the dispatch picks for short prompts by itself (7B shapes, short K)
+                                             (16, 512, 12288, 0.0, 0), (128, 512, 22016, 1.0, 0)])
 def test_prefill_tensor_core_gemm(lcu, m, k, n, beta, tile):
     """fp16 weights with more than 8 rows run on tcgen05 with the accumulator in tensor memory: compared with
     the oracle's binary64-accumulated product (tolerance 2e-3 of the largest output: fp32 accumulation in a
@@ -151,7 +156,9 @@ def test_prefill_tensor_core_gemm(lcu, m, k, n, beta, tile):
                                         # whole waves first, then the shared tiles (2 x 86 tiles for 74 pairs)
                                         (512, 320, 22016, 0.0), (1000, 2048, 2560, 1.0),
                                         # smallest legal K and N, ragged rows
-                                        (131, 64, 512, 1.0), (515, 128, 1024, 0.0)])
+                                        (131, 64, 512, 1.0), (515, 128, 1024, 0.0),
+                                        # short prompts: only the rows that exist are handed over between pairs
+                                        (16, 4096, 1536, 1.0), (100, 2048, 2560, 0.0), (1, 512, 512, 1.0)])
 def test_prefill_gemm_with_balanced_k_steps(lcu, m, k, n, beta, tile):
     """The tcgen05 GEMM that deals the K steps of the last wave's tiles evenly over the SM pairs (partial sums through a
     workspace, added in pair order): against the oracle's binary64-accumulated product, same tolerance as the whole-tile
