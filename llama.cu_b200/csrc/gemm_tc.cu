@@ -69,12 +69,16 @@ __device__ __forceinline__ void st_dsmem_f4(uint32_t addr, float a, float b, flo
 template <int BN, int S>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                                                 __half* out, int m, int N, int K, float beta, int nstages, int a_box_rows,
-                                                                int* err) {
+                                                                int kbs, int* err) {
   // A stage holds the activation box (a_box_rows rows, 2 to 16 KB) and the BN weight rows.  The MMA reads 128 operand rows
   // from the box's address: with a short box the rest comes from whatever follows in the ring, reaches output rows >= m
   // only, and those are never stored.  Short prompts so get up to 12 stages of weights in flight instead of 6.
+  // A stage is kbs (1, 2 or 4) 64-wide k-blocks, brought in by ONE tensor copy per operand (a three-dimensional box:
+  // 64 halves x rows x k-blocks, which lands as kbs swizzled operand tiles one after the other): the copies, not the
+  // bytes, set the pace of a CTA that streams weights for few rows - 0.28 us per k-block with one box per k-block
+  // whether the tile is 32 or 128 wide, on 32 or 148 SMs, with 6 or 11 stages.
   constexpr uint32_t B_BYTES = BN * BK * 2;
-  const uint32_t A_BYTES = (uint32_t)a_box_rows * (BK * 2), STAGE = A_BYTES + B_BYTES;
+  const uint32_t A_BYTES = (uint32_t)a_box_rows * (BK * 2), STAGE = (uint32_t)kbs * (A_BYTES + B_BYTES);
   constexpr int MAXS = TC_MAX_STAGES;
   constexpr uint32_t TM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;  // tensor memory comes in powers of two
   // instruction descriptor: fp32 accumulate, fp16 x fp16, both K-major, N = BN, M = 128
@@ -93,8 +97,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = S > 1 ? (int)cluster_ctarank() : 0;
   const int n0 = (blockIdx.x / S) * BN, m0 = blockIdx.y * BM;
-  const int nk_all = K / BK;
-  const int kb0 = rank * nk_all / S, nk = (rank + 1) * nk_all / S - kb0;
+  const int groups = (K / BK + kbs - 1) / kbs;  // (k-blocks past K in the last group arrive as zeros)
+  const int kb0 = rank * groups / S, nk = (rank + 1) * groups / S - kb0;  // this CTA's groups of k-blocks
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < nstages; ++i) {
@@ -127,8 +131,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         const uint32_t full = smem_u32(&bars[s]);
         const uint32_t dst = base + (uint32_t)s * STAGE;
         mbar_arrive_expect_tx(full, STAGE);
-        tma_load_2d(dst, &map_a, (kb0 + kb) * BK, m0, full);
-        tma_load_2d(dst + A_BYTES, &map_b, (kb0 + kb) * BK, n0, full);
+        tma_load_3d(dst, &map_a, 0, m0, (kb0 + kb) * kbs, full);
+        tma_load_3d(dst + (uint32_t)kbs * A_BYTES, &map_b, 0, n0, (kb0 + kb) * kbs, full);
       }
     }
   } else if (warp == 1) {
@@ -139,11 +143,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         ok = mbar_wait(smem_u32(&bars[s]), use & 1, err, DEV_ERR_FULL_WAIT);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = base + (uint32_t)s * STAGE;
-        const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
+        const uint32_t a_addr = base + (uint32_t)s * STAGE, b_addr = a_addr + (uint32_t)kbs * A_BYTES;
+        for (int j = 0; j < kbs; ++j) {
+          const uint64_t a_desc = smem_desc_sw128(a_addr + (uint32_t)j * A_BYTES), b_desc = smem_desc_sw128(b_addr + (uint32_t)j * B_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k)  // 16 halves = 32 bytes = 2 descriptor address units per K step
-          tc_mma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0);
+          for (int k = 0; k < BK / 16; ++k)  // 16 halves = 32 bytes = 2 descriptor address units per K step
+            tc_mma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | j | k) != 0);
+        }
         tc_commit(smem_u32(&bars[MAXS + s]));  // the stage is free once these MMAs have read it
       }
       tc_commit(smem_u32(&bars[2 * MAXS]));  // accumulator complete (also on the error path: lets the epilogue leave)
@@ -446,15 +452,29 @@ template <int BN, int S>
 int launch_bn(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream) {
   CUtensorMap map_a, map_b;
   const int a_box_rows = m > 64 ? BM : m > 32 ? 64 : m > 16 ? 32 : 16;
-  int rc = make_map(&map_a, lhs, (uint64_t)m, (uint64_t)K, (uint64_t)ldx, a_box_rows, false);
-  if (rc) return rc;
-  rc = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN, true);
-  if (rc) return rc;
-  const size_t STAGE = (size_t)(a_box_rows + BN) * BK * 2;
   constexpr size_t RED = S > 1 ? (size_t)(S - 1) * BM * (BN / S) * 4 : 0;
+  // k-blocks per stage: as many as still leave four stages and two stages' worth of work per CTA
+  int kbs = tc_kb_per_stage();
+  if (kbs <= 0) {
+    kbs = 4;
+    while (kbs > 1 && ((200 * 1024 - RED) / ((size_t)kbs * (a_box_rows + BN) * BK * 2) < 3 || K / BK / S < 2 * kbs)) kbs /= 2;
+  }
+  LCU_REQUIRE(kbs == 1 || kbs == 2 || kbs == 4, "gemm_tc: %d k-blocks per stage is not 1, 2 or 4", kbs);
+  {
+    const uint64_t dims_a[3] = {(uint64_t)BK, (uint64_t)m, (uint64_t)(K / BK)}, str_a[2] = {(uint64_t)ldx * 2, (uint64_t)BK * 2};
+    const uint32_t box_a[3] = {(uint32_t)BK, (uint32_t)a_box_rows, (uint32_t)kbs};
+    int rc = tc_encode_map(&map_a, lhs, 3, dims_a, str_a, box_a);
+    if (rc) return rc;
+    const uint64_t dims_b[3] = {(uint64_t)BK, (uint64_t)N, (uint64_t)(K / BK)}, str_b[2] = {(uint64_t)K * 2, (uint64_t)BK * 2};
+    const uint32_t box_b[3] = {(uint32_t)BK, (uint32_t)BN, (uint32_t)kbs};
+    rc = tc_encode_map(&map_b, w, 3, dims_b, str_b, box_b, true);
+    if (rc) return rc;
+  }
+  const size_t STAGE = (size_t)kbs * (a_box_rows + BN) * BK * 2;
+  const int groups = (K / BK + kbs - 1) / kbs;
   int nstages = (int)((200 * 1024 - RED) / STAGE);
   if (nstages > TC_MAX_STAGES) nstages = TC_MAX_STAGES;
-  if (nstages > K / BK) nstages = K / BK;
+  if (nstages > groups) nstages = groups;
   // (the MMA reads BM operand rows from the last stage's box too: the slack below covers what a short box leaves out)
   const size_t smem = nstages * STAGE + RED + (size_t)(BM - a_box_rows) * BK * 2 + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
   static bool attr_done[16] = {};
@@ -485,7 +505,7 @@ int launch_bn(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, S>, map_a, map_b, out, m, N, K, beta, nstages, a_box_rows, err));
+  LCU_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, S>, map_a, map_b, out, m, N, K, beta, nstages, a_box_rows, kbs, err));
   return LCU_OK;
 }
 
@@ -517,7 +537,8 @@ int launch_pair(__half* out, const __half* lhs, int ldx, const __half* w, int m,
 
 }  // namespace
 
-int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                  bool streamed) {
   LCU_REQUIRE(rank == 2 || rank == 3, "tensor map: rank %d not supported", rank);
   // encoded maps are kept (a map depends on address, shape and box only)
   static std::mutex mu;
@@ -526,6 +547,7 @@ int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* d
   key.append(reinterpret_cast<const char*>(dims), sizeof(uint64_t) * rank);
   key.append(reinterpret_cast<const char*>(strides_bytes), sizeof(uint64_t) * (rank - 1));
   key.append(reinterpret_cast<const char*>(box), sizeof(uint32_t) * rank);
+  key.push_back(streamed ? 's' : 'r');
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -543,11 +565,17 @@ int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* d
     if (i > 0) st[i - 1] = strides_bytes[i - 1];
   }
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                         CU_TENSOR_MAP_SWIZZLE_128B, streamed ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   LCU_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (rank %d) failed with code %d", rank, (int)r);
   if (cache.size() >= 8192) cache.clear();
   cache.emplace(std::move(key), *map);
   return LCU_OK;
+}
+
+int& tc_kb_per_stage() {
+  static int kb = 0;
+  return kb;
 }
 
 int& gemm_tc_sk_mode() {

@@ -23,6 +23,8 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
 // -1 (default) = launch_gemm_tc uses it, with 256- or 512-wide tiles, where its estimate says it wins; 256 / 512 =
 // always, with that tile width, where it divides N; 0 = never
 int& gemm_tc_sk_mode();
+// one-SM kernel: 64-wide k-blocks per stage and tensor copy (0 = as many of 4, 2, 1 as leave four stages)
+int& tc_kb_per_stage();
 bool gemm_tc_sk_supported(int m, int N, int K, int ldx, const void* lhs, const void* w, const void* out, int tile_n);
 int launch_gemm_tc_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream,
                       int tile_n);

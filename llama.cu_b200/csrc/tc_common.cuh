@@ -71,6 +71,8 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 
 // host: cuTensorMapEncodeTiled for fp16 tensors of rank 2 or 3 with 128-byte swizzle (gemm_tc.cu); dims / box innermost
 // first, strides in bytes for dimensions 1 .. rank-1
-int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
+// streamed: the tensor is read once from HBM (weights): L2 sector promotion 256 bytes instead of 128
+int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                  bool streamed = false);
 
 }  // namespace lcu
