@@ -240,6 +240,11 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
                "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
                : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+               "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr)
+               : "memory");
+}
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(cta_mask)
                : "memory");
@@ -259,8 +264,10 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 template <int BN>  // weight rows per pair tile: 128 or 256
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
     gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, __half* out, int m, int N, int K,
-                        float beta, int nstages, int tiles_m, int n_tiles, int* err) {
-  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE = A_BYTES + B_BYTES;
+                        float beta, int nstages, int tiles_m, int n_tiles, int kbs, int* err) {
+  // (a stage is kbs k-blocks, one three-dimensional tensor copy per operand, as in the one-SM kernel)
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2;
+  const uint32_t STAGE = (uint32_t)kbs * (A_BYTES + B_BYTES);
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 2 * BN;
   extern __shared__ uint8_t smem_raw[];
@@ -304,7 +311,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
       for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
         const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;
         const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < nk; ++kb, ++it) {
+        for (int kb = 0; kb < nk; kb += kbs, ++it) {  // (k-blocks past K arrive as zeros)
           const int s = it % nstages;
           const uint32_t ph = (uint32_t)(it / nstages) & 1u;
           ok = mbar_wait(smem_u32(&bars[8 + s]), ph ^ 1u, err, DEV_ERR_EMPTY_WAIT);
@@ -312,8 +319,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
           const uint32_t full_leader = mapa(smem_u32(&bars[s]), 0);
           const uint32_t dst = base + (uint32_t)s * STAGE;
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bars[s]), 2 * STAGE);
-          tma_load_2d_pair(dst, &map_a, kb * BK, m0, full_leader);
-          tma_load_2d_pair(dst + A_BYTES, &map_b, kb * BK, n0, full_leader);
+          tma_load_3d_pair(dst, &map_a, 0, m0, kb, full_leader);
+          tma_load_3d_pair(dst + (uint32_t)kbs * A_BYTES, &map_b, 0, n0, kb, full_leader);
         }
       }
     }
@@ -328,16 +335,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-        for (int kb = 0; kb < nk; ++kb, ++it) {
+        for (int kb = 0; kb < nk; kb += kbs, ++it) {
           const int s = it % nstages;
           const uint32_t ph = (uint32_t)(it / nstages) & 1u;
           ok = mbar_wait(smem_u32(&bars[s]), ph, err, DEV_ERR_FULL_WAIT);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_addr = base + (uint32_t)s * STAGE;
-          const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
+          const uint32_t a_addr = base + (uint32_t)s * STAGE, b_addr = a_addr + (uint32_t)kbs * A_BYTES;
+          for (int j = 0; j < kbs && kb + j < nk; ++j) {
+            const uint64_t a_desc = smem_desc_sw128(a_addr + (uint32_t)j * A_BYTES), b_desc = smem_desc_sw128(b_addr + (uint32_t)j * B_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0);
+            for (int k = 0; k < BK / 16; ++k) tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | j | k) != 0);
+          }
           tc_commit_pair(smem_u32(&bars[8 + s]), 3);  // frees the stage in both CTAs
         }
         tc_commit_pair(smem_u32(&bars[16 + b]), 3);  // accumulator b complete (also after a failed wait: lets the epilogues leave)
@@ -512,11 +521,20 @@ int launch_bn(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
 template <int BN>
 int launch_pair(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream) {
   CUtensorMap map_a, map_b;
-  int rc = make_map(&map_a, lhs, (uint64_t)m, (uint64_t)K, (uint64_t)ldx, BM, false);
-  if (rc) return rc;
-  rc = make_map(&map_b, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN / 2, true);
-  if (rc) return rc;
-  constexpr size_t STAGE = (size_t)(BM + BN / 2) * BK * 2;
+  int kbs = sk_kb_per_stage();  // k-blocks per stage and tensor copy
+  if (kbs <= 0) kbs = 2;
+  if (kbs > 2 || K / BK < 2) kbs = 1;
+  {
+    const uint64_t dims_a[3] = {(uint64_t)BK, (uint64_t)m, (uint64_t)(K / BK)}, str_a[2] = {(uint64_t)ldx * 2, (uint64_t)BK * 2};
+    const uint32_t box_a[3] = {(uint32_t)BK, (uint32_t)BM, (uint32_t)kbs};
+    int rc = tc_encode_map(&map_a, lhs, 3, dims_a, str_a, box_a);
+    if (rc) return rc;
+    const uint64_t dims_b[3] = {(uint64_t)BK, (uint64_t)N, (uint64_t)(K / BK)}, str_b[2] = {(uint64_t)K * 2, (uint64_t)BK * 2};
+    const uint32_t box_b[3] = {(uint32_t)BK, (uint32_t)(BN / 2), (uint32_t)kbs};
+    rc = tc_encode_map(&map_b, w, 3, dims_b, str_b, box_b, true);
+    if (rc) return rc;
+  }
+  const size_t STAGE = (size_t)kbs * (BM + BN / 2) * BK * 2;
   int nstages = (int)((200 * 1024) / STAGE);
   if (nstages > 8) nstages = 8;
   const size_t smem = nstages * STAGE + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
@@ -531,7 +549,7 @@ int launch_pair(__half* out, const __half* lhs, int ldx, const __half* w, int m,
   int clusters = gemv_sm_count() / 2;
   if (clusters > n_tiles) clusters = n_tiles;
   LCU_CUDA(launch_after(gemm_tc_pair_kernel<BN>, dim3(2 * clusters), dim3(TC_THREADS), smem, stream, map_a, map_b, out, m, N, K, beta, nstages, tiles_m,
-                        n_tiles, err));
+                        n_tiles, kbs, err));
   return LCU_OK;
 }
 
@@ -584,16 +602,17 @@ int& gemm_tc_sk_mode() {
 }
 
 // Estimated duration (microseconds) of an [m][K] x [N][K]^T product, m > 128, on the three kernels: whole tiles per SM
-// pair, and the balanced kernel with 256- and 512-wide tiles.  Fitted to timings of the 7B, 13B and 65B products at 256 to
-// 2048 rows (picks within 2 % of the best of the three in sum).
+// pair, and the balanced kernel with 256- and 512-wide tiles.  Fitted to timings of the 7B, 13B and 65B products at 200 to
+// 2048 rows (56 shapes; the picks sum to 10.45 ms against 10.26 ms for the best of the three each time, 11.10 ms for whole
+// tiles alone and 10.51 ms for the balanced 256-wide kernel alone).
 static void gemm_tc_estimates(int m, int N, int K, int sms, double* whole_us, double* t256_us, double* t512_us) {
   const long C = sms / 2, nk = K / BK, tm = (m + 2 * BM - 1) / (2 * BM);
   auto ceil_div_l = [](long a, long b) { return (a + b - 1) / b; };
   double whole;
   if ((m > 2 * BM || N > 8192) && N % 128 == 0) {
     const long n256 = tm * (N / 256);
-    if (N % 256 == 0 && n256 * 4 >= C * 3) whole = ceil_div_l(n256, C) * nk * (n256 > 40 ? 0.465 : 0.40) + 5;
-    else whole = ceil_div_l(tm * (N / 128), C) * nk * 0.42 + 5;
+    if (N % 256 == 0 && n256 * 4 >= C * 3) whole = ceil_div_l(n256, C) * nk * (n256 > 40 ? 0.38 : 0.34) + 5;
+    else whole = ceil_div_l(tm * (N / 128), C) * nk * 0.37 + 5;
   } else {
     const long n128 = (long)((m + BM - 1) / BM) * (N / 128);
     long sp = n128 * 4 <= sms ? 4 : n128 * 2 <= sms ? 2 : 1;
@@ -603,12 +622,12 @@ static void gemm_tc_estimates(int m, int N, int K, int sms, double* whole_us, do
   auto balanced = [&](int bn) -> double {
     if (N % bn) return 1e30;
     const long n = tm * (N / bn), full = n / C, rest = n - full * C;
-    const double per = bn == 256 ? 0.465 : 0.80;
+    const double per = bn == 256 ? 0.41 : 0.80;
     double t = full * (nk * per + (bn == 512 ? 4 : 0)) + 5;
     if (rest) {
       const long cs = std::min(C, std::min(rest * nk, rest * 3));
-      const double per_s = cs > 40 ? per : (bn == 256 ? 0.40 : 0.72);
-      t += (double)(rest * nk) / cs * per_s + (bn == 256 ? 14 : 26);
+      const double per_s = cs > 40 ? per : (bn == 256 ? 0.36 : 0.72);
+      t += (double)(rest * nk) / cs * per_s + (bn == 256 ? 8 : 26);
     }
     return t;
   };

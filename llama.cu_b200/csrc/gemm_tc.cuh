@@ -25,6 +25,8 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
 int& gemm_tc_sk_mode();
 // one-SM kernel: 64-wide k-blocks per stage and tensor copy (0 = as many of 4, 2, 1 as leave four stages)
 int& tc_kb_per_stage();
+// balanced pair kernel: k-blocks per stage and tensor copy (0 = 2)
+int& sk_kb_per_stage();
 bool gemm_tc_sk_supported(int m, int N, int K, int ldx, const void* lhs, const void* w, const void* out, int tile_n);
 int launch_gemm_tc_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream,
                       int tile_n);

@@ -37,6 +37,11 @@ __device__ __forceinline__ void sk_tma_load_pair(uint32_t dst, const CUtensorMap
                "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
                : "memory");
 }
+__device__ __forceinline__ void sk_tma_load_pair_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+               "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr)
+               : "memory");
+}
 __device__ __forceinline__ void sk_commit_pair(uint32_t bar, uint16_t cta_mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(cta_mask)
                : "memory");
@@ -155,10 +160,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
     gemm_tc_sk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_out, int m, int N, int K,
                       float beta, int nstages, int tiles_m, int n_tiles, float* workspace, int* flags, int seq, int* err, int gate_rows,
-                      int share_cap) {
+                      int share_cap, int kbs) {
   constexpr int BN = 256 * NB;
   constexpr int BN_OUT = GATE ? BN / 2 : BN;  // output columns per tile
-  constexpr uint32_t A_BYTES = SK_BM * SK_BK * 2, B_BYTES = 128 * SK_BK * 2, STAGE = A_BYTES + NB * B_BYTES;
+  // a stage holds kbs (1 or 2) k-blocks: [kbs] A tiles, then per accumulator [kbs] B tiles, each operand brought in by one
+  // three-dimensional tensor copy (64 halves x 128 rows x kbs k-blocks)
+  constexpr uint32_t A_BYTES = SK_BM * SK_BK * 2, B_BYTES = 128 * SK_BK * 2;
+  const uint32_t STAGE = (uint32_t)kbs * (A_BYTES + NB * B_BYTES);
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);  // fp32 acc, fp16 x fp16, K-major, N = 256, M = 256
   constexpr int NBUF = NB == 1 ? 2 : 1;  // accumulator buffers: the epilogue of one segment runs under the main loop of the next
   constexpr uint32_t TMEM_COLS = BN * NBUF;
@@ -214,7 +222,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
         // rows of W for this CTA's 128 columns of accumulator h: n0 + h * n_step
         const int n0 = (tile / tiles_m) * BN_OUT + (int)rank * ((GATE && NB == 1) ? gate_rows : 128);
         const int n_step = GATE ? gate_rows : 256;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; kb += kbs, ++it) {  // (a segment of odd length loads one k-block it does not use)
           const int s = it % nstages;
           const uint32_t ph = (uint32_t)(it / nstages) & 1u;
           ok = mbar_wait(smem_u32(&bars[8 + s]), ph ^ 1u, err, DEV_ERR_EMPTY_WAIT);
@@ -222,9 +230,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
           const uint32_t full_leader = mapa(smem_u32(&bars[s]), 0);
           const uint32_t dst = base + (uint32_t)s * STAGE;
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bars[s]), 2 * STAGE);
-          sk_tma_load_pair(dst, &map_a, kb * SK_BK, m0, full_leader);
+          sk_tma_load_pair_3d(dst, &map_a, 0, m0, kb, full_leader);
 #pragma unroll
-          for (int h = 0; h < NB; ++h) sk_tma_load_pair(dst + A_BYTES + h * B_BYTES, &map_b, kb * SK_BK, n0 + h * n_step, full_leader);
+          for (int h = 0; h < NB; ++h)
+            sk_tma_load_pair_3d(dst + (uint32_t)kbs * (A_BYTES + h * B_BYTES), &map_b, 0, n0 + h * n_step, kb, full_leader);
         }
       }
     }
@@ -239,20 +248,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; kb += kbs, ++it) {
           const int s = it % nstages;
           const uint32_t ph = (uint32_t)(it / nstages) & 1u;
           ok = mbar_wait(smem_u32(&bars[s]), ph, err, DEV_ERR_FULL_WAIT);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_addr = base + (uint32_t)s * STAGE;
-          const uint64_t a_desc = smem_desc_sw128(a_addr);
+          const uint32_t a_addr = base + (uint32_t)s * STAGE, b_addr = a_addr + (uint32_t)kbs * A_BYTES;
+          for (int j = 0; j < kbs && kb + j < kb1; ++j) {
+            const uint64_t a_desc = smem_desc_sw128(a_addr + (uint32_t)j * A_BYTES);
 #pragma unroll
-          for (int k = 0; k < SK_BK / 16; ++k) {
+            for (int k = 0; k < SK_BK / 16; ++k) {
 #pragma unroll
-            for (int h = 0; h < NB; ++h)
-              sk_mma_pair(d_tmem + (uint32_t)(h * 256), a_desc + 2 * k, smem_desc_sw128(a_addr + A_BYTES + h * B_BYTES) + 2 * k, IDESC,
-                          (kb > kb0 || k > 0) ? 1u : 0u);
+              for (int h = 0; h < NB; ++h)
+                sk_mma_pair(d_tmem + (uint32_t)(h * 256), a_desc + 2 * k, smem_desc_sw128(b_addr + (uint32_t)(h * kbs + j) * B_BYTES) + 2 * k, IDESC,
+                            (kb + j > kb0 || k > 0) ? 1u : 0u);
+            }
           }
           sk_commit_pair(smem_u32(&bars[8 + s]), 3);  // frees the stage in both CTAs
         }
@@ -510,22 +521,34 @@ int sk_get_workspace(int dev, cudaStream_t stream, size_t partial_floats, int n_
   return LCU_OK;
 }
 
+}  // namespace
+
+int& sk_kb_per_stage() {
+  static int kb = 0;
+  return kb;
+}
+
+namespace {
+
 // GATE: w is the stack [w1; w3] of two [N][K] matrices and out is [m][N]
 template <int NB, bool GATE>
 int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream) {
   constexpr int BN = 256 * NB;
   constexpr int BN_OUT = GATE ? BN / 2 : BN;
   CUtensorMap map_a, map_b;
+  int kbs = sk_kb_per_stage();  // k-blocks per stage and tensor copy
+  if (kbs <= 0) kbs = 2;
+  if (kbs > 2 || K / SK_BK < 2) kbs = 1;
   {
-    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)m}, strides[1] = {(uint64_t)ldx * 2};
-    const uint32_t box[2] = {(uint32_t)SK_BK, (uint32_t)SK_BM};
-    int rc = tc_encode_map(&map_a, lhs, 2, dims, strides, box);
+    const uint64_t dims[3] = {(uint64_t)SK_BK, (uint64_t)m, (uint64_t)(K / SK_BK)}, strides[2] = {(uint64_t)ldx * 2, (uint64_t)SK_BK * 2};
+    const uint32_t box[3] = {(uint32_t)SK_BK, (uint32_t)SK_BM, (uint32_t)kbs};
+    int rc = tc_encode_map(&map_a, lhs, 3, dims, strides, box);
     if (rc) return rc;
   }
   {
-    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)(GATE ? 2 * N : N)}, strides[1] = {(uint64_t)K * 2};
-    const uint32_t box[2] = {(uint32_t)SK_BK, 128u};
-    int rc = tc_encode_map(&map_b, w, 2, dims, strides, box);
+    const uint64_t dims[3] = {(uint64_t)SK_BK, (uint64_t)(GATE ? 2 * N : N), (uint64_t)(K / SK_BK)}, strides[2] = {(uint64_t)K * 2, (uint64_t)SK_BK * 2};
+    const uint32_t box[3] = {(uint32_t)SK_BK, 128u, (uint32_t)kbs};
+    int rc = tc_encode_map(&map_b, w, 3, dims, strides, box, true);
     if (rc) return rc;
   }
   CUtensorMap map_out;
@@ -535,7 +558,7 @@ int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
     int rc = tc_encode_map(&map_out, out, 2, dims, strides, box);
     if (rc) return rc;
   }
-  constexpr size_t STAGE = (size_t)(SK_BM + NB * 128) * SK_BK * 2;
+  const size_t STAGE = (size_t)kbs * (SK_BM + NB * 128) * SK_BK * 2;
   int nstages = (int)((192 * 1024) / STAGE);
   if (nstages > 8) nstages = 8;
   const size_t smem = nstages * STAGE + 32768 /* output staging */ + 1024 /* alignment slack */ + 256 /* barriers, tmem slot */;
@@ -554,7 +577,7 @@ int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
   if (rc) return rc;
   const int seq = ++ws->seq;
   LCU_CUDA(launch_after(gemm_tc_sk_kernel<NB, GATE>, dim3(2 * clusters), dim3(SK_THREADS), smem, stream, map_a, map_b, map_out, m, N, K, beta, nstages,
-                        tiles_m, n_tiles, ws->partials, ws->flags, seq, err, GATE ? N : 0, m <= SK_BM ? 8 : 3));
+                        tiles_m, n_tiles, ws->partials, ws->flags, seq, err, GATE ? N : 0, m <= SK_BM ? 8 : 3, kbs));
   return LCU_OK;
 }
 
