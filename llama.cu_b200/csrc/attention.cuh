@@ -51,4 +51,7 @@ int launch_attention_tc(const attn_params& p, int m, int max_T, __half* scores, 
 // head) with the scores in tensor memory and the probabilities in shared memory; no score buffer.
 int launch_attention_fused(const attn_params& p, int m, int max_T, cudaStream_t stream);
 
+// one-kernel prompt attention: CTA order, 0 = a head's row tiles together (long first), 1 = all heads' long tiles first
+int& attn_fused_order();
+
 }  // namespace lcu

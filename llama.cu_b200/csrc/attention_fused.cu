@@ -20,6 +20,12 @@
 #include "tc_common.cuh"
 
 namespace lcu {
+
+int& attn_fused_order() {
+  static int v = 1;  // measured: 2000 rows, 7B: 135 -> 104 us per layer against 0 (the heavy tiles of the last heads end the kernel)
+  return v;
+}
+
 namespace {
 
 constexpr int FA_BM = 128;       // query rows per CTA
@@ -54,7 +60,8 @@ constexpr uint16_t FA_MASKED = 0xfbff;  // -65504: a key above the diagonal (its
 
 template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 1) attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                                                                   const __grid_constant__ CUtensorMap map_v, const fused_params p, int t_tiles) {
+                                                                   const __grid_constant__ CUtensorMap map_v, const fused_params p, int t_tiles, int m_tiles,
+                                                                   int head_fastest) {
   constexpr int NKB = HD / 64;                       // 64-wide blocks of the head dimension
   constexpr uint32_t BLOCK_BYTES = 128 * 64 * 2;     // 128 rows (or keys) x 64 dims
   constexpr uint32_t OPERAND = NKB * BLOCK_BYTES;    // Q tile, K tile, or V tile (2 x NKB atoms of 64 keys x 64 dims)
@@ -75,7 +82,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attn_fused_kernel(const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * FA_BM, head = blockIdx.y;  // long row tiles first
+  // long row tiles first: over all heads (head_fastest: the kernel then ends with every head's short tiles), or within
+  // each head
+  const int n_heads_grid = (int)gridDim.x / m_tiles;
+  const int mt = head_fastest ? (int)blockIdx.x / n_heads_grid : (int)blockIdx.x % m_tiles;
+  const int head = head_fastest ? (int)blockIdx.x % n_heads_grid : (int)blockIdx.x / m_tiles;
+  const int m0 = (m_tiles - 1 - mt) * FA_BM;
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bars[B_Q]), 1);
@@ -376,7 +388,8 @@ int launch_fused_hd(const attn_params& p, int m, int max_T, cudaStream_t stream)
     attr_done[dev] = true;
   }
   const int m_tiles = (m + FA_BM - 1) / FA_BM, t_tiles = (max_T + FA_BN - 1) / FA_BN;
-  LCU_CUDA(launch_after(attn_fused_kernel<HD>, dim3(m_tiles, p.n_heads), dim3(FA_THREADS), SMEM, stream, map_q, map_k, map_v, q, t_tiles));
+  LCU_CUDA(launch_after(attn_fused_kernel<HD>, dim3(m_tiles * p.n_heads), dim3(FA_THREADS), SMEM, stream, map_q, map_k, map_v, q, t_tiles, m_tiles,
+                        attn_fused_order()));
   return LCU_OK;
 }
 

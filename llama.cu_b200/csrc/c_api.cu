@@ -109,6 +109,7 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "prefill_tc_sk") gemm_tc_sk_mode() = value;
   else if (k == "prefill_tc_kb") tc_kb_per_stage() = value;
   else if (k == "prefill_sk_kb") sk_kb_per_stage() = value;
+  else if (k == "prefill_attn_fused_order") attn_fused_order() = value;
   else if (k == "prefill_gate_fused") gemm_tc_gate_mode() = value;
   else if (k == "prompt_pdl") prompt_pdl() = value;
   else if (k == "tp_debug") tp_set_debug(value);
