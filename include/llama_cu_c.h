@@ -39,7 +39,7 @@ int lcu_set_matmul_type(int type);
  * "int8_factored" (0 = round every dequantized weight to half as the reference does), "prefill_tc_min_rows",
  * "prefill_tc_tile_n", "prefill_tc_pair", "prefill_tc_split", "prefill_tc_sk", "prefill_tc_kb", "prefill_sk_kb" (k-blocks per
  * stage and tensor copy of the one-SM / the pair GEMMs), "prefill_gate_fused", "prefill_u8_deq_min_rows", "prefill_fuse",
- * "prefill_attn_tc", "prefill_attn_tc_min_rows", "prefill_attn_fused_min_rows", "prefill_attn_tiles", "prompt_pdl", "attn_stream",
+ * "prefill_attn_tc", "prefill_attn_tc_min_rows", "prefill_attn_fused_min_rows", "prefill_attn_fused_order", "prefill_attn_tiles", "prompt_pdl", "attn_stream",
  * "use_graph", "use_pdl", "attn_cluster", "loader_staged" (lcu_model_load: 1 = pinned double-buffered asynchronous copies, 0 = a file mapping and one
  * blocking pageable copy per tensor as the reference does).  Unknown keys are rejected. */
 int lcu_set_tuning(const char* key, int value);
