@@ -628,6 +628,7 @@ static void gemm_tc_estimates(int m, int N, int K, int sms, double* whole_us, do
       const long cs = std::min(C, std::min(rest * nk, rest * 3));
       const double per_s = cs > 40 ? per : (bn == 256 ? 0.36 : 0.72);
       t += (double)(rest * nk) / cs * per_s + (bn == 256 ? 8 : 26);
+      if (bn == 256 && full == 0) t += 6;  // no whole wave: every tile is handed over, and nothing hides the first wait
     }
     return t;
   };

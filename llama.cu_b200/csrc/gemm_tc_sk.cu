@@ -104,17 +104,17 @@ struct sk_schedule {
   int C, Cs, c, nk, full_waves, first_split_tile;  // Cs: pairs that take part in the split tiles (every one of them has a K step)
   long long U, u, u1;  // units of the split tiles: all, next of this pair, end of this pair's range
   int wave;
-  __device__ void init(int n_tiles, int nk_, int C_, int c_, int share_cap) {
+  __device__ void init(int n_tiles, int nk_, int C_, int c_) {
     C = C_;
     c = c_;
     nk = nk_;
     full_waves = n_tiles / C;
     first_split_tile = full_waves * C;
     U = (long long)(n_tiles - first_split_tile) * nk;
-    // at most share_cap pairs per shared tile (three for long prompts: the owner adds the other pairs' 256-row sums
-    // one after the other at the very end of the kernel, and what it reads of the first two is requested ahead; eight
-    // for prompts of up to 128 rows, whose sums are small)
-    const long long split_pairs = (long long)(n_tiles - first_split_tile) * share_cap;
+    // at most three pairs per shared tile: its owner adds the other pairs' sums one after the other at the very end of
+    // the kernel, and what it reads of the first two is requested ahead (eight pairs per tile were slower even for
+    // prompts of 16 rows, whose sums are small: 59 against 46 us on the 7B w1|w3)
+    const long long split_pairs = (long long)(n_tiles - first_split_tile) * 3;
     Cs = (int)min(min((long long)C, U), split_pairs);
     u = c < Cs ? sk_first_unit(U, c, Cs) : 0;
     u1 = c < Cs ? sk_first_unit(U, c + 1, Cs) : 0;
@@ -160,7 +160,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
     gemm_tc_sk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_out, int m, int N, int K,
                       float beta, int nstages, int tiles_m, int n_tiles, float* workspace, int* flags, int seq, int* err, int gate_rows,
-                      int share_cap, int kbs) {
+                      int kbs) {
   constexpr int BN = 256 * NB;
   constexpr int BN_OUT = GATE ? BN / 2 : BN;  // output columns per tile
   // a stage holds kbs (1 or 2) k-blocks: [kbs] A tiles, then per accumulator [kbs] B tiles, each operand brought in by one
@@ -184,7 +184,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SK_THREADS, 1)
   const int C = gridDim.x / 2, cluster_id = blockIdx.x / 2;
   const int nk = K / SK_BK;
   sk_schedule sched;
-  sched.init(n_tiles, nk, C, cluster_id, share_cap);
+  sched.init(n_tiles, nk, C, cluster_id);
   int tile, kb0, kb1;
   bool split;
 
@@ -577,7 +577,7 @@ int launch_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, i
   if (rc) return rc;
   const int seq = ++ws->seq;
   LCU_CUDA(launch_after(gemm_tc_sk_kernel<NB, GATE>, dim3(2 * clusters), dim3(SK_THREADS), smem, stream, map_a, map_b, map_out, m, N, K, beta, nstages,
-                        tiles_m, n_tiles, ws->partials, ws->flags, seq, err, GATE ? N : 0, m <= SK_BM ? 8 : 3, kbs));
+                        tiles_m, n_tiles, ws->partials, ws->flags, seq, err, GATE ? N : 0, kbs));
   return LCU_OK;
 }
 
