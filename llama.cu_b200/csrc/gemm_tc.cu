@@ -611,7 +611,8 @@ static void gemm_tc_estimates(int m, int N, int K, int sms, double* whole_us, do
   double whole;
   if ((m > 2 * BM || N > 8192) && N % 128 == 0) {
     const long n256 = tm * (N / 256);
-    if (N % 256 == 0 && n256 * 4 >= C * 3) whole = ceil_div_l(n256, C) * nk * (n256 > 40 ? 0.38 : 0.34) + 5;
+    // (several hundred tiles of a short K: the whole-tile kernel's epilogues weigh more, 0.42 us per K step measured)
+    if (N % 256 == 0 && n256 * 4 >= C * 3) whole = ceil_div_l(n256, C) * nk * (n256 > 300 && nk <= 80 ? 0.42 : n256 > 40 ? 0.38 : 0.34) + 5;
     else whole = ceil_div_l(tm * (N / 128), C) * nk * 0.37 + 5;
   } else {
     const long n128 = (long)((m + BM - 1) / BM) * (N / 128);
