@@ -38,7 +38,7 @@ int lcu_set_matmul_type(int type);
  * "gemv_ctas_per_sm_int8", "gemv_variant", "gemv_warp_stages", "gemv_warp_stages_int8", "gemv_consumer_warps_int8", "gemv_prefetch_kb",
  * "int8_factored" (0 = round every dequantized weight to half as the reference does), "prefill_tc_min_rows",
  * "prefill_tc_tile_n", "prefill_tc_pair", "prefill_tc_split", "prefill_tc_sk", "prefill_tc_kb", "prefill_sk_kb" (k-blocks per
- * stage and tensor copy of the one-SM / the pair GEMMs), "prefill_gate_fused", "prefill_u8_deq_min_rows", "prefill_fuse",
+ * stage and tensor copy of the one-SM / the pair GEMMs), "prefill_gate_fused", "prefill_u8_deq_min_rows", "prefill_u8_shadow", "prefill_fuse",
  * "prefill_attn_tc", "prefill_attn_tc_min_rows", "prefill_attn_fused_min_rows", "prefill_attn_fused_order", "prefill_attn_tiles", "prompt_pdl", "attn_stream",
  * "use_graph", "use_pdl", "attn_cluster", "loader_staged" (lcu_model_load: 1 = pinned double-buffered asynchronous copies, 0 = a file mapping and one
  * blocking pageable copy per tensor as the reference does).  Unknown keys are rejected. */
@@ -135,6 +135,10 @@ int lcu_model_save(void* model, const char* dir);
 int lcu_model_tensor(void* model, const char* name, int which, void** dev_out, uint64_t* bytes_out, int* device_out);
 int lcu_model_params(void* model, void* params40_out);
 uint64_t lcu_model_weight_bytes(void* model);
+/* u8 models: bytes of the fp16 copy of the layer matrices that prompts of 9 tokens or more read (the same halves the
+ * per-pass expansion of llama_cu.cu:287-289 produces, expanded once).  It is built by the first such prompt where the GPU
+ * keeps 6 GB free after it, and not at all with the tuning key "prefill_u8_shadow" = 0; 0 while it does not exist. */
+uint64_t lcu_model_shadow_bytes(void* model);
 void lcu_model_free(void* model);
 /* llama_params::ffn_dim, llama_cu.cu:765-767 */
 uint32_t lcu_ffn_dim(uint32_t dim, uint32_t multiple_of);

@@ -66,6 +66,7 @@ _SIG = {
     "lcu_model_tensor": (C.c_int, [vp, C.c_char_p, C.c_int, C.POINTER(vp), C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
     "lcu_model_params": (C.c_int, [vp, vp]),
     "lcu_model_weight_bytes": (C.c_uint64, [vp]),
+    "lcu_model_shadow_bytes": (C.c_uint64, [vp]),
     "lcu_model_free": (None, [vp]),
     "lcu_ffn_dim": (C.c_uint32, [C.c_uint32, C.c_uint32]),
     "lcu_partition_autopipe": (C.c_int, [vp, C.c_int, vp]),
@@ -325,6 +326,10 @@ class Model:
 
     def weight_bytes(self):
         return lib.lcu_model_weight_bytes(self.handle)
+
+    def shadow_bytes(self):
+        """u8 models: bytes of the fp16 copy of the layer matrices kept for prompts (0 while there is none)."""
+        return lib.lcu_model_shadow_bytes(self.handle)
 
     def close(self):
         if self.handle:

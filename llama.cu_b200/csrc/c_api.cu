@@ -98,6 +98,7 @@ int lcu_set_tuning(const char* key, int value) {
   else if (k == "prefill_tc_min_rows") prefill_tuning_ref().tc_min_rows = value;
   else if (k == "prefill_tc_tile_n") prefill_tuning_ref().tc_tile_n = value;
   else if (k == "prefill_u8_deq_min_rows") prefill_tuning_ref().u8_deq_min_rows = value;
+  else if (k == "prefill_u8_shadow") u8_shadow_mode() = value;
   else if (k == "attn_stream") attention_set_stream_mode(value);
   else if (k == "prefill_fuse") prefill_tuning_ref().fuse = value;
   else if (k == "prefill_attn_tc") prefill_tuning_ref().attn_tc = value;
@@ -363,6 +364,12 @@ int lcu_model_tensor(void* mdl, const char* name, int which, void** dev_out, uin
 int lcu_model_params(void* mdl, void* params40_out) {
   memcpy(params40_out, &((model*)mdl)->params, sizeof(model_params));
   return LCU_OK;
+}
+uint64_t lcu_model_shadow_bytes(void* mdl) {
+  model* m = (model*)mdl;
+  if (!m) return 0;
+  std::lock_guard<std::mutex> lock(m->shadow_mu);
+  return m->shadow_state > 0 ? m->shadow_bytes : 0;
 }
 uint64_t lcu_model_weight_bytes(void* mdl) { return ((model*)mdl)->weight_bytes_total; }
 void lcu_model_free(void* mdl) { delete (model*)mdl; }

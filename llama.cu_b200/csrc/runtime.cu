@@ -150,6 +150,103 @@ model::~model() {
     device_guard g(a.first);
     cudaFree(a.second);
   }
+  for (auto& a : shadow_arenas) {
+    device_guard g(a.first);
+    cudaFree(a.second);
+  }
+}
+
+int& u8_shadow_mode() {
+  static int mode = 1;
+  return mode;
+}
+
+void model::shadow_touch() {
+  std::lock_guard<std::mutex> lock(shadow_mu);
+  if (shadow_state == 1) shadow_state = 2;
+}
+
+bool model::shadow_ready() {
+  std::lock_guard<std::mutex> lock(shadow_mu);
+  if (shadow_state == 1) return true;
+  if (shadow_state < 0) return false;
+  const model_params& p = params;
+  const int bs = p.q_type ? (int)p.quantization_block_size : 0;
+  if (bs == 0 || tp_size != 1 || !u8_shadow_mode()) return false;  // (not remembered: the mode may be switched on later)
+  const size_t d = p.dim, f = ffn;
+  const size_t per_layer = (3 * d * d + d * d + 2 * f * d + d * f) * 2;
+  if (shadow_state == 0) {
+    // one allocation per GPU that holds layers; all or nothing
+    std::vector<std::pair<int, size_t>> need;
+    for (uint32_t l = 0; l < p.n_layers; ++l) {
+      const int dev = part.layer_gpus[l];
+      auto it = std::find_if(need.begin(), need.end(), [&](const std::pair<int, size_t>& a) { return a.first == dev; });
+      if (it == need.end()) need.emplace_back(dev, per_layer);
+      else it->second += per_layer;
+    }
+    bool fits = true;
+    for (auto& n : need) {
+      device_guard g(n.first);
+      size_t free_b = 0, total_b = 0;
+      if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess || free_b < n.second + ((size_t)6 << 30)) fits = false;
+    }
+    if (fits)
+      for (auto& n : need) {
+        device_guard g(n.first);
+        void* base = nullptr;
+        if (cudaMalloc(&base, n.second) != cudaSuccess) {
+          cudaGetLastError();
+          fits = false;
+          break;
+        }
+        shadow_arenas.emplace_back(n.first, base);
+      }
+    if (!fits) {
+      for (auto& a : shadow_arenas) {
+        device_guard g(a.first);
+        cudaFree(a.second);
+      }
+      shadow_arenas.clear();
+      shadow_state = -1;
+      return false;
+    }
+    shadow_layers = layers;
+    std::vector<size_t> used(shadow_arenas.size(), 0);
+    shadow_bytes = 0;
+    for (uint32_t l = 0; l < p.n_layers; ++l) {
+      size_t ai = 0;
+      while (shadow_arenas[ai].first != part.layer_gpus[l]) ++ai;
+      __half* at = reinterpret_cast<__half*>((char*)shadow_arenas[ai].second + used[ai]);
+      layer_weights& S = shadow_layers[l];
+      dev_matrix* order[7] = {&S.wq, &S.wk, &S.wv, &S.wo, &S.w1, &S.w3, &S.w2};
+      for (dev_matrix* mt : order) {
+        mt->w = at;
+        mt->sc = nullptr;
+        mt->bs = 0;
+        at += mt->rows * mt->cols;
+      }
+      used[ai] += per_layer;
+      shadow_bytes += per_layer;
+    }
+  }
+  // (re)fill: the kernel the per-pass expansion uses, the values the reference's tile kernel builds in shared
+  // memory (llama_cu.cu:287-289)
+  bool ok = true;
+  for (uint32_t l = 0; l < p.n_layers && ok; ++l) {
+    device_guard g(part.layer_gpus[l]);
+    const layer_weights& L = layers[l];
+    const layer_weights& S = shadow_layers[l];
+    const dev_matrix* src[7] = {&L.wq, &L.wk, &L.wv, &L.wo, &L.w1, &L.w3, &L.w2};
+    const dev_matrix* dst[7] = {&S.wq, &S.wk, &S.wv, &S.wo, &S.w1, &S.w3, &S.w2};
+    for (int i = 0; i < 7 && ok; ++i)
+      ok = launch_dequantize_absmax_uint8((__half*)dst[i]->w, src[i]->sc, (const uint8_t*)src[i]->w, src[i]->rows, src[i]->cols, bs, nullptr) == LCU_OK;
+  }
+  for (auto& a : shadow_arenas) {
+    device_guard g(a.first);
+    if (cudaDeviceSynchronize() != cudaSuccess) ok = false;
+  }
+  shadow_state = ok ? 1 : -1;
+  return ok;
 }
 
 int model::create(std::unique_ptr<model>& out, const model_params& p, const partition& part, int tp_rank, int tp_size) {
@@ -221,6 +318,7 @@ int model::create(std::unique_ptr<model>& out, const model_params& p, const part
 }
 
 int model::find_tensor(const std::string& name, int which, void** ptr, size_t* bytes, int* device) {
+  shadow_touch();  // (the caller gets a writable pointer)
   for (auto& s : enumerate(*this)) {
     if (s.name != name) continue;
     if (device) *device = s.device;
@@ -382,6 +480,7 @@ int g_loader_staged = 1;
 void set_loader_staged(int on) { g_loader_staged = on; }
 
 int model::load_dir(const std::string& dir) {
+  shadow_touch();
   std::vector<std::unique_ptr<staged_loader>> loaders;  // one per GPU that holds tensors
   auto loader_for = [&](int dev, staged_loader*& out) {
     for (auto& l : loaders)
@@ -426,6 +525,7 @@ int model::load_dir(const std::string& dir) {
 }
 
 int model::fill_synthetic(uint64_t seed, float scale) {
+  shadow_touch();
   for (auto& s : enumerate(*this)) {
     device_guard g(s.device);
     if (!s.mat) {
@@ -922,6 +1022,9 @@ int context_impl::enqueue_prefill(int m_rows) {
   // ahead, into two alternating buffers: the expansion streams from HBM while the GEMM before it keeps the tensor
   // cores busy, instead of the two taking turns.  Job j of a GPU lives in buffer j % 2.
   for (auto& g : gpus) g.deq_issued = g.deq_used = 0;
+  // (or, where the GPU has room, from the fp16 shadow of the whole model: model::shadow_ready)
+  const bool shadow = bs > 0 && matmul_type_ref() != 1 && prefill_tuning_ref().fuse && prefill_tuning_ref().u8_deq_min_rows > 0 &&
+                      m_rows >= prefill_tuning_ref().u8_deq_min_rows && m->shadow_ready();
   auto expand = [&](gpu_state& g, const dev_matrix* const* mats, int n_mats) -> int {
     const int b = (int)(g.deq_issued % 2);
     if (g.deq_issued >= 2) LCU_CUDA(cudaStreamWaitEvent(g.side, g.gemm_done[b], 0));  // the GEMM that read this buffer last
@@ -967,7 +1070,7 @@ int context_impl::enqueue_prefill(int m_rows) {
     if (l > 0 && layer_slot[l - 1] != gi) LCU_TRY(enqueue_hop(layer_slot[l - 1], gi, m_rows));
     gpu_state& g = gpus[gi];
     device_guard dg(g.device);
-    const layer_weights& L = m->layers[l];
+    const layer_weights& L = shadow ? m->shadow_layers[l] : m->layers[l];
     int* err = g.state + 3;
     LCU_TRY(launch_rms_norm(g.norm, g.x, L.attn_norm, m_rows, d, p.norm_eps, g.stream));
     // fp16 weights lie back to back in the arena (wq, wk, wv; w1, w3), and so do the q / new-k / new-v and the h1 / h3
@@ -978,8 +1081,9 @@ int context_impl::enqueue_prefill(int m_rows) {
                               g.h3 == g.h1 + (size_t)opt.context_len * f;
     // u8 weights: the same, with the matrices expanded to fp16 one after the other into the scratch buffer
     const bool pedantic = matmul_type_ref() == 1;  // u8 weights then stay u8 all the way into the pedantic kernel
-    const bool fuse_u8 = !pedantic && pt.fuse && bs > 0 && rows_stacked && pt.u8_deq_min_rows > 0 && m_rows >= pt.u8_deq_min_rows && g.deq != nullptr;
-    const bool fuse = pt.fuse && bs == 0 && m_rows > 8 && rows_stacked;
+    const bool fuse_u8 = !shadow && !pedantic && pt.fuse && bs > 0 && rows_stacked && pt.u8_deq_min_rows > 0 && m_rows >= pt.u8_deq_min_rows &&
+                         g.deq != nullptr;
+    const bool fuse = pt.fuse && (bs == 0 || shadow) && m_rows > 8 && rows_stacked;
     const bool qkv_stacked = fuse_u8 || (fuse && (char*)L.wk.w == (char*)L.wq.w + (size_t)d * d * 2 && (char*)L.wv.w == (char*)L.wk.w + (size_t)d * d * 2);
     const int ldq = qkv_stacked ? 3 * d : d;
     if (qkv_stacked) {

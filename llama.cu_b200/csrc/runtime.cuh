@@ -3,6 +3,7 @@
 #pragma once
 #include <memory>
 #include <string>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -86,6 +87,20 @@ struct model {
   // (whole heads of wq / wk / wv); norm vectors and the embedding table are whole.  tp_size 1 = the whole model.
   int tp_rank = 0, tp_size = 1;
 
+  // fp16 shadow of the u8 layer matrices, for prompt GEMMs.  A prompt of 9 rows or more runs its products on tcgen05
+  // over fp16 operands; expanding every u8 matrix into scratch on every pass costs a 7B prompt about 100 us per layer
+  // at any length (11.0 against 7.7 ms at 512 tokens).  Where the GPU has the room (the shadow takes 2 bytes per
+  // weight: 13 GB for 7B, and is kept only if 6 GB stay free after it) the expansion is done once, by the same
+  // kernel, so prompts read the same halves either way; decode keeps streaming the u8 matrices.  Built by the first
+  // long prompt; rebuilt after a tensor was handed out (it may have been rewritten).
+  std::vector<layer_weights> shadow_layers;  // as `layers`, bs = 0, wq|wk|wv and w1|w3 back to back
+  std::vector<std::pair<int, void*>> shadow_arenas;
+  size_t shadow_bytes = 0;
+  int shadow_state = 0;  // 0 not tried, 1 current, 2 stale, -1 does not fit / not wanted
+  std::mutex shadow_mu;
+  bool shadow_ready();   // builds or refreshes it when needed; false = use the per-pass expansion
+  void shadow_touch();   // a tensor may have been written
+
   ~model();
   // allocates all tensors (uninitialised) according to params and the partition
   static int create(std::unique_ptr<model>& out, const model_params& p, const partition& part, int tp_rank = 0, int tp_size = 1);
@@ -99,6 +114,9 @@ struct model {
   // writes params and every tensor as a weight directory in the reference's layout
   int save_dir(const std::string& dir);
 };
+
+// fp16 shadow of u8 models for prompts (model::shadow_ready): 1 (default) = where it fits, 0 = never
+int& u8_shadow_mode();
 
 // weight-directory loader: 1 (default) = pieces through two pinned buffers with asynchronous copies overlapping the file
 // reads; 0 = the reference's way, a file mapping handed to one blocking copy from pageable memory (llama_cu.cu:699-702)

@@ -138,6 +138,38 @@ def test_long_prompt_with_gate_in_the_gemm_epilogue_against_oracle(lcu, bs):
     model.close()
 
 
+def test_u8_prompt_from_the_fp16_shadow_equals_the_per_pass_expansion(lcu):
+    """u8 models: a prompt of 9 tokens or more reads fp16 copies of the layer matrices - expanded once into a shadow of
+    the model where the GPU has room, or into scratch on every pass.  Same kernel, same halves (llama_cu.cu:287-289):
+    the two must give the same probabilities bit for bit.  The shadow follows the weights: after a tensor was handed
+    out and rewritten, the next prompt sees the new values."""
+    cfg = dict(dim=256, multiple_of=256, n_heads=2, n_layers=3, n_vocab=1000)
+    prompt = O.synth_tokens(40, 31, lo=3, hi=1000)
+    out = {}
+    try:
+        for mode in (0, 1):
+            lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_shadow", mode))
+            model = lcu.Model.synthetic(block_size=128, seed=31, scale=0.08, **cfg)
+            ctx = lcu.Context(model, context_len=64, temperature=0.8)
+            tok = ctx.next_token(prompt)
+            assert (model.shadow_bytes() > 0) == (mode == 1)
+            probs = np.asarray(ctx.probs(), np.uint16).copy()
+            # rewrite one matrix (all bytes 200) and run the prompt again
+            ptr, nbytes, _ = model.tensor("layers.1.feed_forward.w2")
+            lcu.check(lcu.lib.lcu_memcpy_h2d(ptr, lcu._ptr(np.full(nbytes, 200, np.uint8)), nbytes))
+            ctx.clear_tokens()
+            tok2 = ctx.next_token(prompt)
+            probs2 = np.asarray(ctx.probs(), np.uint16).copy()
+            out[mode] = (tok, probs, tok2, probs2)
+            ctx.close()
+            model.close()
+    finally:
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_shadow", 1))
+    assert out[0][0] == out[1][0] and np.array_equal(out[0][1], out[1][1])
+    assert out[0][2] == out[1][2] and np.array_equal(out[0][3], out[1][3])
+    assert not np.array_equal(out[1][1], out[1][3])  # the rewritten matrix did change the result
+
+
 def test_fresh_contexts_repeat_the_same_distribution(lcu):
     """A context is usable the moment it is created: its zeroed arenas and its RoPE table are ordered on the context's
     own stream.  Twenty contexts in a row, each used at once with a context length whose arenas take a while to clear,
