@@ -414,6 +414,9 @@ def measure_decode(lcu, workload, K, W, prompt_len, world, dist, layer_gpus=None
                            "frac_of_nominal_8tbs": round(dom["gbs"] / 8000.0, 4)}
     if with_prefill and ctx_len >= prefill_len + 2:
         res["prefill"] = prefill_sample(lcu, ctx, cfg, ffn, profile == "prefill", prefill_len)
+        if cfg["block_size"]:
+            # u8 models: prompts read an fp16 copy of the layer matrices, expanded once where the GPU has the room
+            res["prefill"]["fp16_shadow_bytes"] = int(model.shadow_bytes())
     ctx.close()
     model.close()
     return res

@@ -166,7 +166,7 @@ void model::shadow_touch() {
   if (shadow_state == 1) shadow_state = 2;
 }
 
-bool model::shadow_ready() {
+bool model::shadow_ready(bool may_allocate) {
   std::lock_guard<std::mutex> lock(shadow_mu);
   if (shadow_state == 1) return true;
   if (shadow_state < 0) return false;
@@ -175,6 +175,7 @@ bool model::shadow_ready() {
   if (bs == 0 || tp_size != 1 || !u8_shadow_mode()) return false;  // (not remembered: the mode may be switched on later)
   const size_t d = p.dim, f = ffn;
   const size_t per_layer = (3 * d * d + d * d + 2 * f * d + d * f) * 2;
+  if (shadow_state == 0 && !may_allocate) return false;
   if (shadow_state == 0) {
     // one allocation per GPU that holds layers; all or nothing
     std::vector<std::pair<int, size_t>> need;
@@ -784,6 +785,9 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
     LCU_CUDA(cudaEventCreate(&c.t0));
     LCU_CUDA(cudaEventCreate(&c.t1));
   }
+  // u8 models: the fp16 shadow for prompts is set up here, next to the context's own arenas, so that next_token never
+  // allocates (a stale shadow is refreshed in place by the next long prompt)
+  if (p.q_type && c.opt.context_len > 8) m->shadow_ready(true);
   out = std::move(ctx);
   return LCU_OK;
 }
@@ -1024,7 +1028,7 @@ int context_impl::enqueue_prefill(int m_rows) {
   for (auto& g : gpus) g.deq_issued = g.deq_used = 0;
   // (or, where the GPU has room, from the fp16 shadow of the whole model: model::shadow_ready)
   const bool shadow = bs > 0 && matmul_type_ref() != 1 && prefill_tuning_ref().fuse && prefill_tuning_ref().u8_deq_min_rows > 0 &&
-                      m_rows >= prefill_tuning_ref().u8_deq_min_rows && m->shadow_ready();
+                      m_rows >= prefill_tuning_ref().u8_deq_min_rows && m->shadow_ready(false);
   auto expand = [&](gpu_state& g, const dev_matrix* const* mats, int n_mats) -> int {
     const int b = (int)(g.deq_issued % 2);
     if (g.deq_issued >= 2) LCU_CUDA(cudaStreamWaitEvent(g.side, g.gemm_done[b], 0));  // the GEMM that read this buffer last

@@ -91,14 +91,17 @@ struct model {
   // over fp16 operands; expanding every u8 matrix into scratch on every pass costs a 7B prompt about 100 us per layer
   // at any length (11.0 against 7.7 ms at 512 tokens).  Where the GPU has the room (the shadow takes 2 bytes per
   // weight: 13 GB for 7B, and is kept only if 6 GB stay free after it) the expansion is done once, by the same
-  // kernel, so prompts read the same halves either way; decode keeps streaming the u8 matrices.  Built by the first
-  // long prompt; rebuilt after a tensor was handed out (it may have been rewritten).
+  // kernel, so prompts read the same halves either way; decode keeps streaming the u8 matrices.  Set up when the
+  // model's first context is created; refreshed by the next long prompt after a tensor was handed out (it may have
+  // been rewritten).
   std::vector<layer_weights> shadow_layers;  // as `layers`, bs = 0, wq|wk|wv and w1|w3 back to back
   std::vector<std::pair<int, void*>> shadow_arenas;
   size_t shadow_bytes = 0;
   int shadow_state = 0;  // 0 not tried, 1 current, 2 stale, -1 does not fit / not wanted
   std::mutex shadow_mu;
-  bool shadow_ready();   // builds or refreshes it when needed; false = use the per-pass expansion
+  // true = usable (refreshed if stale); false = use the per-pass expansion.  Allocates only when told it may
+  // (context creation): a prompt never does.
+  bool shadow_ready(bool may_allocate);
   void shadow_touch();   // a tensor may have been written
 
   ~model();
