@@ -135,7 +135,7 @@ int lcu_model_save(void* model, const char* dir);
 int lcu_model_tensor(void* model, const char* name, int which, void** dev_out, uint64_t* bytes_out, int* device_out);
 int lcu_model_params(void* model, void* params40_out);
 uint64_t lcu_model_weight_bytes(void* model);
-/* u8 models: bytes of the fp16 copy of the layer matrices that prompts of 9 tokens or more read (the same halves the
+/* u8 models: bytes of the fp16 copy of the layer matrices that prompts of 2 tokens or more read (the same halves the
  * per-pass expansion of llama_cu.cu:287-289 produces, expanded once).  It is allocated when the model's first context is
  * created, where the GPU keeps 6 GB free after it, and not at all with the tuning key "prefill_u8_shadow" = 0 (prompts
  * then expand into the context's scratch on every pass); 0 while it does not exist. */

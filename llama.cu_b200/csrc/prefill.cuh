@@ -6,10 +6,12 @@
 namespace lcu {
 
 struct prefill_tuning {
-  int tc_min_rows = 9;  // fp16 weights: this many rows or more go to the tcgen05 GEMM (0 = never)
+  // fp16 weights: this many rows or more go to the tcgen05 GEMM (0 = never).  From 2 rows: measured, a 7B prompt of 2 to 8
+  // tokens takes 4.2 to 6.7 ms through the multi-row GEMV (seven products per layer) and 3.3 ms through the stacked GEMMs.
+  int tc_min_rows = 2;
   int tc_tile_n = 0;    // one-SM kernel: 0 = pick the tile width per shape; a multiple of 32 up to 256 forces it
-  int u8_deq_min_rows = 9;   // u8 weights: this many rows or more take a dequantization pass + the tcgen05 GEMM (0 = never);
-                             // measured at 7B: 9.3 ms for any prompt of 9..47 tokens against 7..34 ms through GEMV passes
+  int u8_deq_min_rows = 2;   // u8 weights: this many rows or more take a dequantization pass + the tcgen05 GEMM (0 = never);
+                             // (GEMV passes of 8 rows: 4.3 to 34 ms for 7B prompts of 2 to 47 tokens)
   int fuse = 1;         // fp16 prompts: wq|wk|wv and w1|w3 as one GEMM each over the stacked matrices
   int attn_tc = 2;      // prompt attention: 2 = one tcgen05 kernel per layer (scores in tensor memory), 1 = three tcgen05 kernels with the
                         // scores in an fp16 buffer (allocated by contexts created while this is 1), 0 = the fused warp-level kernel

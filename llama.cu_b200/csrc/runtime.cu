@@ -787,7 +787,7 @@ int context::create(std::unique_ptr<context>& out, model* m, const context_optio
   }
   // u8 models: the fp16 shadow for prompts is set up here, next to the context's own arenas, so that next_token never
   // allocates (a stale shadow is refreshed in place by the next long prompt)
-  if (p.q_type && c.opt.context_len > 8) m->shadow_ready(true);
+  if (p.q_type && c.opt.context_len >= 2) m->shadow_ready(true);
   out = std::move(ctx);
   return LCU_OK;
 }
@@ -1087,7 +1087,7 @@ int context_impl::enqueue_prefill(int m_rows) {
     const bool pedantic = matmul_type_ref() == 1;  // u8 weights then stay u8 all the way into the pedantic kernel
     const bool fuse_u8 = !shadow && !pedantic && pt.fuse && bs > 0 && rows_stacked && pt.u8_deq_min_rows > 0 && m_rows >= pt.u8_deq_min_rows &&
                          g.deq != nullptr;
-    const bool fuse = pt.fuse && (bs == 0 || shadow) && m_rows > 8 && rows_stacked;
+    const bool fuse = pt.fuse && (bs == 0 || shadow) && pt.tc_min_rows > 0 && m_rows >= pt.tc_min_rows && rows_stacked;
     const bool qkv_stacked = fuse_u8 || (fuse && (char*)L.wk.w == (char*)L.wq.w + (size_t)d * d * 2 && (char*)L.wv.w == (char*)L.wk.w + (size_t)d * d * 2);
     const int ldq = qkv_stacked ? 3 * d : d;
     if (qkv_stacked) {

@@ -142,7 +142,7 @@ def test_prefill_tensor_core_gemm(lcu, m, k, n, beta, tile):
         y_gemv = lcu.matmul_nt(x, w, beta=beta, out_u16=prev) if k % 256 == 0 else None
     finally:
         lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_tile_n", 0))
-        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_min_rows", 9))
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_tc_min_rows", 2))
     scale = max(1.0, float(np.abs(f32(yo)).max()))
     assert np.abs(f32(y) - f32(yo)).max() <= 2e-3 * scale
     if y_gemv is not None:

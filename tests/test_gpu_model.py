@@ -55,11 +55,11 @@ def test_small_model_matches_oracle(lcu, bs, prompt_len, u8_mode):
     prompt = O.synth_tokens(prompt_len, 1234, lo=3, hi=1000)
     mine, theirs = [], []
     # u8 weights: once through the GEMV passes (threshold raised), once through dequantization + tcgen05 GEMM (default)
-    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 9 if prompt_len >= 40 else 1000))
+    lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 2 if prompt_len >= 40 else 1000))
     try:
         t = ctx.next_token(prompt)
     finally:
-        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 9))
+        lcu.check(lcu.lib.lcu_set_tuning(b"prefill_u8_deq_min_rows", 2))
     to = om.next_token(prompt)
     for step in range(20):
         p, po = f32(ctx.probs()), f32(om.probs())
