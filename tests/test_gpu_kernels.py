@@ -124,7 +124,9 @@ def test_matmul_small_shapes(lcu, m, k, n, bs, beta):
                                              (16, 512, 22016, 1.0, 160), (100, 256, 1024, 0.0, 96), (128, 512, 4096, 1.0, 224),
                                              (33, 1024, 2560, 0.0, 192), (64, 256, 1536, 1.0, 256), (9, 64, 32, 0.0, 96),
                                              # the widths the dispatch picks for short prompts by itself (7B shapes, short K)
-                                             (16, 512, 12288, 0.0, 0), (128, 512, 22016, 1.0, 0)])
+                                             (16, 512, 12288, 0.0, 0), (128, 512, 22016, 1.0, 0),
+                                             # K steps that do not fill the last stage of two or four k-blocks (its rest arrives as zeros)
+                                             (50, 320, 1024, 1.0, 0), (20, 192, 4096, 0.0, 0), (120, 704, 4096, 1.0, 128), (2, 4096, 4096, 0.0, 0)])
 def test_prefill_tensor_core_gemm(lcu, m, k, n, beta, tile):
     """fp16 weights with more than 8 rows run on tcgen05 with the accumulator in tensor memory: compared with
     the oracle's binary64-accumulated product (tolerance 2e-3 of the largest output: fp32 accumulation in a
