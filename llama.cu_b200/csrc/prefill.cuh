@@ -28,8 +28,8 @@ prefill_tuning& prefill_tuning_ref();
 // matrix product, and a context then runs single-token steps through the unfused operator sequence of the prompt path.
 int& matmul_type_ref();
 
-// Dispatch: fp16 weights with more than 8 rows go to the tcgen05 GEMM (gemm_tc.cu); up to 8 rows, and
-// u8 weights in passes of 8 rows, go through the weight-streaming GEMV.
+// Dispatch: fp16 weights with at least tc_min_rows (2) rows of a shape the tcgen05 GEMM takes go to it (gemm_tc.cu);
+// one row, other shapes, and u8 weights without scratch (in passes of 8 rows) go through the weight-streaming GEMV.
 // lhs and out are dense row-major ([m][K], [m][N]); err is the device error word.
 // deq / deq_halves: scratch for one dequantized matrix; with it, u8 weights and at least u8_deq_min_rows rows are
 // expanded to fp16 (the values the reference's tile kernel builds in shared memory, llama_cu.cu:222-300) and
