@@ -245,6 +245,10 @@ int lcu_selftest_bounded_wait(int* device_code_out);
  * (x a finite half, scale a positive finite half, |x| within the absmax that rounds to the scale) on the device and
  * returns the number of pairs checked and the number of differing bytes (0). */
 int lcu_selftest_quantizer_arithmetic(uint64_t* checked_out, uint64_t* differences_out);
+/* Host arithmetic only (no device needed): how lcu_matmul_nt_f16 cuts out(m,n) = lhs(m,k) . rhs(n,k)^T for m <= 128 rows on
+ * a GPU of `sms` SMs - the tile width (96 to 256 columns; the last tile may hang over n) and the split-K factor (1, 2 or 4,
+ * 128-wide tiles only) - chosen so that one wave of CTAs streams the matrix in equal shares.  n a multiple of 128, k of 64. */
+int lcu_plan_short_prompt_gemm(int n, int k, int sms, int* tile_n_out, int* split_out);
 /* lcu_matmul_nt_f16_gated forms silu's a / (1 + expf(-a)) (llama_cu.cu:533-539) with a refined reciprocal and one
  * residual correction instead of the IEEE division.  This entry compares the two on the device for all 65536
  * half-precision a (the only values the gate meets) and returns how many were compared and how many differ (0). */

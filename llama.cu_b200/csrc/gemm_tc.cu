@@ -591,6 +591,32 @@ int tc_encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* d
   return LCU_OK;
 }
 
+// Up to 128 rows the product streams the weights once and an SM takes in about 50 GB/s whatever its tile's width, so
+// what counts is that all SMs stream the same number of bytes: tile widths from 96 to 256 (the last tile may hang
+// over N) and split-K for the 128-wide tile are compared by waves x max(bytes per CTA / 50 GB/s, 0.27 us per K step)
+// + 7 us per wave, against the whole matrix at 5.8 TB/s.  7B: w1|w3 (N = 22016) takes 160-wide tiles (138 CTAs, one
+// wave, instead of 172 in two: 51 -> 32 us at 16 rows); N = 4096 keeps 128-wide tiles with K split four ways.
+void gemm_tc_plan_short(int N, int K, int sms, int* tile_n, int* split) {
+  const double nk = K / BK;
+  double best = 1e30;
+  int bn = 128, sp_best = 1;
+  const int widths[6] = {128, 96, 160, 192, 224, 256};
+  for (int i = 0; i < 6; ++i)
+    for (int sp = 1; sp <= (widths[i] == 128 ? 4 : 1); sp *= 2) {
+      if (nk < 8 * sp) continue;
+      const long ctas = (long)((N + widths[i] - 1) / widths[i]) * sp, waves = (ctas + sms - 1) / sms;
+      const double per_cta = std::max(widths[i] * 128.0 * nk / sp / 50e3, nk / sp * 0.27);
+      const double est = std::max(waves * per_cta, (double)N * K * 2 / 5.8e6) + 7.0 * waves + (sp > 1 ? 1.5 : 0.0);
+      if (est < best - 0.5) {  // (ties stay with the earlier candidate)
+        best = est;
+        bn = widths[i];
+        sp_best = sp;
+      }
+    }
+  *tile_n = bn;
+  *split = sp_best;
+}
+
 int& tc_kb_per_stage() {
   static int kb = 0;
   return kb;
@@ -703,28 +729,7 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
   }
   int bn = force_bn, split = force_split;
   if (!bn) bn = N % 128 == 0 ? 128 : N % 64 == 0 ? 64 : 32;  // measured: the widest tile wins even when it leaves SMs idle
-  if (!force_bn && force_split < 0 && m <= BM && N % 128 == 0) {
-    // Up to 128 rows the product streams the weights once and an SM takes in about 50 GB/s whatever its tile's width, so
-    // what counts is that all SMs stream the same number of bytes: tile widths from 96 to 256 (the last tile may hang
-    // over N) and split-K for the 128-wide tile are compared by waves x max(bytes per CTA / 50 GB/s, 0.27 us per K step)
-    // + 7 us per wave, against the whole matrix at 5.8 TB/s.  7B: w1|w3 (N = 22016) takes 160-wide tiles (138 CTAs, one
-    // wave, instead of 172 in two: 51 -> 38 us), wq|wk|wv (12288) 96-wide ones (128 CTAs instead of 96).
-    const double nk = K / BK;
-    double best = 1e30;
-    const int widths[6] = {128, 96, 160, 192, 224, 256};
-    for (int i = 0; i < 6; ++i)
-      for (int sp = 1; sp <= (widths[i] == 128 ? 4 : 1); sp *= 2) {
-        if (nk < 8 * sp) continue;
-        const long ctas = (long)((N + widths[i] - 1) / widths[i]) * sp, waves = (ctas + sms - 1) / sms;
-        const double per_cta = std::max(widths[i] * 128.0 * nk / sp / 50e3, nk / sp * 0.27);
-        const double est = std::max(waves * per_cta, (double)N * K * 2 / 5.8e6) + 7.0 * waves + (sp > 1 ? 1.5 : 0.0);
-        if (est < best - 0.5) {  // (ties stay with the earlier candidate)
-          best = est;
-          bn = widths[i];
-          split = sp;
-        }
-      }
-  }
+  if (!force_bn && force_split < 0 && m <= BM && N % 128 == 0) gemm_tc_plan_short(N, K, sms, &bn, &split);
   LCU_REQUIRE(bn % 32 == 0 && bn >= 32 && bn <= 256, "gemm_tc: tile width %d is not a multiple of 32 up to 256", bn);
   if (bn == 128 && N % 128) split = 1;  // (the split-K clusters own whole 128-wide tiles)
   if (bn == 128) {

@@ -23,6 +23,9 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
 // -1 (default) = launch_gemm_tc uses it, with 256- or 512-wide tiles, where its estimate says it wins; 256 / 512 =
 // always, with that tile width, where it divides N; 0 = never
 int& gemm_tc_sk_mode();
+// one-SM kernel, up to 128 rows, N a multiple of 128: the tile width (96 to 256) and split-K factor (1, 2, 4; 128-wide
+// tiles only) launch_gemm_tc uses on a GPU of `sms` SMs.  Pure host arithmetic.
+void gemm_tc_plan_short(int N, int K, int sms, int* tile_n, int* split);
 // one-SM kernel: 64-wide k-blocks per stage and tensor copy (0 = as many of 4, 2, 1 as leave four stages)
 int& tc_kb_per_stage();
 // balanced pair kernel: k-blocks per stage and tensor copy (0 = 2)

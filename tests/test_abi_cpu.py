@@ -54,6 +54,37 @@ def test_host_side_shapes_and_partitions():
     assert lcu.lib.lcu_set_matmul_type(3) != 0 and lcu.lib.lcu_set_matmul_type(1) == 0 and lcu.lib.lcu_set_matmul_type(4) == 0
 
 
+def test_short_prompt_gemm_plan_fills_one_wave():
+    """Host arithmetic behind lcu_matmul_nt_f16 for up to 128 rows: the weights stream once and every SM takes in about the
+    same rate, so the tile width and split-K factor are chosen for one wave of equal CTAs.  The plan for the reference's
+    model shapes on a 148-SM GPU (7B: dim 4096 / ffn 11008, 13B: 5120 / 13824, 65B: 8192 / 22016)."""
+    lcu = load_package()
+
+    def plan(n, k, sms=148):
+        tile, split = C.c_int(0), C.c_int(0)
+        lcu.check(lcu.lib.lcu_plan_short_prompt_gemm(n, k, sms, C.byref(tile), C.byref(split)))
+        return tile.value, split.value
+
+    # 7B: w1|w3 stacked (N = 22016) as 138 tiles of 160 columns instead of 172 of 128 in two waves; wq|wk|wv as 128 x 96
+    assert plan(22016, 4096) == (160, 1)
+    assert plan(12288, 4096) == (96, 1)
+    # narrow matrices keep 128-wide tiles and split K over a cluster
+    assert plan(4096, 4096) == (128, 4)
+    assert plan(4096, 11008) == (128, 4)
+    # 13B and 65B
+    assert plan(27648, 5120) == (192, 1)
+    assert plan(24576, 8192) == (192, 1)
+    for n, k in ((22016, 4096), (12288, 4096), (4096, 4096), (27648, 5120), (24576, 8192), (32000, 4096), (15360, 5120)):
+        tile, split = plan(n, k)
+        assert tile % 32 == 0 and 96 <= tile <= 256 and split in (1, 2, 4) and (split == 1 or tile == 128)
+        ctas = -(-n // tile) * split
+        assert 74 < ctas <= 148, (n, k, tile, split, ctas)  # one wave, more than half of the SMs busy
+    # a GPU with half the SMs gets wider tiles
+    assert plan(12288, 4096, 74)[0] > plan(12288, 4096, 148)[0]
+    with pytest.raises(lcu.LcuError):
+        plan(100, 4096)
+
+
 def test_oracle_is_not_linked_into_the_product():
     out = subprocess.run(["nm", "-D", "--defined-only", os.path.join(ROOT, "llama.cu_b200", "libllama_cu_b200.so")],
                          capture_output=True, text=True).stdout
