@@ -249,6 +249,9 @@ int lcu_selftest_quantizer_arithmetic(uint64_t* checked_out, uint64_t* differenc
  * a GPU of `sms` SMs - the tile width (96 to 256 columns; the last tile may hang over n) and the split-K factor (1, 2 or 4,
  * 128-wide tiles only) - chosen so that one wave of CTAs streams the matrix in equal shares.  n a multiple of 128, k of 64. */
 int lcu_plan_short_prompt_gemm(int n, int k, int sms, int* tile_n_out, int* split_out);
+/* The same for m > 128 rows: *kernel_out = 0 for whole 256-row tiles per SM pair, 256 or 512 for the kernel that deals the K
+ * steps of the last wave's tiles evenly over the pairs, with tiles that wide (estimates fitted to timings on B200). */
+int lcu_plan_long_prompt_gemm(int m, int n, int k, int sms, int* kernel_out);
 /* lcu_matmul_nt_f16_gated forms silu's a / (1 + expf(-a)) (llama_cu.cu:533-539) with a refined reciprocal and one
  * residual correction instead of the IEEE division.  This entry compares the two on the device for all 65536
  * half-precision a (the only values the gate meets) and returns how many were compared and how many differ (0). */

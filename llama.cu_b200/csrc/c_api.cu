@@ -512,6 +512,11 @@ int lcu_selftest_quantizer_arithmetic(uint64_t* checked_out, uint64_t* differenc
   *differences_out = b;
   return rc;
 }
+int lcu_plan_long_prompt_gemm(int m, int n, int k, int sms, int* kernel_out) {
+  LCU_REQUIRE(m > 128 && n >= 128 && n % 128 == 0 && k >= 64 && k % 64 == 0 && sms >= 2 && kernel_out, "plan_long_prompt_gemm: bad arguments");
+  *kernel_out = gemm_tc_plan_long(m, n, k, sms);
+  return LCU_OK;
+}
 int lcu_plan_short_prompt_gemm(int n, int k, int sms, int* tile_n_out, int* split_out) {
   LCU_REQUIRE(n >= 128 && n % 128 == 0 && k >= 64 && k % 64 == 0 && sms >= 2 && tile_n_out && split_out, "plan_short_prompt_gemm: bad arguments");
   gemm_tc_plan_short(n, k, sms, tile_n_out, split_out);

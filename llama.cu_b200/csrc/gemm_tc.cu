@@ -664,6 +664,21 @@ static void gemm_tc_estimates(int m, int N, int K, int sms, double* whole_us, do
   *t512_us = N >= 2 * K ? balanced(512) : 1e30;
 }
 
+// More than 128 rows: 0 = whole tiles per SM pair, 256 / 512 = the balanced kernel with that tile width (the one whose
+// estimate is lowest; a balanced kernel has to beat whole tiles by 3 %).
+int gemm_tc_plan_long(int m, int N, int K, int sms) {
+  double whole, t256, t512;
+  gemm_tc_estimates(m, N, K, sms, &whole, &t256, &t512);
+  double best = whole;
+  int tile = 0;
+  if (t256 < 0.97 * whole && t256 < best) {
+    best = t256;
+    tile = 256;
+  }
+  if (t512 < 0.97 * whole && t512 < best) tile = 512;
+  return tile;
+}
+
 int& gemm_tc_gate_mode() {
   static int mode = -1;
   return mode;
@@ -701,16 +716,7 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
   if (force_pair < 0 && !force_bn && (m > BM || gemm_tc_sk_mode() > 0)) {
     const int mode = gemm_tc_sk_mode();
     int tile = mode > 0 ? mode : 0;
-    if (mode < 0) {
-      double whole, t256, t512;
-      gemm_tc_estimates(m, N, K, sms, &whole, &t256, &t512);
-      double best = whole;
-      if (t256 < 0.97 * whole && t256 < best) {
-        best = t256;
-        tile = 256;
-      }
-      if (t512 < 0.97 * whole && t512 < best) tile = 512;
-    }
+    if (mode < 0) tile = gemm_tc_plan_long(m, N, K, sms);
     if (tile && gemm_tc_sk_supported(m, N, K, ldx, lhs, w, out, tile)) return launch_gemm_tc_sk(out, lhs, ldx, w, m, N, K, beta, err, stream, tile);
   }
   // Large products: the two-SM kernel, with its 256-wide tile when that still gives (nearly) every SM pair a tile.

@@ -23,6 +23,9 @@ int launch_gemm_tc(__half* out, const __half* lhs, int ldx, const __half* w, int
 // -1 (default) = launch_gemm_tc uses it, with 256- or 512-wide tiles, where its estimate says it wins; 256 / 512 =
 // always, with that tile width, where it divides N; 0 = never
 int& gemm_tc_sk_mode();
+// more than 128 rows: the kernel launch_gemm_tc picks on a GPU of `sms` SMs - 0 whole tiles per SM pair, 256 / 512 the
+// balanced kernel with that tile width.  Pure host arithmetic.
+int gemm_tc_plan_long(int m, int N, int K, int sms);
 // one-SM kernel, up to 128 rows, N a multiple of 128: the tile width (96 to 256) and split-K factor (1, 2, 4; 128-wide
 // tiles only) launch_gemm_tc uses on a GPU of `sms` SMs.  Pure host arithmetic.
 void gemm_tc_plan_short(int N, int K, int sms, int* tile_n, int* split);

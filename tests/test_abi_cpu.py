@@ -85,6 +85,30 @@ def test_short_prompt_gemm_plan_fills_one_wave():
         plan(100, 4096)
 
 
+def test_long_prompt_gemm_plan_follows_the_measurements():
+    """Host arithmetic behind lcu_matmul_nt_f16 for more than 128 rows: whole tiles per SM pair (0) or the kernel that
+    deals the last wave's K steps evenly (256).  Pinned where the two were measured more than 5 % apart on a B200 (7B
+    shapes, microseconds whole / balanced in the comments)."""
+    lcu = load_package()
+
+    def plan(m, n, k, sms=148):
+        out = C.c_int(-1)
+        lcu.check(lcu.lib.lcu_plan_long_prompt_gemm(m, n, k, sms, C.byref(out)))
+        return out.value
+
+    assert plan(512, 22016, 4096) == 256    # 83.1 / 78.5: 172 tiles for 74 pairs, the third wave is a third full
+    assert plan(2048, 22016, 4096) == 256   # 278 / 259
+    assert plan(512, 4096, 4096) == 0       # 28.9 / 33.4: every tile would be handed over
+    assert plan(768, 4096, 4096) == 256     # 48.9 / 34.3
+    assert plan(512, 4096, 11008) == 256    # 82.4 / 66.1
+    assert plan(1024, 4096, 11008) == 0     # 72.3 / 83.3: 64 tiles, one wave
+    for m in (129, 300, 777, 2048, 8192):
+        for n, k in ((4096, 4096), (12288, 4096), (22016, 4096), (27648, 5120), (8192, 22016), (32000, 4096)):
+            assert plan(m, n, k) in (0, 256, 512)
+    with pytest.raises(lcu.LcuError):
+        plan(128, 4096, 4096)
+
+
 def test_oracle_is_not_linked_into_the_product():
     out = subprocess.run(["nm", "-D", "--defined-only", os.path.join(ROOT, "llama.cu_b200", "libllama_cu_b200.so")],
                          capture_output=True, text=True).stdout
