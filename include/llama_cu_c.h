@@ -252,6 +252,11 @@ int lcu_plan_short_prompt_gemm(int n, int k, int sms, int* tile_n_out, int* spli
 /* The same for m > 128 rows: *kernel_out = 0 for whole 256-row tiles per SM pair, 256 or 512 for the kernel that deals the K
  * steps of the last wave's tiles evenly over the pairs, with tiles that wide (estimates fitted to timings on B200). */
 int lcu_plan_long_prompt_gemm(int m, int n, int k, int sms, int* kernel_out);
+/* Host walk of that kernel's work list (no device needed) for n_tiles output tiles of k_steps 64-wide K steps on sm_pairs
+ * pairs of SMs: 0 when every K step of every tile is run by exactly one pair, a pair hands partial sums over at most once,
+ * and each shared tile's owner finds exactly the pairs that ran the rest of it, in order; a positive code names the rule
+ * that failed, -1 bad arguments. */
+int lcu_selftest_balanced_schedule(int n_tiles, int k_steps, int sm_pairs);
 /* lcu_matmul_nt_f16_gated forms silu's a / (1 + expf(-a)) (llama_cu.cu:533-539) with a refined reciprocal and one
  * residual correction instead of the IEEE division.  This entry compares the two on the device for all 65536
  * half-precision a (the only values the gate meets) and returns how many were compared and how many differ (0). */

@@ -56,6 +56,7 @@ _SIG = {
     "lcu_logits_head": (C.c_int, [vp, vp, C.c_int, C.c_float, C.POINTER(C.c_int), vp]),
     "lcu_selftest_bounded_wait": (C.c_int, [C.POINTER(C.c_int)]),
     "lcu_selftest_quantizer_arithmetic": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "lcu_selftest_balanced_schedule": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "lcu_plan_long_prompt_gemm": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]),
     "lcu_plan_short_prompt_gemm": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "lcu_selftest_silu_arithmetic": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),

@@ -512,6 +512,7 @@ int lcu_selftest_quantizer_arithmetic(uint64_t* checked_out, uint64_t* differenc
   *differences_out = b;
   return rc;
 }
+int lcu_selftest_balanced_schedule(int n_tiles, int k_steps, int sm_pairs) { return gemm_tc_sk_check_schedule(n_tiles, k_steps, sm_pairs); }
 int lcu_plan_long_prompt_gemm(int m, int n, int k, int sms, int* kernel_out) {
   LCU_REQUIRE(m > 128 && n >= 128 && n % 128 == 0 && k >= 64 && k % 64 == 0 && sms >= 2 && kernel_out, "plan_long_prompt_gemm: bad arguments");
   *kernel_out = gemm_tc_plan_long(m, n, k, sms);

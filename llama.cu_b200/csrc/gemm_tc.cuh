@@ -37,6 +37,10 @@ bool gemm_tc_sk_supported(int m, int N, int K, int ldx, const void* lhs, const v
 int launch_gemm_tc_sk(__half* out, const __half* lhs, int ldx, const __half* w, int m, int N, int K, float beta, int* err, cudaStream_t stream,
                       int tile_n);
 
+// host walk of the balanced kernel's schedule for n_tiles tiles of nk K steps on C SM pairs: 0 = every K step of every tile
+// runs once and the hand-over of partial sums is consistent (gemm_tc_sk.cu)
+int gemm_tc_sk_check_schedule(int n_tiles, int nk, int C);
+
 // w1|w3 and the SiLU gate as one launch (gemm_tc_sk.cu): out[m][f] = half(silu(half(lhs . w1^T)) * half(lhs . w3^T)) with
 // w13 = [w1; w3] stacked ([2 f][K]); the same bits as the stacked product followed by the gate kernel.
 // gemm_tc_gate_mode: -1 = when the estimate favours it, 256 / 512 = from 129 rows with that many accumulator columns per

@@ -22,6 +22,9 @@
 #include <unordered_map>
 
 #include "gemm_tc.cuh"
+
+#include <algorithm>
+#include <vector>
 #include "tc_common.cuh"
 
 namespace lcu {
@@ -95,7 +98,8 @@ __device__ __forceinline__ bool sk_flag_wait(const int* flag, int value, int* er
 }
 
 // pair c of C runs units [U c / C, U (c + 1) / C)
-__device__ __forceinline__ long long sk_first_unit(long long U, int c, int C) { return U * c / C; }
+__host__ __device__ __forceinline__ long long sk_first_unit(long long U, int c, int C) { return U * c / C; }
+__host__ __device__ __forceinline__ long long sk_min(long long a, long long b) { return a < b ? a : b; }
 
 // A pair's schedule: first whole tiles, tile w C + c in wave w (at any time the pairs work on neighbouring tiles, which
 // share weight panels and keep the working set inside L2), then its share of the K steps of the tiles that do not fill
@@ -104,7 +108,7 @@ struct sk_schedule {
   int C, Cs, c, nk, full_waves, first_split_tile;  // Cs: pairs that take part in the split tiles (every one of them has a K step)
   long long U, u, u1;  // units of the split tiles: all, next of this pair, end of this pair's range
   int wave;
-  __device__ void init(int n_tiles, int nk_, int C_, int c_) {
+  __host__ __device__ void init(int n_tiles, int nk_, int C_, int c_) {
     C = C_;
     c = c_;
     nk = nk_;
@@ -115,13 +119,13 @@ struct sk_schedule {
     // the kernel, and what it reads of the first two is requested ahead (eight pairs per tile were slower even for
     // prompts of 16 rows, whose sums are small: 59 against 46 us on the 7B w1|w3)
     const long long split_pairs = (long long)(n_tiles - first_split_tile) * 3;
-    Cs = (int)min(min((long long)C, U), split_pairs);
+    Cs = (int)sk_min(sk_min((long long)C, U), split_pairs);
     u = c < Cs ? sk_first_unit(U, c, Cs) : 0;
     u1 = c < Cs ? sk_first_unit(U, c + 1, Cs) : 0;
     wave = 0;
   }
   // next segment: K steps [kb0, kb1) of tile `tile`; split = the tile is shared with other pairs
-  __device__ bool next(int& tile, int& kb0, int& kb1, bool& split) {
+  __host__ __device__ bool next(int& tile, int& kb0, int& kb1, bool& split) {
     if (wave < full_waves) {
       tile = wave * C + c;
       kb0 = 0;
@@ -134,13 +138,13 @@ struct sk_schedule {
     const int lt = (int)(u / nk);
     tile = first_split_tile + lt;
     kb0 = (int)(u - (long long)lt * nk);
-    kb1 = (int)min((long long)nk, kb0 + (u1 - u));
+    kb1 = (int)sk_min((long long)nk, kb0 + (u1 - u));
     split = true;
     u += kb1 - kb0;
     return true;
   }
   // pairs after this one that hold later K steps of split tile `tile` (this pair ran its first)
-  __device__ int peers_of(int tile) const {
+  __host__ __device__ int peers_of(int tile) const {
     const long long tile_end = (long long)(tile - first_split_tile + 1) * nk;
     int n = 0;
     while (c + 1 + n < Cs && sk_first_unit(U, c + 1 + n, Cs) < tile_end) ++n;
@@ -603,6 +607,58 @@ int launch_gemm_tc_gated(__half* out, const __half* lhs, int ldx, const __half* 
   LCU_REQUIRE(gemm_tc_gated_supported(m, f, K, ldx, lhs, w13, out) && (tile_n == 256 || (tile_n == 512 && f % 256 == 0)),
               "gemm_tc_gated: unsupported shape m=%d f=%d K=%d ldx=%d tile=%d", m, f, K, ldx, tile_n);
   return tile_n == 512 ? launch_sk<2, true>(out, lhs, ldx, w13, m, f, K, 0.f, err, stream) : launch_sk<1, true>(out, lhs, ldx, w13, m, f, K, 0.f, err, stream);
+}
+
+// The schedule, walked on the host for every pair of a launch: 0 when every K step of every tile is run exactly once,
+// a pair starts inside a tile (and so hands partial sums over) at most once and only with its first shared segment, and
+// the pair that ran a shared tile's first K step finds exactly the pairs after it that ran the rest, in order.
+int gemm_tc_sk_check_schedule(int n_tiles, int nk, int C) {
+  if (n_tiles < 1 || nk < 1 || C < 1) return -1;
+  std::vector<int> owner((size_t)n_tiles * nk, -1);
+  struct seg { int tile, kb0, kb1; };
+  std::vector<std::vector<seg>> segs(C);
+  for (int c = 0; c < C; ++c) {
+    sk_schedule sc;
+    sc.init(n_tiles, nk, C, c);
+    int tile, kb0, kb1, writer_segments = 0, shared_segments = 0;
+    bool split;
+    while (sc.next(tile, kb0, kb1, split)) {
+      if (tile < 0 || tile >= n_tiles || kb0 < 0 || kb1 > nk || kb0 >= kb1) return 1;
+      if (split) ++shared_segments;
+      if (kb0 > 0) {
+        if (!split || shared_segments != 1) return 2;  // only a pair's first shared segment may start inside a tile
+        ++writer_segments;
+      }
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (owner[(size_t)tile * nk + kb] != -1) return 3;
+        owner[(size_t)tile * nk + kb] = c;
+      }
+      segs[c].push_back({tile, kb0, kb1});
+    }
+    if (writer_segments > 1) return 4;
+    if (c < sc.Cs && shared_segments == 0) return 5;  // every pair counted for the shared tiles has a K step of them
+  }
+  for (int v : owner)
+    if (v < 0) return 6;
+  for (int c = 0; c < C; ++c)
+    for (const seg& sg : segs[c]) {
+      if (sg.kb0 != 0) continue;
+      sk_schedule sc;
+      sc.init(n_tiles, nk, C, c);
+      if (sg.kb1 == nk) continue;  // ran the whole tile
+      if (sg.tile < sc.first_split_tile) return 7;
+      const int peers = sc.peers_of(sg.tile);
+      if (peers < 1 || c + peers >= C) return 8;
+      int at = sg.kb1;
+      for (int q = 1; q <= peers; ++q) {  // the next pairs continue the tile, one after the other
+        if (segs[c + q].empty()) return 9;
+        const seg& first_shared = *std::find_if(segs[c + q].begin(), segs[c + q].end(), [&](const seg& x) { return x.tile == sg.tile; });
+        if (first_shared.tile != sg.tile || first_shared.kb0 != at) return 10;
+        at = first_shared.kb1;
+      }
+      if (at != nk) return 11;
+    }
+  return 0;
 }
 
 }  // namespace lcu

@@ -109,6 +109,22 @@ def test_long_prompt_gemm_plan_follows_the_measurements():
         plan(128, 4096, 4096)
 
 
+def test_balanced_gemm_schedule_covers_every_k_step_once():
+    """The prompt GEMM that deals the last wave's K steps evenly over the SM pairs: its work list, walked on the host for
+    every pair of a launch.  Every K step of every tile must be run by exactly one pair; a pair may start inside a tile
+    (and hand partial sums over) once at most, with its first shared segment; the pair that ran a shared tile's first K
+    step must find exactly the following pairs that ran the rest, in order."""
+    lcu = load_package()
+    cases = 0
+    for pairs in (1, 2, 3, 7, 37, 66, 74):
+        for k_steps in (1, 2, 3, 5, 8, 64, 80, 172, 344):
+            for n_tiles in list(range(1, 160)) + [172, 344, 516, 688, 1376]:
+                assert lcu.lib.lcu_selftest_balanced_schedule(n_tiles, k_steps, pairs) == 0, (n_tiles, k_steps, pairs)
+                cases += 1
+    assert cases > 10000
+    assert lcu.lib.lcu_selftest_balanced_schedule(0, 64, 74) == -1
+
+
 def test_oracle_is_not_linked_into_the_product():
     out = subprocess.run(["nm", "-D", "--defined-only", os.path.join(ROOT, "llama.cu_b200", "libllama_cu_b200.so")],
                          capture_output=True, text=True).stdout
