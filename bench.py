@@ -188,12 +188,20 @@ def prefill_sample(lcu, ctx, cfg, ffn, profile=False, prefill_len=PREFILL_LEN):
     if cfg["block_size"] == 0:
         _, _, peak, src = measured_peaks()
         m, k, n = prefill_len, cfg["dim"], 2 * ffn  # the stacked w1|w3 product, the largest GEMM of a prompt pass
-        # (best of three timed loops each: the figure is a kernel timed alone against the burst peak, and the first loop
-        # after the decode measurements runs at whatever clocks those left)
-        ms = min(lcu.bench_matmul_f16_ms(m, k, n, reps=30) for _ in range(3))
+        # The figure is a kernel timed alone against the BURST peak (cuBLAS, best of 10 on an idle GPU): so each of the
+        # three timed loops starts after a pause - right after the decode measurements the GPU sits at its power cap,
+        # and the same kernel then runs 10 to 15 % slower - and the best loop counts.
+        def burst(mm, reps):
+            best_ms = None
+            for _ in range(3):
+                time.sleep(1.5)
+                t = lcu.bench_matmul_f16_ms(mm, k, n, reps=reps)
+                best_ms = t if best_ms is None or t < best_ms else best_ms
+            return best_ms
+        ms = burst(m, 12)
         tf = 2.0 * m * k * n / (ms * 1e-3) / 1e12
         m2 = 2048
-        ms2 = min(lcu.bench_matmul_f16_ms(m2, k, n, reps=15) for _ in range(3))
+        ms2 = burst(m2, 6)
         tf2 = 2.0 * m2 * k * n / (ms2 * 1e-3) / 1e12
         out["gemm_roofline"] = {"bound": "tensor", "kernel": "tcgen05 prompt GEMM (cta_group::2, TMA-fed, accumulators in tensor memory; whole tiles per SM pair or the last wave's K steps dealt evenly, chosen per shape)",
                                 "shape": [m, k, n], "us_per_launch": round(ms * 1e3, 2), "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s",
