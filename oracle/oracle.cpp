@@ -698,6 +698,16 @@ void orc_silu(uint16_t* out, const uint16_t* a, const uint16_t* b, uint64_t n) {
   silu(out, a, b, n);
 }
 
+// The feed-forward's first half as the reference runs it for a prompt (llama_cu.cu:1180-1183): matmul_nt with w1, matmul_nt
+// with w3 - each product stored as halves - then silu on the stored halves.  w13 = [w1; w3], (2 f, k).
+void orc_matmul_nt_f16_gated(uint16_t* out, const uint16_t* lhs, const uint16_t* w13, int m, int k, int f, int acc64) {
+  init_tables();
+  std::vector<uint16_t> a((size_t)m * f), b((size_t)m * f);
+  matmul_nt_f16(a.data(), lhs, w13, m, k, f, 0.f, acc64);
+  matmul_nt_f16(b.data(), lhs, w13 + (size_t)f * k, m, k, f, 0.f, acc64);
+  silu(out, a.data(), b.data(), (uint64_t)m * f);
+}
+
 uint32_t orc_ffn_dim(uint32_t dim, uint32_t multiple_of) {
   params_t p{};
   p.dim = dim;

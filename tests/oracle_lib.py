@@ -43,6 +43,7 @@ def lib():
         "orc_matmul_qkv": (None, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]),
         "orc_attention": (None, [u16p, u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
         "orc_silu": (None, [u16p, u16p, u16p, C.c_uint64]),
+        "orc_matmul_nt_f16_gated": (None, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]),
         "orc_ffn_dim": (C.c_uint32, [C.c_uint32, C.c_uint32]),
         "orc_model_create_synth": (C.c_void_p, [C.c_uint32] * 5 + [C.c_float, C.c_int, C.c_uint64, C.c_float]),
         "orc_model_load": (C.c_void_p, [C.c_char_p]),

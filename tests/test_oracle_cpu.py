@@ -180,6 +180,27 @@ def test_rms_norm_rotary_silu_against_numpy():
     assert (np.abs(f32(o) - want) <= 1e-3 * np.abs(want) + 1e-4).all()
 
 
+def test_gated_product_is_the_two_products_and_the_gate():
+    """orc_matmul_nt_f16_gated - the restatement of llama_cu.cu:1180-1183 that the one-launch GPU operator is checked
+    against - equals matmul_nt with w1, matmul_nt with w3 (halves) and silu on those halves, and matches numpy in
+    double precision up to the three roundings to half."""
+    rng = np.random.default_rng(12)
+    m, k, f = 5, 256, 96
+    x = f16(rng.standard_normal((m, k)))
+    w13 = f16(rng.standard_normal((2 * f, k)) * 0.08)
+    got = np.zeros((m, f), np.uint16)
+    L.orc_matmul_nt_f16_gated(got.reshape(-1), x.reshape(-1), w13.reshape(-1), m, k, f, 1)
+    a, b, want = np.zeros((m, f), np.uint16), np.zeros((m, f), np.uint16), np.zeros((m, f), np.uint16)
+    L.orc_matmul_nt_f16(a.reshape(-1), x.reshape(-1), np.ascontiguousarray(w13[:f]).reshape(-1), m, k, f, 0.0, 1)
+    L.orc_matmul_nt_f16(b.reshape(-1), x.reshape(-1), np.ascontiguousarray(w13[f:]).reshape(-1), m, k, f, 0.0, 1)
+    L.orc_silu(want.reshape(-1), a.reshape(-1), b.reshape(-1), m * f)
+    assert np.array_equal(got, want)
+    xa = f32(x).astype(np.float64) @ f32(w13[:f]).astype(np.float64).T
+    xb = f32(x).astype(np.float64) @ f32(w13[f:]).astype(np.float64).T
+    ref = xa / (1 + np.exp(-xa)) * xb
+    assert np.abs(f32(got) - ref).max() <= 4e-3 * max(1.0, np.abs(ref).max())
+
+
 def test_attention_chain_against_numpy_softmax():
     rng = np.random.default_rng(4)
     m, T, dim, H, sp = 3, 11, 256, 2, 8
